@@ -1,0 +1,471 @@
+"""ctypes binding of include/ggr_attn.h.
+
+Names follow the reference (apimeister/gguf-runner): `AttnContext.decode`
+stands for the rope -> kv_write_token -> attention_token sequence at
+src/engine/runtime/inference.rs:3499-3507, `prefill` for the per-token loop at
+:2981-3017, `prefill_block` for src/engine/runtime/media_prefill.rs:87-118;
+`apply_rope_qk`, `kv_write_token` and `attention_token` are the three reference
+functions one by one. Buffers may be numpy arrays (host memory) or torch CUDA
+tensors (device memory); outputs come back in the same kind.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import numpy as np
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+PTR_HOST, PTR_DEVICE = 0, 1
+DTYPE_F32, DTYPE_BF16 = 0, 1
+KV_F32, KV_BF16, KV_Q8_ROW, KV_Q8_BLOCK32 = 0, 1, 2, 3
+ROPE_NEOX, ROPE_ADJACENT = 0, 1
+ROPE_SEQUENTIAL, ROPE_INTERLEAVED = 0, 1
+SCALE_SCORE, SCALE_Q_PRESCALED = 0, 1
+IMAGE_CAUSAL, IMAGE_BIDIRECTIONAL = 0, 1
+SHARD_NONE, SHARD_KV_SEQUENCE = 0, 2
+IMPL_AUTO, IMPL_SIMT, IMPL_MMA, IMPL_TCGEN05 = 0, 1, 2, 3
+
+KV_FORMATS = {"f32": KV_F32, "bf16": KV_BF16, "q8_row": KV_Q8_ROW, "q8_block32": KV_Q8_BLOCK32}
+
+
+class GgrError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"ggr_attn status {status}: {message}")
+        self.status = status
+        self.message = message
+
+
+class _Config(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_int32),
+        ("n_layers", C.c_int32), ("n_heads", C.c_int32), ("n_kv_heads", C.c_int32), ("head_dim", C.c_int32),
+        ("rope_dim", C.c_int32), ("seq_len", C.c_int32), ("max_batch", C.c_int32),
+        ("rope_theta", C.c_float), ("rope_theta_swa", C.c_float),
+        ("rope_scale_global", C.c_float), ("rope_scale_local", C.c_float),
+        ("rope_style", C.c_int32), ("rope_layout", C.c_int32), ("rope_sections", C.c_int32 * 4),
+        ("swa_theta_on_window_layers", C.c_int32), ("swa_pattern", C.c_int32),
+        ("scale_mode", C.c_int32), ("softmax_mode", C.c_int32), ("kv_format", C.c_int32),
+        ("image_mode", C.c_int32), ("n_layer_windows", C.c_int32),
+        ("layer_windows", C.POINTER(C.c_int32)),
+        ("device", C.c_int32),
+        ("shard_mode", C.c_int32), ("shard_pos_begin", C.c_int32), ("shard_pos_count", C.c_int32),
+        ("n_ranks", C.c_int32), ("rank", C.c_int32),
+        ("decode_impl", C.c_int32), ("prefill_impl", C.c_int32), ("max_splits", C.c_int32),
+    ]
+
+
+# every symbol include/ggr_attn.h declares
+EXPORTED_SYMBOLS = [
+    "ggr_attn_config_init", "ggr_attn_create", "ggr_attn_destroy", "ggr_attn_last_error",
+    "ggr_attn_create_error", "ggr_attn_abi_version", "ggr_attn_set_stream", "ggr_attn_synchronize",
+    "ggr_attn_set_position_plan", "ggr_attn_set_media_blocks", "ggr_attn_visible_keys",
+    "ggr_attn_decode", "ggr_attn_prefill", "ggr_attn_prefill_block",
+    "ggr_attn_apply_rope_qk", "ggr_attn_kv_write_token", "ggr_attn_attention_token",
+    "ggr_attn_decode_partial", "ggr_attn_combine_partials",
+    "ggr_attn_kv_export", "ggr_attn_kv_import", "ggr_attn_kv_read_row", "ggr_attn_launch_count",
+    "ggr_rope_plan_new", "ggr_rope_plan_free", "ggr_rope_plan_append_text", "ggr_rope_plan_append_grid",
+    "ggr_rope_plan_len", "ggr_rope_plan_next_text", "ggr_rope_plan_at", "ggr_rope_plan_export",
+    "ggr_rope_axis", "ggr_media_plan_validate", "ggr_media_chunk_end", "ggr_gemma_layer_windows",
+]
+
+
+def library_path() -> str:
+    return os.path.join(_PKG, "libggr_attn.so")
+
+
+def lib() -> C.CDLL:
+    """Loads libggr_attn.so; raises if it has not been built (no fallback exists)."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = library_path()
+    if not os.path.exists(path):
+        raise RuntimeError(
+            f"{path} is missing: build it with `python -m gguf_runner_b200.build` "
+            "(the attention path has no CPU or PyTorch fallback)")
+    L = C.CDLL(path)
+    vp, i32, i64 = C.c_void_p, C.c_int32, C.c_int64
+    L.ggr_attn_config_init.argtypes = [C.POINTER(_Config)]
+    L.ggr_attn_config_init.restype = None
+    L.ggr_attn_create.argtypes = [C.POINTER(_Config), C.POINTER(vp)]
+    L.ggr_attn_destroy.argtypes = [vp]
+    L.ggr_attn_destroy.restype = None
+    L.ggr_attn_last_error.argtypes = [vp]
+    L.ggr_attn_last_error.restype = C.c_char_p
+    L.ggr_attn_create_error.restype = C.c_char_p
+    L.ggr_attn_set_stream.argtypes = [vp, vp]
+    L.ggr_attn_synchronize.argtypes = [vp]
+    L.ggr_attn_set_position_plan.argtypes = [vp, vp, i32, i32]
+    L.ggr_attn_set_media_blocks.argtypes = [vp, vp, i32, i32]
+    L.ggr_attn_visible_keys.argtypes = [vp, i32, i32, C.POINTER(i32), C.POINTER(i32)]
+    L.ggr_attn_decode.argtypes = [vp, i32, vp, i32, vp, vp, vp, vp, i32]
+    L.ggr_attn_decode_partial.argtypes = [vp, i32, vp, i32, vp, vp, vp, vp, i32]
+    L.ggr_attn_combine_partials.argtypes = [vp, vp, i32, i32, vp, i32]
+    L.ggr_attn_prefill.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, i32, vp, i32]
+    L.ggr_attn_prefill_block.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, i32, vp, i32]
+    L.ggr_attn_apply_rope_qk.argtypes = [vp, i32, i32, vp, vp, i32]
+    L.ggr_attn_kv_write_token.argtypes = [vp, i32, i32, i32, vp, vp, i32]
+    L.ggr_attn_attention_token.argtypes = [vp, i32, i32, i32, vp, vp, i32]
+    L.ggr_attn_kv_export.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp]
+    L.ggr_attn_kv_import.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp]
+    L.ggr_attn_kv_read_row.argtypes = [vp, i32, i32, i32, vp, vp]
+    L.ggr_attn_launch_count.argtypes = [vp]
+    L.ggr_attn_launch_count.restype = i64
+    L.ggr_rope_plan_new.restype = vp
+    L.ggr_rope_plan_free.argtypes = [vp]
+    L.ggr_rope_plan_free.restype = None
+    L.ggr_rope_plan_append_text.argtypes = [vp, i64]
+    L.ggr_rope_plan_append_grid.argtypes = [vp, i64, i64, i64, i64]
+    L.ggr_rope_plan_len.argtypes = [vp]
+    L.ggr_rope_plan_len.restype = i64
+    L.ggr_rope_plan_next_text.argtypes = [vp]
+    L.ggr_rope_plan_next_text.restype = i64
+    L.ggr_rope_plan_at.argtypes = [vp, i64, C.POINTER(i64)]
+    L.ggr_rope_plan_at.restype = None
+    L.ggr_rope_plan_export.argtypes = [vp, vp, i64]
+    L.ggr_rope_plan_export.restype = i64
+    L.ggr_rope_axis.argtypes = [i32, i32, C.POINTER(i32)]
+    L.ggr_media_plan_validate.argtypes = [vp, i32, i64]
+    L.ggr_media_chunk_end.argtypes = [vp, i32, i64, i64, i64, i64]
+    L.ggr_media_chunk_end.restype = i64
+    L.ggr_gemma_layer_windows.argtypes = [i32, i32, i32, vp]
+    _LIB = L
+    return L
+
+
+@dataclass
+class AttnConfig:
+    """The Config / RunState fields the reference's attention reads (src/engine/types.rs:638-695)."""
+    n_layers: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    seq_len: int
+    max_batch: int = 1
+    rope_dim: int = 0
+    rope_theta: float = 500000.0
+    rope_theta_swa: float = 10000.0
+    rope_scale_global: float = 1.0
+    rope_scale_local: float = 1.0
+    rope_style: int = ROPE_NEOX
+    rope_layout: int = ROPE_SEQUENTIAL
+    rope_sections: Sequence[int] = (0, 0, 0, 0)
+    swa_theta_on_window_layers: int = 0
+    swa_pattern: int = 6
+    scale_mode: int = SCALE_SCORE
+    softmax_mode: int = 0
+    kv_format: int = KV_Q8_ROW
+    image_mode: int = IMAGE_CAUSAL
+    layer_windows: Sequence[int] = field(default_factory=tuple)
+    device: int = 0
+    shard_mode: int = SHARD_NONE
+    shard_pos_begin: int = 0
+    shard_pos_count: int = 0
+    n_ranks: int = 1
+    rank: int = 0
+    decode_impl: int = IMPL_AUTO
+    prefill_impl: int = IMPL_AUTO
+    max_splits: int = 0
+
+    @property
+    def q_dim(self) -> int:
+        return self.n_heads * self.head_dim
+
+    @property
+    def kv_dim(self) -> int:
+        return self.n_kv_heads * self.head_dim
+
+    def to_c(self):
+        c = _Config()
+        c.struct_size = C.sizeof(_Config)
+        for name in ("n_layers", "n_heads", "n_kv_heads", "head_dim", "rope_dim", "seq_len", "max_batch",
+                     "rope_theta", "rope_theta_swa", "rope_scale_global", "rope_scale_local", "rope_style",
+                     "rope_layout", "swa_theta_on_window_layers", "swa_pattern", "scale_mode", "softmax_mode",
+                     "kv_format", "image_mode", "device", "shard_mode", "shard_pos_begin", "shard_pos_count",
+                     "n_ranks", "rank", "decode_impl", "prefill_impl", "max_splits"):
+            setattr(c, name, getattr(self, name))
+        for i in range(4):
+            c.rope_sections[i] = int(self.rope_sections[i])
+        windows = (C.c_int32 * max(1, len(self.layer_windows)))(*[int(w) for w in self.layer_windows])
+        c.n_layer_windows = len(self.layer_windows)
+        c.layer_windows = C.cast(windows, C.POINTER(C.c_int32))
+        return c, windows
+
+
+def _is_torch(x) -> bool:
+    return type(x).__module__.startswith("torch")
+
+
+def _ptr(x, want_dtype=None):
+    """(address, ptr_kind) of a numpy array or a torch tensor; checks contiguity."""
+    if x is None:
+        return None, None
+    if _is_torch(x):
+        if not x.is_contiguous():
+            raise ValueError("tensor must be contiguous")
+        return C.c_void_p(x.data_ptr()), (PTR_DEVICE if x.is_cuda else PTR_HOST)
+    a = x
+    if not isinstance(a, np.ndarray) or not a.flags["C_CONTIGUOUS"]:
+        raise ValueError("buffer must be a C-contiguous numpy array or a torch tensor")
+    if want_dtype is not None and a.dtype != want_dtype:
+        raise ValueError(f"buffer dtype {a.dtype} != {want_dtype}")
+    return C.c_void_p(a.ctypes.data), PTR_HOST
+
+
+class AttnContext:
+    """One device KV cache + RoPE state; the KV half of the reference's RunState
+    (malloc_run_state_with_kv_cache_format, src/engine/runtime/inference.rs:1529)."""
+
+    def __init__(self, config: AttnConfig):
+        self.config = config
+        self._L = lib()
+        c, keep = config.to_c()
+        self._keep = keep
+        handle = C.c_void_p()
+        st = self._L.ggr_attn_create(C.byref(c), C.byref(handle))
+        if st != 0:
+            raise GgrError(st, self._L.ggr_attn_create_error().decode())
+        self._h = handle
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._L.ggr_attn_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def _check(self, st: int):
+        if st != 0:
+            raise GgrError(st, self._L.ggr_attn_last_error(self._h).decode())
+
+    # ---- state -------------------------------------------------------------------------
+    def set_stream(self, cuda_stream: int):
+        self._check(self._L.ggr_attn_set_stream(self._h, C.c_void_p(cuda_stream)))
+
+    def synchronize(self):
+        self._check(self._L.ggr_attn_synchronize(self._h))
+
+    def set_position_plan(self, plan: Optional["RopePositionPlan"]):
+        if plan is None:
+            self._check(self._L.ggr_attn_set_position_plan(self._h, None, 0, 0))
+            return
+        rows = plan.export()
+        self._check(self._L.ggr_attn_set_position_plan(
+            self._h, C.c_void_p(rows.ctypes.data), rows.shape[0], plan.next_text_position))
+
+    def set_media_blocks(self, blocks: Sequence[Sequence[int]], prompt_tokens: int):
+        arr = np.ascontiguousarray(np.array(list(blocks), dtype=np.int32).reshape(-1, 2))
+        self._check(self._L.ggr_attn_set_media_blocks(self._h, C.c_void_p(arr.ctypes.data), arr.shape[0],
+                                                       prompt_tokens))
+
+    def visible_keys(self, layer: int, pos: int) -> range:
+        s, e = C.c_int32(), C.c_int32()
+        self._check(self._L.ggr_attn_visible_keys(self._h, layer, pos, C.byref(s), C.byref(e)))
+        return range(s.value, e.value)
+
+    @property
+    def launch_count(self) -> int:
+        return int(self._L.ggr_attn_launch_count(self._h))
+
+    # ---- compute -----------------------------------------------------------------------
+    def _out_like(self, q, shape):
+        if _is_torch(q):
+            import torch
+            return torch.empty(shape, dtype=torch.float32, device=q.device)
+        return np.empty(shape, dtype=np.float32)
+
+    def decode(self, layer: int, pos, q, k, v, out=None):
+        pos = np.ascontiguousarray(np.asarray(pos, dtype=np.int32).reshape(-1))
+        B = pos.shape[0]
+        if out is None:
+            out = self._out_like(q, (B, self.config.q_dim))
+        (qp, kind), (kp, _), (vp, _), (op, _) = _ptr(q), _ptr(k), _ptr(v), _ptr(out)
+        self._check(self._L.ggr_attn_decode(self._h, layer, C.c_void_p(pos.ctypes.data), B, qp, kp, vp, op, kind))
+        return out
+
+    def decode_partial(self, layer: int, pos, q, k, v, partial=None):
+        pos = np.ascontiguousarray(np.asarray(pos, dtype=np.int32).reshape(-1))
+        B = pos.shape[0]
+        if partial is None:
+            partial = self._out_like(q, (B, self.config.n_heads, self.config.head_dim + 2))
+        (qp, kind), (kp, _), (vp, _), (pp, _) = _ptr(q), _ptr(k), _ptr(v), _ptr(partial)
+        self._check(self._L.ggr_attn_decode_partial(self._h, layer, C.c_void_p(pos.ctypes.data), B, qp, kp, vp, pp,
+                                                     kind))
+        return partial
+
+    def combine_partials(self, parts, out=None):
+        n_parts, B = parts.shape[0], parts.shape[1]
+        if out is None:
+            out = self._out_like(parts, (B, self.config.q_dim))
+        (pp, kind), (op, _) = _ptr(parts), _ptr(out)
+        self._check(self._L.ggr_attn_combine_partials(self._h, pp, n_parts, B, op, kind))
+        return out
+
+    def _prefill(self, fn, layer, seq, base_pos, q, k, v, out):
+        m = q.shape[0]
+        if _is_torch(q):
+            import torch
+            in_dtype = DTYPE_BF16 if q.dtype == torch.bfloat16 else DTYPE_F32
+        else:
+            in_dtype = DTYPE_BF16 if q.dtype == np.uint16 else DTYPE_F32
+        if out is None:
+            out = self._out_like(q, (m, self.config.q_dim))
+        (qp, kind), (kp, _), (vp, _), (op, _) = _ptr(q), _ptr(k), _ptr(v), _ptr(out)
+        self._check(fn(self._h, layer, seq, base_pos, m, qp, kp, vp, in_dtype, op, kind))
+        return out
+
+    def prefill(self, layer: int, base_pos: int, q, k, v, seq: int = 0, out=None):
+        """q/k/v: [m, q_dim] / [m, kv_dim], f32, or bf16 (torch.bfloat16 / numpy uint16 bit patterns)."""
+        return self._prefill(self._L.ggr_attn_prefill, layer, seq, base_pos, q, k, v, out)
+
+    def prefill_block(self, layer: int, base_pos: int, q, k, v, seq: int = 0, out=None):
+        return self._prefill(self._L.ggr_attn_prefill_block, layer, seq, base_pos, q, k, v, out)
+
+    def apply_rope_qk(self, layer: int, pos: int, q, k):
+        """Rotates q and k in place (apply_rope_qk, src/engine/runtime/inference.rs:1817)."""
+        (qp, kind), (kp, _) = _ptr(q), _ptr(k)
+        self._check(self._L.ggr_attn_apply_rope_qk(self._h, layer, pos, qp, kp, kind))
+
+    def kv_write_token(self, layer: int, pos: int, k, v, seq: int = 0):
+        (kp, kind), (vp, _) = _ptr(k), _ptr(v)
+        self._check(self._L.ggr_attn_kv_write_token(self._h, seq, layer, pos, kp, vp, kind))
+
+    def attention_token(self, layer: int, pos: int, q, seq: int = 0, out=None):
+        if out is None:
+            out = self._out_like(q, (self.config.q_dim,))
+        (qp, kind), (op, _) = _ptr(q), _ptr(out)
+        self._check(self._L.ggr_attn_attention_token(self._h, seq, layer, pos, qp, op, kind))
+        return out
+
+    # ---- cache access ------------------------------------------------------------------
+    def kv_read_row(self, layer: int, pos: int, seq: int = 0):
+        k = np.empty(self.config.kv_dim, dtype=np.float32)
+        v = np.empty(self.config.kv_dim, dtype=np.float32)
+        self._check(self._L.ggr_attn_kv_read_row(self._h, seq, layer, pos, C.c_void_p(k.ctypes.data),
+                                                  C.c_void_p(v.ctypes.data)))
+        return k, v
+
+    def kv_export(self, layer: int, row0: int, nrows: int, seq: int = 0):
+        kd = self.config.kv_dim
+        kq = np.empty((nrows, kd), dtype=np.int8)
+        vq = np.empty((nrows, kd), dtype=np.int8)
+        ks = np.empty(nrows, dtype=np.float32)
+        vs = np.empty(nrows, dtype=np.float32)
+        self._check(self._L.ggr_attn_kv_export(self._h, layer, seq, row0, nrows, C.c_void_p(kq.ctypes.data),
+                                                C.c_void_p(vq.ctypes.data), C.c_void_p(ks.ctypes.data),
+                                                C.c_void_p(vs.ctypes.data)))
+        return kq, vq, ks, vs
+
+    def kv_import(self, layer: int, row0: int, kq, vq, ks, vs, seq: int = 0):
+        kq = np.ascontiguousarray(kq, dtype=np.int8)
+        vq = np.ascontiguousarray(vq, dtype=np.int8)
+        ks = np.ascontiguousarray(ks, dtype=np.float32)
+        vs = np.ascontiguousarray(vs, dtype=np.float32)
+        self._check(self._L.ggr_attn_kv_import(self._h, layer, seq, row0, kq.shape[0], C.c_void_p(kq.ctypes.data),
+                                                C.c_void_p(vq.ctypes.data), C.c_void_p(ks.ctypes.data),
+                                                C.c_void_p(vs.ctypes.data)))
+
+
+class RopePositionPlan:
+    """Logical T/H/W coordinates per physical KV row (src/engine/positions.rs:3-54)."""
+
+    def __init__(self):
+        self._L = lib()
+        self._h = C.c_void_p(self._L.ggr_rope_plan_new())
+
+    def __del__(self):
+        try:
+            if self._h:
+                self._L.ggr_rope_plan_free(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+    def append_text(self, count: int):
+        if self._L.ggr_rope_plan_append_text(self._h, count) != 0:
+            raise ValueError("text rotary position overflow")
+
+    def append_grid(self, grid: Sequence[int], token_count: int):
+        t, h, w = grid
+        if min(t, h, w) < 0 or max(t, h, w, token_count) >= 2 ** 63:
+            raise ValueError("image rotary grid size overflow")
+        if self._L.ggr_rope_plan_append_grid(self._h, t, h, w, token_count) != 0:
+            raise ValueError(f"image rotary grid {list(grid)} does not hold {token_count} embeddings")
+
+    def __len__(self) -> int:
+        return int(self._L.ggr_rope_plan_len(self._h))
+
+    @property
+    def next_text_position(self) -> int:
+        return int(self._L.ggr_rope_plan_next_text(self._h))
+
+    def at(self, pos: int):
+        out = (C.c_int64 * 3)()
+        self._L.ggr_rope_plan_at(self._h, pos, out)
+        return [int(out[0]), int(out[1]), int(out[2])]
+
+    def export(self) -> np.ndarray:
+        n = len(self)
+        rows = np.zeros((max(n, 1), 3), dtype=np.int32)
+        self._L.ggr_rope_plan_export(self._h, C.c_void_p(rows.ctypes.data), n)
+        return rows[:n]
+
+    @property
+    def positions(self):
+        return self.export().tolist()
+
+
+class MediaAttentionPlan:
+    """Validated image blocks (src/engine/runtime/attention.rs:8-70)."""
+
+    def __init__(self, prompt_tokens: int, blocks: Sequence[Sequence[int]]):
+        self._L = lib()
+        self.prompt_tokens = prompt_tokens
+        self.blocks = [(int(s), int(n)) for s, n in blocks]
+        for s, n in self.blocks:
+            if not (0 <= s < 2 ** 63 and 0 <= n < 2 ** 63):
+                raise ValueError("image attention block range overflow")
+        self._arr = np.ascontiguousarray(np.array(self.blocks, dtype=np.int64).reshape(-1, 2))
+        if self._L.ggr_media_plan_validate(C.c_void_p(self._arr.ctypes.data), len(self.blocks), prompt_tokens) != 0:
+            raise ValueError("image attention blocks must be nonempty, ordered, disjoint, and within the prompt")
+
+    def block_at(self, position: int):
+        for s, n in self.blocks:
+            if s <= position < s + n:
+                return (s, n)
+        return None
+
+    def chunk_end(self, start: int, limit: int, chunk: int) -> int:
+        chunk = min(chunk, 2 ** 63 - 1)
+        r = self._L.ggr_media_chunk_end(C.c_void_p(self._arr.ctypes.data), len(self.blocks), self.prompt_tokens,
+                                        start, limit, chunk)
+        if r < 0:
+            raise ValueError("invalid media prefill chunk")
+        return int(r)
+
+
+def rope_axis(layout: int, frequency: int, sections: Sequence[int]) -> int:
+    sec = (C.c_int32 * 4)(*[int(s) for s in sections])
+    return int(lib().ggr_rope_axis(layout, frequency, sec))
+
+
+def gemma_layer_windows(n_layers: int, window: int, period: int = 6):
+    out = np.zeros(max(n_layers, 1), dtype=np.int32)
+    if lib().ggr_gemma_layer_windows(n_layers, window, period, C.c_void_p(out.ctypes.data)) != 0:
+        raise ValueError("invalid window pattern")
+    return out[:n_layers].tolist()

@@ -1,0 +1,384 @@
+// Split-KV attention over the cache on CUDA cores (f32 accumulation).
+//
+// Device counterpart of attention_token (src/engine/runtime/inference.rs:1970-2530):
+// one launched item is one query token; a CTA owns (split, kv_head, item) and
+// serves all G = n_heads / n_kv_heads query heads of that KV head, so each
+// cache byte is read once (the reference re-reads it per query head).
+//
+// Data movement: every warp runs its own cp.async ring (NST stages of TK keys,
+// 16-byte copies straight from the cache rows into shared memory), so loads
+// stay in flight while the previous tile is reduced. Scores are reduced across
+// the lanes of a key with shuffles; softmax is the online form with base-2
+// exponentials; the per-warp states are merged in shared memory, the per-split
+// states through a scratch buffer by the last CTA to finish (atomic ticket).
+#pragma once
+
+#include "common.cuh"
+
+namespace ggr {
+
+constexpr int kSimtTK = 16;      // keys per pipeline stage of one warp
+constexpr int kSimtWarps = 4;
+
+struct AttnArgs {
+    KvView kv;
+    Items items;
+    Visibility vis;
+    int layer;
+    const float* q;       // [items][q_dim], rotated (and pre-scaled where the mode says so)
+    float score_scale;    // (1/sqrt(D) or 1) * log2(e), folded into q
+    int n_split;
+    float* part;          // scratch [items][Hq][n_split][D + 2]: o (un-normalised), m, l
+    unsigned* counters;   // scratch [items][Hkv] tickets, zero between launches
+    float* out;           // [items][q_dim] final output, or null
+    float* partial_out;   // [items][Hq][D + 2] (o / l, m, l) for cross-rank merging, or null
+    int shard_count;      // positions held locally
+    int stage_bytes;      // bytes of one ring stage of one warp
+};
+
+// f32 view of the 8 elements lane j owns in a cache row slice held in shared
+// memory. Element ownership: f32 -> {4j..4j+3} and {D/2+4j..D/2+4j+3};
+// bf16 / q8 -> {8j..8j+7}.
+template <int FMT>
+__device__ __forceinline__ void load8(const unsigned char* row, int j, int D, const float* scales, float out[8]) {
+    if (FMT == KV_F32) {
+        float4 a = *reinterpret_cast<const float4*>(row + (size_t)(4 * j) * 4);
+        float4 b = *reinterpret_cast<const float4*>(row + (size_t)(D / 2 + 4 * j) * 4);
+        out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
+        out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+    } else if (FMT == KV_BF16) {
+        uint4 u = *reinterpret_cast<const uint4*>(row + (size_t)j * 16);
+        out[0] = __uint_as_float(u.x << 16); out[1] = __uint_as_float(u.x & 0xffff0000u);
+        out[2] = __uint_as_float(u.y << 16); out[3] = __uint_as_float(u.y & 0xffff0000u);
+        out[4] = __uint_as_float(u.z << 16); out[5] = __uint_as_float(u.z & 0xffff0000u);
+        out[6] = __uint_as_float(u.w << 16); out[7] = __uint_as_float(u.w & 0xffff0000u);
+    } else {
+        uint2 u = *reinterpret_cast<const uint2*>(row + (size_t)j * 8);
+        float sc = FMT == KV_Q8_ROW ? scales[0] : scales[j >> 2];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            out[i] = (float)(signed char)((u.x >> (8 * i)) & 0xff) * sc;
+            out[4 + i] = (float)(signed char)((u.y >> (8 * i)) & 0xff) * sc;
+        }
+    }
+}
+
+template <int FMT>
+__device__ __forceinline__ int elem_index(int j, int p, int D) {
+    if (FMT == KV_F32) return p < 4 ? 4 * j + p : D / 2 + 4 * j + (p - 4);
+    return 8 * j + p;
+}
+
+// Issues the cp.async copies of one tile (K rows, V rows, scales) into a stage.
+template <int FMT>
+__device__ __forceinline__ void issue_tile(const AttnArgs& a, unsigned char* stage, int64_t row0, int key0,
+                                           int key_end, int kvh, int lane) {
+    const int D = a.kv.D, eb = a.kv.elem_bytes;
+    const int rowbytes = D * eb;
+    const int gran = (rowbytes % 16 == 0) ? 16 : ((rowbytes % 8 == 0) ? 8 : 4);
+    const int gpr = rowbytes / gran;
+    const int total = kSimtTK * gpr;
+    unsigned char* ks = stage;
+    unsigned char* vs = stage + kSimtTK * rowbytes;
+    const unsigned char* kg = reinterpret_cast<const unsigned char*>(a.kv.k);
+    const unsigned char* vg = reinterpret_cast<const unsigned char*>(a.kv.v);
+    for (int g = lane; g < total; g += 32) {
+        int key = g / gpr, col = g - key * gpr;
+        int t = key0 + key;
+        int valid = t < key_end;
+        int tc = valid ? t : key_end - 1;
+        int64_t src = ((row0 + tc) * a.kv.kv_dim + (int64_t)kvh * D) * eb + (int64_t)col * gran;
+        uint32_t dk = smem_u32(ks + key * rowbytes + col * gran);
+        uint32_t dv = smem_u32(vs + key * rowbytes + col * gran);
+        if (gran == 16) {
+            cp_async_16(dk, kg + src, valid ? 16 : 0);
+            cp_async_16(dv, vg + src, valid ? 16 : 0);
+        } else if (gran == 8) {
+            cp_async_8(dk, kg + src, valid ? 8 : 0);
+            cp_async_8(dv, vg + src, valid ? 8 : 0);
+        } else {
+            cp_async_4(dk, kg + src, valid ? 4 : 0);
+            cp_async_4(dv, vg + src, valid ? 4 : 0);
+        }
+    }
+    if (FMT == KV_Q8_ROW || FMT == KV_Q8_BLOCK32) {
+        const int nsh = FMT == KV_Q8_ROW ? 1 : D / 32;     // scales of this head per key
+        const int nsr = a.kv.n_scales;                      // scales per cache row
+        float* ksc = reinterpret_cast<float*>(stage + 2 * kSimtTK * rowbytes);
+        float* vsc = ksc + kSimtTK * nsh;
+        for (int g = lane; g < kSimtTK * nsh; g += 32) {
+            int key = g / nsh, b = g - key * nsh;
+            int t = key0 + key;
+            int valid = t < key_end;
+            int tc = valid ? t : key_end - 1;
+            int64_t si = (row0 + tc) * nsr + (FMT == KV_Q8_ROW ? 0 : (int64_t)kvh * nsh + b);
+            cp_async_4(smem_u32(ksc + g), a.kv.ks + si, valid ? 4 : 0);
+            cp_async_4(smem_u32(vsc + g), a.kv.vs + si, valid ? 4 : 0);
+        }
+    }
+}
+
+template <int FMT, int GH, int NST>
+__global__ void __launch_bounds__(kSimtWarps * 32) attn_simt_kernel(AttnArgs a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ float s_score[kSimtWarps][GH][kSimtTK];
+    __shared__ int s_last;
+
+    const int D = a.kv.D, G = a.kv.G, Hq = a.kv.Hq;
+    const int split = blockIdx.x, kvh = blockIdx.y, item = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nw = blockDim.x >> 5;  // 1, 2 or 4 warps, each with its own ring
+    const int rowbytes = D * a.kv.elem_bytes;
+
+    int seq, pos;
+    a.items.get(item, seq, pos);
+    int vs, ve;
+    a.vis.range(pos, vs, ve);
+    // keys this rank holds
+    vs = max(vs, a.kv.pos_begin);
+    ve = min(ve, a.kv.pos_begin + a.shard_count);
+    const int T = max(0, ve - vs);
+    const int chunk = (T + a.n_split - 1) / a.n_split;
+    const int s0 = vs + split * chunk;
+    const int s1 = min(ve, s0 + chunk);
+    const int64_t row0 = a.kv.row(seq, a.layer, a.kv.pos_begin);  // cache row of local position 0
+    // positions are addressed relative to pos_begin below
+    const int k0 = s0 - a.kv.pos_begin, k1 = s1 - a.kv.pos_begin;
+
+    // lanes per key and this lane's place
+    int chunks = D / 8;
+    int LPK = 1;
+    while (LPK < chunks) LPK <<= 1;
+    const int KPW = 32 / LPK;
+    const int grp = lane / LPK, j = lane - grp * LPK;
+    const bool active = j < chunks;
+    const int nsh = FMT == KV_Q8_ROW ? 1 : (FMT == KV_Q8_BLOCK32 ? D / 32 : 0);
+
+    unsigned char* ring = smem + (size_t)warp * NST * a.stage_bytes;
+    const int n_tiles_total = k1 > k0 ? (k1 - k0 + kSimtTK - 1) / kSimtTK : 0;
+    // this warp's tiles: warp, warp + W, ...
+    const int my_tiles = n_tiles_total > warp ? (n_tiles_total - warp + nw - 1) / nw : 0;
+
+    for (int g0 = 0; g0 < G; g0 += GH) {
+        float qreg[GH][8], acc[GH][8], m[GH], l[GH];
+#pragma unroll
+        for (int g = 0; g < GH; ++g) {
+            m[g] = -INFINITY;
+            l[g] = 0.0f;
+            const bool hv = g0 + g < G;
+            const float* qh = a.q + ((int64_t)item * Hq + (int64_t)kvh * G + g0 + g) * D;
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+                acc[g][p] = 0.0f;
+                qreg[g][p] = (hv && active) ? qh[elem_index<FMT>(j, p, D)] * a.score_scale : 0.0f;
+            }
+        }
+
+        // prologue: NST - 1 tiles in flight
+#pragma unroll
+        for (int s = 0; s < NST - 1; ++s) {
+            if (s < my_tiles)
+                issue_tile<FMT>(a, ring + (size_t)s * a.stage_bytes, row0, k0 + (warp + s * nw) * kSimtTK, k1,
+                                kvh, lane);
+            cp_async_commit();
+        }
+
+        for (int it = 0; it < my_tiles; ++it) {
+            cp_async_wait<NST - 2>();
+            __syncwarp();
+            const unsigned char* stage = ring + (size_t)(it % NST) * a.stage_bytes;
+            const unsigned char* kt = stage;
+            const unsigned char* vt = stage + kSimtTK * rowbytes;
+            const float* ksc = reinterpret_cast<const float*>(stage + 2 * kSimtTK * rowbytes);
+            const float* vsc = ksc + kSimtTK * nsh;
+            const int key0 = k0 + (warp + it * nw) * kSimtTK;
+
+            // scores of the tile
+            for (int kk = grp; kk < kSimtTK; kk += KPW) {
+                float kf[8];
+                if (active) load8<FMT>(kt + (size_t)kk * rowbytes, j, D, ksc + kk * nsh, kf);
+                const bool valid = key0 + kk < k1;
+#pragma unroll
+                for (int g = 0; g < GH; ++g) {
+                    float s = 0.0f;
+                    if (active) {
+#pragma unroll
+                        for (int p = 0; p < 8; ++p) s = fmaf(qreg[g][p], kf[p], s);
+                    }
+                    for (int o = LPK >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                    if (j == 0) s_score[warp][g][kk] = valid ? s : -INFINITY;
+                }
+            }
+            __syncwarp();
+            // tile maximum, probabilities, running sum
+            float alpha[GH];
+            bool any = false;
+#pragma unroll
+            for (int g = 0; g < GH; ++g) {
+                float sv = lane < kSimtTK ? s_score[warp][g][lane] : -INFINITY;
+                float mx = warp_max(sv);
+                float mn = fmaxf(m[g], mx);
+                float p = (mn == -INFINITY) ? 0.0f : exp2f(sv - mn);
+                float ps = warp_sum(p);
+                alpha[g] = (mn == -INFINITY) ? 1.0f : exp2f(m[g] - mn);
+                l[g] = l[g] * alpha[g] + ps;
+                m[g] = mn;
+                if (lane < kSimtTK) s_score[warp][g][lane] = p;
+                any |= (mx != -INFINITY);
+            }
+            __syncwarp();
+#pragma unroll
+            for (int g = 0; g < GH; ++g) {
+#pragma unroll
+                for (int p = 0; p < 8; ++p) acc[g][p] *= alpha[g];
+            }
+            if (any) {
+                for (int kk = grp; kk < kSimtTK; kk += KPW) {
+                    float vf[8];
+                    if (active) {
+                        load8<FMT>(vt + (size_t)kk * rowbytes, j, D, vsc + kk * nsh, vf);
+#pragma unroll
+                        for (int g = 0; g < GH; ++g) {
+                            float p = s_score[warp][g][kk];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(p, vf[e], acc[g][e]);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            // refill the stage consumed one iteration ago
+            const int nt_ = it + NST - 1;
+            if (nt_ < my_tiles)
+                issue_tile<FMT>(a, ring + (size_t)(nt_ % NST) * a.stage_bytes, row0,
+                                k0 + (warp + nt_ * nw) * kSimtTK, k1, kvh, lane);
+            cp_async_commit();
+        }
+        cp_async_wait<0>();
+
+        // fold the key groups of the warp together
+#pragma unroll
+        for (int g = 0; g < GH; ++g) {
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+                float v = acc[g][p];
+                for (int o = LPK; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                acc[g][p] = v;
+            }
+        }
+        __syncthreads();  // every warp is done with its ring; reuse it as the merge area
+        float* wacc = reinterpret_cast<float*>(smem);            // [W][GH][D]
+        float* wm = wacc + nw * GH * D;                           // [W][GH]
+        float* wl = wm + nw * GH;                                 // [W][GH]
+        if (grp == 0 && active) {
+#pragma unroll
+            for (int g = 0; g < GH; ++g) {
+#pragma unroll
+                for (int p = 0; p < 8; ++p) wacc[(warp * GH + g) * D + elem_index<FMT>(j, p, D)] = acc[g][p];
+            }
+        }
+        if (lane == 0) {
+#pragma unroll
+            for (int g = 0; g < GH; ++g) {
+                wm[warp * GH + g] = m[g];
+                wl[warp * GH + g] = l[g];
+            }
+        }
+        __syncthreads();
+        const int gn = min(GH, G - g0);
+        for (int idx = tid; idx < gn * D; idx += blockDim.x) {
+            int g = idx / D, d = idx - g * D;
+            float ms = -INFINITY;
+            for (int w = 0; w < nw; ++w) ms = fmaxf(ms, wm[w * GH + g]);
+            float o = 0.0f, ls = 0.0f;
+            for (int w = 0; w < nw; ++w) {
+                float mw = wm[w * GH + g];
+                float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - ms);
+                o += f * wacc[(w * GH + g) * D + d];
+                ls += f * wl[w * GH + g];
+            }
+            const int h = kvh * G + g0 + g;
+            if (a.n_split == 1) {
+                float inv = ls > 0.0f ? 1.0f / ls : 0.0f;
+                if (a.partial_out) {
+                    float* po = a.partial_out + ((int64_t)item * Hq + h) * (D + 2);
+                    po[d] = o * inv;
+                    if (d == 0) {
+                        po[D] = ms;
+                        po[D + 1] = ls;
+                    }
+                } else {
+                    a.out[((int64_t)item * Hq + h) * D + d] = o * inv;
+                }
+            } else {
+                float* pp = a.part + (((int64_t)item * Hq + h) * a.n_split + split) * (D + 2);
+                pp[d] = o;
+                if (d == 0) {
+                    pp[D] = ms;
+                    pp[D + 1] = ls;
+                }
+            }
+        }
+        __syncthreads();  // merge area is free again before the next head group refills the ring
+    }
+
+    if (a.n_split == 1) return;
+
+    // last CTA of this (item, kv_head) merges the splits
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        unsigned prev = atomicAdd(&a.counters[item * a.kv.Hkv + kvh], 1u);
+        s_last = (prev == (unsigned)a.n_split - 1u);
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int idx = tid; idx < G * D; idx += blockDim.x) {
+        int g = idx / D, d = idx - g * D;
+        const int h = kvh * G + g;
+        const float* pp = a.part + ((int64_t)item * Hq + h) * a.n_split * (D + 2);
+        float ms = -INFINITY;
+        for (int s = 0; s < a.n_split; ++s) ms = fmaxf(ms, __ldcg(pp + (int64_t)s * (D + 2) + D));
+        float o = 0.0f, ls = 0.0f;
+        for (int s = 0; s < a.n_split; ++s) {
+            float mw = __ldcg(pp + (int64_t)s * (D + 2) + D);
+            float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - ms);
+            o += f * __ldcg(pp + (int64_t)s * (D + 2) + d);
+            ls += f * __ldcg(pp + (int64_t)s * (D + 2) + D + 1);
+        }
+        float inv = ls > 0.0f ? 1.0f / ls : 0.0f;
+        if (a.partial_out) {
+            float* po = a.partial_out + ((int64_t)item * Hq + h) * (D + 2);
+            po[d] = o * inv;
+            if (d == 0) {
+                po[D] = ms;
+                po[D + 1] = ls;
+            }
+        } else {
+            a.out[((int64_t)item * Hq + h) * D + d] = o * inv;
+        }
+    }
+    if (tid == 0) a.counters[item * a.kv.Hkv + kvh] = 0u;  // ready for the next launch
+}
+
+// Merges n_parts partial states [n_parts][items][Hq][D + 2] (o / l, m, l) into out.
+__global__ void combine_partials_kernel(const float* parts, int n_parts, int items, int Hq, int D, float* out) {
+    const int h = blockIdx.x, item = blockIdx.y;
+    const int64_t stride = (int64_t)items * Hq * (D + 2);
+    const float* base = parts + ((int64_t)item * Hq + h) * (D + 2);
+    float ms = -INFINITY;
+    for (int r = 0; r < n_parts; ++r) ms = fmaxf(ms, base[r * stride + D]);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float o = 0.0f, ls = 0.0f;
+        for (int r = 0; r < n_parts; ++r) {
+            float mw = base[r * stride + D], lw = base[r * stride + D + 1];
+            float f = (mw == -INFINITY) ? 0.0f : lw * exp2f(mw - ms);
+            o += f * base[r * stride + d];
+            ls += f;
+        }
+        out[((int64_t)item * Hq + h) * D + d] = ls > 0.0f ? o / ls : 0.0f;
+    }
+}
+
+}  // namespace ggr

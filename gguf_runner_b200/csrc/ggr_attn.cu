@@ -1,0 +1,953 @@
+// Context, launch logic and C ABI of the attention path (see include/ggr_attn.h).
+// There is no CPU fallback: every entry point that computes launches CUDA
+// kernels on the context's device or returns an error status.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../../include/ggr_attn.h"
+#include "attn_mma.cuh"
+#include "attn_simt.cuh"
+#include "common.cuh"
+#include "prefill_tc.cuh"
+#include "rope_append.cuh"
+
+using namespace ggr;
+
+struct ggr_attn_ctx {
+    ggr_attn_config cfg;
+    std::vector<int32_t> windows;
+    int D = 0, kv_dim = 0, q_dim = 0, G = 0, rope_half = 0, rope_dim = 0;
+    float attn_scale = 0.f;
+    int shard_begin = 0, shard_count = 0;
+    int sm_count = 0, smem_optin = 0;
+    cudaStream_t stream = nullptr, own_stream = nullptr;
+    KvView kv{};
+    float* d_freqs = nullptr;
+    float* d_freqs_swa = nullptr;
+    int* d_plan = nullptr;
+    int plan_len = 0, next_text = 0, has_plan = 0;
+    int2* d_blocks = nullptr;
+    std::vector<int2> blocks;
+    // scratch, grown on demand
+    float* d_qrot = nullptr;
+    __nv_bfloat16* d_qrot_h = nullptr;
+    size_t qrot_cap = 0, qrot_h_cap = 0;
+    float* d_part = nullptr;
+    size_t part_cap = 0;
+    unsigned* d_counters = nullptr;
+    size_t counters_cap = 0;
+    // staging for host-pointer calls
+    unsigned char* d_stage[4] = {nullptr, nullptr, nullptr, nullptr};
+    size_t stage_cap[4] = {0, 0, 0, 0};
+    std::string err;
+    int64_t launches = 0;
+};
+
+namespace {
+
+thread_local std::string g_create_err;
+
+int fail(ggr_attn_ctx* c, int status, const std::string& msg) {
+    if (c) c->err = msg;
+    return status;
+}
+
+#define CUDA_TRY(c, expr)                                                                          \
+    do {                                                                                           \
+        cudaError_t e_ = (expr);                                                                   \
+        if (e_ != cudaSuccess)                                                                     \
+            return fail(c, GGR_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(e_));      \
+    } while (0)
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int dev) {
+        cudaGetDevice(&prev);
+        if (prev != dev) cudaSetDevice(dev);
+    }
+    ~DeviceGuard() {
+        int cur = -1;
+        cudaGetDevice(&cur);
+        if (prev >= 0 && cur != prev) cudaSetDevice(prev);
+    }
+};
+
+int elem_bytes_of(int fmt) { return fmt == GGR_KV_F32 ? 4 : (fmt == GGR_KV_BF16 ? 2 : 1); }
+
+template <typename T>
+int ensure(ggr_attn_ctx* c, T** ptr, size_t* cap, size_t need_elems) {
+    if (need_elems <= *cap) return GGR_OK;
+    // earlier launches may still use the old buffer
+    CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    if (*ptr) cudaFree(*ptr);
+    *ptr = nullptr;
+    *cap = 0;
+    size_t want = std::max(need_elems, (size_t)256);
+    cudaError_t e = cudaMalloc((void**)ptr, want * sizeof(T));
+    if (e != cudaSuccess) return fail(c, GGR_ERR_ALLOC, std::string("scratch allocation failed: ") + cudaGetErrorString(e));
+    *cap = want;
+    return GGR_OK;
+}
+
+// src/engine/runtime/inference.rs:1821-1825
+bool is_swa_layer(const ggr_attn_ctx* c, int l) {
+    if (c->windows.empty()) return c->cfg.swa_pattern > 0 && (l % c->cfg.swa_pattern < c->cfg.swa_pattern - 1);
+    return c->windows[l] != 0;
+}
+
+RopeParams rope_params(const ggr_attn_ctx* c, int layer) {
+    RopeParams rp{};
+    const bool swa = is_swa_layer(c, layer);
+    rp.freqs = (c->cfg.swa_theta_on_window_layers && swa) ? c->d_freqs_swa : c->d_freqs;
+    rp.fscale = swa ? c->cfg.rope_scale_local : c->cfg.rope_scale_global;
+    rp.rope_half = c->rope_half;
+    rp.rope_dim = c->rope_dim;
+    rp.style = c->cfg.rope_style;
+    rp.layout = c->cfg.rope_layout;
+    for (int i = 0; i < 4; ++i) rp.sections[i] = c->cfg.rope_sections[i];
+    rp.plan = c->d_plan;
+    rp.plan_len = c->plan_len;
+    rp.next_text = c->next_text;
+    rp.has_plan = c->has_plan;
+    rp.q_prescale = c->attn_scale;
+    rp.do_prescale = c->cfg.scale_mode == GGR_SCALE_Q_PRESCALED;
+    return rp;
+}
+
+Visibility visibility(const ggr_attn_ctx* c, int layer) {
+    Visibility v{};
+    v.window = c->windows.empty() ? 0 : c->windows[layer];
+    v.image_mode = c->cfg.image_mode;
+    v.blocks = c->d_blocks;
+    v.n_blocks = (int)c->blocks.size();
+    return v;
+}
+
+// host copy of Visibility::range (src/engine/runtime/attention.rs:73-97)
+void visible_host(const ggr_attn_ctx* c, int layer, int pos, int* vs, int* ve) {
+    int e = pos + 1;
+    int w = c->windows.empty() ? 0 : c->windows[layer];
+    int s = w > 0 ? std::max(0, e - w) : 0;
+    if (c->cfg.image_mode == GGR_IMAGE_BIDIRECTIONAL) {
+        for (const int2& b : c->blocks) {
+            if (pos >= b.x && pos - b.x < b.y) {
+                s = std::min(s, b.x);
+                e = b.x + b.y;
+                break;
+            }
+        }
+    }
+    *vs = s;
+    *ve = e;
+}
+
+int check_layer(ggr_attn_ctx* c, int layer) {
+    if (layer < 0 || layer >= c->cfg.n_layers) return fail(c, GGR_ERR_RANGE, "layer outside the cache");
+    return GGR_OK;
+}
+
+// ---- launches ----------------------------------------------------------------------------
+
+int launch_rope_append(ggr_attn_ctx* c, int layer, const Items& items, int flags, int in_bf16, const void* q,
+                       const void* k, const void* v, float* q_out, __nv_bfloat16* q_out_h, float* k_out) {
+    RopeAppendArgs a{};
+    a.rope = rope_params(c, layer);
+    a.kv = c->kv;
+    a.items = items;
+    a.layer = layer;
+    a.flags = flags;
+    a.in_bf16 = in_bf16;
+    a.q = q;
+    a.k = k;
+    a.v = v;
+    a.q_out = q_out;
+    a.q_out_h = q_out_h;
+    a.k_out = k_out;
+    a.shard_count = c->shard_count;
+    size_t smem = (size_t)(2 * c->rope_half + 2 * c->kv_dim + 16) * sizeof(float);
+    if (smem > 48 * 1024) {
+        CUDA_TRY(c, cudaFuncSetAttribute(rope_append_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    }
+    rope_append_kernel<<<items.n, 256, smem, c->stream>>>(a);
+    CUDA_TRY(c, cudaGetLastError());
+    c->launches++;
+    return GGR_OK;
+}
+
+struct SimtPlan {
+    int nw, nst, stage_bytes, gh;
+    size_t smem;
+    int ctas_per_sm;
+};
+
+SimtPlan simt_plan(const ggr_attn_ctx* c) {
+    SimtPlan p{};
+    const int rowbytes = c->D * c->kv.elem_bytes;
+    const int nsh = c->kv.fmt == KV_Q8_ROW ? 1 : (c->kv.fmt == KV_Q8_BLOCK32 ? c->D / 32 : 0);
+    int stage = 2 * kSimtTK * rowbytes + 2 * kSimtTK * nsh * 4;
+    stage = (stage + 15) / 16 * 16;
+    p.stage_bytes = stage;
+    int gh = 1;
+    while (gh < c->G && gh < 8) gh <<= 1;
+    p.gh = gh;
+    const int big = 200 * 1024, small = 100 * 1024;
+    int nw = kSimtWarps, nst = 0;
+    for (;; nw >>= 1) {
+        if (nw * 3 * stage <= small) {
+            nst = 3;
+            break;
+        }
+        nst = std::min(4, big / (nw * stage));
+        if (nst >= 2 || nw == 1) break;
+    }
+    if (nst > 4) nst = 4;
+    p.nw = nw;
+    p.nst = std::max(nst, 2);
+    size_t ring = (size_t)p.nw * p.nst * stage;
+    size_t merge = (size_t)p.nw * gh * (c->D + 2) * sizeof(float) + 64;
+    p.smem = std::max(ring, merge);
+    p.ctas_per_sm = std::max(1, std::min(8, (int)((size_t)(c->smem_optin + 1024) / (p.smem + 4096))));
+    return p;
+}
+
+template <int FMT, int GH, int NST>
+int launch_simt_inst(ggr_attn_ctx* c, const AttnArgs& a, dim3 grid, int nw, size_t smem) {
+    static int configured_for = -1;  // device ordinal the attribute was set on
+    if (configured_for != c->cfg.device) {
+        CUDA_TRY(c, cudaFuncSetAttribute(attn_simt_kernel<FMT, GH, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         c->smem_optin));
+        configured_for = c->cfg.device;
+    }
+    attn_simt_kernel<FMT, GH, NST><<<grid, nw * 32, smem, c->stream>>>(a);
+    CUDA_TRY(c, cudaGetLastError());
+    c->launches++;
+    return GGR_OK;
+}
+
+template <int FMT, int GH>
+int launch_simt_nst(ggr_attn_ctx* c, const AttnArgs& a, dim3 grid, const SimtPlan& p) {
+    switch (p.nst) {
+        case 2: return launch_simt_inst<FMT, GH, 2>(c, a, grid, p.nw, p.smem);
+        case 3: return launch_simt_inst<FMT, GH, 3>(c, a, grid, p.nw, p.smem);
+        default: return launch_simt_inst<FMT, GH, 4>(c, a, grid, p.nw, p.smem);
+    }
+}
+
+template <int FMT>
+int launch_simt_gh(ggr_attn_ctx* c, const AttnArgs& a, dim3 grid, const SimtPlan& p) {
+    switch (p.gh) {
+        case 1: return launch_simt_nst<FMT, 1>(c, a, grid, p);
+        case 2: return launch_simt_nst<FMT, 2>(c, a, grid, p);
+        case 4: return launch_simt_nst<FMT, 4>(c, a, grid, p);
+        default: return launch_simt_nst<FMT, 8>(c, a, grid, p);
+    }
+}
+
+int launch_simt(ggr_attn_ctx* c, const AttnArgs& a, dim3 grid, const SimtPlan& p) {
+    switch (c->kv.fmt) {
+        case KV_F32: return launch_simt_gh<KV_F32>(c, a, grid, p);
+        case KV_BF16: return launch_simt_gh<KV_BF16>(c, a, grid, p);
+        case KV_Q8_ROW: return launch_simt_gh<KV_Q8_ROW>(c, a, grid, p);
+        default: return launch_simt_gh<KV_Q8_BLOCK32>(c, a, grid, p);
+    }
+}
+
+bool use_mma_decode(const ggr_attn_ctx* c) {
+    const bool can = c->kv.fmt == KV_BF16 && mma_decode_supported(c->D, c->G);
+    if (c->cfg.decode_impl == GGR_IMPL_MMA) return can;
+    if (c->cfg.decode_impl == GGR_IMPL_SIMT) return false;
+    return can && c->G >= 3;
+}
+
+// Attention over the cache for `items` (already rotated q at q_dev).
+int launch_attention(ggr_attn_ctx* c, int layer, const Items& items, int t_max, const float* q_dev, float* out_dev,
+                     float* partial_dev, bool allow_mma) {
+    AttnArgs a{};
+    a.kv = c->kv;
+    a.items = items;
+    a.vis = visibility(c, layer);
+    a.layer = layer;
+    a.q = q_dev;
+    a.score_scale = (c->cfg.scale_mode == GGR_SCALE_SCORE ? c->attn_scale : 1.0f) * kLog2e;
+    a.out = out_dev;
+    a.partial_out = partial_dev;
+    a.shard_count = c->shard_count;
+
+    const bool mma = allow_mma && use_mma_decode(c);
+    SimtPlan p = simt_plan(c);
+    size_t smem = p.smem;
+    int ctas_per_sm = p.ctas_per_sm;
+    int min_keys = p.nw * kSimtTK * 2;
+    if (mma) {
+        MmaPlan mp = mma_plan(c->D, c->smem_optin);
+        smem = mp.smem;
+        ctas_per_sm = mp.ctas_per_sm;
+        min_keys = mp.min_keys;
+    }
+    a.stage_bytes = p.stage_bytes;
+
+    const int64_t base_ctas = (int64_t)c->kv.Hkv * items.n;
+    const int64_t target = (int64_t)c->sm_count * ctas_per_sm;
+    int n_split = (int)std::max<int64_t>(1, (target + base_ctas - 1) / base_ctas);
+    n_split = std::min(n_split, std::max(1, t_max / min_keys));
+    if (base_ctas >= target) n_split = 1;
+    if (c->cfg.max_splits > 0) n_split = std::min(n_split, c->cfg.max_splits);
+    n_split = std::min(n_split, 512);
+    a.n_split = n_split;
+    if (n_split > 1) {
+        int rc = ensure(c, &c->d_part, &c->part_cap, (size_t)items.n * c->kv.Hq * n_split * (c->D + 2));
+        if (rc) return rc;
+        const size_t before = c->counters_cap;
+        rc = ensure(c, &c->d_counters, &c->counters_cap, (size_t)items.n * c->kv.Hkv);
+        if (rc) return rc;
+        if (c->counters_cap != before)
+            CUDA_TRY(c, cudaMemsetAsync(c->d_counters, 0, c->counters_cap * sizeof(unsigned), c->stream));
+        a.part = c->d_part;
+        a.counters = c->d_counters;
+    }
+    dim3 grid(n_split, c->kv.Hkv, items.n);
+    if (mma) {
+        int rc = launch_mma_decode(a, grid, smem, c->smem_optin, c->cfg.device, c->stream);
+        if (rc != 0) return fail(c, GGR_ERR_CUDA, std::string("mma decode launch: ") + cudaGetErrorString((cudaError_t)rc));
+        c->launches++;
+        return GGR_OK;
+    }
+    return launch_simt(c, a, grid, p);
+}
+
+// copies a caller buffer into a staging slot when the caller's memory is host memory
+int stage_in(ggr_attn_ctx* c, int slot, const void* src, size_t bytes, int ptr_kind, const void** dev) {
+    if (ptr_kind == GGR_PTR_DEVICE) {
+        *dev = src;
+        return GGR_OK;
+    }
+    int rc = ensure(c, &c->d_stage[slot], &c->stage_cap[slot], bytes);
+    if (rc) return rc;
+    CUDA_TRY(c, cudaMemcpyAsync(c->d_stage[slot], src, bytes, cudaMemcpyHostToDevice, c->stream));
+    *dev = c->d_stage[slot];
+    return GGR_OK;
+}
+
+int t_max_of(const ggr_attn_ctx* c, int layer, const int32_t* pos, int n) {
+    int t = 1;
+    for (int i = 0; i < n; ++i) {
+        int vs, ve;
+        visible_host(c, layer, pos[i], &vs, &ve);
+        vs = std::max(vs, c->shard_begin);
+        ve = std::min(ve, c->shard_begin + c->shard_count);
+        t = std::max(t, ve - vs);
+    }
+    return t;
+}
+
+int decode_common(ggr_attn_ctx* c, int layer, const int32_t* pos, int B, const float* q, const float* k,
+                  const float* v, float* out, float* partial, int ptr_kind) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    int rc = check_layer(c, layer);
+    if (rc) return rc;
+    if (B <= 0 || B > c->cfg.max_batch) return fail(c, GGR_ERR_RANGE, "batch larger than max_batch");
+    if (!pos || !q || !k || !v || (!out && !partial)) return fail(c, GGR_ERR_INVALID, "null buffer");
+    for (int b = 0; b < B; ++b)
+        if (pos[b] < 0 || pos[b] >= c->cfg.seq_len) return fail(c, GGR_ERR_RANGE, "position outside the cache");
+    if (c->cfg.shard_mode != GGR_SHARD_NONE && !partial)
+        return fail(c, GGR_ERR_INVALID, "a KV-sequence shard produces partial states: call ggr_attn_decode_partial");
+
+    const size_t qb = (size_t)B * c->q_dim * sizeof(float), kb = (size_t)B * c->kv_dim * sizeof(float);
+    const void *dq, *dk, *dv;
+    if ((rc = stage_in(c, 0, q, qb, ptr_kind, &dq))) return rc;
+    if ((rc = stage_in(c, 1, k, kb, ptr_kind, &dk))) return rc;
+    if ((rc = stage_in(c, 2, v, kb, ptr_kind, &dv))) return rc;
+    const size_t out_elems = partial ? (size_t)B * c->kv.Hq * (c->D + 2) : (size_t)B * c->q_dim;
+    float* dout = partial ? partial : out;
+    if (ptr_kind == GGR_PTR_HOST) {
+        if ((rc = ensure(c, &c->d_stage[3], &c->stage_cap[3], out_elems * sizeof(float)))) return rc;
+        dout = reinterpret_cast<float*>(c->d_stage[3]);
+    }
+    if ((rc = ensure(c, &c->d_qrot, &c->qrot_cap, (size_t)B * c->q_dim))) return rc;
+
+    for (int b0 = 0; b0 < B; b0 += kMaxArgItems) {
+        const int n = std::min(kMaxArgItems, B - b0);
+        Items it{};
+        it.mode = 0;
+        it.seq0 = b0;
+        it.n = n;
+        for (int i = 0; i < n; ++i) it.pos[i] = pos[b0 + i];
+        const float* qc = reinterpret_cast<const float*>(dq) + (size_t)b0 * c->q_dim;
+        const float* kc = reinterpret_cast<const float*>(dk) + (size_t)b0 * c->kv_dim;
+        const float* vc = reinterpret_cast<const float*>(dv) + (size_t)b0 * c->kv_dim;
+        float* qr = c->d_qrot + (size_t)b0 * c->q_dim;
+        rc = launch_rope_append(c, layer, it, RF_ROTATE | RF_WRITE_Q | RF_APPEND, 0, qc, kc, vc, qr, nullptr, nullptr);
+        if (rc) return rc;
+        const int t_max = t_max_of(c, layer, pos + b0, n);
+        float* oc = partial ? nullptr : dout + (size_t)b0 * c->q_dim;
+        float* pc = partial ? dout + (size_t)b0 * c->kv.Hq * (c->D + 2) : nullptr;
+        rc = launch_attention(c, layer, it, t_max, qr, oc, pc, true);
+        if (rc) return rc;
+    }
+    if (ptr_kind == GGR_PTR_HOST) {
+        CUDA_TRY(c, cudaMemcpyAsync(partial ? partial : out, dout, out_elems * sizeof(float), cudaMemcpyDeviceToHost,
+                                    c->stream));
+        CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    }
+    return GGR_OK;
+}
+
+int prefill_common(ggr_attn_ctx* c, int layer, int seq, int base_pos, int m, const void* q, const void* k,
+                   const void* v, int in_dtype, float* out, int ptr_kind, bool block_mode) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    int rc = check_layer(c, layer);
+    if (rc) return rc;
+    if (seq < 0 || seq >= c->cfg.max_batch) return fail(c, GGR_ERR_RANGE, "sequence outside the cache");
+    if (m <= 0 || base_pos < 0 || (int64_t)base_pos + m > c->cfg.seq_len)
+        return fail(c, GGR_ERR_RANGE, "prefill rows outside the cache");
+    if (!q || !k || !v || !out) return fail(c, GGR_ERR_INVALID, "null buffer");
+    if (in_dtype != GGR_DTYPE_F32 && in_dtype != GGR_DTYPE_BF16) return fail(c, GGR_ERR_INVALID, "unknown input dtype");
+    if (c->cfg.shard_mode != GGR_SHARD_NONE)
+        return fail(c, GGR_ERR_UNSUPPORTED, "prefill runs on an unsharded context (shard heads across contexts instead)");
+    if (c->cfg.image_mode == GGR_IMAGE_BIDIRECTIONAL) {
+        for (const int2& b : c->blocks) {
+            const bool overlap = b.x < base_pos + m && base_pos < b.x + b.y;
+            if (!block_mode && overlap)
+                // src/engine/runtime/inference.rs:2750-2757
+                return fail(c, GGR_ERR_INVALID, "batched prefill cannot include complete-block image attention");
+            if (block_mode && overlap && (b.x < base_pos || b.x + b.y > base_pos + m))
+                return fail(c, GGR_ERR_INVALID, "staged prefill must cover whole image blocks");
+        }
+    }
+    const size_t es = in_dtype == GGR_DTYPE_BF16 ? 2 : 4;
+    const void *dq, *dk, *dv;
+    if ((rc = stage_in(c, 0, q, (size_t)m * c->q_dim * es, ptr_kind, &dq))) return rc;
+    if ((rc = stage_in(c, 1, k, (size_t)m * c->kv_dim * es, ptr_kind, &dk))) return rc;
+    if ((rc = stage_in(c, 2, v, (size_t)m * c->kv_dim * es, ptr_kind, &dv))) return rc;
+    float* dout = out;
+    if (ptr_kind == GGR_PTR_HOST) {
+        if ((rc = ensure(c, &c->d_stage[3], &c->stage_cap[3], (size_t)m * c->q_dim * sizeof(float)))) return rc;
+        dout = reinterpret_cast<float*>(c->d_stage[3]);
+    }
+
+    const bool tc = prefill_tc_usable(c->cfg.prefill_impl, c->kv.fmt, c->D, c->G);
+    if ((rc = ensure(c, &c->d_qrot, &c->qrot_cap, tc ? (size_t)1 : (size_t)m * c->q_dim))) return rc;
+    if (tc && (rc = ensure(c, &c->d_qrot_h, &c->qrot_h_cap, (size_t)m * c->q_dim))) return rc;
+
+    // rope + append for every row first; causality is enforced by the mask, not by write order
+    const int max_items = 65535;
+    for (int i0 = 0; i0 < m; i0 += max_items) {
+        const int n = std::min(max_items, m - i0);
+        Items it{};
+        it.mode = 1;
+        it.seq0 = seq;
+        it.base_pos = base_pos + i0;
+        it.n = n;
+        const unsigned char* qc = reinterpret_cast<const unsigned char*>(dq) + (size_t)i0 * c->q_dim * es;
+        const unsigned char* kc = reinterpret_cast<const unsigned char*>(dk) + (size_t)i0 * c->kv_dim * es;
+        const unsigned char* vc = reinterpret_cast<const unsigned char*>(dv) + (size_t)i0 * c->kv_dim * es;
+        rc = launch_rope_append(c, layer, it, RF_ROTATE | RF_WRITE_Q | RF_APPEND, in_dtype == GGR_DTYPE_BF16, qc, kc, vc,
+                                tc ? nullptr : c->d_qrot + (size_t)i0 * c->q_dim,
+                                tc ? c->d_qrot_h + (size_t)i0 * c->q_dim : nullptr, nullptr);
+        if (rc) return rc;
+    }
+    if (tc) {
+        PrefillTcArgs a{};
+        a.kv = c->kv;
+        a.vis = visibility(c, layer);
+        a.layer = layer;
+        a.seq = seq;
+        a.base_pos = base_pos;
+        a.m = m;
+        a.q = c->d_qrot_h;
+        a.out = dout;
+        a.score_scale = (c->cfg.scale_mode == GGR_SCALE_SCORE ? c->attn_scale : 1.0f) * kLog2e;
+        std::string msg;
+        rc = launch_prefill_tc(a, c->sm_count, c->smem_optin, c->cfg.device, c->stream, &msg);
+        if (rc) return fail(c, rc, msg);
+        c->launches++;
+    } else {
+        for (int i0 = 0; i0 < m; i0 += max_items) {
+            const int n = std::min(max_items, m - i0);
+            Items it{};
+            it.mode = 1;
+            it.seq0 = seq;
+            it.base_pos = base_pos + i0;
+            it.n = n;
+            int t_max = 1;
+            {
+                // widest visible range of the chunk (ranges end at pos + 1 or at a block end)
+                int vs, ve;
+                visible_host(c, layer, base_pos + i0 + n - 1, &vs, &ve);
+                t_max = std::max(1, ve - vs);
+                visible_host(c, layer, base_pos + i0, &vs, &ve);
+                t_max = std::max(t_max, ve - vs);
+            }
+            rc = launch_attention(c, layer, it, t_max, c->d_qrot + (size_t)i0 * c->q_dim, dout + (size_t)i0 * c->q_dim,
+                                  nullptr, false);
+            if (rc) return rc;
+        }
+    }
+    if (ptr_kind == GGR_PTR_HOST) {
+        CUDA_TRY(c, cudaMemcpyAsync(out, dout, (size_t)m * c->q_dim * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+        CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    }
+    return GGR_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ggr_attn_abi_version(void) { return GGR_ATTN_ABI_VERSION; }
+
+void ggr_attn_config_init(ggr_attn_config* cfg) {
+    if (!cfg) return;
+    std::memset(cfg, 0, sizeof(*cfg));
+    cfg->struct_size = (int32_t)sizeof(*cfg);
+    cfg->max_batch = 1;
+    cfg->rope_theta = 500000.0f;    // src/vendors/llama.rs:13-15
+    cfg->rope_theta_swa = 10000.0f; // src/vendors/mod.rs:962
+    cfg->rope_scale_global = 1.0f;
+    cfg->rope_scale_local = 1.0f;
+    cfg->swa_pattern = 6;           // src/vendors/mod.rs:963
+    cfg->kv_format = GGR_KV_Q8_ROW;
+    cfg->n_ranks = 1;
+}
+
+const char* ggr_attn_create_error(void) { return g_create_err.c_str(); }
+
+int ggr_attn_create(const ggr_attn_config* cfg, ggr_attn_ctx** out) {
+    auto bad = [&](int st, const char* msg) {
+        g_create_err = msg;
+        return st;
+    };
+    if (!cfg || !out) return bad(GGR_ERR_INVALID, "null argument");
+    *out = nullptr;
+    if (cfg->struct_size != (int32_t)sizeof(ggr_attn_config)) return bad(GGR_ERR_INVALID, "ggr_attn_config size mismatch");
+    // src/engine/runtime/inference.rs:1533-1546
+    for (float s : {cfg->rope_scale_global, cfg->rope_scale_local})
+        if (!std::isfinite(s) || s <= 0.0f) return bad(GGR_ERR_INVALID, "RoPE frequency scales must be finite and positive");
+    if (cfg->n_layer_windows != 0) {
+        bool wrong = cfg->n_layer_windows != cfg->n_layers || !cfg->layer_windows;
+        for (int i = 0; !wrong && i < cfg->n_layer_windows; ++i) wrong = cfg->layer_windows[i] < 0;
+        if (wrong) return bad(GGR_ERR_INVALID, "attention policy requires one positive window or global entry per layer");
+    }
+    if (cfg->n_layers <= 0 || cfg->n_heads <= 0 || cfg->n_kv_heads <= 0 || cfg->head_dim <= 0 || cfg->seq_len <= 0 ||
+        cfg->max_batch <= 0 || cfg->n_heads % cfg->n_kv_heads != 0)
+        return bad(GGR_ERR_INVALID, "invalid attention shape");
+    if (cfg->head_dim % 8 != 0 || cfg->head_dim > 256)
+        return bad(GGR_ERR_UNSUPPORTED, "head_dim must be a multiple of 8 and at most 256");
+    if (cfg->kv_format < GGR_KV_F32 || cfg->kv_format > GGR_KV_Q8_BLOCK32) return bad(GGR_ERR_INVALID, "unknown kv_format");
+    if (cfg->kv_format == GGR_KV_Q8_BLOCK32 && cfg->head_dim % 32 != 0)
+        return bad(GGR_ERR_UNSUPPORTED, "q8 block scales need head_dim to be a multiple of 32");
+    int rope_dim = cfg->rope_dim > 0 ? cfg->rope_dim : cfg->head_dim;
+    if (rope_dim > cfg->head_dim || (rope_dim & 1)) return bad(GGR_ERR_INVALID, "rope_dim must be even and at most head_dim");
+    if (cfg->rope_style == GGR_ROPE_ADJACENT && rope_dim != cfg->head_dim)
+        return bad(GGR_ERR_INVALID, "adjacent-pair RoPE rotates the whole head: rope_dim must equal head_dim");
+    if (!(cfg->rope_theta > 0.0f) || !std::isfinite(cfg->rope_theta)) return bad(GGR_ERR_INVALID, "rope_theta must be positive");
+    int shard_begin = 0, shard_count = cfg->seq_len;
+    if (cfg->shard_mode == GGR_SHARD_KV_SEQUENCE) {
+        shard_begin = cfg->shard_pos_begin;
+        shard_count = cfg->shard_pos_count;
+        if (shard_begin < 0 || shard_count <= 0 || (int64_t)shard_begin + shard_count > cfg->seq_len)
+            return bad(GGR_ERR_INVALID, "shard position range outside the cache");
+    } else if (cfg->shard_mode != GGR_SHARD_NONE) {
+        return bad(GGR_ERR_INVALID, "unknown shard_mode");
+    }
+
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev <= 0) return bad(GGR_ERR_CUDA, "no CUDA device is available");
+    if (cfg->device < 0 || cfg->device >= ndev) return bad(GGR_ERR_INVALID, "device ordinal out of range");
+    DeviceGuard guard(cfg->device);
+
+    ggr_attn_ctx* c = new ggr_attn_ctx();
+    c->cfg = *cfg;
+    c->cfg.layer_windows = nullptr;
+    if (cfg->n_layer_windows) c->windows.assign(cfg->layer_windows, cfg->layer_windows + cfg->n_layer_windows);
+    c->D = cfg->head_dim;
+    c->kv_dim = cfg->n_kv_heads * c->D;
+    c->q_dim = cfg->n_heads * c->D;
+    c->G = cfg->n_heads / cfg->n_kv_heads;
+    c->rope_dim = rope_dim;
+    c->rope_half = rope_dim / 2;
+    c->attn_scale = 1.0f / sqrtf((float)c->D);  // src/engine/runtime/inference.rs:1745
+    c->shard_begin = shard_begin;
+    c->shard_count = shard_count;
+
+    auto cleanup = [&](int st, const std::string& msg) {
+        g_create_err = msg;
+        ggr_attn_destroy(c);
+        return st;
+    };
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, cfg->device) != cudaSuccess) return cleanup(GGR_ERR_CUDA, "cudaGetDeviceProperties failed");
+    c->sm_count = prop.multiProcessorCount;
+    c->smem_optin = (int)prop.sharedMemPerBlockOptin;
+    if (cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking) != cudaSuccess)
+        return cleanup(GGR_ERR_CUDA, "cudaStreamCreate failed");
+    c->stream = c->own_stream;
+
+    // RoPE frequency tables (src/engine/runtime/inference.rs:1590-1609), computed on the host like the reference
+    std::vector<float> fr(c->rope_half), frs(c->rope_half);
+    const float swa_theta = cfg->rope_theta_swa > 0.0f ? cfg->rope_theta_swa : 10000.0f;
+    for (int i = 0; i < c->rope_half; ++i) {
+        const float e = (float)(i * 2) / (float)rope_dim;
+        fr[i] = 1.0f / powf(cfg->rope_theta, e);
+        frs[i] = 1.0f / powf(swa_theta, e);
+    }
+    const size_t fb = std::max<size_t>(1, c->rope_half) * sizeof(float);
+    if (cudaMalloc((void**)&c->d_freqs, fb) != cudaSuccess || cudaMalloc((void**)&c->d_freqs_swa, fb) != cudaSuccess)
+        return cleanup(GGR_ERR_ALLOC, "unable to allocate RoPE tables");
+    cudaMemcpy(c->d_freqs, fr.data(), c->rope_half * sizeof(float), cudaMemcpyHostToDevice);
+    cudaMemcpy(c->d_freqs_swa, frs.data(), c->rope_half * sizeof(float), cudaMemcpyHostToDevice);
+
+    // KV cache (src/engine/runtime/inference.rs:1615-1630)
+    KvView& kv = c->kv;
+    kv.fmt = cfg->kv_format;
+    kv.D = c->D;
+    kv.kv_dim = c->kv_dim;
+    kv.Hkv = cfg->n_kv_heads;
+    kv.Hq = cfg->n_heads;
+    kv.G = c->G;
+    kv.n_layers = cfg->n_layers;
+    kv.rows = shard_count;
+    kv.pos_begin = shard_begin;
+    kv.elem_bytes = elem_bytes_of(cfg->kv_format);
+    kv.n_scales = cfg->kv_format == GGR_KV_Q8_ROW ? 1 : (cfg->kv_format == GGR_KV_Q8_BLOCK32 ? c->kv_dim / 32 : 0);
+    const size_t rows = (size_t)cfg->max_batch * cfg->n_layers * shard_count;
+    const size_t bytes = rows * c->kv_dim * kv.elem_bytes;
+    char buf[160];
+    if (cudaMalloc(&kv.k, bytes) != cudaSuccess || cudaMalloc(&kv.v, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        // wording follows src/engine/runtime/inference.rs:130-164
+        snprintf(buf, sizeof buf, "unable to allocate kv cache (%zu bytes). Try reducing the context size.", 2 * bytes);
+        return cleanup(GGR_ERR_ALLOC, buf);
+    }
+    cudaMemsetAsync(kv.k, 0, bytes, c->stream);
+    cudaMemsetAsync(kv.v, 0, bytes, c->stream);
+    if (kv.n_scales) {
+        const size_t sb = rows * kv.n_scales * sizeof(float);
+        if (cudaMalloc((void**)&kv.ks, sb) != cudaSuccess || cudaMalloc((void**)&kv.vs, sb) != cudaSuccess) {
+            cudaGetLastError();
+            return cleanup(GGR_ERR_ALLOC, "unable to allocate kv scale buffers");
+        }
+        cudaMemsetAsync(kv.ks, 0, sb, c->stream);
+        cudaMemsetAsync(kv.vs, 0, sb, c->stream);
+    }
+    if (cudaStreamSynchronize(c->stream) != cudaSuccess) return cleanup(GGR_ERR_CUDA, "device initialisation failed");
+    g_create_err.clear();
+    *out = c;
+    return GGR_OK;
+}
+
+void ggr_attn_destroy(ggr_attn_ctx* c) {
+    if (!c) return;
+    DeviceGuard guard(c->cfg.device);
+    if (c->stream) cudaStreamSynchronize(c->stream);
+    cudaFree(c->kv.k);
+    cudaFree(c->kv.v);
+    cudaFree(c->kv.ks);
+    cudaFree(c->kv.vs);
+    cudaFree(c->d_freqs);
+    cudaFree(c->d_freqs_swa);
+    cudaFree(c->d_plan);
+    cudaFree(c->d_blocks);
+    cudaFree(c->d_qrot);
+    cudaFree(c->d_qrot_h);
+    cudaFree(c->d_part);
+    cudaFree(c->d_counters);
+    for (auto* p : c->d_stage) cudaFree(p);
+    if (c->own_stream) cudaStreamDestroy(c->own_stream);
+    delete c;
+}
+
+const char* ggr_attn_last_error(const ggr_attn_ctx* ctx) { return ctx ? ctx->err.c_str() : "null context"; }
+int64_t ggr_attn_launch_count(const ggr_attn_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+int ggr_attn_set_stream(ggr_attn_ctx* c, void* cuda_stream) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    c->stream = cuda_stream ? (cudaStream_t)cuda_stream : c->own_stream;
+    return GGR_OK;
+}
+
+int ggr_attn_synchronize(ggr_attn_ctx* c) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    return GGR_OK;
+}
+
+int ggr_attn_set_position_plan(ggr_attn_ctx* c, const int32_t* thw, int32_t n, int32_t next_text_pos) {
+    if (!c || n < 0 || (n > 0 && !thw) || next_text_pos < 0) return fail(c, GGR_ERR_INVALID, "invalid position plan");
+    DeviceGuard guard(c->cfg.device);
+    CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    cudaFree(c->d_plan);
+    c->d_plan = nullptr;
+    c->plan_len = n;
+    c->next_text = next_text_pos;
+    c->has_plan = (n > 0 || next_text_pos != 0) ? 1 : 0;
+    if (n > 0) {
+        if (cudaMalloc((void**)&c->d_plan, (size_t)n * 3 * sizeof(int)) != cudaSuccess)
+            return fail(c, GGR_ERR_ALLOC, "unable to allocate the position plan");
+        CUDA_TRY(c, cudaMemcpy(c->d_plan, thw, (size_t)n * 3 * sizeof(int), cudaMemcpyHostToDevice));
+    }
+    return GGR_OK;
+}
+
+int ggr_attn_set_media_blocks(ggr_attn_ctx* c, const int32_t* start_len, int32_t n, int32_t prompt_tokens) {
+    if (!c || n < 0 || (n > 0 && !start_len)) return fail(c, GGR_ERR_INVALID, "invalid media blocks");
+    std::vector<int64_t> sl(2 * (size_t)n);
+    for (int i = 0; i < 2 * n; ++i) sl[i] = start_len[i];
+    if (ggr_media_plan_validate(sl.data(), n, prompt_tokens) != GGR_OK)
+        return fail(c, GGR_ERR_INVALID,
+                    "image attention blocks must be nonempty, ordered, disjoint, and within the prompt");
+    DeviceGuard guard(c->cfg.device);
+    CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    cudaFree(c->d_blocks);
+    c->d_blocks = nullptr;
+    c->blocks.clear();
+    for (int i = 0; i < n; ++i) c->blocks.push_back(make_int2(start_len[2 * i], start_len[2 * i + 1]));
+    if (n > 0) {
+        if (cudaMalloc((void**)&c->d_blocks, (size_t)n * sizeof(int2)) != cudaSuccess)
+            return fail(c, GGR_ERR_ALLOC, "unable to allocate media blocks");
+        CUDA_TRY(c, cudaMemcpy(c->d_blocks, c->blocks.data(), (size_t)n * sizeof(int2), cudaMemcpyHostToDevice));
+    }
+    return GGR_OK;
+}
+
+int ggr_attn_visible_keys(const ggr_attn_ctx* c, int32_t layer, int32_t pos, int32_t* start, int32_t* end) {
+    if (!c || !start || !end || layer < 0 || layer >= c->cfg.n_layers || pos < 0) return GGR_ERR_INVALID;
+    visible_host(c, layer, pos, start, end);
+    return GGR_OK;
+}
+
+int ggr_attn_decode(ggr_attn_ctx* c, int32_t layer, const int32_t* pos, int32_t B, const float* q, const float* k,
+                    const float* v, float* out, int32_t ptr_kind) {
+    if (!out) return fail(c, GGR_ERR_INVALID, "null buffer");
+    return decode_common(c, layer, pos, B, q, k, v, out, nullptr, ptr_kind);
+}
+
+int ggr_attn_decode_partial(ggr_attn_ctx* c, int32_t layer, const int32_t* pos, int32_t B, const float* q,
+                            const float* k, const float* v, float* partial, int32_t ptr_kind) {
+    if (!partial) return fail(c, GGR_ERR_INVALID, "null buffer");
+    return decode_common(c, layer, pos, B, q, k, v, nullptr, partial, ptr_kind);
+}
+
+int ggr_attn_combine_partials(ggr_attn_ctx* c, const float* parts, int32_t n_parts, int32_t B, float* out,
+                              int32_t ptr_kind) {
+    if (!c) return GGR_ERR_INVALID;
+    if (!parts || !out || n_parts <= 0 || B <= 0) return fail(c, GGR_ERR_INVALID, "invalid combine arguments");
+    DeviceGuard guard(c->cfg.device);
+    const size_t in_bytes = (size_t)n_parts * B * c->kv.Hq * (c->D + 2) * sizeof(float);
+    const size_t out_bytes = (size_t)B * c->q_dim * sizeof(float);
+    const void* dp;
+    int rc = stage_in(c, 0, parts, in_bytes, ptr_kind, &dp);
+    if (rc) return rc;
+    float* dout = out;
+    if (ptr_kind == GGR_PTR_HOST) {
+        if ((rc = ensure(c, &c->d_stage[3], &c->stage_cap[3], out_bytes))) return rc;
+        dout = reinterpret_cast<float*>(c->d_stage[3]);
+    }
+    combine_partials_kernel<<<dim3(c->kv.Hq, B), 128, 0, c->stream>>>(reinterpret_cast<const float*>(dp), n_parts, B,
+                                                                      c->kv.Hq, c->D, dout);
+    CUDA_TRY(c, cudaGetLastError());
+    c->launches++;
+    if (ptr_kind == GGR_PTR_HOST) {
+        CUDA_TRY(c, cudaMemcpyAsync(out, dout, out_bytes, cudaMemcpyDeviceToHost, c->stream));
+        CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    }
+    return GGR_OK;
+}
+
+int ggr_attn_prefill(ggr_attn_ctx* c, int32_t layer, int32_t seq, int32_t base_pos, int32_t m, const void* q,
+                     const void* k, const void* v, int32_t in_dtype, float* out, int32_t ptr_kind) {
+    return prefill_common(c, layer, seq, base_pos, m, q, k, v, in_dtype, out, ptr_kind, false);
+}
+
+int ggr_attn_prefill_block(ggr_attn_ctx* c, int32_t layer, int32_t seq, int32_t base_pos, int32_t m, const void* q,
+                           const void* k, const void* v, int32_t in_dtype, float* out, int32_t ptr_kind) {
+    return prefill_common(c, layer, seq, base_pos, m, q, k, v, in_dtype, out, ptr_kind, true);
+}
+
+int ggr_attn_apply_rope_qk(ggr_attn_ctx* c, int32_t layer, int32_t pos, float* q, float* k, int32_t ptr_kind) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    int rc = check_layer(c, layer);
+    if (rc) return rc;
+    if (!q || !k || pos < 0) return fail(c, GGR_ERR_INVALID, "invalid rope arguments");
+    const size_t qb = (size_t)c->q_dim * sizeof(float), kb = (size_t)c->kv_dim * sizeof(float);
+    // the rotation reads pairs, so it never runs in place: inputs go through staging
+    if ((rc = ensure(c, &c->d_stage[0], &c->stage_cap[0], qb))) return rc;
+    if ((rc = ensure(c, &c->d_stage[1], &c->stage_cap[1], kb))) return rc;
+    if ((rc = ensure(c, &c->d_stage[2], &c->stage_cap[2], kb))) return rc;
+    if ((rc = ensure(c, &c->d_qrot, &c->qrot_cap, (size_t)c->q_dim))) return rc;
+    const cudaMemcpyKind in_kind = ptr_kind == GGR_PTR_HOST ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice;
+    const cudaMemcpyKind out_kind = ptr_kind == GGR_PTR_HOST ? cudaMemcpyDeviceToHost : cudaMemcpyDeviceToDevice;
+    CUDA_TRY(c, cudaMemcpyAsync(c->d_stage[0], q, qb, in_kind, c->stream));
+    CUDA_TRY(c, cudaMemcpyAsync(c->d_stage[1], k, kb, in_kind, c->stream));
+    Items it{};
+    it.mode = 0;
+    it.seq0 = 0;
+    it.n = 1;
+    it.pos[0] = pos;
+    rc = launch_rope_append(c, layer, it, RF_ROTATE | RF_WRITE_Q | RF_WRITE_K, 0, c->d_stage[0], c->d_stage[1], nullptr,
+                            c->d_qrot, nullptr, reinterpret_cast<float*>(c->d_stage[2]));
+    if (rc) return rc;
+    CUDA_TRY(c, cudaMemcpyAsync(q, c->d_qrot, qb, out_kind, c->stream));
+    CUDA_TRY(c, cudaMemcpyAsync(k, c->d_stage[2], kb, out_kind, c->stream));
+    if (ptr_kind == GGR_PTR_HOST) CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    return GGR_OK;
+}
+
+int ggr_attn_kv_write_token(ggr_attn_ctx* c, int32_t seq, int32_t layer, int32_t pos, const float* k, const float* v,
+                            int32_t ptr_kind) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    int rc = check_layer(c, layer);
+    if (rc) return rc;
+    if (!k || !v) return fail(c, GGR_ERR_INVALID, "null buffer");
+    if (seq < 0 || seq >= c->cfg.max_batch || pos < 0 || pos >= c->cfg.seq_len)
+        return fail(c, GGR_ERR_RANGE, "cache row outside the cache");
+    const size_t kb = (size_t)c->kv_dim * sizeof(float);
+    const void *dk, *dv;
+    if ((rc = stage_in(c, 1, k, kb, ptr_kind, &dk))) return rc;
+    if ((rc = stage_in(c, 2, v, kb, ptr_kind, &dv))) return rc;
+    Items it{};
+    it.mode = 0;
+    it.seq0 = seq;
+    it.n = 1;
+    it.pos[0] = pos;
+    rc = launch_rope_append(c, layer, it, RF_APPEND, 0, nullptr, dk, dv, nullptr, nullptr, nullptr);
+    if (rc) return rc;
+    if (ptr_kind == GGR_PTR_HOST) CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    return GGR_OK;
+}
+
+int ggr_attn_attention_token(ggr_attn_ctx* c, int32_t seq, int32_t layer, int32_t pos, const float* q, float* out,
+                             int32_t ptr_kind) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    int rc = check_layer(c, layer);
+    if (rc) return rc;
+    if (!q || !out) return fail(c, GGR_ERR_INVALID, "null buffer");
+    if (seq < 0 || seq >= c->cfg.max_batch || pos < 0 || pos >= c->cfg.seq_len)
+        return fail(c, GGR_ERR_RANGE, "cache row outside the cache");
+    if (c->cfg.shard_mode != GGR_SHARD_NONE) return fail(c, GGR_ERR_UNSUPPORTED, "use ggr_attn_decode_partial on a shard");
+    const size_t qb = (size_t)c->q_dim * sizeof(float);
+    const void* dq;
+    if ((rc = stage_in(c, 0, q, qb, ptr_kind, &dq))) return rc;
+    float* dout = out;
+    if (ptr_kind == GGR_PTR_HOST) {
+        if ((rc = ensure(c, &c->d_stage[3], &c->stage_cap[3], qb))) return rc;
+        dout = reinterpret_cast<float*>(c->d_stage[3]);
+    }
+    Items it{};
+    it.mode = 0;
+    it.seq0 = seq;
+    it.n = 1;
+    it.pos[0] = pos;
+    const int t_max = t_max_of(c, layer, &pos, 1);
+    rc = launch_attention(c, layer, it, t_max, reinterpret_cast<const float*>(dq), dout, nullptr, true);
+    if (rc) return rc;
+    if (ptr_kind == GGR_PTR_HOST) {
+        CUDA_TRY(c, cudaMemcpyAsync(out, dout, qb, cudaMemcpyDeviceToHost, c->stream));
+        CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    }
+    return GGR_OK;
+}
+
+static int kv_rows_check(ggr_attn_ctx* c, int layer, int seq, int row0, int nrows) {
+    int rc = check_layer(c, layer);
+    if (rc) return rc;
+    if (seq < 0 || seq >= c->cfg.max_batch || row0 < c->shard_begin || nrows < 0 ||
+        (int64_t)row0 + nrows > (int64_t)c->shard_begin + c->shard_count)
+        return fail(c, GGR_ERR_RANGE, "rows outside the cache");
+    return GGR_OK;
+}
+
+int ggr_attn_kv_export(ggr_attn_ctx* c, int32_t layer, int32_t seq, int32_t row0, int32_t nrows, int8_t* k_q8,
+                       int8_t* v_q8, float* k_scale, float* v_scale) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    if (c->kv.fmt != KV_Q8_ROW) return fail(c, GGR_ERR_UNSUPPORTED, "export needs the q8 row-scale cache format");
+    int rc = kv_rows_check(c, layer, seq, row0, nrows);
+    if (rc) return rc;
+    if (nrows == 0) return GGR_OK;
+    CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    const int64_t r = c->kv.row(seq, layer, row0);
+    const size_t nb = (size_t)nrows * c->kv_dim;
+    CUDA_TRY(c, cudaMemcpy(k_q8, (int8_t*)c->kv.k + r * c->kv_dim, nb, cudaMemcpyDeviceToHost));
+    CUDA_TRY(c, cudaMemcpy(v_q8, (int8_t*)c->kv.v + r * c->kv_dim, nb, cudaMemcpyDeviceToHost));
+    CUDA_TRY(c, cudaMemcpy(k_scale, c->kv.ks + r, (size_t)nrows * sizeof(float), cudaMemcpyDeviceToHost));
+    CUDA_TRY(c, cudaMemcpy(v_scale, c->kv.vs + r, (size_t)nrows * sizeof(float), cudaMemcpyDeviceToHost));
+    return GGR_OK;
+}
+
+int ggr_attn_kv_import(ggr_attn_ctx* c, int32_t layer, int32_t seq, int32_t row0, int32_t nrows, const int8_t* k_q8,
+                       const int8_t* v_q8, const float* k_scale, const float* v_scale) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    if (c->kv.fmt != KV_Q8_ROW) return fail(c, GGR_ERR_UNSUPPORTED, "import needs the q8 row-scale cache format");
+    int rc = kv_rows_check(c, layer, seq, row0, nrows);
+    if (rc) return rc;
+    if (nrows == 0) return GGR_OK;
+    CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    const int64_t r = c->kv.row(seq, layer, row0);
+    const size_t nb = (size_t)nrows * c->kv_dim;
+    CUDA_TRY(c, cudaMemcpy((int8_t*)c->kv.k + r * c->kv_dim, k_q8, nb, cudaMemcpyHostToDevice));
+    CUDA_TRY(c, cudaMemcpy((int8_t*)c->kv.v + r * c->kv_dim, v_q8, nb, cudaMemcpyHostToDevice));
+    CUDA_TRY(c, cudaMemcpy(c->kv.ks + r, k_scale, (size_t)nrows * sizeof(float), cudaMemcpyHostToDevice));
+    CUDA_TRY(c, cudaMemcpy(c->kv.vs + r, v_scale, (size_t)nrows * sizeof(float), cudaMemcpyHostToDevice));
+    return GGR_OK;
+}
+
+int ggr_attn_kv_read_row(ggr_attn_ctx* c, int32_t seq, int32_t layer, int32_t pos, float* k_out, float* v_out) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    int rc = kv_rows_check(c, layer, seq, pos, 1);
+    if (rc) return rc;
+    CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    const int64_t r = c->kv.row(seq, layer, pos);
+    const int n = c->kv_dim, eb = c->kv.elem_bytes;
+    std::vector<unsigned char> kb((size_t)n * eb), vb((size_t)n * eb);
+    CUDA_TRY(c, cudaMemcpy(kb.data(), (unsigned char*)c->kv.k + r * n * eb, kb.size(), cudaMemcpyDeviceToHost));
+    CUDA_TRY(c, cudaMemcpy(vb.data(), (unsigned char*)c->kv.v + r * n * eb, vb.size(), cudaMemcpyDeviceToHost));
+    std::vector<float> ks(std::max(1, c->kv.n_scales)), vs(std::max(1, c->kv.n_scales));
+    if (c->kv.n_scales) {
+        CUDA_TRY(c, cudaMemcpy(ks.data(), c->kv.ks + r * c->kv.n_scales, c->kv.n_scales * sizeof(float), cudaMemcpyDeviceToHost));
+        CUDA_TRY(c, cudaMemcpy(vs.data(), c->kv.vs + r * c->kv.n_scales, c->kv.n_scales * sizeof(float), cudaMemcpyDeviceToHost));
+    }
+    for (int i = 0; i < n; ++i) {
+        switch (c->kv.fmt) {
+            case KV_F32:
+                k_out[i] = reinterpret_cast<float*>(kb.data())[i];
+                v_out[i] = reinterpret_cast<float*>(vb.data())[i];
+                break;
+            case KV_BF16: {
+                uint32_t a = (uint32_t)reinterpret_cast<uint16_t*>(kb.data())[i] << 16;
+                uint32_t b = (uint32_t)reinterpret_cast<uint16_t*>(vb.data())[i] << 16;
+                std::memcpy(&k_out[i], &a, 4);
+                std::memcpy(&v_out[i], &b, 4);
+                break;
+            }
+            case KV_Q8_ROW:
+                k_out[i] = (float)reinterpret_cast<int8_t*>(kb.data())[i] * ks[0];
+                v_out[i] = (float)reinterpret_cast<int8_t*>(vb.data())[i] * vs[0];
+                break;
+            default:
+                k_out[i] = (float)reinterpret_cast<int8_t*>(kb.data())[i] * ks[i / 32];
+                v_out[i] = (float)reinterpret_cast<int8_t*>(vb.data())[i] * vs[i / 32];
+                break;
+        }
+    }
+    return GGR_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,208 @@
+// RoPE of q and k plus the KV-cache append for one item (one token) per CTA.
+//
+// Restates, for the device, apply_rope_qk (src/engine/runtime/inference.rs:1817-1874),
+// rebuild_rope_cache (:1485-1523) and kv_write_token (:1877-1918). The
+// rotation uses separately rounded multiplies and adds (no FMA contraction)
+// so a rotated value differs from the reference's only through cos/sin.
+#pragma once
+
+#include "common.cuh"
+
+namespace ggr {
+
+enum RopeFlags : int {
+    RF_ROTATE = 1,       // apply RoPE to q and k (else they are taken as already rotated)
+    RF_WRITE_Q = 2,      // write rotated q to q_out (f32) and / or q_out_h (bf16)
+    RF_APPEND = 4,       // store k, v into the cache row
+    RF_WRITE_K = 8,      // write rotated k to k_out (apply_rope_qk called on its own)
+};
+
+struct RopeAppendArgs {
+    RopeParams rope;
+    KvView kv;
+    Items items;
+    int layer;
+    int flags;
+    int in_bf16;  // q/k/v inputs are bf16 instead of f32
+    const void* q;
+    const void* k;
+    const void* v;
+    float* q_out;             // [items][q_dim]
+    __nv_bfloat16* q_out_h;   // optional bf16 copy, same shape
+    float* k_out;             // [items][kv_dim]
+    int shard_count;          // positions held locally (append only when pos is inside)
+};
+
+__device__ __forceinline__ float load_in(const void* p, int64_t idx, int in_bf16) {
+    if (in_bf16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[idx]);
+    return reinterpret_cast<const float*>(p)[idx];
+}
+
+// One rotated element of a head (NeoX split-half or adjacent pairs).
+__device__ __forceinline__ float rope_elem(const void* x, int64_t base, int i, int D, const RopeParams& rp,
+                                           const float* cs, const float* sn, int in_bf16) {
+    if (rp.style == 0) {
+        const int half = rp.rope_half;
+        if (i < half) {
+            float v0 = load_in(x, base + i, in_bf16), v1 = load_in(x, base + i + half, in_bf16);
+            return __fsub_rn(__fmul_rn(v0, cs[i]), __fmul_rn(v1, sn[i]));
+        } else if (i < rp.rope_dim) {
+            int j = i - half;
+            float v0 = load_in(x, base + j, in_bf16), v1 = load_in(x, base + i, in_bf16);
+            return __fadd_rn(__fmul_rn(v0, sn[j]), __fmul_rn(v1, cs[j]));
+        }
+        return load_in(x, base + i, in_bf16);
+    } else {
+        int j = i >> 1;
+        if ((i & 1) == 0) {
+            float v0 = load_in(x, base + i, in_bf16), v1 = load_in(x, base + i + 1, in_bf16);
+            return __fsub_rn(__fmul_rn(v0, cs[j]), __fmul_rn(v1, sn[j]));
+        }
+        float v0 = load_in(x, base + i - 1, in_bf16), v1 = load_in(x, base + i, in_bf16);
+        return __fadd_rn(__fmul_rn(v0, sn[j]), __fmul_rn(v1, cs[j]));
+    }
+}
+
+__device__ __forceinline__ int8_t q8_code(float x, float inv) {
+    // src/engine/runtime/inference.rs:264-266: round half away from zero, clamp to +-127
+    float r = roundf(__fmul_rn(x, inv));
+    r = fminf(127.0f, fmaxf(-127.0f, r));
+    return (int8_t)r;
+}
+
+__global__ void __launch_bounds__(256) rope_append_kernel(RopeAppendArgs a) {
+    extern __shared__ float sm[];
+    const int D = a.kv.D, kv_dim = a.kv.kv_dim, q_dim = a.kv.Hq * D;
+    const int half = a.rope.rope_half;
+    float* cs = sm;
+    float* sn = cs + half;
+    float* krow = sn + half;
+    float* vrow = krow + kv_dim;
+    float* red = vrow + kv_dim;  // 2 * 8 partial maxima
+
+    const int item = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
+    int seq, pos;
+    a.items.get(item, seq, pos);
+
+    if (a.flags & RF_ROTATE) {
+        for (int i = tid; i < half; i += nt) {
+            int axis = rope_axis(a.rope.layout, i, a.rope.sections);
+            int coord = pos;
+            if (a.rope.has_plan) {
+                coord = pos < a.rope.plan_len ? a.rope.plan[pos * 3 + axis]
+                                              : a.rope.next_text + (pos - a.rope.plan_len);
+            }
+            float val = __fmul_rn(__fmul_rn((float)coord, a.rope.freqs[i]), a.rope.fscale);
+            float s, c;
+            sincosf(val, &s, &c);
+            cs[i] = c;
+            sn[i] = s;
+        }
+        __syncthreads();
+    }
+
+    const int64_t qb = (int64_t)item * q_dim, kb = (int64_t)item * kv_dim;
+    if (a.flags & RF_WRITE_Q) {
+        for (int idx = tid; idx < q_dim; idx += nt) {
+            int h = idx / D, i = idx - h * D;
+            float r = (a.flags & RF_ROTATE) ? rope_elem(a.q, qb + (int64_t)h * D, i, D, a.rope, cs, sn, a.in_bf16)
+                                            : load_in(a.q, qb + idx, a.in_bf16);
+            if (a.rope.do_prescale) r = __fmul_rn(r, a.rope.q_prescale);
+            if (a.q_out) a.q_out[qb + idx] = r;
+            if (a.q_out_h) a.q_out_h[qb + idx] = __float2bfloat16_rn(r);
+        }
+    }
+    if (!(a.flags & (RF_APPEND | RF_WRITE_K))) return;
+
+    for (int idx = tid; idx < kv_dim; idx += nt) {
+        int h = idx / D, i = idx - h * D;
+        krow[idx] = (a.flags & RF_ROTATE) ? rope_elem(a.k, kb + (int64_t)h * D, i, D, a.rope, cs, sn, a.in_bf16)
+                                          : load_in(a.k, kb + idx, a.in_bf16);
+        if (a.flags & RF_APPEND) vrow[idx] = load_in(a.v, kb + idx, a.in_bf16);
+    }
+    __syncthreads();
+    if (a.flags & RF_WRITE_K) {
+        for (int idx = tid; idx < kv_dim; idx += nt) a.k_out[kb + idx] = krow[idx];
+    }
+    if (!(a.flags & RF_APPEND)) return;
+    if (pos < a.kv.pos_begin || pos >= a.kv.pos_begin + a.shard_count) return;  // another rank owns this row
+
+    const int64_t r = a.kv.row(seq, a.layer, pos);
+    const int64_t off = r * kv_dim;
+    switch (a.kv.fmt) {
+        case KV_F32: {
+            float* kc = reinterpret_cast<float*>(a.kv.k) + off;
+            float* vc = reinterpret_cast<float*>(a.kv.v) + off;
+            for (int idx = tid; idx < kv_dim; idx += nt) {
+                kc[idx] = krow[idx];
+                vc[idx] = vrow[idx];
+            }
+            break;
+        }
+        case KV_BF16: {
+            __nv_bfloat16* kc = reinterpret_cast<__nv_bfloat16*>(a.kv.k) + off;
+            __nv_bfloat16* vc = reinterpret_cast<__nv_bfloat16*>(a.kv.v) + off;
+            for (int idx = tid; idx < kv_dim; idx += nt) {
+                kc[idx] = __float2bfloat16_rn(krow[idx]);
+                vc[idx] = __float2bfloat16_rn(vrow[idx]);
+            }
+            break;
+        }
+        case KV_Q8_ROW: {
+            // one scale per row over all KV heads (src/engine/runtime/inference.rs:1906-1916)
+            float mk = 0.0f, mv = 0.0f;
+            for (int idx = tid; idx < kv_dim; idx += nt) {
+                mk = fmaxf(mk, fabsf(krow[idx]));
+                mv = fmaxf(mv, fabsf(vrow[idx]));
+            }
+            mk = warp_max(mk);
+            mv = warp_max(mv);
+            if ((tid & 31) == 0) {
+                red[tid >> 5] = mk;
+                red[8 + (tid >> 5)] = mv;
+            }
+            __syncthreads();
+            mk = 0.0f;
+            mv = 0.0f;
+            for (int w = 0; w < (nt >> 5); ++w) {
+                mk = fmaxf(mk, red[w]);
+                mv = fmaxf(mv, red[8 + w]);
+            }
+            int8_t* kc = reinterpret_cast<int8_t*>(a.kv.k) + off;
+            int8_t* vc = reinterpret_cast<int8_t*>(a.kv.v) + off;
+            float invk = mk == 0.0f ? 0.0f : __fdiv_rn(127.0f, mk);
+            float invv = mv == 0.0f ? 0.0f : __fdiv_rn(127.0f, mv);
+            for (int idx = tid; idx < kv_dim; idx += nt) {
+                kc[idx] = mk == 0.0f ? (int8_t)0 : q8_code(krow[idx], invk);
+                vc[idx] = mv == 0.0f ? (int8_t)0 : q8_code(vrow[idx], invv);
+            }
+            if (tid == 0) {
+                a.kv.ks[r] = mk == 0.0f ? 1.0f : __fdiv_rn(mk, 127.0f);
+                a.kv.vs[r] = mv == 0.0f ? 1.0f : __fdiv_rn(mv, 127.0f);
+            }
+            break;
+        }
+        case KV_Q8_BLOCK32: {
+            // one scale per 32 elements (src/engine/runtime/inference.rs:1888-1905)
+            const int nb = kv_dim / 32;
+            int8_t* kc = reinterpret_cast<int8_t*>(a.kv.k) + off;
+            int8_t* vc = reinterpret_cast<int8_t*>(a.kv.v) + off;
+            const int lane = tid & 31, warp = tid >> 5, nw = nt >> 5;
+            for (int b = warp; b < nb; b += nw) {
+                float xk = krow[b * 32 + lane], xv = vrow[b * 32 + lane];
+                float mk = warp_max(fabsf(xk)), mv = warp_max(fabsf(xv));
+                float invk = mk == 0.0f ? 0.0f : __fdiv_rn(127.0f, mk);
+                float invv = mv == 0.0f ? 0.0f : __fdiv_rn(127.0f, mv);
+                kc[b * 32 + lane] = mk == 0.0f ? (int8_t)0 : q8_code(xk, invk);
+                vc[b * 32 + lane] = mv == 0.0f ? (int8_t)0 : q8_code(xv, invv);
+                if (lane == 0) {
+                    a.kv.ks[r * nb + b] = mk == 0.0f ? 1.0f : __fdiv_rn(mk, 127.0f);
+                    a.kv.vs[r * nb + b] = mv == 0.0f ? 1.0f : __fdiv_rn(mv, 127.0f);
+                }
+            }
+            break;
+        }
+    }
+}
+
+}  // namespace ggr

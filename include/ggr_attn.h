@@ -1,0 +1,229 @@
+/*
+ * ggr_attn.h - C ABI of the B200 (sm_100a) attention path for gguf-runner.
+ *
+ * One opaque context per generation replaces the KV-cache half of the
+ * reference's RunState; the entry points replace the rope -> append -> attend
+ * sequence the reference runs per layer. All reference citations are paths
+ * inside apimeister/gguf-runner.
+ *
+ * Conventions
+ *  - every call returns a ggr_status; nothing aborts or traps. A nonzero
+ *    status leaves a message in ggr_attn_last_error(ctx).
+ *  - all pointers are caller-owned. `ptr_kind` says whether the q/k/v/out
+ *    buffers of a call live in host memory (the unmodified engine: the call
+ *    copies in, runs, copies out and synchronises) or in device memory (the
+ *    call only enqueues work on the context's stream).
+ *  - position arrays and plan tables are always host memory.
+ *  - calls on one context are serialised by the caller; different contexts are
+ *    independent (the reference forks one RunState per concurrent generation).
+ *  - no CPU fallback exists: a missing device or a failed launch is an error.
+ */
+#ifndef GGR_ATTN_H
+#define GGR_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GGR_ATTN_ABI_VERSION 1
+
+typedef enum ggr_status {
+    GGR_OK = 0,
+    GGR_ERR_INVALID = 1,     /* bad argument or configuration */
+    GGR_ERR_CUDA = 2,        /* a CUDA runtime call failed */
+    GGR_ERR_ALLOC = 3,       /* device or host allocation failed */
+    GGR_ERR_RANGE = 4,       /* layer / position / batch outside the cache */
+    GGR_ERR_UNSUPPORTED = 5, /* shape or mode this build has no kernel for */
+    GGR_ERR_TIMEOUT = 6,     /* a bounded device-side wait ran out */
+    GGR_ERR_COMM = 7         /* collective setup or call failed */
+} ggr_status;
+
+enum { GGR_PTR_HOST = 0, GGR_PTR_DEVICE = 1 };
+enum { GGR_DTYPE_F32 = 0, GGR_DTYPE_BF16 = 1 };
+enum { GGR_KV_F32 = 0, GGR_KV_BF16 = 1, GGR_KV_Q8_ROW = 2, GGR_KV_Q8_BLOCK32 = 3 };
+enum { GGR_ROPE_NEOX = 0, GGR_ROPE_ADJACENT = 1 };
+enum { GGR_ROPE_SEQUENTIAL = 0, GGR_ROPE_INTERLEAVED = 1 };
+enum { GGR_SCALE_SCORE = 0, GGR_SCALE_Q_PRESCALED = 1 };
+enum { GGR_IMAGE_CAUSAL = 0, GGR_IMAGE_BIDIRECTIONAL = 1 };
+enum { GGR_SHARD_NONE = 0, GGR_SHARD_KV_SEQUENCE = 2 };
+enum { GGR_IMPL_AUTO = 0, GGR_IMPL_SIMT = 1, GGR_IMPL_MMA = 2, GGR_IMPL_TCGEN05 = 3 };
+
+typedef struct ggr_attn_ctx ggr_attn_ctx;
+
+/*
+ * Mirrors the Config / RunState fields the reference's attention reads
+ * (src/engine/types.rs:638-695, filled at src/vendors/mod.rs:906-1032 and
+ * src/vendors/gemma.rs:20-106).
+ */
+typedef struct ggr_attn_config {
+    int32_t struct_size; /* sizeof(ggr_attn_config), checked by create */
+    int32_t n_layers, n_heads, n_kv_heads, head_dim;
+    int32_t rope_dim;  /* 0 = head_dim (src/engine/runtime/inference.rs:1590-1594) */
+    int32_t seq_len;   /* cache capacity in positions per layer and sequence */
+    int32_t max_batch; /* independent sequences held by this context (reference: 1) */
+    float rope_theta, rope_theta_swa; /* rope_theta_swa <= 0 selects 10000 */
+    float rope_scale_global, rope_scale_local;
+    int32_t rope_style;  /* GGR_ROPE_NEOX: pairs (i, i+rope_dim/2); GGR_ROPE_ADJACENT: pairs (2j, 2j+1) */
+    int32_t rope_layout; /* GGR_ROPE_INTERLEAVED selects the T/H/W axis per frequency */
+    int32_t rope_sections[4];
+    int32_t swa_theta_on_window_layers; /* gemma3: window layers use rope_theta_swa */
+    int32_t swa_pattern;  /* layer kind when layer_windows is empty: l % p < p-1 */
+    int32_t scale_mode;   /* GGR_SCALE_* */
+    int32_t softmax_mode; /* 0 two-pass, 1 online in the reference; the device always runs an online softmax */
+    int32_t kv_format;    /* GGR_KV_* */
+    int32_t image_mode;   /* GGR_IMAGE_* */
+    int32_t n_layer_windows;      /* 0 or n_layers */
+    const int32_t* layer_windows; /* window per layer counting the current token, 0 = global */
+    int32_t device;               /* CUDA device ordinal */
+    /* KV-sequence sharding (long-context decode): this context holds the
+     * positions [shard_pos_begin, shard_pos_begin + shard_pos_count) of every
+     * layer and sequence. shard_mode GGR_SHARD_NONE holds all of them. */
+    int32_t shard_mode, shard_pos_begin, shard_pos_count;
+    int32_t n_ranks, rank;
+    int32_t decode_impl;  /* GGR_IMPL_*: kernel family for decode, AUTO picks by shape */
+    int32_t prefill_impl; /* GGR_IMPL_*: kernel family for prefill */
+    int32_t max_splits;   /* 0 = automatic split-KV factor */
+} ggr_attn_config;
+
+/* Fills *cfg with the reference's defaults (theta 5e5, swa theta 1e4,
+ * swa_pattern 6, scales 1, NeoX off ...; src/vendors/mod.rs:955-964,
+ * src/vendors/llama.rs:13-15). */
+void ggr_attn_config_init(ggr_attn_config* cfg);
+
+/* Replaces malloc_run_state_with_kv_cache_format (KV and RoPE part,
+ * src/engine/runtime/inference.rs:1529-1748): validates RoPE scales and the
+ * window list exactly as :1533-1546, allocates the device KV cache
+ * [sequence][layer][position][kv_dim] in the configured format and the RoPE
+ * frequency tables. */
+int ggr_attn_create(const ggr_attn_config* cfg, ggr_attn_ctx** out);
+/* Replaces dropping the RunState at the end of generate_from_prefill
+ * (src/app/generation.rs:4610). */
+void ggr_attn_destroy(ggr_attn_ctx* ctx);
+const char* ggr_attn_last_error(const ggr_attn_ctx* ctx);
+/* Message of a failed ggr_attn_create (which returns no context). Thread-local. */
+const char* ggr_attn_create_error(void);
+int ggr_attn_abi_version(void);
+
+/* Work of device-pointer calls is enqueued on this CUDA stream (a
+ * cudaStream_t); the default is a stream the context owns. */
+int ggr_attn_set_stream(ggr_attn_ctx* ctx, void* cuda_stream);
+int ggr_attn_synchronize(ggr_attn_ctx* ctx);
+
+/* Replaces assigning RunState::rope_position_plan (src/app/generation.rs:4614;
+ * semantics of RopePositionPlan::at, src/engine/positions.rs:46-54): thw holds
+ * n rows of logical (t, h, w); rows beyond n continue at next_text_pos. n = 0
+ * and next_text_pos = 0 clears the plan. */
+int ggr_attn_set_position_plan(ggr_attn_ctx* ctx, const int32_t* thw, int32_t n, int32_t next_text_pos);
+/* Replaces assigning RunState::media_attention_plan (src/app/generation.rs:4615-4618)
+ * with the validation of MediaAttentionPlan::new (src/engine/runtime/attention.rs:9-28):
+ * start_len holds n rows of (token_start, token_len). */
+int ggr_attn_set_media_blocks(ggr_attn_ctx* ctx, const int32_t* start_len, int32_t n, int32_t prompt_tokens);
+/* LanguageAttentionPolicy::visible_keys (src/engine/runtime/attention.rs:73-97). */
+int ggr_attn_visible_keys(const ggr_attn_ctx* ctx, int32_t layer, int32_t pos, int32_t* start, int32_t* end);
+
+/*
+ * Fused decode step: for each of B sequences, rope(q, k) + append(k, v) at
+ * pos[b] + attention over the visible cache rows. Replaces the three calls at
+ * src/engine/runtime/inference.rs:3499-3507 (apply_rope_qk :1817,
+ * kv_write_token :1877, attention_token :1970). q is [B][n_heads*head_dim],
+ * k and v are [B][n_kv_heads*head_dim] (f32, before RoPE, after bias / QK
+ * norm), out is [B][n_heads*head_dim] f32, head-major like RunState::xb.
+ * Sequence b of the cache belongs to batch entry b.
+ */
+int ggr_attn_decode(ggr_attn_ctx* ctx, int32_t layer, const int32_t* pos, int32_t B, const float* q,
+                    const float* k, const float* v, float* out, int32_t ptr_kind);
+
+/*
+ * Prefill of m consecutive tokens of sequence `seq` starting at base_pos;
+ * token i sees exactly what attention_token would at position base_pos + i.
+ * Replaces the per-token loop of transformer_prefill_batch
+ * (src/engine/runtime/inference.rs:2981-3017). q/k/v are token-major
+ * ([m][q_dim], [m][kv_dim]) in in_dtype; out is f32 [m][q_dim]. Like the
+ * reference (:2750-2757) it rejects a chunk that overlaps a bidirectional
+ * image block.
+ */
+int ggr_attn_prefill(ggr_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t base_pos, int32_t m, const void* q,
+                     const void* k, const void* v, int32_t in_dtype, float* out, int32_t ptr_kind);
+
+/* Staged prefill of one complete image block: every row is roped and appended
+ * first, then every row attends with block-wide visibility. Replaces the two
+ * passes of transformer_prefill_image_block (src/engine/runtime/media_prefill.rs:87-118). */
+int ggr_attn_prefill_block(ggr_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t base_pos, int32_t m,
+                           const void* q, const void* k, const void* v, int32_t in_dtype, float* out,
+                           int32_t ptr_kind);
+
+/* The reference's three functions one by one, for callers that keep its call
+ * order (and for known-answer tests). Buffers are f32. */
+/* apply_rope_qk (src/engine/runtime/inference.rs:1817-1874): rotates q
+ * [n_heads*head_dim] and k [n_kv_heads*head_dim] in place. */
+int ggr_attn_apply_rope_qk(ggr_attn_ctx* ctx, int32_t layer, int32_t pos, float* q, float* k, int32_t ptr_kind);
+/* kv_write_token (src/engine/runtime/inference.rs:1877-1918): stores an
+ * already rotated k and v as cache row (seq, layer, pos). */
+int ggr_attn_kv_write_token(ggr_attn_ctx* ctx, int32_t seq, int32_t layer, int32_t pos, const float* k,
+                            const float* v, int32_t ptr_kind);
+/* attention_token (src/engine/runtime/inference.rs:1970-2530): q is already
+ * rotated (and pre-scaled in GGR_SCALE_Q_PRESCALED mode). */
+int ggr_attn_attention_token(ggr_attn_ctx* ctx, int32_t seq, int32_t layer, int32_t pos, const float* q,
+                             float* out, int32_t ptr_kind);
+
+/*
+ * KV-sequence sharding (no counterpart in the reference, which is single
+ * process): every rank holds a slab of positions, runs the fused decode over
+ * its slab and emits, per (sequence, query head), a partial softmax state
+ * (o[head_dim] already divided by l, m, l) with m in base-2 units
+ * (score * log2 e) and l = sum 2^(s - m). The owner of pos[b] appends the
+ * row. partial is [B][n_heads][head_dim + 2] f32. A rank whose slab misses
+ * the visible range emits (0, -inf, 0).
+ */
+int ggr_attn_decode_partial(ggr_attn_ctx* ctx, int32_t layer, const int32_t* pos, int32_t B, const float* q,
+                            const float* k, const float* v, float* partial, int32_t ptr_kind);
+/* Merges n_parts partial states laid out [n_parts][B][n_heads][head_dim + 2]
+ * into out [B][n_heads*head_dim]. */
+int ggr_attn_combine_partials(ggr_attn_ctx* ctx, const float* parts, int32_t n_parts, int32_t B, float* out,
+                              int32_t ptr_kind);
+
+/* Rows [row0, row0 + nrows) of one layer of one sequence in the reference's
+ * Q8 row layout (int8 codes [nrows][kv_dim] and one f32 scale per row), the
+ * layout its prefill cache serialises (src/app/prefill_cache.rs:214-249) and
+ * re-injects (:380-510). Only for kv_format GGR_KV_Q8_ROW. Host buffers. */
+int ggr_attn_kv_export(ggr_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t row0, int32_t nrows, int8_t* k_q8,
+                       int8_t* v_q8, float* k_scale, float* v_scale);
+int ggr_attn_kv_import(ggr_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t row0, int32_t nrows,
+                       const int8_t* k_q8, const int8_t* v_q8, const float* k_scale, const float* v_scale);
+/* Dequantised f32 view of one cache row (any format), for tests. Host buffers. */
+int ggr_attn_kv_read_row(ggr_attn_ctx* ctx, int32_t seq, int32_t layer, int32_t pos, float* k_out, float* v_out);
+
+/* Number of kernels this context has launched since it was created. */
+int64_t ggr_attn_launch_count(const ggr_attn_ctx* ctx);
+
+/* Host-side planners restated from the reference, usable without a device. */
+typedef struct ggr_rope_plan ggr_rope_plan;
+ggr_rope_plan* ggr_rope_plan_new(void);
+void ggr_rope_plan_free(ggr_rope_plan* plan);
+/* RopePositionPlan::append_text (src/engine/positions.rs:4-13) */
+int ggr_rope_plan_append_text(ggr_rope_plan* plan, int64_t count);
+/* RopePositionPlan::append_grid (src/engine/positions.rs:16-44) */
+int ggr_rope_plan_append_grid(ggr_rope_plan* plan, int64_t t, int64_t h, int64_t w, int64_t token_count);
+int64_t ggr_rope_plan_len(const ggr_rope_plan* plan);
+int64_t ggr_rope_plan_next_text(const ggr_rope_plan* plan);
+/* RopePositionPlan::at (src/engine/positions.rs:46-54) */
+void ggr_rope_plan_at(const ggr_rope_plan* plan, int64_t pos, int64_t out[3]);
+/* copies min(n, len) rows of (t, h, w) as int32 into out; returns rows copied */
+int64_t ggr_rope_plan_export(const ggr_rope_plan* plan, int32_t* out, int64_t n);
+/* RopePositionLayout::axis (src/engine/positions.rs:57-72) */
+int32_t ggr_rope_axis(int32_t layout, int32_t frequency, const int32_t sections[4]);
+/* MediaAttentionPlan::new validation (src/engine/runtime/attention.rs:9-28): 0 if valid */
+int ggr_media_plan_validate(const int64_t* start_len, int32_t n, int64_t prompt_tokens);
+/* MediaAttentionPlan::chunk_end (src/engine/runtime/attention.rs:43-70): end position or a negative status */
+int64_t ggr_media_chunk_end(const int64_t* start_len, int32_t n, int64_t prompt_tokens, int64_t start,
+                            int64_t limit, int64_t chunk);
+/* Gemma3 window list from (window, period) (src/vendors/gemma.rs:92-100) */
+int ggr_gemma_layer_windows(int32_t n_layers, int32_t window, int32_t period, int32_t* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GGR_ATTN_H */

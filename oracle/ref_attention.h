@@ -1,0 +1,96 @@
+/*
+ * TEST INFRASTRUCTURE - CPU oracle for the gguf-runner attention path.
+ *
+ * A plain C++ restatement of the reference's CPU arithmetic for RoPE, the
+ * KV-cache append and causal / sliding-window GQA attention. It exists only so
+ * that tests, the smoke check and the benchmark's CPU-baseline leg can compare
+ * the CUDA path with it; no product code may call it.
+ *
+ * Pinning: the RoPE, position-plan, axis, visibility and block-validation
+ * known-answer tests of the reference are restated against this oracle. The
+ * numeric output of attention_token itself has no golden vector anywhere in
+ * the reference, so for that function: parity unpinned (the oracle follows the
+ * cited lines, but nothing from the reference's own runs checks it here; the
+ * reference is Rust and no Rust toolchain exists in the build image).
+ */
+#ifndef GGR_ORACLE_REF_ATTENTION_H
+#define GGR_ORACLE_REF_ATTENTION_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Field order mirrors the product's ggr_attn_config prefix so one ctypes
+ * Structure can describe both in the tests. */
+typedef struct ora_config {
+    int32_t n_layers, n_heads, n_kv_heads, head_dim, rope_dim, seq_len, max_batch;
+    float rope_theta, rope_theta_swa, rope_scale_global, rope_scale_local;
+    int32_t rope_style;   /* 0 = NeoX split-half, 1 = adjacent pairs */
+    int32_t rope_layout;  /* 0 = sequential, 1 = interleaved T/H/W */
+    int32_t rope_sections[4];
+    int32_t swa_theta_on_window_layers; /* gemma3: window layers use rope_theta_swa */
+    int32_t swa_pattern;  /* layer-kind fallback when layer_windows is empty */
+    int32_t scale_mode;   /* 0 = score *= 1/sqrt(D), 1 = q pre-scaled after RoPE */
+    int32_t softmax_mode; /* 0 = two-pass, 1 = online */
+    int32_t kv_format;    /* 0 f32, 1 bf16, 2 q8 row scale, 3 q8 block-32 scales */
+    int32_t image_mode;   /* 0 causal, 1 bidirectional image blocks */
+    int32_t n_layer_windows;
+    const int32_t* layer_windows; /* n_layer_windows entries, 0 = global */
+} ora_config;
+
+typedef struct ora_ctx ora_ctx;
+
+/* returns 0 or a negative status; *err (optional) receives a static message */
+int ora_create(const ora_config* cfg, ora_ctx** out, const char** err);
+void ora_destroy(ora_ctx* ctx);
+void ora_set_threads(ora_ctx* ctx, int n);
+int ora_threads_available(void);
+
+int ora_set_position_plan(ora_ctx* ctx, const int32_t* thw, int32_t n, int32_t next_text_pos);
+int ora_set_media_blocks(ora_ctx* ctx, const int32_t* start_len, int32_t n, int32_t prompt_tokens);
+
+/* the three reference functions, with explicit buffers instead of RunState */
+void ora_rope_angles(ora_ctx* ctx, int32_t layer, int32_t pos, float* cos_out, float* sin_out);
+void ora_apply_rope_qk(ora_ctx* ctx, int32_t layer, int32_t pos, float* q, float* k);
+void ora_kv_write_token(ora_ctx* ctx, int32_t seq, int32_t layer, int32_t pos, const float* k, const float* v);
+void ora_attention_token(ora_ctx* ctx, int32_t seq, int32_t layer, int32_t pos, const float* q, float* out);
+void ora_visible_keys(ora_ctx* ctx, int32_t layer, int32_t pos, int32_t* start, int32_t* end);
+
+/* call-site compositions: decode (one token per sequence), per-token prefill
+ * loop, staged image-block prefill */
+void ora_decode(ora_ctx* ctx, int32_t layer, const int32_t* pos, int32_t B, const float* q, const float* k,
+                const float* v, float* out);
+void ora_prefill(ora_ctx* ctx, int32_t layer, int32_t seq, int32_t base_pos, int32_t m, const float* q,
+                 const float* k, const float* v, float* out);
+void ora_prefill_block(ora_ctx* ctx, int32_t layer, int32_t seq, int32_t base_pos, int32_t m, const float* q,
+                       const float* k, const float* v, float* out);
+
+/* cache readers (dequantised view and raw q8 codes) for append parity */
+void ora_kv_read_row(ora_ctx* ctx, int32_t seq, int32_t layer, int32_t pos, float* k_out, float* v_out);
+int ora_kv_read_q8(ora_ctx* ctx, int32_t seq, int32_t layer, int32_t pos, int8_t* k_q, int8_t* v_q,
+                   float* k_scale, float* v_scale);
+
+/* host-side planners restated from the reference, for known-answer tests */
+typedef struct ora_plan ora_plan;
+ora_plan* ora_plan_new(void);
+void ora_plan_free(ora_plan* p);
+int ora_plan_append_text(ora_plan* p, int64_t count);
+int ora_plan_append_grid(ora_plan* p, int64_t t, int64_t h, int64_t w, int64_t token_count);
+int64_t ora_plan_len(const ora_plan* p);
+int64_t ora_plan_next_text(const ora_plan* p);
+void ora_plan_at(const ora_plan* p, int64_t pos, int64_t out[3]);
+int32_t ora_rope_axis(int32_t layout, int32_t frequency, const int32_t sections[4]);
+int ora_media_plan_validate(const int64_t* start_len, int32_t n, int64_t prompt_tokens);
+int64_t ora_media_chunk_end(const int64_t* start_len, int32_t n, int64_t prompt_tokens, int64_t start,
+                            int64_t limit, int64_t chunk);
+int ora_gemma_layer_windows(int32_t n_layers, int32_t window, int32_t period, int32_t* out);
+
+uint16_t ora_f32_to_bf16(float x);
+float ora_bf16_to_f32(uint16_t h);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,254 @@
+"""ctypes access to the CPU oracle (oracle/libggr_oracle.so) for tests, the
+smoke check and the benchmark's CPU-baseline leg. Test infrastructure only."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ORACLE_DIR = os.path.join(ROOT, "oracle")
+_LIB = None
+
+
+class OraConfig(C.Structure):
+    _fields_ = [
+        ("n_layers", C.c_int32), ("n_heads", C.c_int32), ("n_kv_heads", C.c_int32), ("head_dim", C.c_int32),
+        ("rope_dim", C.c_int32), ("seq_len", C.c_int32), ("max_batch", C.c_int32),
+        ("rope_theta", C.c_float), ("rope_theta_swa", C.c_float),
+        ("rope_scale_global", C.c_float), ("rope_scale_local", C.c_float),
+        ("rope_style", C.c_int32), ("rope_layout", C.c_int32), ("rope_sections", C.c_int32 * 4),
+        ("swa_theta_on_window_layers", C.c_int32), ("swa_pattern", C.c_int32),
+        ("scale_mode", C.c_int32), ("softmax_mode", C.c_int32), ("kv_format", C.c_int32),
+        ("image_mode", C.c_int32), ("n_layer_windows", C.c_int32),
+        ("layer_windows", C.POINTER(C.c_int32)),
+    ]
+
+
+def build(force: bool = False) -> str:
+    path = os.path.join(ORACLE_DIR, "libggr_oracle.so")
+    src = [os.path.join(ORACLE_DIR, f) for f in ("ref_attention.cpp", "ref_attention.h", "Makefile")]
+    stale = (not os.path.exists(path)) or any(os.path.getmtime(s) > os.path.getmtime(path) for s in src)
+    if force or stale:
+        subprocess.run(["make", "-C", ORACLE_DIR, "-B"], check=True, capture_output=True)
+    return path
+
+
+def lib() -> C.CDLL:
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    L = C.CDLL(build())
+    vp, i32, i64 = C.c_void_p, C.c_int32, C.c_int64
+    L.ora_create.argtypes = [C.POINTER(OraConfig), C.POINTER(vp), C.POINTER(C.c_char_p)]
+    L.ora_destroy.argtypes = [vp]
+    L.ora_destroy.restype = None
+    L.ora_set_threads.argtypes = [vp, C.c_int]
+    L.ora_set_threads.restype = None
+    L.ora_set_position_plan.argtypes = [vp, vp, i32, i32]
+    L.ora_set_media_blocks.argtypes = [vp, vp, i32, i32]
+    L.ora_rope_angles.argtypes = [vp, i32, i32, vp, vp]
+    L.ora_rope_angles.restype = None
+    L.ora_apply_rope_qk.argtypes = [vp, i32, i32, vp, vp]
+    L.ora_apply_rope_qk.restype = None
+    L.ora_kv_write_token.argtypes = [vp, i32, i32, i32, vp, vp]
+    L.ora_kv_write_token.restype = None
+    L.ora_attention_token.argtypes = [vp, i32, i32, i32, vp, vp]
+    L.ora_attention_token.restype = None
+    L.ora_visible_keys.argtypes = [vp, i32, i32, C.POINTER(i32), C.POINTER(i32)]
+    L.ora_visible_keys.restype = None
+    L.ora_decode.argtypes = [vp, i32, vp, i32, vp, vp, vp, vp]
+    L.ora_decode.restype = None
+    L.ora_prefill.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp]
+    L.ora_prefill.restype = None
+    L.ora_prefill_block.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp]
+    L.ora_prefill_block.restype = None
+    L.ora_kv_read_row.argtypes = [vp, i32, i32, i32, vp, vp]
+    L.ora_kv_read_row.restype = None
+    L.ora_kv_read_q8.argtypes = [vp, i32, i32, i32, vp, vp, vp, vp]
+    L.ora_plan_new.restype = vp
+    L.ora_plan_free.argtypes = [vp]
+    L.ora_plan_free.restype = None
+    L.ora_plan_append_text.argtypes = [vp, i64]
+    L.ora_plan_append_grid.argtypes = [vp, i64, i64, i64, i64]
+    L.ora_plan_len.argtypes = [vp]
+    L.ora_plan_len.restype = i64
+    L.ora_plan_next_text.argtypes = [vp]
+    L.ora_plan_next_text.restype = i64
+    L.ora_plan_at.argtypes = [vp, i64, C.POINTER(i64)]
+    L.ora_plan_at.restype = None
+    L.ora_rope_axis.argtypes = [i32, i32, C.POINTER(i32)]
+    L.ora_media_plan_validate.argtypes = [vp, i32, i64]
+    L.ora_media_chunk_end.argtypes = [vp, i32, i64, i64, i64, i64]
+    L.ora_media_chunk_end.restype = i64
+    L.ora_gemma_layer_windows.argtypes = [i32, i32, i32, vp]
+    L.ora_f32_to_bf16.argtypes = [C.c_float]
+    L.ora_f32_to_bf16.restype = C.c_uint16
+    L.ora_bf16_to_f32.argtypes = [C.c_uint16]
+    L.ora_bf16_to_f32.restype = C.c_float
+    _LIB = L
+    return L
+
+
+def _p(a):
+    return C.c_void_p(a.ctypes.data)
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+class OraclePlan:
+    def __init__(self):
+        self.L = lib()
+        self.h = C.c_void_p(self.L.ora_plan_new())
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.L.ora_plan_free(self.h)
+            self.h = None
+
+    def append_text(self, n):
+        return self.L.ora_plan_append_text(self.h, n)
+
+    def append_grid(self, grid, count):
+        return self.L.ora_plan_append_grid(self.h, grid[0], grid[1], grid[2], count)
+
+    def __len__(self):
+        return int(self.L.ora_plan_len(self.h))
+
+    @property
+    def next_text_position(self):
+        return int(self.L.ora_plan_next_text(self.h))
+
+    def at(self, pos):
+        out = (C.c_int64 * 3)()
+        self.L.ora_plan_at(self.h, pos, out)
+        return [int(x) for x in out]
+
+    @property
+    def positions(self):
+        return [self.at(i) for i in range(len(self))]
+
+
+class Oracle:
+    """CPU restatement of the reference attention path, configured from the same
+    fields as gguf_runner_b200.AttnConfig (any object with those attributes)."""
+
+    def __init__(self, cfg, threads: int = 1):
+        self.L = lib()
+        self.cfg = cfg
+        c = OraConfig()
+        for name in ("n_layers", "n_heads", "n_kv_heads", "head_dim", "rope_dim", "seq_len", "max_batch",
+                     "rope_theta", "rope_theta_swa", "rope_scale_global", "rope_scale_local", "rope_style",
+                     "rope_layout", "swa_theta_on_window_layers", "swa_pattern", "scale_mode", "softmax_mode",
+                     "kv_format", "image_mode"):
+            setattr(c, name, getattr(cfg, name))
+        for i in range(4):
+            c.rope_sections[i] = int(cfg.rope_sections[i])
+        w = list(cfg.layer_windows)
+        self._w = (C.c_int32 * max(1, len(w)))(*w)
+        c.n_layer_windows = len(w)
+        c.layer_windows = C.cast(self._w, C.POINTER(C.c_int32))
+        h = C.c_void_p()
+        err = C.c_char_p()
+        st = self.L.ora_create(C.byref(c), C.byref(h), C.byref(err))
+        if st != 0:
+            raise ValueError(err.value.decode() if err.value else f"oracle status {st}")
+        self.h = h
+        self.q_dim = cfg.n_heads * cfg.head_dim
+        self.kv_dim = cfg.n_kv_heads * cfg.head_dim
+        self.L.ora_set_threads(self.h, threads)
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.L.ora_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        self.close()
+
+    def set_threads(self, n):
+        self.L.ora_set_threads(self.h, n)
+
+    def set_position_plan(self, rows, next_text):
+        rows = np.ascontiguousarray(np.asarray(rows, dtype=np.int32).reshape(-1, 3))
+        self.L.ora_set_position_plan(self.h, _p(rows), rows.shape[0], next_text)
+
+    def set_media_blocks(self, blocks, prompt_tokens):
+        arr = np.ascontiguousarray(np.asarray(blocks, dtype=np.int32).reshape(-1, 2))
+        if self.L.ora_set_media_blocks(self.h, _p(arr), arr.shape[0], prompt_tokens) != 0:
+            raise ValueError("invalid blocks")
+
+    def rope_angles(self, layer, pos):
+        half = (self.cfg.rope_dim or self.cfg.head_dim) // 2
+        c = np.empty(half, np.float32)
+        s = np.empty(half, np.float32)
+        self.L.ora_rope_angles(self.h, layer, pos, _p(c), _p(s))
+        return c, s
+
+    def apply_rope_qk(self, layer, pos, q, k):
+        self.L.ora_apply_rope_qk(self.h, layer, pos, _p(q), _p(k))
+
+    def kv_write_token(self, layer, pos, k, v, seq=0):
+        k, v = _f32(k), _f32(v)
+        self.L.ora_kv_write_token(self.h, seq, layer, pos, _p(k), _p(v))
+
+    def attention_token(self, layer, pos, q, seq=0):
+        q = _f32(q)
+        out = np.empty(self.q_dim, np.float32)
+        self.L.ora_attention_token(self.h, seq, layer, pos, _p(q), _p(out))
+        return out
+
+    def visible_keys(self, layer, pos):
+        s, e = C.c_int32(), C.c_int32()
+        self.L.ora_visible_keys(self.h, layer, pos, C.byref(s), C.byref(e))
+        return range(s.value, e.value)
+
+    def decode(self, layer, pos, q, k, v):
+        pos = np.ascontiguousarray(np.asarray(pos, np.int32).reshape(-1))
+        q, k, v = _f32(q), _f32(k), _f32(v)
+        out = np.empty((pos.shape[0], self.q_dim), np.float32)
+        self.L.ora_decode(self.h, layer, _p(pos), pos.shape[0], _p(q), _p(k), _p(v), _p(out))
+        return out
+
+    def prefill(self, layer, base_pos, q, k, v, seq=0, block=False):
+        q, k, v = _f32(q), _f32(k), _f32(v)
+        m = q.shape[0]
+        out = np.empty((m, self.q_dim), np.float32)
+        fn = self.L.ora_prefill_block if block else self.L.ora_prefill
+        fn(self.h, layer, seq, base_pos, m, _p(q), _p(k), _p(v), _p(out))
+        return out
+
+    def kv_read_row(self, layer, pos, seq=0):
+        k = np.empty(self.kv_dim, np.float32)
+        v = np.empty(self.kv_dim, np.float32)
+        self.L.ora_kv_read_row(self.h, seq, layer, pos, _p(k), _p(v))
+        return k, v
+
+    def kv_read_q8(self, layer, pos, seq=0):
+        kq = np.empty(self.kv_dim, np.int8)
+        vq = np.empty(self.kv_dim, np.int8)
+        ns = 1 if self.cfg.kv_format == 2 else self.kv_dim // 32
+        ks = np.empty(ns, np.float32)
+        vs = np.empty(ns, np.float32)
+        if self.L.ora_kv_read_q8(self.h, seq, layer, pos, _p(kq), _p(vq), _p(ks), _p(vs)) != 0:
+            raise ValueError("not a q8 cache")
+        return kq, vq, ks, vs
+
+
+def bf16_round(a: np.ndarray) -> np.ndarray:
+    """Round-to-nearest-even to bf16, returned as f32 (src/engine/io/gguf.rs:107-116)."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    bits = a.view(np.uint32).astype(np.uint64)
+    rounded = ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16) << 16
+    return rounded.astype(np.uint32).view(np.float32).reshape(a.shape)
+
+
+def bf16_bits(a: np.ndarray) -> np.ndarray:
+    """bf16 bit patterns (uint16) of an f32 array, round-to-nearest-even."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    bits = a.view(np.uint32).astype(np.uint64)
+    return ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16).astype(np.uint16).reshape(a.shape)
