@@ -1,0 +1,484 @@
+#!/usr/bin/env python
+"""Benchmark of the attention path on B200.
+
+Default workload (the one the JSON line reports): Llama-3-8B-shaped causal
+prefill attention (config 2 of BASELINE.json): 32 layers, 32 query / 8 KV heads,
+head_dim 128, one sequence of 4096 tokens, bf16 q/k/v, RoPE + append + causal
+GQA attention per layer, f32 output. A step is one pass over all 32 layers.
+With N GPUs every rank processes its own sequence (independent sequences,
+no data-path collective): weak scaling.
+
+Extra objects in the same line: `decode` (Qwen3-30B-A3B-shaped split-KV decode,
+config 3, achieved HBM GB/s) at N=1 and `decode_seq_split` (Qwen2.5-14B-shaped
+long-context decode, config 5, KV sequence split over the ranks with an NCCL
+all-gather of the partial softmax states) at N>1.
+
+`--impl reference` times the CPU restatement of the reference's attention
+(oracle/) on the host cores for the same workload, on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+S_PREFILL = 4096
+N_LAYERS_PREFILL = 32
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=self.out, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        sm, smmax, reasons = [], [], set()
+        with open(self.path) as f:
+            for line in f:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    smmax.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                     parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        os.unlink(self.path)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(smmax)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def visible_pairs_causal(S: int) -> int:
+    return S * (S + 1) // 2
+
+
+# ---- CPU reference arm --------------------------------------------------------------------------------
+
+def cpu_prefill_sample(stride: int = 16, threads: int = 0):
+    """Times the oracle (the reference's per-token CPU attention) on every `stride`-th query
+    position of one Llama-3-8B-shaped layer over a fully populated Q8 cache, and scales by the
+    visible (query, key) pairs to a whole layer. Returns (tokens/s for the 32-layer pass, info)."""
+    from gguf_runner_b200 import presets
+    from gguf_runner_b200.binding import KV_Q8_ROW
+    from tests.oracle_binding import Oracle, lib as oracle_lib
+
+    cores = threads or oracle_lib().ora_threads_available()
+    cfg = presets.llama3_8b_prefill(n_layers=1, seq_len=S_PREFILL, kv_format=KV_Q8_ROW)
+    ora = Oracle(cfg, threads=cores)
+    rng = np.random.default_rng(1002)
+    k = rng.standard_normal((S_PREFILL, cfg.kv_dim)).astype(np.float32)
+    v = rng.standard_normal((S_PREFILL, cfg.kv_dim)).astype(np.float32)
+    qd = np.zeros(cfg.q_dim, np.float32)
+    for pos in range(S_PREFILL):  # populate the cache (untimed): rope + append only
+        kr = k[pos].copy()
+        ora.apply_rope_qk(0, pos, qd.copy(), kr)
+        ora.kv_write_token(0, pos, kr, v[pos])
+    positions = list(range(stride - 1, S_PREFILL, stride))
+    qs = rng.standard_normal((len(positions), cfg.q_dim)).astype(np.float32)
+
+    def one_pass():
+        t0 = time.perf_counter()
+        for i, pos in enumerate(positions):
+            q = qs[i].copy()
+            kr = k[pos].copy()
+            ora.apply_rope_qk(0, pos, q, kr)
+            ora.kv_write_token(0, pos, kr, v[pos])
+            ora.attention_token(0, pos, q)
+        return time.perf_counter() - t0
+
+    pairs_sample = sum(p + 1 for p in positions)
+    scale = visible_pairs_causal(S_PREFILL) / pairs_sample
+    info = {"cores": cores, "kind": "port",
+            "sample": f"one layer, every {stride}th query position of S={S_PREFILL} ({len(positions)} tokens) over a "
+                      f"populated q8_row cache; layer time = sample time x {scale:.2f} (visible-pair ratio), "
+                      f"x {N_LAYERS_PREFILL} layers"}
+    return one_pass, scale, info, ora
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    one_pass, scale, info, _ora = cpu_prefill_sample(stride=args.cpu_stride)
+    for _ in range(args.warmup):
+        one_pass()
+    times = [one_pass() for _ in range(args.steps)]
+    t = float(np.mean(times))
+    step_s = t * scale * N_LAYERS_PREFILL
+    value = S_PREFILL / step_s
+    line = {
+        "impl": "reference", "metric": "prefill attention tokens/s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": dict(info, value=value, unit="tokens/s"),
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus: int):
+    return {"workload": "Llama-3-8B-shaped causal prefill attention (BASELINE.json configs[1]): 32 layers, 32 q / 8 kv "
+                        "heads, head_dim 128, batch 1, S=4096, bf16 q/k/v, adjacent-pair RoPE theta 5e5, f32 out",
+            "sequences": n_gpus, "seq_len": S_PREFILL, "layers": N_LAYERS_PREFILL,
+            "parallelism": f"{n_gpus} independent sequences, one per GPU" if n_gpus > 1 else "single GPU",
+            "l2": "each step streams 1.6 GB of q/k/v, 0.5 GB of cache and 2.1 GB of output per GPU, far above the 126 MB L2"}
+
+
+# ---- GPU arm ---------------------------------------------------------------------------------------------
+
+class RawCuda:
+    """Lets torch view device memory owned by the library (__cuda_array_interface__)."""
+
+    def __init__(self, ptr, nbytes):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+def fill_cache_random(torch, ctx, seed):
+    """Fills a bf16 / f32 cache with N(0,1) values (synthetic stand-in for appended rows)."""
+    k, v, _, _, nbytes = ctx.kv_device_ptrs()
+    dt = torch.bfloat16 if ctx.config.kv_format == 1 else torch.float32
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(seed)
+    for ptr in (k, v):
+        flat = torch.as_tensor(RawCuda(ptr, nbytes), device="cuda").view(dt)
+        step = 1 << 28
+        for i in range(0, flat.numel(), step):
+            n = min(step, flat.numel() - i)
+            flat[i:i + n] = torch.randn(n, generator=gen, device="cuda", dtype=torch.float32).to(dt)
+
+
+def bench_prefill(torch, dist, args, rank, world, local_rank, peaks):
+    import gguf_runner_b200 as g
+    from gguf_runner_b200 import presets
+
+    cfg = presets.llama3_8b_prefill(n_layers=N_LAYERS_PREFILL, seq_len=S_PREFILL, device=local_rank)
+    ctx = g.AttnContext(cfg)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1002 + rank)
+    S, L = S_PREFILL, N_LAYERS_PREFILL
+
+    def rnd(*shape):
+        return torch.randn(*shape, generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+
+    q = [rnd(S, cfg.q_dim) for _ in range(L)]
+    k = [rnd(S, cfg.kv_dim) for _ in range(L)]
+    v = [rnd(S, cfg.kv_dim) for _ in range(L)]
+    out = [torch.empty(S, cfg.q_dim, device="cuda", dtype=torch.float32) for _ in range(L)]
+
+    def step():
+        for l in range(L):
+            ctx.prefill(l, 0, q[l], k[l], v[l], out=out[l])
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    sync_all()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ctx.set_kernel_timing(True)
+    launches0 = ctx.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    sync_all()
+    elapsed_ms = e0.elapsed_time(e1)
+    attn_ms, attn_n = ctx.kernel_time(0)
+    rope_ms, rope_n = ctx.kernel_time(1)
+    ctx.set_kernel_timing(False)
+    clocks = sampler.stop() if rank == 0 else None
+    launches = ctx.launch_count - launches0
+    if world > 1:
+        t = torch.tensor([elapsed_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    ms_per_step = elapsed_ms / args.steps
+    value = world * S / (ms_per_step * 1e-3)
+
+    flops_per_launch = 4.0 * cfg.n_heads * cfg.head_dim * visible_pairs_causal(S)
+    achieved = flops_per_launch / (attn_ms / attn_n * 1e-3) / 1e12
+    # a kernel timed inside a seconds-long step: compare with the sustained cuBLAS figure
+    peak = peaks["bf16_tflops_sustained"]
+    roofline = {"bound": "tensor", "kernel": "prefill attention (one launch per layer)", "achieved": achieved,
+                "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                "peak_source": peaks["source"] + " (sustained cuBLAS bf16)",
+                "flops_per_launch": flops_per_launch, "avg_launch_ms": attn_ms / attn_n,
+                "rope_append_avg_ms": rope_ms / max(1, rope_n)}
+
+    # end to end through the C ABI with host buffers (pinned): H2D of q/k/v and D2H of out inside the timed region
+    hq = [torch.empty(S, cfg.q_dim, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    hk = [torch.empty(S, cfg.kv_dim, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    hv = [torch.empty(S, cfg.kv_dim, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    hout = torch.empty(S, cfg.q_dim, dtype=torch.float32).pin_memory()
+    for i in range(2):
+        hq[i].copy_(q[i])
+        hk[i].copy_(k[i])
+        hv[i].copy_(v[i])
+    torch.cuda.synchronize()
+
+    def e2e_step():
+        for l in range(L):
+            ctx.prefill(l, 0, hq[l & 1], hk[l & 1], hv[l & 1], out=hout)
+
+    e2e_step()
+    sync_all()
+    e2e_steps = max(1, min(args.steps, 3))
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    h2d = L * (S * cfg.q_dim + 2 * S * cfg.kv_dim) * 2
+    d2h = L * S * cfg.q_dim * 4
+    e2e = {"value": world * S / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+           "ms_per_step": e2e_s * 1e3}
+    ctx.close()
+    del q, k, v, out
+    torch.cuda.empty_cache()
+    return value, ms_per_step, roofline, e2e, clocks, launches
+
+
+def bench_decode_cfg3(torch, args, local_rank, peaks, B=8):
+    """Qwen3-30B-A3B-shaped decode: 48 layers, 32 q / 4 kv heads, T=32768, bf16 cache, one new token per step."""
+    import gguf_runner_b200 as g
+    from gguf_runner_b200 import presets
+    T, L = 32768, 48
+    cfg = presets.qwen3_30b_a3b_decode(n_layers=L, seq_len=T, max_batch=B, device=local_rank)
+    ctx = g.AttnContext(cfg)
+    fill_cache_random(torch, ctx, 1003)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(2003)
+    q = torch.randn(L, B, cfg.q_dim, generator=gen, device="cuda")
+    k = torch.randn(L, B, cfg.kv_dim, generator=gen, device="cuda")
+    v = torch.randn(L, B, cfg.kv_dim, generator=gen, device="cuda")
+    out = torch.empty(L, B, cfg.q_dim, device="cuda")
+    pos = [T - 1] * B
+
+    def step():
+        for l in range(L):
+            ctx.decode(l, pos, q[l], k[l], v[l], out=out[l])
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    torch.cuda.synchronize()
+    ctx.set_kernel_timing(True)
+    steps = max(3, args.steps)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms_per_step = e0.elapsed_time(e1) / steps
+    attn_ms, attn_n = ctx.kernel_time(0)
+    ctx.set_kernel_timing(False)
+    bytes_per_launch = B * T * cfg.n_kv_heads * cfg.head_dim * 2 * 2  # K and V, bf16
+    achieved = bytes_per_launch / (attn_ms / attn_n * 1e-3) / 1e9
+    res = {"workload": f"Qwen3-30B-A3B-shaped decode (configs[2]): 48 layers, 32 q / 4 kv heads, T=32768, B={B}, bf16 cache",
+           "tokens_per_s": B / (ms_per_step * 1e-3), "ms_per_step": ms_per_step,
+           "roofline": {"bound": "hbm", "kernel": "split-KV decode attention", "achieved": achieved,
+                        "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                        "bytes_per_launch": bytes_per_launch, "avg_launch_ms": attn_ms / attn_n,
+                        "peak_source": peaks["source"], "traffic": None}}
+    ctx.close()
+    torch.cuda.empty_cache()
+    return res
+
+
+def bench_decode_seq_split(torch, dist, args, rank, world, local_rank, peaks):
+    """Qwen2.5-14B-shaped long-context decode (configs[4]): T=131072, B=16, the KV sequence split into one
+    contiguous slab per rank; partial (o, m, l) all-gathered with NCCL and merged on every rank."""
+    import gguf_runner_b200 as g
+    from gguf_runner_b200 import presets
+    from gguf_runner_b200.binding import SHARD_KV_SEQUENCE
+    T, L, B = 131072, 48, 16
+    per = T // world
+    per_layer_bytes = B * per * 8 * 128 * 2 * 2
+    n_res = int(max(1, min(L, (100 << 30) // per_layer_bytes)))
+    cfg = presets.qwen25_14b_decode(n_layers=n_res, seq_len=T, max_batch=B, device=local_rank,
+                                    shard_mode=SHARD_KV_SEQUENCE, shard_pos_begin=rank * per, shard_pos_count=per,
+                                    n_ranks=world, rank=rank)
+    ctx = g.AttnContext(cfg)
+    fill_cache_random(torch, ctx, 1005 + rank)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(2005)  # q/k/v are replicated: same seed on every rank
+    q = torch.randn(n_res, B, cfg.q_dim, generator=gen, device="cuda")
+    k = torch.randn(n_res, B, cfg.kv_dim, generator=gen, device="cuda")
+    v = torch.randn(n_res, B, cfg.kv_dim, generator=gen, device="cuda")
+    part = torch.empty(B, cfg.n_heads, cfg.head_dim + 2, device="cuda")
+    gathered = torch.empty(world, B, cfg.n_heads, cfg.head_dim + 2, device="cuda")
+    out = torch.empty(B, cfg.q_dim, device="cuda")
+    pos = [T - 1] * B
+
+    def step():
+        for l in range(L):
+            r = l % n_res
+            ctx.decode_partial(r, pos, q[r], k[r], v[r], partial=part)
+            dist.all_gather_into_tensor(gathered, part)
+            ctx.combine_partials(gathered, out=out)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    ctx.set_kernel_timing(True)
+    steps = max(3, args.steps)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step = float(t.item()) / steps
+    attn_ms, attn_n = ctx.kernel_time(0)
+    ctx.set_kernel_timing(False)
+    bytes_per_launch = per_layer_bytes
+    achieved = bytes_per_launch / (attn_ms / attn_n * 1e-3) / 1e9
+    res = {"workload": f"Qwen2.5-14B-shaped decode (configs[4]): 48 layers, 40 q / 8 kv heads, T=131072, B=16, bf16 cache, "
+                       f"KV sequence split over {world} GPUs ({per} positions each), {n_res} resident layers cycled",
+           "tokens_per_s": B / (ms_per_step * 1e-3), "ms_per_step": ms_per_step,
+           "per_gpu_roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                "frac": achieved / peaks["hbm_gbs"], "bytes_per_launch": bytes_per_launch,
+                                "avg_launch_ms": attn_ms / attn_n},
+           "exchange_bytes_per_layer_per_gpu": B * cfg.n_heads * (cfg.head_dim + 2) * 4}
+    ctx.close()
+    torch.cuda.empty_cache()
+    return res
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the attention path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    peaks = measured_peaks()
+
+    value, ms_per_step, roofline, e2e, clocks, launches = bench_prefill(torch, dist, args, rank, world, local_rank, peaks)
+    extras = {}
+    if not args.no_extras:
+        if world == 1:
+            extras["decode"] = bench_decode_cfg3(torch, args, local_rank, peaks, B=args.decode_batch)
+        else:
+            extras["decode_seq_split"] = bench_decode_seq_split(torch, dist, args, rank, world, local_rank, peaks)
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        one_pass, scale, info, _ora = cpu_prefill_sample(stride=args.cpu_stride)
+        one_pass()
+        t = one_pass()
+        cpu = dict(info, value=S_PREFILL / (t * scale * N_LAYERS_PREFILL), unit="tokens/s")
+
+    if rank == 0:
+        line = {
+            "metric": "prefill attention tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": workload_config(world), "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+            "gpu_launches": launches, "clocks": clocks,
+        }
+        line.update(extras)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-extras", action="store_true", help="skip the decode extras")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--decode-batch", type=int, default=8)
+    ap.add_argument("--cpu-stride", type=int, default=16)
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -68,6 +68,7 @@ EXPORTED_SYMBOLS = [
     "ggr_attn_apply_rope_qk", "ggr_attn_kv_write_token", "ggr_attn_attention_token",
     "ggr_attn_decode_partial", "ggr_attn_combine_partials",
     "ggr_attn_kv_export", "ggr_attn_kv_import", "ggr_attn_kv_read_row", "ggr_attn_launch_count",
+    "ggr_attn_set_kernel_timing", "ggr_attn_kernel_time", "ggr_attn_kv_device_ptrs",
     "ggr_rope_plan_new", "ggr_rope_plan_free", "ggr_rope_plan_append_text", "ggr_rope_plan_append_grid",
     "ggr_rope_plan_len", "ggr_rope_plan_next_text", "ggr_rope_plan_at", "ggr_rope_plan_export",
     "ggr_rope_axis", "ggr_media_plan_validate", "ggr_media_chunk_end", "ggr_gemma_layer_windows",
@@ -116,6 +117,10 @@ def lib() -> C.CDLL:
     L.ggr_attn_kv_read_row.argtypes = [vp, i32, i32, i32, vp, vp]
     L.ggr_attn_launch_count.argtypes = [vp]
     L.ggr_attn_launch_count.restype = i64
+    L.ggr_attn_set_kernel_timing.argtypes = [vp, i32]
+    L.ggr_attn_kernel_time.argtypes = [vp, i32, C.POINTER(C.c_double), C.POINTER(i64), i32]
+    L.ggr_attn_kv_device_ptrs.argtypes = [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp),
+                                          C.POINTER(C.c_uint64)]
     L.ggr_rope_plan_new.restype = vp
     L.ggr_rope_plan_free.argtypes = [vp]
     L.ggr_rope_plan_free.restype = None
@@ -231,6 +236,18 @@ class AttnContext:
         if st != 0:
             raise GgrError(st, self._L.ggr_attn_create_error().decode())
         self._h = handle
+        self._stream = None
+
+    def _follow_torch_stream(self, *tensors):
+        """Device-pointer calls are enqueued on torch's current stream, so they are
+        ordered with the kernels that produced the tensors and those that read the result."""
+        for t in tensors:
+            if t is not None and _is_torch(t) and t.is_cuda:
+                import torch
+                handle = torch.cuda.current_stream(t.device).cuda_stream or 1  # 0 is the legacy default stream
+                if handle != self._stream:
+                    self.set_stream(handle)
+                return
 
     def close(self):
         if getattr(self, "_h", None):
@@ -255,7 +272,10 @@ class AttnContext:
 
     # ---- state -------------------------------------------------------------------------
     def set_stream(self, cuda_stream: int):
+        """cuda_stream: a cudaStream_t value; 0 selects the stream the context owns,
+        1 (cudaStreamLegacy) the legacy default stream."""
         self._check(self._L.ggr_attn_set_stream(self._h, C.c_void_p(cuda_stream)))
+        self._stream = cuda_stream
 
     def synchronize(self):
         self._check(self._L.ggr_attn_synchronize(self._h))
@@ -282,6 +302,22 @@ class AttnContext:
     def launch_count(self) -> int:
         return int(self._L.ggr_attn_launch_count(self._h))
 
+    def set_kernel_timing(self, enable: bool):
+        self._check(self._L.ggr_attn_set_kernel_timing(self._h, 1 if enable else 0))
+
+    def kernel_time(self, kind: int = 0, reset: bool = True):
+        """(summed device milliseconds, launches) of one kernel kind: 0 attention, 1 rope/append, 2 merge."""
+        ms, n = C.c_double(), C.c_int64()
+        self._check(self._L.ggr_attn_kernel_time(self._h, kind, C.byref(ms), C.byref(n), 1 if reset else 0))
+        return ms.value, n.value
+
+    def kv_device_ptrs(self):
+        """Device addresses (k, v, k_scale, v_scale) and the byte size of the K (or V) array."""
+        k, v, ks, vs, nb = C.c_void_p(), C.c_void_p(), C.c_void_p(), C.c_void_p(), C.c_uint64()
+        self._check(self._L.ggr_attn_kv_device_ptrs(self._h, C.byref(k), C.byref(v), C.byref(ks), C.byref(vs),
+                                                     C.byref(nb)))
+        return k.value, v.value, ks.value, vs.value, nb.value
+
     # ---- compute -----------------------------------------------------------------------
     def _out_like(self, q, shape):
         if _is_torch(q):
@@ -294,6 +330,7 @@ class AttnContext:
         B = pos.shape[0]
         if out is None:
             out = self._out_like(q, (B, self.config.q_dim))
+        self._follow_torch_stream(q)
         (qp, kind), (kp, _), (vp, _), (op, _) = _ptr(q), _ptr(k), _ptr(v), _ptr(out)
         self._check(self._L.ggr_attn_decode(self._h, layer, C.c_void_p(pos.ctypes.data), B, qp, kp, vp, op, kind))
         return out
@@ -303,6 +340,7 @@ class AttnContext:
         B = pos.shape[0]
         if partial is None:
             partial = self._out_like(q, (B, self.config.n_heads, self.config.head_dim + 2))
+        self._follow_torch_stream(q)
         (qp, kind), (kp, _), (vp, _), (pp, _) = _ptr(q), _ptr(k), _ptr(v), _ptr(partial)
         self._check(self._L.ggr_attn_decode_partial(self._h, layer, C.c_void_p(pos.ctypes.data), B, qp, kp, vp, pp,
                                                      kind))
@@ -312,6 +350,7 @@ class AttnContext:
         n_parts, B = parts.shape[0], parts.shape[1]
         if out is None:
             out = self._out_like(parts, (B, self.config.q_dim))
+        self._follow_torch_stream(parts)
         (pp, kind), (op, _) = _ptr(parts), _ptr(out)
         self._check(self._L.ggr_attn_combine_partials(self._h, pp, n_parts, B, op, kind))
         return out
@@ -325,6 +364,7 @@ class AttnContext:
             in_dtype = DTYPE_BF16 if q.dtype == np.uint16 else DTYPE_F32
         if out is None:
             out = self._out_like(q, (m, self.config.q_dim))
+        self._follow_torch_stream(q)
         (qp, kind), (kp, _), (vp, _), (op, _) = _ptr(q), _ptr(k), _ptr(v), _ptr(out)
         self._check(fn(self._h, layer, seq, base_pos, m, qp, kp, vp, in_dtype, op, kind))
         return out
@@ -338,16 +378,19 @@ class AttnContext:
 
     def apply_rope_qk(self, layer: int, pos: int, q, k):
         """Rotates q and k in place (apply_rope_qk, src/engine/runtime/inference.rs:1817)."""
+        self._follow_torch_stream(q)
         (qp, kind), (kp, _) = _ptr(q), _ptr(k)
         self._check(self._L.ggr_attn_apply_rope_qk(self._h, layer, pos, qp, kp, kind))
 
     def kv_write_token(self, layer: int, pos: int, k, v, seq: int = 0):
+        self._follow_torch_stream(k)
         (kp, kind), (vp, _) = _ptr(k), _ptr(v)
         self._check(self._L.ggr_attn_kv_write_token(self._h, seq, layer, pos, kp, vp, kind))
 
     def attention_token(self, layer: int, pos: int, q, seq: int = 0, out=None):
         if out is None:
             out = self._out_like(q, (self.config.q_dim,))
+        self._follow_torch_stream(q)
         (qp, kind), (op, _) = _ptr(q), _ptr(out)
         self._check(self._L.ggr_attn_attention_token(self._h, seq, layer, pos, qp, op, kind))
         return out

@@ -36,6 +36,86 @@ struct AttnArgs {
     int stage_bytes;      // bytes of one ring stage of one warp
 };
 
+// Writes one head's merged state: the final output row, a (o / l, m, l)
+// partial for cross-rank merging, or nothing when a later stage will.
+__device__ __forceinline__ void store_final(const AttnArgs& a, int item, int h, int d, float o, float ms, float ls) {
+    const int D = a.kv.D, Hq = a.kv.Hq;
+    const float inv = ls > 0.0f ? 1.0f / ls : 0.0f;
+    if (a.partial_out) {
+        float* po = a.partial_out + ((int64_t)item * Hq + h) * (D + 2);
+        po[d] = o * inv;
+        if (d == 0) {
+            po[D] = ms;
+            po[D + 1] = ls;
+        }
+    } else {
+        a.out[((int64_t)item * Hq + h) * D + d] = o * inv;
+    }
+}
+
+// Merges the per-warp online-softmax states of a CTA (wacc [nw][RS][D] un-normalised,
+// wm / wl [nw][RS]) for heads g0 .. g0+gn-1 of this KV head and stores them: final
+// when the launch has one split, else into the split scratch.
+__device__ __forceinline__ void cta_merge_store(const AttnArgs& a, const float* wacc, const float* wm, const float* wl,
+                                                int nw, int RS, int g0, int gn, int item, int kvh, int split) {
+    const int D = a.kv.D, G = a.kv.G, Hq = a.kv.Hq;
+    for (int idx = threadIdx.x; idx < gn * D; idx += blockDim.x) {
+        const int g = idx / D, d = idx - g * D;
+        float ms = -INFINITY;
+        for (int w = 0; w < nw; ++w) ms = fmaxf(ms, wm[w * RS + g]);
+        float o = 0.0f, ls = 0.0f;
+        for (int w = 0; w < nw; ++w) {
+            const float mw = wm[w * RS + g];
+            const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - ms);
+            o += f * wacc[(w * RS + g) * D + d];
+            ls += f * wl[w * RS + g];
+        }
+        const int h = kvh * G + g0 + g;
+        if (a.n_split == 1) {
+            store_final(a, item, h, d, o, ms, ls);
+        } else {
+            float* pp = a.part + (((int64_t)item * Hq + h) * a.n_split + split) * (D + 2);
+            pp[d] = o;
+            if (d == 0) {
+                pp[D] = ms;
+                pp[D + 1] = ls;
+            }
+        }
+    }
+}
+
+// The last CTA of a (token, kv head) to arrive (atomic ticket) merges the
+// per-split states from the scratch buffer and resets the ticket.
+__device__ __forceinline__ void split_merge_store(const AttnArgs& a, int item, int kvh, int* s_last) {
+    if (a.n_split == 1) return;
+    const int D = a.kv.D, G = a.kv.G, Hq = a.kv.Hq;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned prev = atomicAdd(&a.counters[item * a.kv.Hkv + kvh], 1u);
+        *s_last = (prev == (unsigned)a.n_split - 1u);
+    }
+    __syncthreads();
+    if (!*s_last) return;
+    __threadfence();
+    for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+        const int g = idx / D, d = idx - g * D;
+        const int h = kvh * G + g;
+        const float* pp = a.part + ((int64_t)item * Hq + h) * a.n_split * (D + 2);
+        float ms = -INFINITY;
+        for (int s = 0; s < a.n_split; ++s) ms = fmaxf(ms, __ldcg(pp + (int64_t)s * (D + 2) + D));
+        float o = 0.0f, ls = 0.0f;
+        for (int s = 0; s < a.n_split; ++s) {
+            const float mw = __ldcg(pp + (int64_t)s * (D + 2) + D);
+            const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - ms);
+            o += f * __ldcg(pp + (int64_t)s * (D + 2) + d);
+            ls += f * __ldcg(pp + (int64_t)s * (D + 2) + D + 1);
+        }
+        store_final(a, item, h, d, o, ms, ls);
+    }
+    if (threadIdx.x == 0) a.counters[item * a.kv.Hkv + kvh] = 0u;  // ready for the next launch
+}
+
 // f32 view of the 8 elements lane j owns in a cache row slice held in shared
 // memory. Element ownership: f32 -> {4j..4j+3} and {D/2+4j..D/2+4j+3};
 // bf16 / q8 -> {8j..8j+7}.
@@ -285,81 +365,11 @@ __global__ void __launch_bounds__(kSimtWarps * 32) attn_simt_kernel(AttnArgs a) 
             }
         }
         __syncthreads();
-        const int gn = min(GH, G - g0);
-        for (int idx = tid; idx < gn * D; idx += blockDim.x) {
-            int g = idx / D, d = idx - g * D;
-            float ms = -INFINITY;
-            for (int w = 0; w < nw; ++w) ms = fmaxf(ms, wm[w * GH + g]);
-            float o = 0.0f, ls = 0.0f;
-            for (int w = 0; w < nw; ++w) {
-                float mw = wm[w * GH + g];
-                float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - ms);
-                o += f * wacc[(w * GH + g) * D + d];
-                ls += f * wl[w * GH + g];
-            }
-            const int h = kvh * G + g0 + g;
-            if (a.n_split == 1) {
-                float inv = ls > 0.0f ? 1.0f / ls : 0.0f;
-                if (a.partial_out) {
-                    float* po = a.partial_out + ((int64_t)item * Hq + h) * (D + 2);
-                    po[d] = o * inv;
-                    if (d == 0) {
-                        po[D] = ms;
-                        po[D + 1] = ls;
-                    }
-                } else {
-                    a.out[((int64_t)item * Hq + h) * D + d] = o * inv;
-                }
-            } else {
-                float* pp = a.part + (((int64_t)item * Hq + h) * a.n_split + split) * (D + 2);
-                pp[d] = o;
-                if (d == 0) {
-                    pp[D] = ms;
-                    pp[D + 1] = ls;
-                }
-            }
-        }
+        cta_merge_store(a, wacc, wm, wl, nw, GH, g0, min(GH, G - g0), item, kvh, split);
         __syncthreads();  // merge area is free again before the next head group refills the ring
     }
 
-    if (a.n_split == 1) return;
-
-    // last CTA of this (item, kv_head) merges the splits
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        unsigned prev = atomicAdd(&a.counters[item * a.kv.Hkv + kvh], 1u);
-        s_last = (prev == (unsigned)a.n_split - 1u);
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    for (int idx = tid; idx < G * D; idx += blockDim.x) {
-        int g = idx / D, d = idx - g * D;
-        const int h = kvh * G + g;
-        const float* pp = a.part + ((int64_t)item * Hq + h) * a.n_split * (D + 2);
-        float ms = -INFINITY;
-        for (int s = 0; s < a.n_split; ++s) ms = fmaxf(ms, __ldcg(pp + (int64_t)s * (D + 2) + D));
-        float o = 0.0f, ls = 0.0f;
-        for (int s = 0; s < a.n_split; ++s) {
-            float mw = __ldcg(pp + (int64_t)s * (D + 2) + D);
-            float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - ms);
-            o += f * __ldcg(pp + (int64_t)s * (D + 2) + d);
-            ls += f * __ldcg(pp + (int64_t)s * (D + 2) + D + 1);
-        }
-        float inv = ls > 0.0f ? 1.0f / ls : 0.0f;
-        if (a.partial_out) {
-            float* po = a.partial_out + ((int64_t)item * Hq + h) * (D + 2);
-            po[d] = o * inv;
-            if (d == 0) {
-                po[D] = ms;
-                po[D + 1] = ls;
-            }
-        } else {
-            a.out[((int64_t)item * Hq + h) * D + d] = o * inv;
-        }
-    }
-    if (tid == 0) a.counters[item * a.kv.Hkv + kvh] = 0u;  // ready for the next launch
+    split_merge_store(a, item, kvh, &s_last);
 }
 
 // Merges n_parts partial states [n_parts][items][Hq][D + 2] (o / l, m, l) into out.

@@ -48,6 +48,10 @@ struct ggr_attn_ctx {
     size_t stage_cap[4] = {0, 0, 0, 0};
     std::string err;
     int64_t launches = 0;
+    // optional per-kernel timing: event pairs per kind (0 attention, 1 rope/append, 2 merge)
+    bool timing = false;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> ev[3];
+    size_t ev_used[3] = {0, 0, 0};
 };
 
 namespace {
@@ -148,6 +152,27 @@ void visible_host(const ggr_attn_ctx* c, int layer, int pos, int* vs, int* ve) {
     *ve = e;
 }
 
+// Brackets one launch with events when kernel timing is on.
+struct LaunchTimer {
+    ggr_attn_ctx* c;
+    cudaEvent_t stop = nullptr;
+    LaunchTimer(ggr_attn_ctx* ctx, int kind) : c(ctx) {
+        if (!c->timing) return;
+        auto& pool = c->ev[kind];
+        if (c->ev_used[kind] == pool.size()) {
+            cudaEvent_t a = nullptr, b = nullptr;
+            if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) return;
+            pool.emplace_back(a, b);
+        }
+        auto& pr = pool[c->ev_used[kind]++];
+        cudaEventRecord(pr.first, c->stream);
+        stop = pr.second;
+    }
+    ~LaunchTimer() {
+        if (stop) cudaEventRecord(stop, c->stream);
+    }
+};
+
 int check_layer(ggr_attn_ctx* c, int layer) {
     if (layer < 0 || layer >= c->cfg.n_layers) return fail(c, GGR_ERR_RANGE, "layer outside the cache");
     return GGR_OK;
@@ -175,7 +200,10 @@ int launch_rope_append(ggr_attn_ctx* c, int layer, const Items& items, int flags
     if (smem > 48 * 1024) {
         CUDA_TRY(c, cudaFuncSetAttribute(rope_append_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     }
-    rope_append_kernel<<<items.n, 256, smem, c->stream>>>(a);
+    {
+        LaunchTimer t(c, 1);
+        rope_append_kernel<<<items.n, 256, smem, c->stream>>>(a);
+    }
     CUDA_TRY(c, cudaGetLastError());
     c->launches++;
     return GGR_OK;
@@ -221,11 +249,16 @@ template <int FMT, int GH, int NST>
 int launch_simt_inst(ggr_attn_ctx* c, const AttnArgs& a, dim3 grid, int nw, size_t smem) {
     static int configured_for = -1;  // device ordinal the attribute was set on
     if (configured_for != c->cfg.device) {
+        cudaFuncAttributes fa;
+        CUDA_TRY(c, cudaFuncGetAttributes(&fa, attn_simt_kernel<FMT, GH, NST>));
         CUDA_TRY(c, cudaFuncSetAttribute(attn_simt_kernel<FMT, GH, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         c->smem_optin));
+                                         c->smem_optin - (int)fa.sharedSizeBytes));
         configured_for = c->cfg.device;
     }
-    attn_simt_kernel<FMT, GH, NST><<<grid, nw * 32, smem, c->stream>>>(a);
+    {
+        LaunchTimer t(c, 0);
+        attn_simt_kernel<FMT, GH, NST><<<grid, nw * 32, smem, c->stream>>>(a);
+    }
     CUDA_TRY(c, cudaGetLastError());
     c->launches++;
     return GGR_OK;
@@ -314,7 +347,11 @@ int launch_attention(ggr_attn_ctx* c, int layer, const Items& items, int t_max, 
     }
     dim3 grid(n_split, c->kv.Hkv, items.n);
     if (mma) {
-        int rc = launch_mma_decode(a, grid, smem, c->smem_optin, c->cfg.device, c->stream);
+        int rc;
+        {
+            LaunchTimer t(c, 0);
+            rc = launch_mma_decode(a, grid, smem, c->smem_optin, c->cfg.device, c->stream);
+        }
         if (rc != 0) return fail(c, GGR_ERR_CUDA, std::string("mma decode launch: ") + cudaGetErrorString((cudaError_t)rc));
         c->launches++;
         return GGR_OK;
@@ -467,7 +504,10 @@ int prefill_common(ggr_attn_ctx* c, int layer, int seq, int base_pos, int m, con
         a.out = dout;
         a.score_scale = (c->cfg.scale_mode == GGR_SCALE_SCORE ? c->attn_scale : 1.0f) * kLog2e;
         std::string msg;
-        rc = launch_prefill_tc(a, c->sm_count, c->smem_optin, c->cfg.device, c->stream, &msg);
+        {
+            LaunchTimer t(c, 0);
+            rc = launch_prefill_tc(a, c->sm_count, c->smem_optin, c->cfg.device, c->stream, &msg);
+        }
         if (rc) return fail(c, rc, msg);
         c->launches++;
     } else {
@@ -662,6 +702,11 @@ void ggr_attn_destroy(ggr_attn_ctx* c) {
     cudaFree(c->d_part);
     cudaFree(c->d_counters);
     for (auto* p : c->d_stage) cudaFree(p);
+    for (auto& pool : c->ev)
+        for (auto& pr : pool) {
+            cudaEventDestroy(pr.first);
+            cudaEventDestroy(pr.second);
+        }
     if (c->own_stream) cudaStreamDestroy(c->own_stream);
     delete c;
 }
@@ -681,6 +726,43 @@ int ggr_attn_synchronize(ggr_attn_ctx* c) {
     if (!c) return GGR_ERR_INVALID;
     DeviceGuard guard(c->cfg.device);
     CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    return GGR_OK;
+}
+
+int ggr_attn_set_kernel_timing(ggr_attn_ctx* c, int32_t enable) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    c->timing = enable != 0;
+    for (auto& u : c->ev_used) u = 0;
+    return GGR_OK;
+}
+
+int ggr_attn_kernel_time(ggr_attn_ctx* c, int32_t kind, double* total_ms, int64_t* launches, int32_t reset) {
+    if (!c || kind < 0 || kind > 2 || !total_ms || !launches) return fail(c, GGR_ERR_INVALID, "invalid timing query");
+    DeviceGuard guard(c->cfg.device);
+    CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    double sum = 0.0;
+    for (size_t i = 0; i < c->ev_used[kind]; ++i) {
+        float ms = 0.f;
+        CUDA_TRY(c, cudaEventElapsedTime(&ms, c->ev[kind][i].first, c->ev[kind][i].second));
+        sum += ms;
+    }
+    *total_ms = sum;
+    *launches = (int64_t)c->ev_used[kind];
+    if (reset) c->ev_used[kind] = 0;
+    return GGR_OK;
+}
+
+int ggr_attn_kv_device_ptrs(ggr_attn_ctx* c, void** k, void** v, float** k_scale, float** v_scale,
+                            uint64_t* array_bytes) {
+    if (!c) return GGR_ERR_INVALID;
+    if (k) *k = c->kv.k;
+    if (v) *v = c->kv.v;
+    if (k_scale) *k_scale = c->kv.ks;
+    if (v_scale) *v_scale = c->kv.vs;
+    if (array_bytes)
+        *array_bytes = (uint64_t)c->cfg.max_batch * c->cfg.n_layers * c->shard_count * c->kv_dim * c->kv.elem_bytes;
     return GGR_OK;
 }
 
@@ -755,8 +837,11 @@ int ggr_attn_combine_partials(ggr_attn_ctx* c, const float* parts, int32_t n_par
         if ((rc = ensure(c, &c->d_stage[3], &c->stage_cap[3], out_bytes))) return rc;
         dout = reinterpret_cast<float*>(c->d_stage[3]);
     }
-    combine_partials_kernel<<<dim3(c->kv.Hq, B), 128, 0, c->stream>>>(reinterpret_cast<const float*>(dp), n_parts, B,
-                                                                      c->kv.Hq, c->D, dout);
+    {
+        LaunchTimer t(c, 2);
+        combine_partials_kernel<<<dim3(c->kv.Hq, B), 128, 0, c->stream>>>(reinterpret_cast<const float*>(dp), n_parts,
+                                                                          B, c->kv.Hq, c->D, dout);
+    }
     CUDA_TRY(c, cudaGetLastError());
     c->launches++;
     if (ptr_kind == GGR_PTR_HOST) {

@@ -108,7 +108,8 @@ const char* ggr_attn_create_error(void);
 int ggr_attn_abi_version(void);
 
 /* Work of device-pointer calls is enqueued on this CUDA stream (a
- * cudaStream_t); the default is a stream the context owns. */
+ * cudaStream_t); NULL selects the non-blocking stream the context owns (the
+ * default), cudaStreamLegacy the legacy default stream. */
 int ggr_attn_set_stream(ggr_attn_ctx* ctx, void* cuda_stream);
 int ggr_attn_synchronize(ggr_attn_ctx* ctx);
 
@@ -198,6 +199,23 @@ int ggr_attn_kv_read_row(ggr_attn_ctx* ctx, int32_t seq, int32_t layer, int32_t 
 
 /* Number of kernels this context has launched since it was created. */
 int64_t ggr_attn_launch_count(const ggr_attn_ctx* ctx);
+
+/* Per-kernel device timing (the counterpart of the reference's PROF_ATTN_NS
+ * counter, src/engine/profiling.rs:8-41): when enabled, every launch is
+ * bracketed by CUDA events on the context's stream. kind 0 = attention
+ * kernels, 1 = rope/append kernels, 2 = partial-state merges.
+ * ggr_attn_kernel_time synchronises the stream, returns the summed device
+ * time in milliseconds and the number of launches since the last reset, and
+ * resets the counters when `reset` is nonzero. */
+int ggr_attn_set_kernel_timing(ggr_attn_ctx* ctx, int32_t enable);
+int ggr_attn_kernel_time(ggr_attn_ctx* ctx, int32_t kind, double* total_ms, int64_t* launches, int32_t reset);
+
+/* Device addresses of the cache arrays (layout: [sequence][layer][position -
+ * shard_pos_begin][kv_dim] in the configured format; scales are null unless
+ * the format is q8) and the byte size of one of the K / V arrays. For hosts
+ * that keep K/V producers on the device, and for synthetic cache fills. */
+int ggr_attn_kv_device_ptrs(ggr_attn_ctx* ctx, void** k, void** v, float** k_scale, float** v_scale,
+                            uint64_t* array_bytes);
 
 /* Host-side planners restated from the reference, usable without a device. */
 typedef struct ggr_rope_plan ggr_rope_plan;
