@@ -48,6 +48,12 @@ struct ggr_attn_ctx {
     size_t stage_cap[4] = {0, 0, 0, 0};
     std::string err;
     int64_t launches = 0;
+    // tensor maps over the whole K and V arrays (bf16 caches) for the TMA prefill kernel
+    CUtensorMap tmK, tmV;
+    bool have_tmaps = false;
+    // error word the kernels raise when a bounded wait runs out (mapped pinned host memory)
+    int* h_err = nullptr;
+    int* d_err = nullptr;
     // optional per-kernel timing: event pairs per kind (0 attention, 1 rope/append, 2 merge)
     bool timing = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> ev[3];
@@ -471,7 +477,9 @@ int prefill_common(ggr_attn_ctx* c, int layer, int seq, int base_pos, int m, con
         dout = reinterpret_cast<float*>(c->d_stage[3]);
     }
 
-    const bool tc = prefill_tc_usable(c->cfg.prefill_impl, c->kv.fmt, c->D, c->G);
+    const bool tc = c->have_tmaps && prefill_tc_usable(c->cfg.prefill_impl, c->kv.fmt, c->D, c->G);
+    if (c->cfg.prefill_impl == GGR_IMPL_TCGEN05 && !tc)
+        return fail(c, GGR_ERR_UNSUPPORTED, "the tensor-core prefill kernel needs a bf16 cache and head_dim 64 or 128");
     if ((rc = ensure(c, &c->d_qrot, &c->qrot_cap, tc ? (size_t)1 : (size_t)m * c->q_dim))) return rc;
     if (tc && (rc = ensure(c, &c->d_qrot_h, &c->qrot_h_cap, (size_t)m * c->q_dim))) return rc;
 
@@ -503,10 +511,11 @@ int prefill_common(ggr_attn_ctx* c, int layer, int seq, int base_pos, int m, con
         a.q = c->d_qrot_h;
         a.out = dout;
         a.score_scale = (c->cfg.scale_mode == GGR_SCALE_SCORE ? c->attn_scale : 1.0f) * kLog2e;
+        a.err = c->d_err;
         std::string msg;
         {
             LaunchTimer t(c, 0);
-            rc = launch_prefill_tc(a, c->sm_count, c->smem_optin, c->cfg.device, c->stream, &msg);
+            rc = launch_prefill_tc(a, c->tmK, c->tmV, c->cfg.device, c->stream, &msg);
         }
         if (rc) return fail(c, rc, msg);
         c->launches++;
@@ -535,6 +544,10 @@ int prefill_common(ggr_attn_ctx* c, int layer, int seq, int base_pos, int m, con
     if (ptr_kind == GGR_PTR_HOST) {
         CUDA_TRY(c, cudaMemcpyAsync(out, dout, (size_t)m * c->q_dim * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
         CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+        if (c->h_err && *c->h_err) {
+            *c->h_err = 0;
+            return fail(c, GGR_ERR_TIMEOUT, "a bounded wait inside the prefill kernel ran out");
+        }
     }
     return GGR_OK;
 }
@@ -679,6 +692,16 @@ int ggr_attn_create(const ggr_attn_config* cfg, ggr_attn_ctx** out) {
         cudaMemsetAsync(kv.ks, 0, sb, c->stream);
         cudaMemsetAsync(kv.vs, 0, sb, c->stream);
     }
+    if (cudaHostAlloc((void**)&c->h_err, sizeof(int), cudaHostAllocMapped) != cudaSuccess ||
+        cudaHostGetDevicePointer((void**)&c->d_err, c->h_err, 0) != cudaSuccess) {
+        cudaGetLastError();
+        return cleanup(GGR_ERR_ALLOC, "unable to allocate the error word");
+    }
+    *c->h_err = 0;
+    if (prefill_tc_shape_ok(kv.fmt, c->D)) {
+        c->have_tmaps = make_tmap_bf16(&c->tmK, kv.k, (uint64_t)c->kv_dim, (uint64_t)rows) &&
+                        make_tmap_bf16(&c->tmV, kv.v, (uint64_t)c->kv_dim, (uint64_t)rows);
+    }
     if (cudaStreamSynchronize(c->stream) != cudaSuccess) return cleanup(GGR_ERR_CUDA, "device initialisation failed");
     g_create_err.clear();
     *out = c;
@@ -702,6 +725,7 @@ void ggr_attn_destroy(ggr_attn_ctx* c) {
     cudaFree(c->d_part);
     cudaFree(c->d_counters);
     for (auto* p : c->d_stage) cudaFree(p);
+    if (c->h_err) cudaFreeHost(c->h_err);
     for (auto& pool : c->ev)
         for (auto& pr : pool) {
             cudaEventDestroy(pr.first);
@@ -726,6 +750,10 @@ int ggr_attn_synchronize(ggr_attn_ctx* c) {
     if (!c) return GGR_ERR_INVALID;
     DeviceGuard guard(c->cfg.device);
     CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    if (c->h_err && *c->h_err) {
+        *c->h_err = 0;
+        return fail(c, GGR_ERR_TIMEOUT, "a bounded wait inside a kernel ran out");
+    }
     return GGR_OK;
 }
 

@@ -1,9 +1,549 @@
-// placeholder
+// Flash-style causal / windowed GQA prefill on the 5th-generation tensor cores.
+//
+// Device counterpart of the per-token prefill loop of the reference
+// (src/engine/runtime/inference.rs:2981-3017 calling attention_token :1970):
+// every query row sees exactly the key interval visible_keys gives it
+// (src/engine/runtime/attention.rs:73-97). RoPE and the cache append have
+// already been applied by rope_append_kernel; K and V tiles are read from the
+// bf16 cache rows themselves.
+//
+// One CTA owns two consecutive 128-row query tiles of one query head and walks
+// the visible 128-key tiles of the KV head:
+//   warp 8       TMA producer: Q tiles once, then K and V tiles into 2-stage rings
+//                (cp.async.bulk.tensor, 128-byte swizzle, mbarrier complete_tx)
+//   warp 9       MMA issuer: S_t = Q_t K^T and O_t += P_t V with tcgen05.mma,
+//                accumulators in TMEM (S0 S1 O0 O1 = 512 columns); P_t is read
+//                straight from TMEM where the softmax wrote it over S_t
+//   warps 0-3    softmax of query tile 0 (one thread per query row)
+//   warps 4-7    softmax of query tile 1
+// The two query tiles ping-pong: while one tile's softmax runs on the CUDA
+// cores, the tensor core works on the other tile. Online softmax with base-2
+// exponentials; O is rescaled in TMEM only when a row maximum grows by more
+// than 2^8 (the stale maximum stays exact because l uses the same reference).
+//
+// Every wait is bounded: when a limit runs out the CTA raises an abort flag,
+// all roles leave their loops, TMEM is freed and the host sees GGR_ERR_TIMEOUT.
 #pragma once
+
+#include <cuda.h>
+
 #include <string>
+
 #include "common.cuh"
+
 namespace ggr {
-struct PrefillTcArgs { KvView kv; Visibility vis; int layer, seq, base_pos, m; const __nv_bfloat16* q; float* out; float score_scale; };
-inline bool prefill_tc_usable(int, int, int, int) { return false; }
-inline int launch_prefill_tc(const PrefillTcArgs&, int, int, int, cudaStream_t, std::string* msg) { *msg = "not built"; return 5; }
+
+struct PrefillTcArgs {
+    KvView kv;
+    Visibility vis;
+    int layer, seq, base_pos, m;
+    const __nv_bfloat16* q;  // [m][Hq*D] rotated queries (bf16)
+    float* out;              // [m][Hq*D]
+    float score_scale;       // (1/sqrt(D) or 1) * log2(e)
+    int* err;                // device-visible error word (mapped host memory)
+};
+
+constexpr int kTcBM = 128;       // query rows per tile
+constexpr int kTcBN = 128;       // keys per tile
+constexpr int kTcThreads = 320;  // 8 softmax warps + producer + MMA issuer
+constexpr uint32_t kTcSpinLimit = 1u << 24;
+
+namespace tc {
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the limit ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t it = 0; it < kTcSpinLimit; ++it) {
+        if (mbar_test(bar, parity)) return true;
+        if ((it & 255u) == 255u) {
+            if (*abort_flag) return false;
+            __nanosleep(32);
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// D[tmem] (+)= A[smem desc] * B[smem desc]
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem desc]
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, tile base 1024-byte aligned.
+// lbo / sbo in bytes.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3ffffu) >> 4);
+    d |= (uint64_t)((lbo >> 4) & 0x3fffu) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3fffu) << 32;
+    d |= (uint64_t)1 << 46;  // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;  // 128-byte swizzle
+    return d;
+}
+
+// Instruction descriptor: bf16 x bf16 -> f32, M = 128.
+__host__ __device__ constexpr uint32_t idesc_bf16(int n, int b_mn_major) {
+    return (1u << 4)                      // accumulator f32
+           | (1u << 7)                    // A bf16
+           | (1u << 10)                   // B bf16
+           | ((uint32_t)b_mn_major << 16) // B major-ness (0 = K, 1 = MN)
+           | ((uint32_t)(n >> 3) << 17)   // N / 8
+           | ((uint32_t)(128 >> 4) << 24);  // M / 16
+}
+
+}  // namespace tc
+
+template <int D>
+__global__ void __launch_bounds__(kTcThreads, 1)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                  const __grid_constant__ CUtensorMap tmV, PrefillTcArgs a) {
+    using namespace tc;
+    constexpr int NBLK = D / 64;                    // 64-element (128-byte) column blocks of a tile
+    constexpr uint32_t BLK_BYTES = 128 * 128;       // one [128 rows][128 bytes] swizzled block
+    constexpr uint32_t TILE_BYTES = NBLK * BLK_BYTES;
+    constexpr uint32_t O_COL0 = 256;                // S0 at 0, S1 at 128, O tiles from 256
+
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t bars[16];
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sQ = smem_base;                       // [2][TILE_BYTES]
+    const uint32_t sK = sQ + 2 * TILE_BYTES;             // [2 stages][TILE_BYTES]
+    const uint32_t sV = sK + 2 * TILE_BYTES;             // [2 stages][TILE_BYTES]
+
+    const uint32_t bar0 = smem_u32(bars);
+    const uint32_t q_full = bar0;
+    auto k_full = [&](int s) { return bar0 + 8u * (1 + s); };
+    auto k_empty = [&](int s) { return bar0 + 8u * (3 + s); };
+    auto v_full = [&](int s) { return bar0 + 8u * (5 + s); };
+    auto v_empty = [&](int s) { return bar0 + 8u * (7 + s); };
+    auto s_full = [&](int t) { return bar0 + 8u * (9 + t); };
+    auto p_full = [&](int t) { return bar0 + 8u * (11 + t); };
+    auto o_final = [&](int t) { return bar0 + 8u * (13 + t); };
+
+    // which query rows and head
+    const int Hq = a.kv.Hq, G = a.kv.G;
+    const int n_pairs = (a.m + 2 * kTcBM - 1) / (2 * kTcBM);
+    const int pair = n_pairs - 1 - (int)(blockIdx.x / Hq);  // long (late) tiles first
+    const int h = blockIdx.x % Hq;
+    const int kvh = h / G;
+    const int q_row0 = pair * 2 * kTcBM;
+
+    // visible key tiles of each query tile (ranges are monotone in the query position)
+    int lo_t[2], hi_t[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        const int r0 = q_row0 + t * kTcBM;
+        if (r0 >= a.m) {
+            lo_t[t] = hi_t[t] = 0;
+            continue;
+        }
+        const int r1 = min(a.m, r0 + kTcBM) - 1;
+        int vs0, ve0, vs1, ve1;
+        a.vis.range(a.base_pos + r0, vs0, ve0);
+        a.vis.range(a.base_pos + r1, vs1, ve1);
+        lo_t[t] = min(vs0, vs1) / kTcBN;
+        hi_t[t] = (max(ve0, ve1) + kTcBN - 1) / kTcBN;
+    }
+    const bool act0 = hi_t[0] > lo_t[0], act1 = hi_t[1] > lo_t[1];
+    int lo = act0 ? lo_t[0] : lo_t[1], hi = act0 ? hi_t[0] : hi_t[1];
+    if (act0 && act1) {
+        lo = min(lo_t[0], lo_t[1]);
+        hi = max(hi_t[0], hi_t[1]);
+    }
+    auto active = [&](int t, int j) { return j >= lo_t[t] && j < hi_t[t]; };
+
+    if (tid == 0) {
+        s_abort = 0;
+        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(k_full(s), 1);
+            mbar_init(k_empty(s), 1);
+            mbar_init(v_full(s), 1);
+            mbar_init(v_empty(s), 1);
+            mbar_init(s_full(s), 1);
+            mbar_init(p_full(s), kTcBM);
+            mbar_init(o_final(s), 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 9) {
+        tmem_alloc(smem_u32(&s_tmem_base), 512);
+        tmem_relinquish();
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem = s_tmem_base;
+    volatile int* abortp = &s_abort;
+    const int64_t row_base = a.kv.row(a.seq, a.layer, 0);
+
+    if (warp == 8) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            const int nq = (act0 ? 1 : 0) + (act1 ? 1 : 0);
+            mbar_expect_tx(q_full, nq * TILE_BYTES);
+            for (int t = 0; t < 2; ++t) {
+                if (!(t == 0 ? act0 : act1)) continue;
+                for (int b = 0; b < NBLK; ++b)
+                    tma_load_2d(sQ + t * TILE_BYTES + b * BLK_BYTES, &tmQ, h * D + b * 64, q_row0 + t * kTcBM, q_full);
+            }
+            for (int j = lo; j < hi; ++j) {
+                const int n = j - lo, s = n & 1;
+                const uint32_t ph = ((n >> 1) & 1) ^ 1;
+                const int y = (int)(row_base + (int64_t)j * kTcBN);
+                if (!mbar_wait(k_empty(s), ph, abortp)) break;
+                mbar_expect_tx(k_full(s), TILE_BYTES);
+                for (int b = 0; b < NBLK; ++b)
+                    tma_load_2d(sK + s * TILE_BYTES + b * BLK_BYTES, &tmK, kvh * D + b * 64, y, k_full(s));
+                if (!mbar_wait(v_empty(s), ph, abortp)) break;
+                mbar_expect_tx(v_full(s), TILE_BYTES);
+                for (int b = 0; b < NBLK; ++b)
+                    tma_load_2d(sV + s * TILE_BYTES + b * BLK_BYTES, &tmV, kvh * D + b * 64, y, v_full(s));
+            }
+        }
+    } else if (warp == 9) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0 && hi > lo) {
+            constexpr uint32_t IDESC_QK = idesc_bf16(kTcBN, 0);
+            constexpr uint32_t IDESC_PV = idesc_bf16(D, 1);
+            auto issue_qk = [&](int t, int s) {
+                // S_t = Q_t K^T: both operands K-major, 16 head elements per instruction
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint32_t off = (ks >> 2) * BLK_BYTES + (ks & 3) * 32;
+                    mma_ss(tmem + t * 128, smem_desc(sQ + t * TILE_BYTES + off, 16, 1024),
+                           smem_desc(sK + s * TILE_BYTES + off, 16, 1024), IDESC_QK, ks > 0 ? 1u : 0u);
+                }
+            };
+            auto issue_pv = [&](int t, int s, bool accumulate) {
+                // O_t += P_t V: P from TMEM (two bf16 per column), V MN-major, 16 keys per instruction
+#pragma unroll
+                for (int ks = 0; ks < kTcBN / 16; ++ks) {
+                    mma_ts(tmem + O_COL0 + t * D, tmem + t * 128 + ks * 8,
+                           smem_desc(sV + s * TILE_BYTES + ks * 16 * 128, BLK_BYTES, 1024), IDESC_PV,
+                           (accumulate || ks > 0) ? 1u : 0u);
+                }
+            };
+            bool ok = mbar_wait(q_full, 0, abortp);
+            if (ok) ok = mbar_wait(k_full(0), 0, abortp);
+            if (ok) {
+                fence_after_sync();
+                for (int t = 0; t < 2; ++t)
+                    if (active(t, lo)) {
+                        issue_qk(t, 0);
+                        mma_commit(s_full(t));
+                    }
+                mma_commit(k_empty(0));
+            }
+            for (int j = lo; ok && j < hi; ++j) {
+                const int n = j - lo, s = n & 1;
+                const bool has_next = j + 1 < hi;
+                if (!(ok = mbar_wait(v_full(s), (n >> 1) & 1, abortp))) break;
+                bool next_k_ready = false;
+                for (int t = 0; t < 2 && ok; ++t) {
+                    if (active(t, j)) {
+                        if (!(ok = mbar_wait(p_full(t), (j - lo_t[t]) & 1, abortp))) break;
+                        fence_after_sync();
+                        issue_pv(t, s, j > lo_t[t]);
+                        if (j == hi_t[t] - 1) mma_commit(o_final(t));
+                    }
+                    if (has_next && active(t, j + 1)) {
+                        if (!next_k_ready) {
+                            if (!(ok = mbar_wait(k_full(s ^ 1), ((n + 1) >> 1) & 1, abortp))) break;
+                            fence_after_sync();
+                            next_k_ready = true;
+                        }
+                        issue_qk(t, s ^ 1);
+                        mma_commit(s_full(t));
+                    }
+                }
+                if (!ok) break;
+                mma_commit(v_empty(s));
+                if (has_next) mma_commit(k_empty(s ^ 1));
+            }
+        }
+    } else {
+        // ---------------- softmax warps: one thread per query row ----------------
+        const int t = warp >> 2;
+        const int row = (warp & 3) * 32 + lane;
+        const int qi = q_row0 + t * kTcBM + row;
+        const bool valid = qi < a.m;
+        int vs = 0, ve = 0;
+        if (valid) a.vis.range(a.base_pos + qi, vs, ve);
+        const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+        const uint32_t tS = tmem + lane_addr + t * 128;
+        const uint32_t tO = tmem + lane_addr + O_COL0 + t * D;
+        const float c = a.score_scale;
+        const float thr = 8.0f / c;
+        float m_used = -INFINITY, l = 0.0f;
+        bool ok = true;
+        const int n_t = hi_t[t] - lo_t[t];
+        for (int j = lo_t[t]; j < hi_t[t]; ++j) {
+            const int k = j - lo_t[t];
+            if (!(ok = mbar_wait(s_full(t), k & 1, abortp))) break;
+            fence_after_sync();
+            uint32_t sr[4][32];
+#pragma unroll
+            for (int cidx = 0; cidx < 4; ++cidx) tmem_ld32(tS + cidx * 32, sr[cidx]);
+            tmem_wait_ld();
+            const int key0 = j * kTcBN;
+            if (key0 < vs || key0 + kTcBN > ve) {
+#pragma unroll
+                for (int cidx = 0; cidx < 4; ++cidx)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int key = key0 + cidx * 32 + i;
+                        if (key < vs || key >= ve) sr[cidx][i] = 0xff800000u;  // -inf
+                    }
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int cidx = 0; cidx < 4; ++cidx)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sr[cidx][i]));
+            // lazy rescale of the running output
+            const bool need = mx > m_used + thr;
+            float alpha = 1.0f;
+            if (need) {
+                alpha = exp2f((m_used - mx) * c);  // 0 when nothing was accumulated yet
+                m_used = mx;
+            }
+            if (k > 0 && __any_sync(0xffffffffu, need)) {
+#pragma unroll
+                for (int cidx = 0; cidx < D / 32; ++cidx) {
+                    uint32_t orow[32];
+                    tmem_ld32(tO + cidx * 32, orow);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
+                    tmem_st32(tO + cidx * 32, orow);
+                }
+            }
+            l *= alpha;
+            const float mref = (m_used == -INFINITY) ? 0.0f : m_used;
+            const float neg = -mref * c;
+            float psum = 0.0f;
+#pragma unroll
+            for (int cidx = 0; cidx < 4; ++cidx) {
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float p0 = exp2f(fmaf(__uint_as_float(sr[cidx][2 * i]), c, neg));
+                    const float p1 = exp2f(fmaf(__uint_as_float(sr[cidx][2 * i + 1]), c, neg));
+                    psum += p0 + p1;
+                    __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+                    pk[i] = *reinterpret_cast<uint32_t*>(&pb);
+                }
+                tmem_st16(tS + cidx * 16, pk);
+            }
+            l += psum;
+            tmem_wait_st();
+            fence_before_sync();
+            mbar_arrive(p_full(t));
+        }
+        if (ok && n_t > 0) ok = mbar_wait(o_final(t), 0, abortp);
+        if (ok && n_t > 0) {
+            fence_after_sync();
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            float* orow_g = a.out + ((int64_t)qi * Hq + h) * D;
+#pragma unroll
+            for (int cidx = 0; cidx < D / 32; ++cidx) {
+                uint32_t orow[32];
+                tmem_ld32(tO + cidx * 32, orow);
+                tmem_wait_ld();
+                if (valid) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        float4 o4 = make_float4(__uint_as_float(orow[i]) * inv, __uint_as_float(orow[i + 1]) * inv,
+                                                __uint_as_float(orow[i + 2]) * inv, __uint_as_float(orow[i + 3]) * inv);
+                        *reinterpret_cast<float4*>(orow_g + cidx * 32 + i) = o4;
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------- common tail ----------------
+    if (s_abort) {
+        // let copies that are still in flight land before shared memory is released
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    if (warp == 9) tmem_dealloc(tmem, 512);
+    if (tid == 0 && s_abort && a.err) atomicExch(a.err, 1);
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+
+typedef CUresult (*PFN_tmapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                        const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                        CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline PFN_tmapEncodeTiled tmap_encoder() {
+    static PFN_tmapEncodeTiled fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess &&
+            qr == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_tmapEncodeTiled>(p);
+    }
+    return fn;
+}
+
+// 2-D bf16 row-major tensor [rows][cols], box = 64 columns x 128 rows, 128-byte swizzle
+inline bool make_tmap_bf16(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows) {
+    PFN_tmapEncodeTiled enc = tmap_encoder();
+    if (!enc) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * 2};
+    cuuint32_t box[2] = {64, 128};
+    cuuint32_t estr[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+inline bool prefill_tc_shape_ok(int fmt, int D) { return fmt == KV_BF16 && (D == 64 || D == 128); }
+
+inline bool prefill_tc_usable(int impl, int fmt, int D, int /*G*/) {
+    if (impl == 1 /* GGR_IMPL_SIMT */) return false;
+    return prefill_tc_shape_ok(fmt, D);
+}
+
+inline size_t prefill_tc_smem(int D) { return (size_t)6 * (D / 64) * 128 * 128 + 1024; }
+
+template <int D>
+inline int launch_prefill_tc_inst(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                                  const PrefillTcArgs& a, int device, cudaStream_t stream, std::string* msg) {
+    static int configured_for = -1;
+    const size_t smem = prefill_tc_smem(D);
+    if (configured_for != device) {
+        cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            *msg = std::string("prefill kernel attribute: ") + cudaGetErrorString(e);
+            return 2;
+        }
+        configured_for = device;
+    }
+    const int n_pairs = (a.m + 2 * kTcBM - 1) / (2 * kTcBM);
+    prefill_tc_kernel<D><<<n_pairs * a.kv.Hq, kTcThreads, smem, stream>>>(tq, tk, tv, a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        *msg = std::string("prefill kernel launch: ") + cudaGetErrorString(e);
+        return 2;
+    }
+    return 0;
+}
+
+// tk / tv describe the whole K and V cache arrays as [rows][kv_dim].
+inline int launch_prefill_tc(const PrefillTcArgs& a, const CUtensorMap& tk, const CUtensorMap& tv, int device,
+                             cudaStream_t stream, std::string* msg) {
+    CUtensorMap tq;
+    if (!make_tmap_bf16(&tq, a.q, (uint64_t)a.kv.Hq * a.kv.D, (uint64_t)a.m)) {
+        *msg = "cuTensorMapEncodeTiled failed for the query tensor";
+        return 2;
+    }
+    switch (a.kv.D) {
+        case 64: return launch_prefill_tc_inst<64>(tq, tk, tv, a, device, stream, msg);
+        case 128: return launch_prefill_tc_inst<128>(tq, tk, tv, a, device, stream, msg);
+        default: *msg = "no tensor-core prefill kernel for this head_dim"; return 5;
+    }
+}
+
+}  // namespace ggr
