@@ -298,6 +298,27 @@ int launch_simt(ggr_attn_ctx* c, const AttnArgs& a, dim3 grid, const SimtPlan& p
     }
 }
 
+// Split-KV factor: the grid is base_ctas * n CTAs running `slots` at a time, each CTA walking
+// ceil(T / n) keys. Picks the n with the fewest key-steps on the critical path (waves * keys per
+// CTA, plus a fixed per-CTA cost), so the last wave is not left almost empty.
+int choose_splits(int64_t base_ctas, int64_t slots, int t_max, int min_keys, int max_splits) {
+    int limit = std::max(1, t_max / std::max(1, min_keys));
+    limit = std::min(limit, 512);
+    if (max_splits > 0) limit = std::min(limit, max_splits);
+    const int overhead = 96;  // keys' worth of prologue / merge work per CTA
+    int best = 1;
+    int64_t best_cost = -1;
+    for (int n = 1; n <= limit; ++n) {
+        const int64_t waves = (base_ctas * n + slots - 1) / slots;
+        const int64_t cost = waves * ((t_max + n - 1) / n + overhead);
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            best = n;
+        }
+    }
+    return best;
+}
+
 bool use_mma_decode(const ggr_attn_ctx* c) {
     const bool can = c->kv.fmt == KV_BF16 && mma_decode_supported(c->D, c->G);
     if (c->cfg.decode_impl == GGR_IMPL_MMA) return can;
@@ -332,13 +353,8 @@ int launch_attention(ggr_attn_ctx* c, int layer, const Items& items, int t_max, 
     }
     a.stage_bytes = p.stage_bytes;
 
-    const int64_t base_ctas = (int64_t)c->kv.Hkv * items.n;
-    const int64_t target = (int64_t)c->sm_count * ctas_per_sm;
-    int n_split = (int)std::max<int64_t>(1, (target + base_ctas - 1) / base_ctas);
-    n_split = std::min(n_split, std::max(1, t_max / min_keys));
-    if (base_ctas >= target) n_split = 1;
-    if (c->cfg.max_splits > 0) n_split = std::min(n_split, c->cfg.max_splits);
-    n_split = std::min(n_split, 512);
+    int n_split = choose_splits((int64_t)c->kv.Hkv * items.n, (int64_t)c->sm_count * ctas_per_sm, t_max, min_keys,
+                                c->cfg.max_splits);
     a.n_split = n_split;
     if (n_split > 1) {
         int rc = ensure(c, &c->d_part, &c->part_cap, (size_t)items.n * c->kv.Hq * n_split * (c->D + 2));
