@@ -69,6 +69,7 @@ EXPORTED_SYMBOLS = [
     "ggr_attn_decode_partial", "ggr_attn_combine_partials",
     "ggr_attn_kv_export", "ggr_attn_kv_import", "ggr_attn_kv_read_row", "ggr_attn_launch_count",
     "ggr_attn_set_kernel_timing", "ggr_attn_kernel_time", "ggr_attn_kv_device_ptrs",
+    "ggr_attn_attention_tokens_static",
     "ggr_rope_plan_new", "ggr_rope_plan_free", "ggr_rope_plan_append_text", "ggr_rope_plan_append_grid",
     "ggr_rope_plan_len", "ggr_rope_plan_next_text", "ggr_rope_plan_at", "ggr_rope_plan_export",
     "ggr_rope_axis", "ggr_media_plan_validate", "ggr_media_chunk_end", "ggr_gemma_layer_windows",
@@ -117,6 +118,7 @@ def lib() -> C.CDLL:
     L.ggr_attn_kv_read_row.argtypes = [vp, i32, i32, i32, vp, vp]
     L.ggr_attn_launch_count.argtypes = [vp]
     L.ggr_attn_launch_count.restype = i64
+    L.ggr_attn_attention_tokens_static.argtypes = [vp, i32, vp, i32, vp, vp]
     L.ggr_attn_set_kernel_timing.argtypes = [vp, i32]
     L.ggr_attn_kernel_time.argtypes = [vp, i32, C.POINTER(C.c_double), C.POINTER(i64), i32]
     L.ggr_attn_kv_device_ptrs.argtypes = [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp),
@@ -393,6 +395,20 @@ class AttnContext:
         self._follow_torch_stream(q)
         (qp, kind), (op, _) = _ptr(q), _ptr(out)
         self._check(self._L.ggr_attn_attention_token(self._h, seq, layer, pos, qp, op, kind))
+        return out
+
+    def attention_tokens_static(self, layer: int, pos, q, out=None):
+        """Attention of B already rotated query rows (torch CUDA tensors) using the library's
+        built-in scratch array: nothing is allocated by the call (see include/ggr_attn.h)."""
+        pos = np.ascontiguousarray(np.asarray(pos, dtype=np.int32).reshape(-1))
+        if not (_is_torch(q) and q.is_cuda):
+            raise ValueError("attention_tokens_static takes device memory only")
+        if out is None:
+            out = self._out_like(q, (pos.shape[0], self.config.q_dim))
+        self._follow_torch_stream(q)
+        (qp, _), (op, _) = _ptr(q), _ptr(out)
+        self._check(self._L.ggr_attn_attention_tokens_static(self._h, layer, C.c_void_p(pos.ctypes.data),
+                                                              pos.shape[0], qp, op))
         return out
 
     # ---- cache access ------------------------------------------------------------------

@@ -8,6 +8,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -1080,3 +1081,118 @@ int ggr_attn_kv_read_row(ggr_attn_ctx* c, int32_t seq, int32_t layer, int32_t po
 }
 
 }  // extern "C"
+
+// ---- allocation-free attention over the cache ----------------------------------------------------
+//
+// ggr_attn_attention_tokens_static is for hosts that must not allocate device memory while they
+// decode: an engine that handed every byte of HBM to its KV caches and weights at start-up (so a
+// cudaMalloc in the token loop could fail), or one that runs its decode step where an allocation's
+// implicit device-wide synchronisation is not acceptable. The split-KV kernels need scratch (the
+// per-split partial states and one ticket per (sequence, kv head)); here that scratch is a fixed
+// array inside the library image instead of memory grown with cudaMalloc.
+
+#define GGR_STATIC_SCRATCH_BYTES (8u << 20)
+#define GGR_STATIC_TICKET_BYTES (64u << 10)
+#define GGR_STATIC_MAX_DEVICES 64
+
+static __device__ __align__(256) unsigned char g_static_scratch[GGR_STATIC_SCRATCH_BYTES];
+
+namespace {
+
+std::mutex g_static_mu;
+unsigned char* g_static_ptr[GGR_STATIC_MAX_DEVICES] = {};
+
+// Device address of g_static_scratch on the context's device. In host code the array's name is
+// only a handle, so the address comes from cudaGetSymbolAddress, asked once per device with that
+// device current (the caller holds a DeviceGuard).
+int static_scratch(ggr_attn_ctx* c, unsigned char** out) {
+    const int dev = c->cfg.device;
+    if (dev < 0 || dev >= GGR_STATIC_MAX_DEVICES) return fail(c, GGR_ERR_UNSUPPORTED, "device ordinal above 63");
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_ptr[dev]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || !p)
+            return fail(c, GGR_ERR_CUDA, std::string("cudaGetSymbolAddress(static scratch): ") + cudaGetErrorString(e));
+        g_static_ptr[dev] = static_cast<unsigned char*>(p);
+    }
+    *out = g_static_ptr[dev];
+    return GGR_OK;
+}
+
+}  // namespace
+
+extern "C" int ggr_attn_attention_tokens_static(ggr_attn_ctx* c, int32_t layer, const int32_t* pos, int32_t B,
+                                                const float* q_dev, float* out_dev) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    int rc = check_layer(c, layer);
+    if (rc) return rc;
+    if (!pos || !q_dev || !out_dev) return fail(c, GGR_ERR_INVALID, "null buffer");
+    if (c->cfg.shard_mode != GGR_SHARD_NONE) return fail(c, GGR_ERR_UNSUPPORTED, "not available on a KV-sequence shard");
+    if (B <= 0 || B > c->cfg.max_batch) return fail(c, GGR_ERR_RANGE, "batch larger than max_batch");
+    if (B > kMaxArgItems) return fail(c, GGR_ERR_RANGE, "the allocation-free entry point takes at most 128 sequences per call");
+    for (int b = 0; b < B; ++b)
+        if (pos[b] < 0 || pos[b] >= c->cfg.seq_len) return fail(c, GGR_ERR_RANGE, "position outside the cache");
+    const size_t part_cap = (GGR_STATIC_SCRATCH_BYTES - GGR_STATIC_TICKET_BYTES) / sizeof(float);
+    const size_t per_split = (size_t)B * c->kv.Hq * (c->D + 2);
+    const size_t tickets = (size_t)B * c->kv.Hkv;
+    if (2 * per_split > part_cap || tickets * sizeof(unsigned) > GGR_STATIC_TICKET_BYTES) {
+        char buf[200];
+        snprintf(buf, sizeof buf,
+                 "static scratch too small: B*n_heads*(head_dim+2) = %zu floats per split, the 8 MiB array holds two "
+                 "splits only up to %zu", per_split, part_cap / 2);
+        return fail(c, GGR_ERR_RANGE, buf);
+    }
+    unsigned char* scratch = nullptr;
+    if ((rc = static_scratch(c, &scratch))) return rc;
+
+    Items it{};
+    it.mode = 0;
+    it.seq0 = 0;
+    it.n = B;
+    for (int i = 0; i < B; ++i) it.pos[i] = pos[i];
+    AttnArgs a{};
+    a.kv = c->kv;
+    a.items = it;
+    a.vis = visibility(c, layer);
+    a.layer = layer;
+    a.q = q_dev;
+    a.score_scale = (c->cfg.scale_mode == GGR_SCALE_SCORE ? c->attn_scale : 1.0f) * kLog2e;
+    a.out = out_dev;
+    a.partial_out = nullptr;
+    a.shard_count = c->shard_count;
+    const bool mma = use_mma_decode(c);
+    SimtPlan p = simt_plan(c);
+    size_t smem = p.smem;
+    int ctas_per_sm = p.ctas_per_sm, min_keys = p.nw * kSimtTK * 2;
+    if (mma) {
+        MmaPlan mp = mma_plan(c->D, c->smem_optin);
+        smem = mp.smem;
+        ctas_per_sm = mp.ctas_per_sm;
+        min_keys = mp.min_keys;
+    }
+    a.stage_bytes = p.stage_bytes;
+    const int t_max = t_max_of(c, layer, pos, B);
+    int fit = (int)std::min<size_t>(512, part_cap / per_split);  // splits the array can hold
+    if (c->cfg.max_splits > 0) fit = std::min(fit, c->cfg.max_splits);
+    a.n_split = choose_splits((int64_t)c->kv.Hkv * B, (int64_t)c->sm_count * ctas_per_sm, t_max, min_keys, fit);
+    if (a.n_split > 1) {
+        a.counters = reinterpret_cast<unsigned*>(scratch);
+        a.part = reinterpret_cast<float*>(scratch + GGR_STATIC_TICKET_BYTES);
+        // the array keeps whatever the previous call (of any context) left: tickets must start at zero
+        CUDA_TRY(c, cudaMemsetAsync(a.counters, 0, tickets * sizeof(unsigned), c->stream));
+    }
+    dim3 grid(a.n_split, c->kv.Hkv, B);
+    if (mma) {
+        int e;
+        {
+            LaunchTimer t(c, 0);
+            e = launch_mma_decode(a, grid, smem, c->smem_optin, c->cfg.device, c->stream);
+        }
+        if (e != 0) return fail(c, GGR_ERR_CUDA, std::string("mma decode launch: ") + cudaGetErrorString((cudaError_t)e));
+        c->launches++;
+        return GGR_OK;
+    }
+    return launch_simt(c, a, grid, p);
+}

@@ -197,6 +197,35 @@ int ggr_attn_kv_import(ggr_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t ro
 /* Dequantised f32 view of one cache row (any format), for tests. Host buffers. */
 int ggr_attn_kv_read_row(ggr_attn_ctx* ctx, int32_t seq, int32_t layer, int32_t pos, float* k_out, float* v_out);
 
+/*
+ * Allocation-free variant of ggr_attn_attention_token for B sequences (no
+ * counterpart in the reference, whose attention needs no scratch beyond
+ * RunState::att). It is meant for hosts that cannot allocate device memory in
+ * their decode loop: an engine that gave all of HBM to its caches and weights
+ * at start-up, so a later cudaMalloc may fail, or one whose token loop must
+ * not hit the device-wide synchronisation an allocation implies. The split-KV
+ * scratch (partial softmax states and tickets) lives in a fixed 8 MiB array
+ * inside the library image; every GPU that loads the library carries that
+ * array until the process exits.
+ *
+ * q_dev is [B][n_heads*head_dim] f32, already rotated (and pre-scaled in
+ * GGR_SCALE_Q_PRESCALED mode); out_dev is [B][n_heads*head_dim] f32; both are
+ * device memory. Sequence b attends from position pos[b] (host array). The
+ * work is enqueued on the context's stream.
+ *
+ * Limits: B <= 128, and two splits' worth of state, 2*B*n_heads*(head_dim+2)
+ * floats, must fit in the array (about 1M floats per split); larger calls
+ * return GGR_ERR_RANGE. The split count is lowered to what the array holds.
+ * The first call on a device looks up the array's device address; make that
+ * call before any stream capture. Calls made after that allocate nothing.
+ * All contexts and calls on a device share the one array: it still holds the
+ * previous call's data (the tickets are cleared at the start of each call),
+ * so two such calls whose kernels overlap on the GPU race with each other;
+ * issue them on one stream or order them with events.
+ */
+int ggr_attn_attention_tokens_static(ggr_attn_ctx* ctx, int32_t layer, const int32_t* pos, int32_t B,
+                                     const float* q_dev, float* out_dev);
+
 /* Number of kernels this context has launched since it was created. */
 int64_t ggr_attn_launch_count(const ggr_attn_ctx* ctx);
 
