@@ -416,6 +416,43 @@ def bench_decode_seq_split(torch, dist, args, rank, world, local_rank, peaks):
     return res
 
 
+def run_small_case(args):
+    """Small single-GPU cases for profiler captures (`ncu ... python bench.py --case NAME`): a few launches of
+    one kernel on inputs above the L2 size but at most ~1 GB on the device. Prints no benchmark line."""
+    import torch
+    import gguf_runner_b200 as g
+    from gguf_runner_b200 import presets
+    torch.cuda.set_device(0)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1)
+    if args.case == "prefill_small":
+        # one Llama-3-8B-shaped layer pair: S=4096, 32 q / 8 kv heads, bf16 (0.5 GB on the device)
+        cfg = presets.llama3_8b_prefill(n_layers=2, seq_len=S_PREFILL)
+        ctx = g.AttnContext(cfg)
+        q = torch.randn(S_PREFILL, cfg.q_dim, generator=gen, device="cuda").to(torch.bfloat16)
+        k = torch.randn(S_PREFILL, cfg.kv_dim, generator=gen, device="cuda").to(torch.bfloat16)
+        v = torch.randn(S_PREFILL, cfg.kv_dim, generator=gen, device="cuda").to(torch.bfloat16)
+        for _ in range(3):
+            for l in range(2):
+                out = ctx.prefill(l, 0, q, k, v)
+    elif args.case == "decode_small":
+        # two Qwen3-30B-A3B-shaped layers: T=32768, B=8, bf16 cache (1 GB on the device)
+        B, T = 8, 32768
+        cfg = presets.qwen3_30b_a3b_decode(n_layers=2, seq_len=T, max_batch=B)
+        ctx = g.AttnContext(cfg)
+        fill_cache_random(torch, ctx, 3)
+        q = torch.randn(B, cfg.q_dim, generator=gen, device="cuda")
+        k = torch.randn(B, cfg.kv_dim, generator=gen, device="cuda")
+        v = torch.randn(B, cfg.kv_dim, generator=gen, device="cuda")
+        for _ in range(3):
+            for l in range(2):
+                out = ctx.decode(l, [T - 1] * B, q, k, v)
+    else:
+        raise SystemExit(f"unknown case {args.case}")
+    torch.cuda.synchronize()
+    print("case", args.case, "done, mean |out| =", float(out.abs().mean()))
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -471,9 +508,13 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--decode-batch", type=int, default=8)
     ap.add_argument("--cpu-stride", type=int, default=16)
+    ap.add_argument("--case", default=None, help="run a small profiling case (prefill_small, decode_small) and exit")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
+    if args.case:
+        run_small_case(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

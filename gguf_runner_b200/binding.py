@@ -69,7 +69,7 @@ EXPORTED_SYMBOLS = [
     "ggr_attn_decode_partial", "ggr_attn_combine_partials",
     "ggr_attn_kv_export", "ggr_attn_kv_import", "ggr_attn_kv_read_row", "ggr_attn_launch_count",
     "ggr_attn_set_kernel_timing", "ggr_attn_kernel_time", "ggr_attn_kv_device_ptrs",
-    "ggr_attn_attention_tokens_static",
+    "ggr_attn_attention_tokens_static", "ggr_attn_last_split_count",
     "ggr_rope_plan_new", "ggr_rope_plan_free", "ggr_rope_plan_append_text", "ggr_rope_plan_append_grid",
     "ggr_rope_plan_len", "ggr_rope_plan_next_text", "ggr_rope_plan_at", "ggr_rope_plan_export",
     "ggr_rope_axis", "ggr_media_plan_validate", "ggr_media_chunk_end", "ggr_gemma_layer_windows",
@@ -118,6 +118,7 @@ def lib() -> C.CDLL:
     L.ggr_attn_kv_read_row.argtypes = [vp, i32, i32, i32, vp, vp]
     L.ggr_attn_launch_count.argtypes = [vp]
     L.ggr_attn_launch_count.restype = i64
+    L.ggr_attn_last_split_count.argtypes = [vp]
     L.ggr_attn_attention_tokens_static.argtypes = [vp, i32, vp, i32, vp, vp]
     L.ggr_attn_set_kernel_timing.argtypes = [vp, i32]
     L.ggr_attn_kernel_time.argtypes = [vp, i32, C.POINTER(C.c_double), C.POINTER(i64), i32]
@@ -303,6 +304,10 @@ class AttnContext:
     @property
     def launch_count(self) -> int:
         return int(self._L.ggr_attn_launch_count(self._h))
+
+    @property
+    def last_split_count(self) -> int:
+        return int(self._L.ggr_attn_last_split_count(self._h))
 
     def set_kernel_timing(self, enable: bool):
         self._check(self._L.ggr_attn_set_kernel_timing(self._h, 1 if enable else 0))

@@ -34,6 +34,7 @@ struct AttnArgs {
     float* partial_out;   // [items][Hq][D + 2] (o / l, m, l) for cross-rank merging, or null
     int shard_count;      // positions held locally
     int stage_bytes;      // bytes of one ring stage of one warp
+    int* err;             // raised when a bounded wait runs out (kernels that wait on mbarriers)
 };
 
 // Writes one head's merged state: the final output row, a (o / l, m, l)
@@ -85,33 +86,59 @@ __device__ __forceinline__ void cta_merge_store(const AttnArgs& a, const float* 
 }
 
 // The last CTA of a (token, kv head) to arrive (atomic ticket) merges the
-// per-split states from the scratch buffer and resets the ticket.
-__device__ __forceinline__ void split_merge_store(const AttnArgs& a, int item, int kvh, int* s_last) {
+// per-split states from the scratch buffer and resets the ticket. `wsm` is
+// shared memory for G * n_split weights (the drained ring is reused).
+__device__ __forceinline__ void split_merge_store(const AttnArgs& a, int item, int kvh, int* s_last, float* wsm) {
     if (a.n_split == 1) return;
-    const int D = a.kv.D, G = a.kv.G, Hq = a.kv.Hq;
+    const int D = a.kv.D, G = a.kv.G, Hq = a.kv.Hq, NS = a.n_split;
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
         unsigned prev = atomicAdd(&a.counters[item * a.kv.Hkv + kvh], 1u);
-        *s_last = (prev == (unsigned)a.n_split - 1u);
+        *s_last = (prev == (unsigned)NS - 1u);
     }
     __syncthreads();
     if (!*s_last) return;
     __threadfence();
+    const float* base = a.part + ((int64_t)item * Hq + (int64_t)kvh * G) * NS * (D + 2);
+    // pass 1: one weight per (head, split): w = 2^(m_s - max m); all loads independent
+    for (int idx = threadIdx.x; idx < G * NS; idx += blockDim.x)
+        wsm[idx] = __ldcg(base + (int64_t)idx * (D + 2) + D);
+    __syncthreads();
+    float* lsum = wsm + G * NS;  // [G] merged l
+    for (int g = threadIdx.x; g < G; g += blockDim.x) {
+        float ms = -INFINITY;
+        for (int sidx = 0; sidx < NS; ++sidx) ms = fmaxf(ms, wsm[g * NS + sidx]);
+        float ls = 0.0f;
+        for (int sidx = 0; sidx < NS; ++sidx) {
+            const float mw = wsm[g * NS + sidx];
+            const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - ms);
+            wsm[g * NS + sidx] = f;
+            ls += f * __ldcg(base + (int64_t)(g * NS + sidx) * (D + 2) + D + 1);
+        }
+        lsum[g] = ls;
+        lsum[G + g] = ms;
+    }
+    __syncthreads();
+    // pass 2: weighted sum of the split outputs, four independent loads in flight per thread
     for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
         const int g = idx / D, d = idx - g * D;
-        const int h = kvh * G + g;
-        const float* pp = a.part + ((int64_t)item * Hq + h) * a.n_split * (D + 2);
-        float ms = -INFINITY;
-        for (int s = 0; s < a.n_split; ++s) ms = fmaxf(ms, __ldcg(pp + (int64_t)s * (D + 2) + D));
-        float o = 0.0f, ls = 0.0f;
-        for (int s = 0; s < a.n_split; ++s) {
-            const float mw = __ldcg(pp + (int64_t)s * (D + 2) + D);
-            const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - ms);
-            o += f * __ldcg(pp + (int64_t)s * (D + 2) + d);
-            ls += f * __ldcg(pp + (int64_t)s * (D + 2) + D + 1);
+        const float* pp = base + (int64_t)g * NS * (D + 2) + d;
+        const float* w = wsm + g * NS;
+        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+        int sidx = 0;
+        for (; sidx + 4 <= NS; sidx += 4) {
+            const float x0 = __ldcg(pp + (int64_t)(sidx + 0) * (D + 2));
+            const float x1 = __ldcg(pp + (int64_t)(sidx + 1) * (D + 2));
+            const float x2 = __ldcg(pp + (int64_t)(sidx + 2) * (D + 2));
+            const float x3 = __ldcg(pp + (int64_t)(sidx + 3) * (D + 2));
+            o0 = fmaf(w[sidx], x0, o0);
+            o1 = fmaf(w[sidx + 1], x1, o1);
+            o2 = fmaf(w[sidx + 2], x2, o2);
+            o3 = fmaf(w[sidx + 3], x3, o3);
         }
-        store_final(a, item, h, d, o, ms, ls);
+        for (; sidx < NS; ++sidx) o0 = fmaf(w[sidx], __ldcg(pp + (int64_t)sidx * (D + 2)), o0);
+        store_final(a, item, kvh * G + g, d, (o0 + o1) + (o2 + o3), lsum[G + g], lsum[g]);
     }
     if (threadIdx.x == 0) a.counters[item * a.kv.Hkv + kvh] = 0u;  // ready for the next launch
 }
@@ -369,7 +396,7 @@ __global__ void __launch_bounds__(kSimtWarps * 32) attn_simt_kernel(AttnArgs a) 
         __syncthreads();  // merge area is free again before the next head group refills the ring
     }
 
-    split_merge_store(a, item, kvh, &s_last);
+    split_merge_store(a, item, kvh, &s_last, reinterpret_cast<float*>(smem));
 }
 
 // Merges n_parts partial states [n_parts][items][Hq][D + 2] (o / l, m, l) into out.

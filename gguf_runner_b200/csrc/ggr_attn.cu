@@ -49,9 +49,13 @@ struct ggr_attn_ctx {
     size_t stage_cap[4] = {0, 0, 0, 0};
     std::string err;
     int64_t launches = 0;
+    int last_splits = 0;  // split-KV factor of the most recent attention launch
     // tensor maps over the whole K and V arrays (bf16 caches) for the TMA prefill kernel
     CUtensorMap tmK, tmV;
     bool have_tmaps = false;
+    // the same arrays with a 64 x 16 box for the TMA-fed decode kernel
+    CUtensorMap tmK16, tmV16;
+    bool have_tmaps16 = false;
     // error word the kernels raise when a bounded wait runs out (mapped pinned host memory)
     int* h_err = nullptr;
     int* d_err = nullptr;
@@ -209,7 +213,10 @@ int launch_rope_append(ggr_attn_ctx* c, int layer, const Items& items, int flags
     }
     {
         LaunchTimer t(c, 1);
-        rope_append_kernel<<<items.n, 256, smem, c->stream>>>(a);
+        if (rope_append_fast_ok(a))
+            rope_append_bf16_kernel<<<items.n, 256, 0, c->stream>>>(a);
+        else
+            rope_append_kernel<<<items.n, 256, smem, c->stream>>>(a);
     }
     CUDA_TRY(c, cudaGetLastError());
     c->launches++;
@@ -299,20 +306,28 @@ int launch_simt(ggr_attn_ctx* c, const AttnArgs& a, dim3 grid, const SimtPlan& p
     }
 }
 
-// Split-KV factor: the grid is base_ctas * n CTAs running `slots` at a time, each CTA walking
-// ceil(T / n) keys. Picks the n with the fewest key-steps on the critical path (waves * keys per
-// CTA, plus a fixed per-CTA cost), so the last wave is not left almost empty.
-int choose_splits(int64_t base_ctas, int64_t slots, int t_max, int min_keys, int max_splits) {
+// Split-KV factor. The grid is base_ctas * n CTAs running `slots` at a time, each CTA streaming
+// ceil(T / n) keys of `bytes_per_key` bytes. A wave of c concurrent CTAs moves data at
+// min(per-CTA rate, HBM rate / c) per CTA and costs a fixed start/finish time; merging n splits
+// costs a little per split. The constants are measured on B200 (TMA-fed decode kernel: ~65 GB/s per
+// CTA alone, ~6.2 TB/s for the whole GPU, ~8 us per wave). Picks the n with the smallest modelled time.
+int choose_splits(int64_t base_ctas, int64_t slots, int t_max, int min_keys, int max_splits, double bytes_per_key,
+                  double cta_rate) {
     int limit = std::max(1, t_max / std::max(1, min_keys));
     limit = std::min(limit, 512);
     if (max_splits > 0) limit = std::min(limit, max_splits);
-    const int overhead = 96;  // keys' worth of prologue / merge work per CTA
+    const double hbm_rate = 6.2e12, t_wave = 8e-6;
     int best = 1;
-    int64_t best_cost = -1;
+    double best_cost = -1.0;
     for (int n = 1; n <= limit; ++n) {
-        const int64_t waves = (base_ctas * n + slots - 1) / slots;
-        const int64_t cost = waves * ((t_max + n - 1) / n + overhead);
-        if (best_cost < 0 || cost < best_cost) {
+        const int64_t ctas = base_ctas * n;
+        const int64_t full = ctas / slots, rem = ctas % slots;
+        const double bytes = (double)((t_max + n - 1) / n) * bytes_per_key;
+        double cost = 0.0;
+        if (full > 0) cost += (double)full * (t_wave + bytes / std::min(cta_rate, hbm_rate / (double)slots));
+        if (rem > 0) cost += t_wave + bytes / std::min(cta_rate, hbm_rate / (double)rem);
+        if (n > 1) cost += 2e-6 + 0.25e-6 * n;
+        if (best_cost < 0.0 || cost < best_cost) {
             best_cost = cost;
             best = n;
         }
@@ -342,21 +357,30 @@ int launch_attention(ggr_attn_ctx* c, int layer, const Items& items, int t_max, 
     a.shard_count = c->shard_count;
 
     const bool mma = allow_mma && use_mma_decode(c);
+    const bool tma = mma && c->have_tmaps16 && c->cfg.decode_impl != GGR_IMPL_MMA;
     SimtPlan p = simt_plan(c);
     size_t smem = p.smem;
     int ctas_per_sm = p.ctas_per_sm;
     int min_keys = p.nw * kSimtTK * 2;
     if (mma) {
-        MmaPlan mp = mma_plan(c->D, c->smem_optin);
+        MmaPlan mp = tma ? mma_tma_plan(c->D, c->smem_optin) : mma_plan(c->D, c->smem_optin);
         smem = mp.smem;
         ctas_per_sm = mp.ctas_per_sm;
         min_keys = mp.min_keys;
     }
     a.stage_bytes = p.stage_bytes;
+    a.err = c->d_err;
 
+    const double bytes_per_key = 2.0 * c->D * c->kv.elem_bytes;
+    const double cta_rate = tma ? 65e9 : 40e9;
     int n_split = choose_splits((int64_t)c->kv.Hkv * items.n, (int64_t)c->sm_count * ctas_per_sm, t_max, min_keys,
-                                c->cfg.max_splits);
+                                c->cfg.max_splits, bytes_per_key, cta_rate);
     a.n_split = n_split;
+    c->last_splits = n_split;
+    // the split merge stages one weight per (head, split) in shared memory
+    const size_t merge_smem = n_split > 1 ? ((size_t)c->G * n_split + 2 * c->G) * sizeof(float) : 0;
+    smem = std::max(smem, merge_smem);
+    p.smem = std::max(p.smem, merge_smem);
     if (n_split > 1) {
         int rc = ensure(c, &c->d_part, &c->part_cap, (size_t)items.n * c->kv.Hq * n_split * (c->D + 2));
         if (rc) return rc;
@@ -373,7 +397,8 @@ int launch_attention(ggr_attn_ctx* c, int layer, const Items& items, int t_max, 
         int rc;
         {
             LaunchTimer t(c, 0);
-            rc = launch_mma_decode(a, grid, smem, c->smem_optin, c->cfg.device, c->stream);
+            rc = tma ? launch_mma_tma_decode(c->tmK16, c->tmV16, a, grid, smem, c->smem_optin, c->cfg.device, c->stream)
+                     : launch_mma_decode(a, grid, smem, c->smem_optin, c->cfg.device, c->stream);
         }
         if (rc != 0) return fail(c, GGR_ERR_CUDA, std::string("mma decode launch: ") + cudaGetErrorString((cudaError_t)rc));
         c->launches++;
@@ -456,6 +481,10 @@ int decode_common(ggr_attn_ctx* c, int layer, const int32_t* pos, int B, const f
         CUDA_TRY(c, cudaMemcpyAsync(partial ? partial : out, dout, out_elems * sizeof(float), cudaMemcpyDeviceToHost,
                                     c->stream));
         CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+        if (c->h_err && *c->h_err) {
+            *c->h_err = 0;
+            return fail(c, GGR_ERR_TIMEOUT, "a bounded wait inside the decode kernel ran out");
+        }
     }
     return GGR_OK;
 }
@@ -719,6 +748,10 @@ int ggr_attn_create(const ggr_attn_config* cfg, ggr_attn_ctx** out) {
         c->have_tmaps = make_tmap_bf16(&c->tmK, kv.k, (uint64_t)c->kv_dim, (uint64_t)rows) &&
                         make_tmap_bf16(&c->tmV, kv.v, (uint64_t)c->kv_dim, (uint64_t)rows);
     }
+    if (kv.fmt == KV_BF16 && mma_tma_decode_supported(c->D) && rows < ((size_t)1 << 31)) {
+        c->have_tmaps16 = make_tmap_bf16(&c->tmK16, kv.k, (uint64_t)c->kv_dim, (uint64_t)rows, kTmaTK) &&
+                          make_tmap_bf16(&c->tmV16, kv.v, (uint64_t)c->kv_dim, (uint64_t)rows, kTmaTK);
+    }
     if (cudaStreamSynchronize(c->stream) != cudaSuccess) return cleanup(GGR_ERR_CUDA, "device initialisation failed");
     g_create_err.clear();
     *out = c;
@@ -754,6 +787,7 @@ void ggr_attn_destroy(ggr_attn_ctx* c) {
 
 const char* ggr_attn_last_error(const ggr_attn_ctx* ctx) { return ctx ? ctx->err.c_str() : "null context"; }
 int64_t ggr_attn_launch_count(const ggr_attn_ctx* ctx) { return ctx ? ctx->launches : 0; }
+int32_t ggr_attn_last_split_count(const ggr_attn_ctx* ctx) { return ctx ? ctx->last_splits : 0; }
 
 int ggr_attn_set_stream(ggr_attn_ctx* c, void* cuda_stream) {
     if (!c) return GGR_ERR_INVALID;
@@ -1163,11 +1197,13 @@ extern "C" int ggr_attn_attention_tokens_static(ggr_attn_ctx* c, int32_t layer, 
     a.partial_out = nullptr;
     a.shard_count = c->shard_count;
     const bool mma = use_mma_decode(c);
+    const bool tma = mma && c->have_tmaps16 && c->cfg.decode_impl != GGR_IMPL_MMA;
+    a.err = c->d_err;
     SimtPlan p = simt_plan(c);
     size_t smem = p.smem;
     int ctas_per_sm = p.ctas_per_sm, min_keys = p.nw * kSimtTK * 2;
     if (mma) {
-        MmaPlan mp = mma_plan(c->D, c->smem_optin);
+        MmaPlan mp = tma ? mma_tma_plan(c->D, c->smem_optin) : mma_plan(c->D, c->smem_optin);
         smem = mp.smem;
         ctas_per_sm = mp.ctas_per_sm;
         min_keys = mp.min_keys;
@@ -1176,7 +1212,12 @@ extern "C" int ggr_attn_attention_tokens_static(ggr_attn_ctx* c, int32_t layer, 
     const int t_max = t_max_of(c, layer, pos, B);
     int fit = (int)std::min<size_t>(512, part_cap / per_split);  // splits the array can hold
     if (c->cfg.max_splits > 0) fit = std::min(fit, c->cfg.max_splits);
-    a.n_split = choose_splits((int64_t)c->kv.Hkv * B, (int64_t)c->sm_count * ctas_per_sm, t_max, min_keys, fit);
+    a.n_split = choose_splits((int64_t)c->kv.Hkv * B, (int64_t)c->sm_count * ctas_per_sm, t_max, min_keys, fit,
+                              2.0 * c->D * c->kv.elem_bytes, tma ? 65e9 : 40e9);
+    c->last_splits = a.n_split;
+    const size_t merge_smem = a.n_split > 1 ? ((size_t)c->G * a.n_split + 2 * c->G) * sizeof(float) : 0;
+    smem = std::max(smem, merge_smem);
+    p.smem = std::max(p.smem, merge_smem);
     if (a.n_split > 1) {
         a.counters = reinterpret_cast<unsigned*>(scratch);
         a.part = reinterpret_cast<float*>(scratch + GGR_STATIC_TICKET_BYTES);
@@ -1188,7 +1229,8 @@ extern "C" int ggr_attn_attention_tokens_static(ggr_attn_ctx* c, int32_t layer, 
         int e;
         {
             LaunchTimer t(c, 0);
-            e = launch_mma_decode(a, grid, smem, c->smem_optin, c->cfg.device, c->stream);
+            e = tma ? launch_mma_tma_decode(c->tmK16, c->tmV16, a, grid, smem, c->smem_optin, c->cfg.device, c->stream)
+                    : launch_mma_decode(a, grid, smem, c->smem_optin, c->cfg.device, c->stream);
         }
         if (e != 0) return fail(c, GGR_ERR_CUDA, std::string("mma decode launch: ") + cudaGetErrorString((cudaError_t)e));
         c->launches++;

@@ -25,11 +25,10 @@
 // all roles leave their loops, TMEM is freed and the host sees GGR_ERR_TIMEOUT.
 #pragma once
 
-#include <cuda.h>
-
 #include <string>
 
 #include "common.cuh"
+#include "sm100_utils.cuh"
 
 namespace ggr {
 
@@ -45,142 +44,8 @@ struct PrefillTcArgs {
 
 constexpr int kTcBM = 128;       // query rows per tile
 constexpr int kTcBN = 128;       // keys per tile
-constexpr int kTcThreads = 320;  // 8 softmax warps + producer + MMA issuer
-constexpr uint32_t kTcSpinLimit = 1u << 24;
+constexpr int kTcThreads = 384;  // 8 softmax warps + a control warpgroup (producer, MMA issuer, 2 idle)
 
-namespace tc {
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait: false when the limit ran out or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t it = 0; it < kTcSpinLimit; ++it) {
-        if (mbar_test(bar, parity)) return true;
-        if ((it & 255u) == 255u) {
-            if (*abort_flag) return false;
-            __nanosleep(32);
-        }
-    }
-    *abort_flag = 1;
-    return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
-        : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void mma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-// D[tmem] (+)= A[smem desc] * B[smem desc]
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
-        : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem desc]
-__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc)
-        : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
-        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
-        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-        : "memory");
-}
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-        : "memory");
-}
-
-// Shared-memory matrix descriptor, 128-byte swizzle, tile base 1024-byte aligned.
-// lbo / sbo in bytes.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3ffffu) >> 4);
-    d |= (uint64_t)((lbo >> 4) & 0x3fffu) << 16;
-    d |= (uint64_t)((sbo >> 4) & 0x3fffu) << 32;
-    d |= (uint64_t)1 << 46;  // descriptor version of this architecture
-    d |= (uint64_t)2 << 61;  // 128-byte swizzle
-    return d;
-}
-
-// Instruction descriptor: bf16 x bf16 -> f32, M = 128.
-__host__ __device__ constexpr uint32_t idesc_bf16(int n, int b_mn_major) {
-    return (1u << 4)                      // accumulator f32
-           | (1u << 7)                    // A bf16
-           | (1u << 10)                   // B bf16
-           | ((uint32_t)b_mn_major << 16) // B major-ness (0 = K, 1 = MN)
-           | ((uint32_t)(n >> 3) << 17)   // N / 8
-           | ((uint32_t)(128 >> 4) << 24);  // M / 16
-}
-
-}  // namespace tc
 
 template <int D>
 __global__ void __launch_bounds__(kTcThreads, 1)
@@ -270,7 +135,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     volatile int* abortp = &s_abort;
     const int64_t row_base = a.kv.row(a.seq, a.layer, 0);
 
-    if (warp == 8) {
+    if (warp >= 8) {
+      // control warpgroup: gives registers up; warps 10 and 11 have no role
+      reg_dec40();
+      if (warp == 8) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             const int nq = (act0 ? 1 : 0) + (act1 ? 1 : 0);
@@ -294,7 +162,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                     tma_load_2d(sV + s * TILE_BYTES + b * BLK_BYTES, &tmV, kvh * D + b * 64, y, v_full(s));
             }
         }
-    } else if (warp == 9) {
+      } else if (warp == 9) {
         // ---------------- MMA issuer ----------------
         if (lane == 0 && hi > lo) {
             constexpr uint32_t IDESC_QK = idesc_bf16(kTcBN, 0);
@@ -355,8 +223,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 if (has_next) mma_commit(k_empty(s ^ 1));
             }
         }
+      }
     } else {
         // ---------------- softmax warps: one thread per query row ----------------
+        reg_inc232();
         const int t = warp >> 2;
         const int row = (warp & 3) * 32 + lane;
         const int qi = q_row0 + t * kTcBM + row;
@@ -389,16 +259,22 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                         if (key < vs || key >= ve) sr[cidx][i] = 0xff800000u;  // -inf
                     }
             }
-            float mx = -INFINITY;
+            float mxa = -INFINITY, mxb = -INFINITY, mxc = -INFINITY, mxd = -INFINITY;
 #pragma unroll
             for (int cidx = 0; cidx < 4; ++cidx)
 #pragma unroll
-                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sr[cidx][i]));
+                for (int i = 0; i < 32; i += 4) {
+                    mxa = fmaxf(mxa, __uint_as_float(sr[cidx][i]));
+                    mxb = fmaxf(mxb, __uint_as_float(sr[cidx][i + 1]));
+                    mxc = fmaxf(mxc, __uint_as_float(sr[cidx][i + 2]));
+                    mxd = fmaxf(mxd, __uint_as_float(sr[cidx][i + 3]));
+                }
+            const float mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
             // lazy rescale of the running output
             const bool need = mx > m_used + thr;
             float alpha = 1.0f;
             if (need) {
-                alpha = exp2f((m_used - mx) * c);  // 0 when nothing was accumulated yet
+                alpha = ex2((m_used - mx) * c);  // 0 when nothing was accumulated yet
                 m_used = mx;
             }
             if (k > 0 && __any_sync(0xffffffffu, need)) {
@@ -415,20 +291,28 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             l *= alpha;
             const float mref = (m_used == -INFINITY) ? 0.0f : m_used;
             const float neg = -mref * c;
-            float psum = 0.0f;
+            float ps0 = 0.0f, ps1 = 0.0f, ps2 = 0.0f, ps3 = 0.0f;
 #pragma unroll
             for (int cidx = 0; cidx < 4; ++cidx) {
                 uint32_t pk[16];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float p0 = exp2f(fmaf(__uint_as_float(sr[cidx][2 * i]), c, neg));
-                    const float p1 = exp2f(fmaf(__uint_as_float(sr[cidx][2 * i + 1]), c, neg));
-                    psum += p0 + p1;
-                    __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-                    pk[i] = *reinterpret_cast<uint32_t*>(&pb);
+                for (int i = 0; i < 16; i += 2) {
+                    const float p0 = ex2(fmaf(__uint_as_float(sr[cidx][2 * i]), c, neg));
+                    const float p1 = ex2(fmaf(__uint_as_float(sr[cidx][2 * i + 1]), c, neg));
+                    const float p2 = ex2(fmaf(__uint_as_float(sr[cidx][2 * i + 2]), c, neg));
+                    const float p3 = ex2(fmaf(__uint_as_float(sr[cidx][2 * i + 3]), c, neg));
+                    ps0 += p0;
+                    ps1 += p1;
+                    ps2 += p2;
+                    ps3 += p3;
+                    __nv_bfloat162 pa = __floats2bfloat162_rn(p0, p1);
+                    __nv_bfloat162 pb = __floats2bfloat162_rn(p2, p3);
+                    pk[i] = *reinterpret_cast<uint32_t*>(&pa);
+                    pk[i + 1] = *reinterpret_cast<uint32_t*>(&pb);
                 }
                 tmem_st16(tS + cidx * 16, pk);
             }
+            const float psum = (ps0 + ps1) + (ps2 + ps3);
             l += psum;
             tmem_wait_st();
             fence_before_sync();
@@ -469,35 +353,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 }
 
 // ---- host side ---------------------------------------------------------------------------------
-
-typedef CUresult (*PFN_tmapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                        const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                        CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-inline PFN_tmapEncodeTiled tmap_encoder() {
-    static PFN_tmapEncodeTiled fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult qr;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess &&
-            qr == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<PFN_tmapEncodeTiled>(p);
-    }
-    return fn;
-}
-
-// 2-D bf16 row-major tensor [rows][cols], box = 64 columns x 128 rows, 128-byte swizzle
-inline bool make_tmap_bf16(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows) {
-    PFN_tmapEncodeTiled enc = tmap_encoder();
-    if (!enc) return false;
-    cuuint64_t dims[2] = {cols, rows};
-    cuuint64_t strides[1] = {cols * 2};
-    cuuint32_t box[2] = {64, 128};
-    cuuint32_t estr[2] = {1, 1};
-    return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
 
 inline bool prefill_tc_shape_ok(int fmt, int D) { return fmt == KV_BF16 && (D == 64 || D == 128); }
 

@@ -205,4 +205,126 @@ __global__ void __launch_bounds__(256) rope_append_kernel(RopeAppendArgs a) {
     }
 }
 
+// ---- vectorised variant for the tensor-core prefill: bf16 inputs, bf16 cache, bf16 rotated q ----
+// Same arithmetic as rope_append_kernel, but every thread moves 16-byte vectors (8 bf16) and a
+// token needs one pass of the CTA: q, k and v tasks are spread over the 256 threads.
+
+__device__ __forceinline__ void unpack8(const uint4& u, float f[8]) {
+    f[0] = __uint_as_float(u.x << 16); f[1] = __uint_as_float(u.x & 0xffff0000u);
+    f[2] = __uint_as_float(u.y << 16); f[3] = __uint_as_float(u.y & 0xffff0000u);
+    f[4] = __uint_as_float(u.z << 16); f[5] = __uint_as_float(u.z & 0xffff0000u);
+    f[6] = __uint_as_float(u.w << 16); f[7] = __uint_as_float(u.w & 0xffff0000u);
+}
+__device__ __forceinline__ uint4 pack8(const float f[8]) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+    __nv_bfloat162 c = __floats2bfloat162_rn(f[4], f[5]), d = __floats2bfloat162_rn(f[6], f[7]);
+    uint4 u;
+    u.x = *reinterpret_cast<uint32_t*>(&a);
+    u.y = *reinterpret_cast<uint32_t*>(&b);
+    u.z = *reinterpret_cast<uint32_t*>(&c);
+    u.w = *reinterpret_cast<uint32_t*>(&d);
+    return u;
+}
+
+// Rotates head vector `vi` (8 elements) of a head starting at src; writes the result(s) to dst.
+// NeoX: the thread owning a low-half vector also produces its partner in the high half.
+__device__ __forceinline__ void rope_vec8(const __nv_bfloat16* src, __nv_bfloat16* dst, int vi, const RopeParams& rp,
+                                          const float* cs, const float* sn, float scale, bool do_scale) {
+    const int e0 = vi * 8;
+    const uint4 u = *reinterpret_cast<const uint4*>(src + e0);
+    float x[8];
+    unpack8(u, x);
+    if (rp.style == 0) {
+        const int half = rp.rope_half;
+        if (e0 < half) {
+            const uint4 w = *reinterpret_cast<const uint4*>(src + e0 + half);
+            float y[8], lo[8], hi[8];
+            unpack8(w, y);
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+                const float c = cs[e0 + p], s = sn[e0 + p];
+                lo[p] = __fsub_rn(__fmul_rn(x[p], c), __fmul_rn(y[p], s));
+                hi[p] = __fadd_rn(__fmul_rn(x[p], s), __fmul_rn(y[p], c));
+                if (do_scale) {
+                    lo[p] = __fmul_rn(lo[p], scale);
+                    hi[p] = __fmul_rn(hi[p], scale);
+                }
+            }
+            *reinterpret_cast<uint4*>(dst + e0) = pack8(lo);
+            *reinterpret_cast<uint4*>(dst + e0 + half) = pack8(hi);
+        } else if (e0 >= rp.rope_dim) {
+            if (do_scale) {
+#pragma unroll
+                for (int p = 0; p < 8; ++p) x[p] = __fmul_rn(x[p], scale);
+                *reinterpret_cast<uint4*>(dst + e0) = pack8(x);
+            } else {
+                *reinterpret_cast<uint4*>(dst + e0) = u;
+            }
+        }
+    } else {
+        float r[8];
+#pragma unroll
+        for (int p = 0; p < 8; p += 2) {
+            const int j = (e0 + p) >> 1;
+            const float c = cs[j], s = sn[j];
+            r[p] = __fsub_rn(__fmul_rn(x[p], c), __fmul_rn(x[p + 1], s));
+            r[p + 1] = __fadd_rn(__fmul_rn(x[p], s), __fmul_rn(x[p + 1], c));
+            if (do_scale) {
+                r[p] = __fmul_rn(r[p], scale);
+                r[p + 1] = __fmul_rn(r[p + 1], scale);
+            }
+        }
+        *reinterpret_cast<uint4*>(dst + e0) = pack8(r);
+    }
+}
+
+inline bool rope_append_fast_ok(const RopeAppendArgs& a) {
+    const int D = a.kv.D;
+    return a.in_bf16 && a.kv.fmt == KV_BF16 && a.q_out_h && !a.q_out && !a.k_out &&
+           a.flags == (RF_ROTATE | RF_WRITE_Q | RF_APPEND) && D % 8 == 0 && a.rope.rope_half <= 128 &&
+           (a.rope.style == 1 || (a.rope.rope_half % 8 == 0 && a.rope.rope_dim % 8 == 0)) && a.kv.pos_begin == 0;
+}
+
+__global__ void __launch_bounds__(256) rope_append_bf16_kernel(RopeAppendArgs a) {
+    __shared__ float cs[128], sn[128];
+    const int D = a.kv.D, kv_dim = a.kv.kv_dim, Hq = a.kv.Hq, Hkv = a.kv.Hkv, q_dim = Hq * D;
+    const int half = a.rope.rope_half;
+    const int item = blockIdx.x, tid = threadIdx.x;
+    int seq, pos;
+    a.items.get(item, seq, pos);
+    if (tid < half) {
+        const int axis = rope_axis(a.rope.layout, tid, a.rope.sections);
+        int coord = pos;
+        if (a.rope.has_plan)
+            coord = pos < a.rope.plan_len ? a.rope.plan[pos * 3 + axis] : a.rope.next_text + (pos - a.rope.plan_len);
+        const float val = __fmul_rn(__fmul_rn((float)coord, a.rope.freqs[tid]), a.rope.fscale);
+        float s, c;
+        sincosf(val, &s, &c);
+        cs[tid] = c;
+        sn[tid] = s;
+    }
+    __syncthreads();
+    const int vph = D / 8;  // vectors per head
+    const __nv_bfloat16* q = reinterpret_cast<const __nv_bfloat16*>(a.q) + (int64_t)item * q_dim;
+    const __nv_bfloat16* k = reinterpret_cast<const __nv_bfloat16*>(a.k) + (int64_t)item * kv_dim;
+    const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(a.v) + (int64_t)item * kv_dim;
+    __nv_bfloat16* qo = a.q_out_h + (int64_t)item * q_dim;
+    const int64_t off = a.kv.row(seq, a.layer, pos) * kv_dim;
+    __nv_bfloat16* kc = reinterpret_cast<__nv_bfloat16*>(a.kv.k) + off;
+    __nv_bfloat16* vc = reinterpret_cast<__nv_bfloat16*>(a.kv.v) + off;
+    const int nq = Hq * vph, nk = Hkv * vph, total = nq + 2 * nk;
+    for (int task = tid; task < total; task += blockDim.x) {
+        if (task < nq) {
+            const int h = task / vph, vi = task - h * vph;
+            rope_vec8(q + h * D, qo + h * D, vi, a.rope, cs, sn, a.rope.q_prescale, a.rope.do_prescale != 0);
+        } else if (task < nq + nk) {
+            const int t2 = task - nq, h = t2 / vph, vi = t2 - h * vph;
+            rope_vec8(k + h * D, kc + h * D, vi, a.rope, cs, sn, 1.0f, false);
+        } else {
+            const int t2 = task - nq - nk;
+            *reinterpret_cast<uint4*>(vc + t2 * 8) = *reinterpret_cast<const uint4*>(v + t2 * 8);
+        }
+    }
+}
+
 }  // namespace ggr

@@ -49,6 +49,8 @@ enum { GGR_ROPE_SEQUENTIAL = 0, GGR_ROPE_INTERLEAVED = 1 };
 enum { GGR_SCALE_SCORE = 0, GGR_SCALE_Q_PRESCALED = 1 };
 enum { GGR_IMAGE_CAUSAL = 0, GGR_IMAGE_BIDIRECTIONAL = 1 };
 enum { GGR_SHARD_NONE = 0, GGR_SHARD_KV_SEQUENCE = 2 };
+/* decode: SIMT = CUDA cores, MMA = mma.sync fed by cp.async, AUTO = mma.sync fed by TMA where the shape allows;
+ * prefill: SIMT = CUDA cores, TCGEN05 / AUTO = tcgen05 + TMEM where the shape allows */
 enum { GGR_IMPL_AUTO = 0, GGR_IMPL_SIMT = 1, GGR_IMPL_MMA = 2, GGR_IMPL_TCGEN05 = 3 };
 
 typedef struct ggr_attn_ctx ggr_attn_ctx;
@@ -228,6 +230,8 @@ int ggr_attn_attention_tokens_static(ggr_attn_ctx* ctx, int32_t layer, const int
 
 /* Number of kernels this context has launched since it was created. */
 int64_t ggr_attn_launch_count(const ggr_attn_ctx* ctx);
+/* Split-KV factor the most recent decode / attention launch of this context used. */
+int32_t ggr_attn_last_split_count(const ggr_attn_ctx* ctx);
 
 /* Per-kernel device timing (the counterpart of the reference's PROF_ATTN_NS
  * counter, src/engine/profiling.rs:8-41): when enabled, every launch is

@@ -8,7 +8,7 @@ import pytest
 
 import gguf_runner_b200 as g
 from gguf_runner_b200 import presets
-from gguf_runner_b200.binding import (AttnConfig, GgrError, IMPL_MMA, IMPL_SIMT, KV_BF16, KV_F32, KV_Q8_BLOCK32,
+from gguf_runner_b200.binding import (AttnConfig, GgrError, IMPL_AUTO, IMPL_MMA, IMPL_SIMT, KV_BF16, KV_F32, KV_Q8_BLOCK32,
                                       KV_Q8_ROW, ROPE_ADJACENT, ROPE_INTERLEAVED, ROPE_NEOX, SCALE_Q_PRESCALED,
                                       SHARD_KV_SEQUENCE)
 from tests.oracle_binding import Oracle, bf16_bits, bf16_round
@@ -269,7 +269,7 @@ def test_batched_decode_independent_sequences():
     assert np.max(np.abs(got - want)) <= 2e-2
 
 
-@pytest.mark.parametrize("impl", [IMPL_SIMT, IMPL_MMA])
+@pytest.mark.parametrize("impl", [IMPL_AUTO, IMPL_SIMT, IMPL_MMA])
 @pytest.mark.parametrize("n_heads,n_kv_heads", [(32, 4), (40, 8), (12, 4), (16, 1)])
 def test_decode_kernel_families_bf16(impl, n_heads, n_kv_heads):
     cfg = AttnConfig(n_layers=1, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=128, seq_len=1200,
