@@ -215,6 +215,10 @@ int launch_rope_append(ggr_attn_ctx* c, int layer, const Items& items, int flags
         LaunchTimer t(c, 1);
         if (rope_append_fast_ok(a))
             rope_append_bf16_kernel<<<items.n, 256, 0, c->stream>>>(a);
+        else if (rope_append_vec_ok(a) && smem + 16 <= 48 * 1024 && in_bf16)
+            rope_append_vec_kernel<__nv_bfloat16><<<items.n, 256, smem + 16, c->stream>>>(a);
+        else if (rope_append_vec_ok(a) && smem + 16 <= 48 * 1024)
+            rope_append_vec_kernel<float><<<items.n, 256, smem + 16, c->stream>>>(a);
         else
             rope_append_kernel<<<items.n, 256, smem, c->stream>>>(a);
     }
@@ -310,13 +314,13 @@ int launch_simt(ggr_attn_ctx* c, const AttnArgs& a, dim3 grid, const SimtPlan& p
 // ceil(T / n) keys of `bytes_per_key` bytes. A wave of c concurrent CTAs moves data at
 // min(per-CTA rate, HBM rate / c) per CTA and costs a fixed start/finish time; merging n splits
 // costs a little per split. The constants are measured on B200 (TMA-fed decode kernel: ~65 GB/s per
-// CTA alone, ~6.2 TB/s for the whole GPU, ~8 us per wave). Picks the n with the smallest modelled time.
+// CTA alone, ~6.6 TB/s for the whole GPU, ~8 us per wave). Picks the n with the smallest modelled time.
 int choose_splits(int64_t base_ctas, int64_t slots, int t_max, int min_keys, int max_splits, double bytes_per_key,
                   double cta_rate) {
     int limit = std::max(1, t_max / std::max(1, min_keys));
     limit = std::min(limit, 512);
     if (max_splits > 0) limit = std::min(limit, max_splits);
-    const double hbm_rate = 6.2e12, t_wave = 8e-6;
+    const double hbm_rate = 6.6e12, t_wave = 8e-6;
     int best = 1;
     double best_cost = -1.0;
     for (int n = 1; n <= limit; ++n) {

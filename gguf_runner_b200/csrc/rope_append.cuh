@@ -327,4 +327,201 @@ __global__ void __launch_bounds__(256) rope_append_bf16_kernel(RopeAppendArgs a)
     }
 }
 
+// ---- vectorised general variant -------------------------------------------------------------------
+// Same results as rope_append_kernel for f32 or bf16 inputs and every cache format, with 8-element
+// (16 / 32 byte) loads and stores and one task per thread instead of element loops whose loads the
+// compiler has to serialise. Needs the rotated span to be a multiple of 8 elements.
+
+template <typename TIn>
+__device__ __forceinline__ void load8_in(const TIn* p, float x[8]);
+template <>
+__device__ __forceinline__ void load8_in<float>(const float* p, float x[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+    x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8_in<__nv_bfloat16>(const __nv_bfloat16* p, float x[8]) {
+    unpack8(*reinterpret_cast<const uint4*>(p), x);
+}
+__device__ __forceinline__ void store8_f32(float* p, const float x[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(x[0], x[1], x[2], x[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(x[4], x[5], x[6], x[7]);
+}
+
+// Rotates vector vi of a head. Returns the number of result vectors (0, 1 or 2): r0 belongs at
+// element e0, r1 (NeoX partner) at e0 + rope_half.
+template <typename TIn>
+__device__ __forceinline__ int rope_task8(const TIn* head, int vi, const RopeParams& rp, const float* cs, const float* sn,
+                                          bool rotate, float r0[8], float r1[8]) {
+    const int e0 = vi * 8;
+    float x[8];
+    if (!rotate) {
+        load8_in<TIn>(head + e0, r0);
+        return 1;
+    }
+    if (rp.style == 0) {
+        const int half = rp.rope_half;
+        if (e0 < half) {
+            float y[8];
+            load8_in<TIn>(head + e0, x);
+            load8_in<TIn>(head + e0 + half, y);
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+                const float c = cs[e0 + p], s = sn[e0 + p];
+                r0[p] = __fsub_rn(__fmul_rn(x[p], c), __fmul_rn(y[p], s));
+                r1[p] = __fadd_rn(__fmul_rn(x[p], s), __fmul_rn(y[p], c));
+            }
+            return 2;
+        }
+        if (e0 < rp.rope_dim) return 0;  // produced by the low-half partner
+        load8_in<TIn>(head + e0, r0);
+        return 1;
+    }
+    load8_in<TIn>(head + e0, x);
+#pragma unroll
+    for (int p = 0; p < 8; p += 2) {
+        const int j = (e0 + p) >> 1;
+        const float c = cs[j], s = sn[j];
+        r0[p] = __fsub_rn(__fmul_rn(x[p], c), __fmul_rn(x[p + 1], s));
+        r0[p + 1] = __fadd_rn(__fmul_rn(x[p], s), __fmul_rn(x[p + 1], c));
+    }
+    return 1;
+}
+
+inline bool rope_append_vec_ok(const RopeAppendArgs& a) {
+    const bool span_ok = a.rope.style == 1 || (a.rope.rope_half % 8 == 0 && a.rope.rope_dim % 8 == 0);
+    return span_ok && a.kv.D % 8 == 0 && a.kv.fmt != KV_Q8_BLOCK32;
+}
+
+template <typename TIn>
+__global__ void __launch_bounds__(256) rope_append_vec_kernel(RopeAppendArgs a) {
+    extern __shared__ float sm[];
+    const int D = a.kv.D, kv_dim = a.kv.kv_dim, Hq = a.kv.Hq, Hkv = a.kv.Hkv, q_dim = Hq * D;
+    const int half = a.rope.rope_half;
+    float* cs = sm;
+    float* sn = cs + half;
+    float* krow = sm + ((2 * half + 3) & ~3);  // 16-byte aligned rows
+    float* vrow = krow + kv_dim;
+    float* red = vrow + kv_dim;
+    const int item = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
+    int seq, pos;
+    a.items.get(item, seq, pos);
+    const bool rotate = (a.flags & RF_ROTATE) != 0;
+    if (rotate) {
+        for (int i = tid; i < half; i += nt) {
+            const int axis = rope_axis(a.rope.layout, i, a.rope.sections);
+            int coord = pos;
+            if (a.rope.has_plan)
+                coord = pos < a.rope.plan_len ? a.rope.plan[pos * 3 + axis] : a.rope.next_text + (pos - a.rope.plan_len);
+            const float val = __fmul_rn(__fmul_rn((float)coord, a.rope.freqs[i]), a.rope.fscale);
+            float s, c;
+            sincosf(val, &s, &c);
+            cs[i] = c;
+            sn[i] = s;
+        }
+        __syncthreads();
+    }
+    const int vph = D / 8;
+    const TIn* q = reinterpret_cast<const TIn*>(a.q) + (int64_t)item * q_dim;
+    const TIn* k = reinterpret_cast<const TIn*>(a.k) + (int64_t)item * kv_dim;
+    const TIn* v = reinterpret_cast<const TIn*>(a.v) + (int64_t)item * kv_dim;
+    const bool do_q = (a.flags & RF_WRITE_Q) != 0;
+    const bool do_k = (a.flags & (RF_APPEND | RF_WRITE_K)) != 0;
+    const bool do_v = (a.flags & RF_APPEND) != 0;
+    const int nq = do_q ? Hq * vph : 0, nk = do_k ? Hkv * vph : 0, nv = do_v ? Hkv * vph : 0;
+    for (int task = tid; task < nq + nk + nv; task += nt) {
+        float r0[8], r1[8];
+        if (task < nq) {
+            const int h = task / vph, vi = task - h * vph;
+            const int n = rope_task8<TIn>(q + h * D, vi, a.rope, cs, sn, rotate, r0, r1);
+            const int64_t o = (int64_t)item * q_dim + h * D + vi * 8;
+            for (int r = 0; r < n; ++r) {
+                float* x = r == 0 ? r0 : r1;
+                const int64_t oo = o + (r == 0 ? 0 : half);
+                if (a.rope.do_prescale) {
+#pragma unroll
+                    for (int p = 0; p < 8; ++p) x[p] = __fmul_rn(x[p], a.rope.q_prescale);
+                }
+                if (a.q_out) store8_f32(a.q_out + oo, x);
+                if (a.q_out_h) *reinterpret_cast<uint4*>(a.q_out_h + oo) = pack8(x);
+            }
+        } else if (task < nq + nk) {
+            const int t2 = task - nq, h = t2 / vph, vi = t2 - h * vph;
+            const int n = rope_task8<TIn>(k + h * D, vi, a.rope, cs, sn, rotate, r0, r1);
+            if (n >= 1) store8_f32(krow + h * D + vi * 8, r0);
+            if (n == 2) store8_f32(krow + h * D + vi * 8 + half, r1);
+        } else {
+            const int t2 = task - nq - nk;
+            load8_in<TIn>(v + t2 * 8, r0);
+            store8_f32(vrow + t2 * 8, r0);
+        }
+    }
+    if (!do_k) return;
+    __syncthreads();
+    const int nvec = kv_dim / 8;
+    if (a.flags & RF_WRITE_K) {
+        float* ko = a.k_out + (int64_t)item * kv_dim;
+        for (int t2 = tid; t2 < nvec; t2 += nt) store8_f32(ko + t2 * 8, krow + t2 * 8);
+    }
+    if (!do_v) return;
+    if (pos < a.kv.pos_begin || pos >= a.kv.pos_begin + a.shard_count) return;  // another rank owns this row
+    const int64_t r = a.kv.row(seq, a.layer, pos);
+    const int64_t off = r * kv_dim;
+    if (a.kv.fmt == KV_F32) {
+        float* kc = reinterpret_cast<float*>(a.kv.k) + off;
+        float* vc = reinterpret_cast<float*>(a.kv.v) + off;
+        for (int t2 = tid; t2 < nvec; t2 += nt) {
+            store8_f32(kc + t2 * 8, krow + t2 * 8);
+            store8_f32(vc + t2 * 8, vrow + t2 * 8);
+        }
+    } else if (a.kv.fmt == KV_BF16) {
+        __nv_bfloat16* kc = reinterpret_cast<__nv_bfloat16*>(a.kv.k) + off;
+        __nv_bfloat16* vc = reinterpret_cast<__nv_bfloat16*>(a.kv.v) + off;
+        for (int t2 = tid; t2 < nvec; t2 += nt) {
+            *reinterpret_cast<uint4*>(kc + t2 * 8) = pack8(krow + t2 * 8);
+            *reinterpret_cast<uint4*>(vc + t2 * 8) = pack8(vrow + t2 * 8);
+        }
+    } else {  // KV_Q8_ROW: one scale per row over all KV heads (src/engine/runtime/inference.rs:1906-1916)
+        float mk = 0.0f, mv = 0.0f;
+        for (int idx = tid; idx < kv_dim; idx += nt) {
+            mk = fmaxf(mk, fabsf(krow[idx]));
+            mv = fmaxf(mv, fabsf(vrow[idx]));
+        }
+        mk = warp_max(mk);
+        mv = warp_max(mv);
+        if ((tid & 31) == 0) {
+            red[tid >> 5] = mk;
+            red[8 + (tid >> 5)] = mv;
+        }
+        __syncthreads();
+        mk = 0.0f;
+        mv = 0.0f;
+        for (int w = 0; w < (nt >> 5); ++w) {
+            mk = fmaxf(mk, red[w]);
+            mv = fmaxf(mv, red[8 + w]);
+        }
+        const float invk = mk == 0.0f ? 0.0f : __fdiv_rn(127.0f, mk);
+        const float invv = mv == 0.0f ? 0.0f : __fdiv_rn(127.0f, mv);
+        int8_t* kc = reinterpret_cast<int8_t*>(a.kv.k) + off;
+        int8_t* vc = reinterpret_cast<int8_t*>(a.kv.v) + off;
+        for (int t2 = tid; t2 < nvec; t2 += nt) {
+            uint32_t kw[2] = {0, 0}, vw[2] = {0, 0};
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+                const int8_t kq = mk == 0.0f ? (int8_t)0 : q8_code(krow[t2 * 8 + p], invk);
+                const int8_t vq = mv == 0.0f ? (int8_t)0 : q8_code(vrow[t2 * 8 + p], invv);
+                kw[p >> 2] |= (uint32_t)(uint8_t)kq << (8 * (p & 3));
+                vw[p >> 2] |= (uint32_t)(uint8_t)vq << (8 * (p & 3));
+            }
+            *reinterpret_cast<uint2*>(kc + t2 * 8) = make_uint2(kw[0], kw[1]);
+            *reinterpret_cast<uint2*>(vc + t2 * 8) = make_uint2(vw[0], vw[1]);
+        }
+        if (tid == 0) {
+            a.kv.ks[r] = mk == 0.0f ? 1.0f : __fdiv_rn(mk, 127.0f);
+            a.kv.vs[r] = mv == 0.0f ? 1.0f : __fdiv_rn(mv, 127.0f);
+        }
+    }
+}
+
 }  // namespace ggr
