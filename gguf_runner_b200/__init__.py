@@ -18,3 +18,4 @@ from .binding import (  # noqa: F401
     rope_axis,
 )
 from . import presets  # noqa: F401
+from . import sharding  # noqa: F401
