@@ -17,6 +17,7 @@
 #include "attn_simt.cuh"
 #include "common.cuh"
 #include "prefill_tc.cuh"
+#include "prefill_tc_wide.cuh"
 #include "rope_append.cuh"
 
 using namespace ggr;
@@ -53,6 +54,9 @@ struct ggr_attn_ctx {
     // tensor maps over the whole K and V arrays (bf16 caches) for the TMA prefill kernel
     CUtensorMap tmK, tmV;
     bool have_tmaps = false;
+    // the same arrays with a 64 x 64 box for the head_dim 256 prefill kernel
+    CUtensorMap tmK64, tmV64;
+    bool have_tmaps64 = false;
     // the same arrays with a 64 x 16 box for the TMA-fed decode kernel
     CUtensorMap tmK16, tmV16;
     bool have_tmaps16 = false;
@@ -527,9 +531,10 @@ int prefill_common(ggr_attn_ctx* c, int layer, int seq, int base_pos, int m, con
         dout = reinterpret_cast<float*>(c->d_stage[3]);
     }
 
-    const bool tc = c->have_tmaps && prefill_tc_usable(c->cfg.prefill_impl, c->kv.fmt, c->D, c->G);
+    const bool wide = c->have_tmaps64 && c->cfg.prefill_impl != GGR_IMPL_SIMT;
+    const bool tc = wide || (c->have_tmaps && prefill_tc_usable(c->cfg.prefill_impl, c->kv.fmt, c->D, c->G));
     if (c->cfg.prefill_impl == GGR_IMPL_TCGEN05 && !tc)
-        return fail(c, GGR_ERR_UNSUPPORTED, "the tensor-core prefill kernel needs a bf16 cache and head_dim 64 or 128");
+        return fail(c, GGR_ERR_UNSUPPORTED, "the tensor-core prefill kernels need a bf16 cache and head_dim 64, 128 or 256");
     if ((rc = ensure(c, &c->d_qrot, &c->qrot_cap, tc ? (size_t)1 : (size_t)m * c->q_dim))) return rc;
     if (tc && (rc = ensure(c, &c->d_qrot_h, &c->qrot_h_cap, (size_t)m * c->q_dim))) return rc;
 
@@ -565,7 +570,8 @@ int prefill_common(ggr_attn_ctx* c, int layer, int seq, int base_pos, int m, con
         std::string msg;
         {
             LaunchTimer t(c, 0);
-            rc = launch_prefill_tc(a, c->tmK, c->tmV, c->cfg.device, c->stream, &msg);
+            rc = wide ? launch_prefill_tc_wide(a, c->tmK64, c->tmV64, c->cfg.device, c->stream, &msg)
+                      : launch_prefill_tc(a, c->tmK, c->tmV, c->cfg.device, c->stream, &msg);
         }
         if (rc) return fail(c, rc, msg);
         c->launches++;
@@ -748,9 +754,13 @@ int ggr_attn_create(const ggr_attn_config* cfg, ggr_attn_ctx** out) {
         return cleanup(GGR_ERR_ALLOC, "unable to allocate the error word");
     }
     *c->h_err = 0;
-    if (prefill_tc_shape_ok(kv.fmt, c->D)) {
+    if (prefill_tc_shape_ok(kv.fmt, c->D) && rows < ((size_t)1 << 31)) {
         c->have_tmaps = make_tmap_bf16(&c->tmK, kv.k, (uint64_t)c->kv_dim, (uint64_t)rows) &&
                         make_tmap_bf16(&c->tmV, kv.v, (uint64_t)c->kv_dim, (uint64_t)rows);
+    }
+    if (kv.fmt == KV_BF16 && c->D == 256 && rows < ((size_t)1 << 31)) {
+        c->have_tmaps64 = make_tmap_bf16(&c->tmK64, kv.k, (uint64_t)c->kv_dim, (uint64_t)rows, kTwBN) &&
+                          make_tmap_bf16(&c->tmV64, kv.v, (uint64_t)c->kv_dim, (uint64_t)rows, kTwBN);
     }
     if (kv.fmt == KV_BF16 && mma_tma_decode_supported(c->D) && rows < ((size_t)1 << 31)) {
         c->have_tmaps16 = make_tmap_bf16(&c->tmK16, kv.k, (uint64_t)c->kv_dim, (uint64_t)rows, kTmaTK) &&

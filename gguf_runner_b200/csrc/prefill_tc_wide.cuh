@@ -1,0 +1,327 @@
+// Tensor-core prefill for head_dim 256 (Gemma-3-shaped layers): same algorithm as prefill_tc_kernel,
+// different tiling because the output accumulator alone takes 256 TMEM columns.
+//
+// One CTA owns ONE 128-row query tile of one query head and walks the visible 64-key tiles:
+//   warp 4       TMA producer (Q once; K and V tiles of 64 keys into 2-stage rings)
+//   warp 5       MMA issuer: S[b] = Q K^T (N = 64) into one of two S buffers, O += P V (N = 256)
+//   warps 0-3    softmax, one thread per query row
+// TMEM columns: S0 0-63, S1 64-127, O 128-383. The score tile of step j+1 is computed while the
+// softmax of step j runs; because QK(j+1) is issued before PV(j), the softmax waits for PV(j-1)
+// (pv_done) before it may rescale O.
+// Shared memory: Q 64 KB + 2 x 32 KB K + 2 x 32 KB V = 192 KB. Every wait is bounded.
+#pragma once
+
+#include <string>
+
+#include "common.cuh"
+#include "prefill_tc.cuh"
+#include "sm100_utils.cuh"
+
+namespace ggr {
+
+constexpr int kTwBN = 64;        // keys per tile
+constexpr int kTwThreads = 256;  // softmax warpgroup + control warpgroup
+
+template <int D>
+__global__ void __launch_bounds__(kTwThreads, 1)
+prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                       const __grid_constant__ CUtensorMap tmV, PrefillTcArgs a) {
+    using namespace tc;
+    constexpr int NBLK = D / 64;
+    constexpr uint32_t QBLK = 128 * 128;         // [128 rows][128 bytes]
+    constexpr uint32_t KBLK = kTwBN * 128;       // [64 rows][128 bytes]
+    constexpr uint32_t Q_BYTES = NBLK * QBLK;
+    constexpr uint32_t KV_BYTES = NBLK * KBLK;
+    constexpr uint32_t O_COL0 = 128;
+
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t bars[16];
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sQ = smem_base;
+    const uint32_t sK = sQ + Q_BYTES;        // [2 stages][KV_BYTES]
+    const uint32_t sV = sK + 2 * KV_BYTES;   // [2 stages][KV_BYTES]
+
+    const uint32_t bar0 = smem_u32(bars);
+    const uint32_t q_full = bar0;
+    auto k_full = [&](int s) { return bar0 + 8u * (1 + s); };
+    auto k_empty = [&](int s) { return bar0 + 8u * (3 + s); };
+    auto v_full = [&](int s) { return bar0 + 8u * (5 + s); };
+    auto v_empty = [&](int s) { return bar0 + 8u * (7 + s); };
+    auto s_full = [&](int b) { return bar0 + 8u * (9 + b); };
+    const uint32_t p_full = bar0 + 8u * 11, pv_done = bar0 + 8u * 12, o_final = bar0 + 8u * 13;
+
+    const int Hq = a.kv.Hq, G = a.kv.G;
+    const int n_tiles = (a.m + kTcBM - 1) / kTcBM;
+    const int qt = n_tiles - 1 - (int)(blockIdx.x / Hq);  // long (late) tiles first
+    const int h = blockIdx.x % Hq;
+    const int kvh = h / G;
+    const int q_row0 = qt * kTcBM;
+
+    int lo, hi;
+    {
+        const int r1 = min(a.m, q_row0 + kTcBM) - 1;
+        int vs0, ve0, vs1, ve1;
+        a.vis.range(a.base_pos + q_row0, vs0, ve0);
+        a.vis.range(a.base_pos + r1, vs1, ve1);
+        lo = min(vs0, vs1) / kTwBN;
+        hi = (max(ve0, ve1) + kTwBN - 1) / kTwBN;
+    }
+
+    if (tid == 0) {
+        s_abort = 0;
+        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(k_full(s), 1);
+            mbar_init(k_empty(s), 1);
+            mbar_init(v_full(s), 1);
+            mbar_init(v_empty(s), 1);
+            mbar_init(s_full(s), 1);
+        }
+        mbar_init(p_full, kTcBM);
+        mbar_init(pv_done, 1);
+        mbar_init(o_final, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) {
+        tmem_alloc(smem_u32(&s_tmem_base), 512);
+        tmem_relinquish();
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem = s_tmem_base;
+    volatile int* abortp = &s_abort;
+    const int64_t row_base = a.kv.row(a.seq, a.layer, 0);
+
+    if (warp == 4) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            mbar_expect_tx(q_full, Q_BYTES);
+            for (int b = 0; b < NBLK; ++b) tma_load_2d(sQ + b * QBLK, &tmQ, h * D + b * 64, q_row0, q_full);
+            for (int j = lo; j < hi; ++j) {
+                const int n = j - lo, s = n & 1;
+                const uint32_t ph = ((n >> 1) & 1) ^ 1;
+                const int y = (int)(row_base + (int64_t)j * kTwBN);
+                if (!mbar_wait(k_empty(s), ph, abortp)) break;
+                mbar_expect_tx(k_full(s), KV_BYTES);
+                for (int b = 0; b < NBLK; ++b)
+                    tma_load_2d(sK + s * KV_BYTES + b * KBLK, &tmK, kvh * D + b * 64, y, k_full(s));
+                if (!mbar_wait(v_empty(s), ph, abortp)) break;
+                mbar_expect_tx(v_full(s), KV_BYTES);
+                for (int b = 0; b < NBLK; ++b)
+                    tma_load_2d(sV + s * KV_BYTES + b * KBLK, &tmV, kvh * D + b * 64, y, v_full(s));
+            }
+        }
+    } else if (warp == 5) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0 && hi > lo) {
+            constexpr uint32_t IDESC_QK = idesc_bf16(kTwBN, 0);
+            constexpr uint32_t IDESC_PV = idesc_bf16(D, 1);
+            auto issue_qk = [&](int buf, int s) {
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    mma_ss(tmem + buf * kTwBN, smem_desc(sQ + (ks >> 2) * QBLK + (ks & 3) * 32, 16, 1024),
+                           smem_desc(sK + s * KV_BYTES + (ks >> 2) * KBLK + (ks & 3) * 32, 16, 1024), IDESC_QK,
+                           ks > 0 ? 1u : 0u);
+                }
+            };
+            auto issue_pv = [&](int buf, int s, bool accumulate) {
+#pragma unroll
+                for (int ks = 0; ks < kTwBN / 16; ++ks) {
+                    mma_ts(tmem + O_COL0, tmem + buf * kTwBN + ks * 8,
+                           smem_desc(sV + s * KV_BYTES + ks * 16 * 128, KBLK, 1024), IDESC_PV,
+                           (accumulate || ks > 0) ? 1u : 0u);
+                }
+            };
+            bool ok = mbar_wait(q_full, 0, abortp);
+            if (ok) ok = mbar_wait(k_full(0), 0, abortp);
+            if (ok) {
+                fence_after_sync();
+                issue_qk(0, 0);
+                mma_commit(s_full(0));
+                mma_commit(k_empty(0));
+            }
+            for (int j = lo; ok && j < hi; ++j) {
+                const int n = j - lo, s = n & 1;
+                if (j + 1 < hi) {
+                    if (!(ok = mbar_wait(k_full(s ^ 1), ((n + 1) >> 1) & 1, abortp))) break;
+                    fence_after_sync();
+                    issue_qk((n + 1) & 1, s ^ 1);
+                    mma_commit(s_full((n + 1) & 1));
+                    mma_commit(k_empty(s ^ 1));
+                }
+                if (!(ok = mbar_wait(v_full(s), (n >> 1) & 1, abortp))) break;
+                if (!(ok = mbar_wait(p_full, n & 1, abortp))) break;
+                fence_after_sync();
+                issue_pv(n & 1, s, n > 0);
+                mma_commit(pv_done);
+                mma_commit(v_empty(s));
+                if (j == hi - 1) mma_commit(o_final);
+            }
+        }
+    } else if (warp < 4) {
+        // ---------------- softmax: one thread per query row ----------------
+        const int row = warp * 32 + lane;
+        const int qi = q_row0 + row;
+        const bool valid = qi < a.m;
+        int vs = 0, ve = 0;
+        if (valid) a.vis.range(a.base_pos + qi, vs, ve);
+        const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+        const uint32_t tO = tmem + lane_addr + O_COL0;
+        const float c = a.score_scale;
+        const float thr = 8.0f / c;
+        float m_used = -INFINITY, l = 0.0f;
+        bool ok = true;
+        for (int j = lo; j < hi; ++j) {
+            const int n = j - lo, buf = n & 1;
+            const uint32_t tS = tmem + lane_addr + buf * kTwBN;
+            if (!(ok = mbar_wait(s_full(buf), (n >> 1) & 1, abortp))) break;
+            fence_after_sync();
+            uint32_t sr[2][32];
+            tmem_ld32(tS, sr[0]);
+            tmem_ld32(tS + 32, sr[1]);
+            tmem_wait_ld();
+            const int key0 = j * kTwBN;
+            if (key0 < vs || key0 + kTwBN > ve) {
+#pragma unroll
+                for (int cidx = 0; cidx < 2; ++cidx)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int key = key0 + cidx * 32 + i;
+                        if (key < vs || key >= ve) sr[cidx][i] = 0xff800000u;  // -inf
+                    }
+            }
+            float mxa = -INFINITY, mxb = -INFINITY, mxc = -INFINITY, mxd = -INFINITY;
+#pragma unroll
+            for (int cidx = 0; cidx < 2; ++cidx)
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                    mxa = fmaxf(mxa, __uint_as_float(sr[cidx][i]));
+                    mxb = fmaxf(mxb, __uint_as_float(sr[cidx][i + 1]));
+                    mxc = fmaxf(mxc, __uint_as_float(sr[cidx][i + 2]));
+                    mxd = fmaxf(mxd, __uint_as_float(sr[cidx][i + 3]));
+                }
+            const float mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
+            const bool need = mx > m_used + thr;
+            float alpha = 1.0f;
+            if (need) {
+                alpha = ex2((m_used - mx) * c);
+                m_used = mx;
+            }
+            if (n > 0) {
+                // O must be quiet before it is rescaled: PV(j-1) was issued after QK(j)
+                if (!(ok = mbar_wait(pv_done, (n - 1) & 1, abortp))) break;
+                fence_after_sync();
+                if (__any_sync(0xffffffffu, need)) {
+#pragma unroll
+                    for (int cidx = 0; cidx < D / 32; ++cidx) {
+                        uint32_t orow[32];
+                        tmem_ld32(tO + cidx * 32, orow);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
+                        tmem_st32(tO + cidx * 32, orow);
+                    }
+                }
+            }
+            l *= alpha;
+            const float mref = (m_used == -INFINITY) ? 0.0f : m_used;
+            const float neg = -mref * c;
+            float ps0 = 0.0f, ps1 = 0.0f, ps2 = 0.0f, ps3 = 0.0f;
+#pragma unroll
+            for (int cidx = 0; cidx < 2; ++cidx) {
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; i += 2) {
+                    const float p0 = ex2(fmaf(__uint_as_float(sr[cidx][2 * i]), c, neg));
+                    const float p1 = ex2(fmaf(__uint_as_float(sr[cidx][2 * i + 1]), c, neg));
+                    const float p2 = ex2(fmaf(__uint_as_float(sr[cidx][2 * i + 2]), c, neg));
+                    const float p3 = ex2(fmaf(__uint_as_float(sr[cidx][2 * i + 3]), c, neg));
+                    ps0 += p0;
+                    ps1 += p1;
+                    ps2 += p2;
+                    ps3 += p3;
+                    __nv_bfloat162 pa = __floats2bfloat162_rn(p0, p1);
+                    __nv_bfloat162 pb = __floats2bfloat162_rn(p2, p3);
+                    pk[i] = *reinterpret_cast<uint32_t*>(&pa);
+                    pk[i + 1] = *reinterpret_cast<uint32_t*>(&pb);
+                }
+                tmem_st16(tS + cidx * 16, pk);
+            }
+            l += (ps0 + ps1) + (ps2 + ps3);
+            tmem_wait_st();
+            fence_before_sync();
+            mbar_arrive(p_full);
+        }
+        if (ok && hi > lo) ok = mbar_wait(o_final, 0, abortp);
+        if (ok && hi > lo) {
+            fence_after_sync();
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            float* orow_g = a.out + ((int64_t)qi * Hq + h) * D;
+#pragma unroll
+            for (int cidx = 0; cidx < D / 32; ++cidx) {
+                uint32_t orow[32];
+                tmem_ld32(tO + cidx * 32, orow);
+                tmem_wait_ld();
+                if (valid) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        float4 o4 = make_float4(__uint_as_float(orow[i]) * inv, __uint_as_float(orow[i + 1]) * inv,
+                                                __uint_as_float(orow[i + 2]) * inv, __uint_as_float(orow[i + 3]) * inv);
+                        *reinterpret_cast<float4*>(orow_g + cidx * 32 + i) = o4;
+                    }
+                }
+            }
+        }
+    }
+
+    if (s_abort) {
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    if (warp == 5) tmem_dealloc(tmem, 512);
+    if (tid == 0 && s_abort && a.err) atomicExch(a.err, 1);
+}
+
+inline size_t prefill_tc_wide_smem(int D) { return (size_t)(D / 64) * (128 * 128 + 4 * kTwBN * 128) + 1024; }
+
+// tq: [m][q_dim] with a 64 x 128 box; tk / tv: whole cache arrays with a 64 x 64 box
+inline int launch_prefill_tc_wide(const PrefillTcArgs& a, const CUtensorMap& tk, const CUtensorMap& tv, int device,
+                                  cudaStream_t stream, std::string* msg) {
+    CUtensorMap tq;
+    if (!make_tmap_bf16(&tq, a.q, (uint64_t)a.kv.Hq * a.kv.D, (uint64_t)a.m)) {
+        *msg = "cuTensorMapEncodeTiled failed for the query tensor";
+        return 2;
+    }
+    if (a.kv.D != 256) {
+        *msg = "the wide tensor-core prefill kernel is built for head_dim 256";
+        return 5;
+    }
+    static int configured_for = -1;
+    const size_t smem = prefill_tc_wide_smem(256);
+    if (configured_for != device) {
+        cudaError_t e = cudaFuncSetAttribute(prefill_tc_wide_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
+        if (e != cudaSuccess) {
+            *msg = std::string("prefill kernel attribute: ") + cudaGetErrorString(e);
+            return 2;
+        }
+        configured_for = device;
+    }
+    const int n_tiles = (a.m + kTcBM - 1) / kTcBM;
+    prefill_tc_wide_kernel<256><<<n_tiles * a.kv.Hq, kTwThreads, smem, stream>>>(tq, tk, tv, a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        *msg = std::string("prefill kernel launch: ") + cudaGetErrorString(e);
+        return 2;
+    }
+    return 0;
+}
+
+}  // namespace ggr
