@@ -311,6 +311,120 @@ def bench_prefill(torch, dist, args, rank, world, local_rank, peaks):
     return value, ms_per_step, roofline, e2e, clocks, launches
 
 
+def bench_prefill_gemma(torch, args, local_rank, peaks):
+    """Gemma-3-4B-shaped chunked prefill (configs[3]): 34 layers (window 1024 on 5 of every 6), 8 q / 4 kv heads,
+    head_dim 256, context 32768 processed in 2048-token chunks against the accumulated bf16 cache."""
+    import gguf_runner_b200 as g
+    from gguf_runner_b200 import presets
+    S, chunk, L = 32768, 2048, 34
+    cfg = presets.gemma3_4b_prefill(n_layers=L, seq_len=S, device=local_rank)
+    ctx = g.AttnContext(cfg)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1004)
+    # one chunk of inputs per layer kind is reused for every chunk and layer: the cache rows differ per layer
+    q = torch.randn(chunk, cfg.q_dim, generator=gen, device="cuda").to(torch.bfloat16)
+    k = torch.randn(chunk, cfg.kv_dim, generator=gen, device="cuda").to(torch.bfloat16)
+    v = torch.randn(chunk, cfg.kv_dim, generator=gen, device="cuda").to(torch.bfloat16)
+    out = torch.empty(chunk, cfg.q_dim, device="cuda")
+
+    def step():
+        for c0 in range(0, S, chunk):
+            for l in range(L):
+                ctx.prefill(l, c0, q, k, v, out=out)
+
+    step()
+    torch.cuda.synchronize()
+    ctx.set_kernel_timing(True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    attn_ms, attn_n = ctx.kernel_time(0)
+    ctx.set_kernel_timing(False)
+    pairs_global = S * (S + 1) // 2
+    w = 1024
+    pairs_local = sum(min(p + 1, w) for p in range(S))
+    flops = 4.0 * cfg.n_heads * cfg.head_dim * (5 * pairs_global + 29 * pairs_local)
+    achieved = flops / (attn_ms * 1e-3) / 1e12
+    res = {"workload": "Gemma-3-4B-shaped chunked prefill (configs[3]): 34 layers (29 with window 1024, 5 global), 8 q / "
+                       "4 kv heads, head_dim 256, context 32768 in 2048-token chunks, bf16",
+           "tokens_per_s": S / (ms * 1e-3), "ms_per_pass": ms,
+           "roofline": {"bound": "tensor", "kernel": "prefill attention, head_dim 256 (all launches of the pass)",
+                        "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                        "frac": achieved / peaks["bf16_tflops_sustained"], "flops_per_pass": flops,
+                        "attention_ms_per_pass": attn_ms, "launches": attn_n, "peak_source": peaks["source"]}}
+    ctx.close()
+    torch.cuda.empty_cache()
+    return res
+
+
+def bench_decode_cfg1(torch, args, local_rank, peaks):
+    """Qwen3-0.6B-shaped decode (configs[0]): 28 layers, 16 q / 8 kv heads, T=2048, batch 1, f32 cache.
+    16.8 MB per layer is ~2.6 us of HBM time, below a kernel launch: the step is launch-bound, so the
+    28-layer step is timed both as plain launches and replayed from a CUDA graph."""
+    import gguf_runner_b200 as g
+    from gguf_runner_b200 import presets
+    from gguf_runner_b200.binding import KV_F32
+    T, L = 2048, 28
+    cfg = presets.qwen3_0p6b_decode(n_layers=L, seq_len=T, kv_format=KV_F32, device=local_rank)
+    ctx = g.AttnContext(cfg)
+    fill_cache_random(torch, ctx, 1001)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(2001)
+    q = torch.randn(L, 1, cfg.q_dim, generator=gen, device="cuda")
+    k = torch.randn(L, 1, cfg.kv_dim, generator=gen, device="cuda")
+    v = torch.randn(L, 1, cfg.kv_dim, generator=gen, device="cuda")
+    out = torch.empty(L, 1, cfg.q_dim, device="cuda")
+    pos = [T - 1]
+
+    def step():
+        for l in range(L):
+            ctx.decode(l, pos, q[l], k[l], v[l], out=out[l])
+
+    def timed(fn, reps):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    plain_ms = timed(step, 20)
+    graph_ms = None
+    try:
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            step()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                step()
+        torch.cuda.synchronize()
+        graph_ms = timed(graph.replay, 50)
+    except Exception as e:  # capture is an optimisation of the host loop, not part of the path
+        graph_ms = None
+        graph_err = repr(e)[:200]
+    bytes_per_step = L * T * cfg.kv_dim * 4 * 2
+    best = min(x for x in (plain_ms, graph_ms) if x)
+    res = {"workload": "Qwen3-0.6B-shaped decode (configs[0]): 28 layers, 16 q / 8 kv heads, T=2048, batch 1, f32 cache",
+           "ms_per_step_plain_launches": plain_ms, "ms_per_step_cuda_graph": graph_ms,
+           "tokens_per_s": 1.0 / (best * 1e-3),
+           "roofline": {"bound": "hbm", "achieved": bytes_per_step / (best * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
+                        "unit": "GB/s", "frac": bytes_per_step / (best * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                        "bytes_per_step": bytes_per_step, "note": "whole 28-layer step (launch-bound), not one kernel"}}
+    if graph_ms is None:
+        res["cuda_graph_error"] = graph_err
+    ctx.close()
+    torch.cuda.empty_cache()
+    return res
+
+
 def bench_decode_cfg3(torch, args, local_rank, peaks, B=8):
     """Qwen3-30B-A3B-shaped decode: 48 layers, 32 q / 4 kv heads, T=32768, bf16 cache, one new token per step."""
     import gguf_runner_b200 as g
@@ -480,6 +594,10 @@ def run_ours(args):
     if not args.no_extras:
         if world == 1:
             extras["decode"] = bench_decode_cfg3(torch, args, local_rank, peaks, B=args.decode_batch)
+            if args.all_configs:
+                extras["decode_sweep"] = [bench_decode_cfg3(torch, args, local_rank, peaks, B=b) for b in (1, 32)]
+                extras["prefill_chunked_gemma"] = bench_prefill_gemma(torch, args, local_rank, peaks)
+                extras["decode_small_f32"] = bench_decode_cfg1(torch, args, local_rank, peaks)
         else:
             extras["decode_seq_split"] = bench_decode_seq_split(torch, dist, args, rank, world, local_rank, peaks)
 
@@ -514,6 +632,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the decode extras")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--decode-batch", type=int, default=8)
+    ap.add_argument("--all-configs", action="store_true", help="also run configs[0], configs[2] at B=1/32 and configs[3]")
     ap.add_argument("--cpu-stride", type=int, default=16)
     ap.add_argument("--case", default=None, help="run a small profiling case (prefill_small, decode_small) and exit")
     args = ap.parse_args()

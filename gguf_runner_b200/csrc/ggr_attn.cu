@@ -63,6 +63,9 @@ struct ggr_attn_ctx {
     // error word the kernels raise when a bounded wait runs out (mapped pinned host memory)
     int* h_err = nullptr;
     int* d_err = nullptr;
+    // copy streams and events of the pipelined host-buffer prefill
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;
+    std::vector<cudaEvent_t> ev_in, ev_done;
     // optional per-kernel timing: event pairs per kind (0 attention, 1 rope/append, 2 merge)
     bool timing = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> ev[3];
@@ -187,6 +190,19 @@ struct LaunchTimer {
         if (stop) cudaEventRecord(stop, c->stream);
     }
 };
+
+int ensure_copy_streams(ggr_attn_ctx* c, int n_pieces) {
+    if (!c->copy_in) CUDA_TRY(c, cudaStreamCreateWithFlags(&c->copy_in, cudaStreamNonBlocking));
+    if (!c->copy_out) CUDA_TRY(c, cudaStreamCreateWithFlags(&c->copy_out, cudaStreamNonBlocking));
+    while ((int)c->ev_in.size() < n_pieces) {
+        cudaEvent_t a = nullptr, b = nullptr;
+        CUDA_TRY(c, cudaEventCreateWithFlags(&a, cudaEventDisableTiming));
+        CUDA_TRY(c, cudaEventCreateWithFlags(&b, cudaEventDisableTiming));
+        c->ev_in.push_back(a);
+        c->ev_done.push_back(b);
+    }
+    return GGR_OK;
+}
 
 int check_layer(ggr_attn_ctx* c, int layer) {
     if (layer < 0 || layer >= c->cfg.n_layers) return fail(c, GGR_ERR_RANGE, "layer outside the cache");
@@ -521,13 +537,18 @@ int prefill_common(ggr_attn_ctx* c, int layer, int seq, int base_pos, int m, con
         }
     }
     const size_t es = in_dtype == GGR_DTYPE_BF16 ? 2 : 4;
-    const void *dq, *dk, *dv;
-    if ((rc = stage_in(c, 0, q, (size_t)m * c->q_dim * es, ptr_kind, &dq))) return rc;
-    if ((rc = stage_in(c, 1, k, (size_t)m * c->kv_dim * es, ptr_kind, &dk))) return rc;
-    if ((rc = stage_in(c, 2, v, (size_t)m * c->kv_dim * es, ptr_kind, &dv))) return rc;
+    const bool host = ptr_kind == GGR_PTR_HOST;
+    const unsigned char *dq = static_cast<const unsigned char*>(q), *dk = static_cast<const unsigned char*>(k),
+                        *dv = static_cast<const unsigned char*>(v);
     float* dout = out;
-    if (ptr_kind == GGR_PTR_HOST) {
+    if (host) {
+        if ((rc = ensure(c, &c->d_stage[0], &c->stage_cap[0], (size_t)m * c->q_dim * es))) return rc;
+        if ((rc = ensure(c, &c->d_stage[1], &c->stage_cap[1], (size_t)m * c->kv_dim * es))) return rc;
+        if ((rc = ensure(c, &c->d_stage[2], &c->stage_cap[2], (size_t)m * c->kv_dim * es))) return rc;
         if ((rc = ensure(c, &c->d_stage[3], &c->stage_cap[3], (size_t)m * c->q_dim * sizeof(float)))) return rc;
+        dq = c->d_stage[0];
+        dk = c->d_stage[1];
+        dv = c->d_stage[2];
         dout = reinterpret_cast<float*>(c->d_stage[3]);
     }
 
@@ -538,72 +559,104 @@ int prefill_common(ggr_attn_ctx* c, int layer, int seq, int base_pos, int m, con
     if ((rc = ensure(c, &c->d_qrot, &c->qrot_cap, tc ? (size_t)1 : (size_t)m * c->q_dim))) return rc;
     if (tc && (rc = ensure(c, &c->d_qrot_h, &c->qrot_h_cap, (size_t)m * c->q_dim))) return rc;
 
-    // rope + append for every row first; causality is enforced by the mask, not by write order
-    const int max_items = 65535;
-    for (int i0 = 0; i0 < m; i0 += max_items) {
-        const int n = std::min(max_items, m - i0);
-        Items it{};
-        it.mode = 1;
-        it.seq0 = seq;
-        it.base_pos = base_pos + i0;
-        it.n = n;
-        const unsigned char* qc = reinterpret_cast<const unsigned char*>(dq) + (size_t)i0 * c->q_dim * es;
-        const unsigned char* kc = reinterpret_cast<const unsigned char*>(dk) + (size_t)i0 * c->kv_dim * es;
-        const unsigned char* vc = reinterpret_cast<const unsigned char*>(dv) + (size_t)i0 * c->kv_dim * es;
-        rc = launch_rope_append(c, layer, it, RF_ROTATE | RF_WRITE_Q | RF_APPEND, in_dtype == GGR_DTYPE_BF16, qc, kc, vc,
-                                tc ? nullptr : c->d_qrot + (size_t)i0 * c->q_dim,
-                                tc ? c->d_qrot_h + (size_t)i0 * c->q_dim : nullptr, nullptr);
-        if (rc) return rc;
-    }
-    if (tc) {
-        PrefillTcArgs a{};
-        a.kv = c->kv;
-        a.vis = visibility(c, layer);
-        a.layer = layer;
-        a.seq = seq;
-        a.base_pos = base_pos;
-        a.m = m;
-        a.q = c->d_qrot_h;
-        a.out = dout;
-        a.score_scale = (c->cfg.scale_mode == GGR_SCALE_SCORE ? c->attn_scale : 1.0f) * kLog2e;
-        a.err = c->d_err;
-        std::string msg;
-        {
-            LaunchTimer t(c, 0);
-            rc = wide ? launch_prefill_tc_wide(a, c->tmK64, c->tmV64, c->cfg.device, c->stream, &msg)
-                      : launch_prefill_tc(a, c->tmK, c->tmV, c->cfg.device, c->stream, &msg);
-        }
-        if (rc) return fail(c, rc, msg);
-        c->launches++;
-    } else {
-        for (int i0 = 0; i0 < m; i0 += max_items) {
-            const int n = std::min(max_items, m - i0);
+    // rope + append of rows [i0, i0 + n): causality is enforced by the mask, not by write order
+    auto append_rows = [&](int i0, int n) -> int {
+        const int max_items = 65535;
+        for (int j0 = i0; j0 < i0 + n; j0 += max_items) {
+            const int cnt = std::min(max_items, i0 + n - j0);
             Items it{};
             it.mode = 1;
             it.seq0 = seq;
-            it.base_pos = base_pos + i0;
-            it.n = n;
-            int t_max = 1;
+            it.base_pos = base_pos + j0;
+            it.n = cnt;
+            int r = launch_rope_append(c, layer, it, RF_ROTATE | RF_WRITE_Q | RF_APPEND, in_dtype == GGR_DTYPE_BF16,
+                                       dq + (size_t)j0 * c->q_dim * es, dk + (size_t)j0 * c->kv_dim * es,
+                                       dv + (size_t)j0 * c->kv_dim * es, tc ? nullptr : c->d_qrot + (size_t)j0 * c->q_dim,
+                                       tc ? c->d_qrot_h + (size_t)j0 * c->q_dim : nullptr, nullptr);
+            if (r) return r;
+        }
+        return GGR_OK;
+    };
+    // attention of rows [i0, i0 + n) over the cache (their own rows must already be appended)
+    auto attend_rows = [&](int i0, int n) -> int {
+        if (tc) {
+            PrefillTcArgs a{};
+            a.kv = c->kv;
+            a.vis = visibility(c, layer);
+            a.layer = layer;
+            a.seq = seq;
+            a.base_pos = base_pos + i0;
+            a.m = n;
+            a.q = c->d_qrot_h + (size_t)i0 * c->q_dim;
+            a.out = dout + (size_t)i0 * c->q_dim;
+            a.score_scale = (c->cfg.scale_mode == GGR_SCALE_SCORE ? c->attn_scale : 1.0f) * kLog2e;
+            a.err = c->d_err;
+            std::string msg;
+            int r;
             {
-                // widest visible range of the chunk (ranges end at pos + 1 or at a block end)
-                int vs, ve;
-                visible_host(c, layer, base_pos + i0 + n - 1, &vs, &ve);
-                t_max = std::max(1, ve - vs);
-                visible_host(c, layer, base_pos + i0, &vs, &ve);
-                t_max = std::max(t_max, ve - vs);
+                LaunchTimer t(c, 0);
+                r = wide ? launch_prefill_tc_wide(a, c->tmK64, c->tmV64, c->cfg.device, c->stream, &msg)
+                         : launch_prefill_tc(a, c->tmK, c->tmV, c->cfg.device, c->stream, &msg);
             }
-            rc = launch_attention(c, layer, it, t_max, c->d_qrot + (size_t)i0 * c->q_dim, dout + (size_t)i0 * c->q_dim,
-                                  nullptr, false);
-            if (rc) return rc;
+            if (r) return fail(c, r, msg);
+            c->launches++;
+            return GGR_OK;
         }
+        const int max_items = 65535;
+        for (int j0 = i0; j0 < i0 + n; j0 += max_items) {
+            const int cnt = std::min(max_items, i0 + n - j0);
+            Items it{};
+            it.mode = 1;
+            it.seq0 = seq;
+            it.base_pos = base_pos + j0;
+            it.n = cnt;
+            // widest visible range of the rows (ranges end at pos + 1 or at a block end)
+            int vs, ve;
+            visible_host(c, layer, base_pos + j0 + cnt - 1, &vs, &ve);
+            int t_max = std::max(1, ve - vs);
+            visible_host(c, layer, base_pos + j0, &vs, &ve);
+            t_max = std::max(t_max, ve - vs);
+            int r = launch_attention(c, layer, it, t_max, c->d_qrot + (size_t)j0 * c->q_dim, dout + (size_t)j0 * c->q_dim,
+                                     nullptr, false);
+            if (r) return r;
+        }
+        return GGR_OK;
+    };
+
+    if (!host) {
+        if ((rc = append_rows(0, m))) return rc;
+        return attend_rows(0, m);
     }
-    if (ptr_kind == GGR_PTR_HOST) {
-        CUDA_TRY(c, cudaMemcpyAsync(out, dout, (size_t)m * c->q_dim * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
-        CUDA_TRY(c, cudaStreamSynchronize(c->stream));
-        if (c->h_err && *c->h_err) {
-            *c->h_err = 0;
-            return fail(c, GGR_ERR_TIMEOUT, "a bounded wait inside the prefill kernel ran out");
-        }
+
+    // Host buffers: rows move in pieces so that the copy-in of piece p+1, the kernels of piece p and the
+    // copy-out of piece p-1 overlap (three streams). A staged image block needs all its rows appended
+    // before any row attends, so it is one piece.
+    const int piece = block_mode ? m : 1024;
+    const int n_pieces = (m + piece - 1) / piece;
+    if ((rc = ensure_copy_streams(c, n_pieces))) return rc;
+    for (int p = 0; p < n_pieces; ++p) {
+        const int i0 = p * piece, n = std::min(piece, m - i0);
+        const size_t qo = (size_t)i0 * c->q_dim * es, ko = (size_t)i0 * c->kv_dim * es;
+        CUDA_TRY(c, cudaMemcpyAsync(c->d_stage[0] + qo, static_cast<const unsigned char*>(q) + qo, (size_t)n * c->q_dim * es,
+                                    cudaMemcpyHostToDevice, c->copy_in));
+        CUDA_TRY(c, cudaMemcpyAsync(c->d_stage[1] + ko, static_cast<const unsigned char*>(k) + ko, (size_t)n * c->kv_dim * es,
+                                    cudaMemcpyHostToDevice, c->copy_in));
+        CUDA_TRY(c, cudaMemcpyAsync(c->d_stage[2] + ko, static_cast<const unsigned char*>(v) + ko, (size_t)n * c->kv_dim * es,
+                                    cudaMemcpyHostToDevice, c->copy_in));
+        CUDA_TRY(c, cudaEventRecord(c->ev_in[p], c->copy_in));
+        CUDA_TRY(c, cudaStreamWaitEvent(c->stream, c->ev_in[p], 0));
+        if ((rc = append_rows(i0, n))) return rc;
+        if ((rc = attend_rows(i0, n))) return rc;
+        CUDA_TRY(c, cudaEventRecord(c->ev_done[p], c->stream));
+        CUDA_TRY(c, cudaStreamWaitEvent(c->copy_out, c->ev_done[p], 0));
+        CUDA_TRY(c, cudaMemcpyAsync(out + (size_t)i0 * c->q_dim, dout + (size_t)i0 * c->q_dim,
+                                    (size_t)n * c->q_dim * sizeof(float), cudaMemcpyDeviceToHost, c->copy_out));
+    }
+    CUDA_TRY(c, cudaStreamSynchronize(c->copy_out));
+    CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    if (c->h_err && *c->h_err) {
+        *c->h_err = 0;
+        return fail(c, GGR_ERR_TIMEOUT, "a bounded wait inside the prefill kernel ran out");
     }
     return GGR_OK;
 }
@@ -790,6 +843,10 @@ void ggr_attn_destroy(ggr_attn_ctx* c) {
     cudaFree(c->d_counters);
     for (auto* p : c->d_stage) cudaFree(p);
     if (c->h_err) cudaFreeHost(c->h_err);
+    for (auto e : c->ev_in) cudaEventDestroy(e);
+    for (auto e : c->ev_done) cudaEventDestroy(e);
+    if (c->copy_in) cudaStreamDestroy(c->copy_in);
+    if (c->copy_out) cudaStreamDestroy(c->copy_out);
     for (auto& pool : c->ev)
         for (auto& pr : pool) {
             cudaEventDestroy(pr.first);

@@ -9,7 +9,7 @@
 
 namespace ggr {
 
-constexpr uint32_t kTcSpinLimit = 1u << 24;
+constexpr uint32_t kTcSpinLimit = 1u << 18;
 
 namespace tc {
 
@@ -33,14 +33,25 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: false when the limit ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the limit ran out or another role already gave up. try_wait parks the
+// thread in hardware for up to the hinted time instead of spinning on shared memory, which would
+// compete with the tensor core's operand reads; the loop bounds the total wait to about a second.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_test(bar, parity)) return true;
     for (uint32_t it = 0; it < kTcSpinLimit; ++it) {
-        if (mbar_test(bar, parity)) return true;
-        if ((it & 255u) == 255u) {
-            if (*abort_flag) return false;
-            __nanosleep(32);
-        }
+        if (mbar_try(bar, parity, 4000u)) return true;
+        if ((it & 15u) == 15u && *abort_flag) return false;
     }
     *abort_flag = 1;
     return false;
