@@ -75,6 +75,9 @@ struct ggr_attn_ctx {
 namespace {
 
 thread_local std::string g_create_err;
+#ifdef GGR_TC_TRACE
+long long* g_tc_trace = nullptr;
+#endif
 
 int fail(ggr_attn_ctx* c, int status, const std::string& msg) {
     if (c) c->err = msg;
@@ -591,6 +594,9 @@ int prefill_common(ggr_attn_ctx* c, int layer, int seq, int base_pos, int m, con
             a.out = dout + (size_t)i0 * c->q_dim;
             a.score_scale = (c->cfg.scale_mode == GGR_SCALE_SCORE ? c->attn_scale : 1.0f) * kLog2e;
             a.err = c->d_err;
+#ifdef GGR_TC_TRACE
+            a.trace = g_tc_trace;
+#endif
             std::string msg;
             int r;
             {
@@ -1309,3 +1315,8 @@ extern "C" int ggr_attn_attention_tokens_static(ggr_attn_ctx* c, int32_t layer, 
     }
     return launch_simt(c, a, grid, p);
 }
+
+#ifdef GGR_TC_TRACE
+// diagnostic builds only: device buffer of 32 int64 cycle counters written by CTA 0 of the prefill kernel
+extern "C" void ggr_attn_debug_set_trace(long long* device_ptr) { g_tc_trace = device_ptr; }
+#endif

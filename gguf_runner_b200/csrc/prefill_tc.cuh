@@ -40,6 +40,9 @@ struct PrefillTcArgs {
     float* out;              // [m][Hq*D]
     float score_scale;       // (1/sqrt(D) or 1) * log2(e)
     int* err;                // device-visible error word (mapped host memory)
+#ifdef GGR_TC_TRACE
+    long long* trace;        // cycle counters of CTA 0 (diagnostic builds only)
+#endif
 };
 
 constexpr int kTcBM = 128;       // query rows per tile
@@ -137,7 +140,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
     if (warp >= 8) {
       // control warpgroup: gives registers up; warps 10 and 11 have no role
-      reg_dec40();
+      reg_release();
       if (warp == 8) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
@@ -164,69 +167,94 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
       } else if (warp == 9) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0 && hi > lo) {
+        if (hi > lo) {  // the whole warp runs the loop, one elected lane issues
             constexpr uint32_t IDESC_QK = idesc_bf16(kTcBN, 0);
             constexpr uint32_t IDESC_PV = idesc_bf16(D, 1);
+            // Descriptors are built once; an MMA adds its byte offset (in 16-byte units) to the start
+            // address field, so the issue loop is a few integer adds per instruction. (Rebuilding the
+            // 64-bit descriptors per MMA under the 40-register cap made every issue cost ~110 cycles.)
+            const uint64_t dQ = smem_desc(sQ, 16, 1024), dK = smem_desc(sK, 16, 1024);
+            const uint64_t dV = smem_desc(sV, BLK_BYTES, 1024);
             auto issue_qk = [&](int t, int s) {
                 // S_t = Q_t K^T: both operands K-major, 16 head elements per instruction
+                const uint64_t a0 = dQ + (uint64_t)((t * TILE_BYTES) >> 4), b0 = dK + (uint64_t)((s * TILE_BYTES) >> 4);
+                const uint32_t d = tmem + t * 128;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint32_t off = (ks >> 2) * BLK_BYTES + (ks & 3) * 32;
-                    mma_ss(tmem + t * 128, smem_desc(sQ + t * TILE_BYTES + off, 16, 1024),
-                           smem_desc(sK + s * TILE_BYTES + off, 16, 1024), IDESC_QK, ks > 0 ? 1u : 0u);
+                    const uint32_t off = ((ks >> 2) * BLK_BYTES + (ks & 3) * 32) >> 4;
+                    mma_ss_e(d, a0 + off, b0 + off, IDESC_QK, ks > 0 ? 1u : 0u);
                 }
             };
             auto issue_pv = [&](int t, int s, bool accumulate) {
                 // O_t += P_t V: P from TMEM (two bf16 per column), V MN-major, 16 keys per instruction
+                const uint64_t b0 = dV + (uint64_t)((s * TILE_BYTES) >> 4);
+                const uint32_t d = tmem + O_COL0 + t * D, p0 = tmem + t * 128;
+                mma_ts_e(d, p0, b0, IDESC_PV, accumulate ? 1u : 0u);
 #pragma unroll
-                for (int ks = 0; ks < kTcBN / 16; ++ks) {
-                    mma_ts(tmem + O_COL0 + t * D, tmem + t * 128 + ks * 8,
-                           smem_desc(sV + s * TILE_BYTES + ks * 16 * 128, BLK_BYTES, 1024), IDESC_PV,
-                           (accumulate || ks > 0) ? 1u : 0u);
-                }
+                for (int ks = 1; ks < kTcBN / 16; ++ks) mma_ts_e(d, p0 + ks * 8, b0 + (uint64_t)((ks * 16 * 128) >> 4), IDESC_PV, 1u);
             };
-            bool ok = mbar_wait(q_full, 0, abortp);
-            if (ok) ok = mbar_wait(k_full(0), 0, abortp);
+#ifdef GGR_TC_TRACE
+            long long tr_v = 0, tr_p0 = 0, tr_p1 = 0, tr_k = 0, tr_issue = 0, tr_issue_qk = 0, tr_t0 = clock64(), tr_x;
+#define TRACE_ADD(var) do { long long now_ = clock64(); var += now_ - tr_x; tr_x = now_; } while (0)
+#define TRACE_MARK() tr_x = clock64()
+#else
+#define TRACE_ADD(var)
+#define TRACE_MARK()
+#endif
+            bool ok = mbar_wait_warp(q_full, 0, abortp);
+            if (ok) ok = mbar_wait_warp(k_full(0), 0, abortp);
             if (ok) {
                 fence_after_sync();
                 for (int t = 0; t < 2; ++t)
                     if (active(t, lo)) {
                         issue_qk(t, 0);
-                        mma_commit(s_full(t));
+                        mma_commit_e(s_full(t));
                     }
-                mma_commit(k_empty(0));
+                mma_commit_e(k_empty(0));
             }
             for (int j = lo; ok && j < hi; ++j) {
                 const int n = j - lo, s = n & 1;
                 const bool has_next = j + 1 < hi;
-                if (!(ok = mbar_wait(v_full(s), (n >> 1) & 1, abortp))) break;
+                TRACE_MARK();
+                if (!(ok = mbar_wait_warp(v_full(s), (n >> 1) & 1, abortp))) break;
+                TRACE_ADD(tr_v);
                 bool next_k_ready = false;
                 for (int t = 0; t < 2 && ok; ++t) {
                     if (active(t, j)) {
-                        if (!(ok = mbar_wait(p_full(t), (j - lo_t[t]) & 1, abortp))) break;
+                        if (!(ok = mbar_wait_warp(p_full(t), (j - lo_t[t]) & 1, abortp))) break;
+                        if (t == 0) { TRACE_ADD(tr_p0); } else { TRACE_ADD(tr_p1); }
                         fence_after_sync();
                         issue_pv(t, s, j > lo_t[t]);
-                        if (j == hi_t[t] - 1) mma_commit(o_final(t));
+                        if (j == hi_t[t] - 1) mma_commit_e(o_final(t));
+                        TRACE_ADD(tr_issue);
                     }
                     if (has_next && active(t, j + 1)) {
                         if (!next_k_ready) {
-                            if (!(ok = mbar_wait(k_full(s ^ 1), ((n + 1) >> 1) & 1, abortp))) break;
+                            if (!(ok = mbar_wait_warp(k_full(s ^ 1), ((n + 1) >> 1) & 1, abortp))) break;
+                            TRACE_ADD(tr_k);
                             fence_after_sync();
                             next_k_ready = true;
                         }
                         issue_qk(t, s ^ 1);
-                        mma_commit(s_full(t));
+                        mma_commit_e(s_full(t));
+                        TRACE_ADD(tr_issue_qk);
                     }
                 }
                 if (!ok) break;
-                mma_commit(v_empty(s));
-                if (has_next) mma_commit(k_empty(s ^ 1));
+                mma_commit_e(v_empty(s));
+                if (has_next) mma_commit_e(k_empty(s ^ 1));
             }
+#ifdef GGR_TC_TRACE
+            if (blockIdx.x == 0 && a.trace) {
+                a.trace[0] = clock64() - tr_t0; a.trace[1] = tr_v; a.trace[2] = tr_p0; a.trace[3] = tr_p1;
+                a.trace[4] = tr_k; a.trace[5] = tr_issue; a.trace[6] = hi - lo; a.trace[7] = tr_issue_qk;
+            }
+#endif
         }
       }
     } else {
         // ---------------- softmax warps: one thread per query row ----------------
-        reg_inc232();
+        reg_acquire();
         const int t = warp >> 2;
         const int row = (warp & 3) * 32 + lane;
         const int qi = q_row0 + t * kTcBM + row;
@@ -241,14 +269,20 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         float m_used = -INFINITY, l = 0.0f;
         bool ok = true;
         const int n_t = hi_t[t] - lo_t[t];
+#ifdef GGR_TC_TRACE
+        long long ts_wait = 0, ts_ld = 0, ts_max = 0, ts_resc = 0, ts_exp = 0, ts_t0 = clock64(), tr_x;
+#endif
         for (int j = lo_t[t]; j < hi_t[t]; ++j) {
             const int k = j - lo_t[t];
+            TRACE_MARK();
             if (!(ok = mbar_wait(s_full(t), k & 1, abortp))) break;
+            TRACE_ADD(ts_wait);
             fence_after_sync();
             uint32_t sr[4][32];
 #pragma unroll
             for (int cidx = 0; cidx < 4; ++cidx) tmem_ld32(tS + cidx * 32, sr[cidx]);
             tmem_wait_ld();
+            TRACE_ADD(ts_ld);
             const int key0 = j * kTcBN;
             if (key0 < vs || key0 + kTcBN > ve) {
 #pragma unroll
@@ -270,6 +304,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                     mxd = fmaxf(mxd, __uint_as_float(sr[cidx][i + 3]));
                 }
             const float mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
+            TRACE_ADD(ts_max);
             // lazy rescale of the running output
             const bool need = mx > m_used + thr;
             float alpha = 1.0f;
@@ -289,6 +324,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 }
             }
             l *= alpha;
+            TRACE_ADD(ts_resc);
             const float mref = (m_used == -INFINITY) ? 0.0f : m_used;
             const float neg = -mref * c;
             float ps0 = 0.0f, ps1 = 0.0f, ps2 = 0.0f, ps3 = 0.0f;
@@ -317,7 +353,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             tmem_wait_st();
             fence_before_sync();
             mbar_arrive(p_full(t));
+            TRACE_ADD(ts_exp);
         }
+#ifdef GGR_TC_TRACE
+        if (blockIdx.x == 0 && a.trace && (tid & 127) == 0) {
+            long long* o = a.trace + 8 + t * 8;
+            o[0] = clock64() - ts_t0; o[1] = ts_wait; o[2] = ts_ld; o[3] = ts_max; o[4] = ts_resc; o[5] = ts_exp; o[6] = n_t;
+        }
+#endif
         if (ok && n_t > 0) ok = mbar_wait(o_final(t), 0, abortp);
         if (ok && n_t > 0) {
             fence_after_sync();

@@ -118,49 +118,51 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         }
     } else if (warp == 5) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0 && hi > lo) {
+        if (hi > lo) {  // the whole warp runs the loop, one elected lane issues
             constexpr uint32_t IDESC_QK = idesc_bf16(kTwBN, 0);
             constexpr uint32_t IDESC_PV = idesc_bf16(D, 1);
+            const uint64_t dQ = smem_desc(sQ, 16, 1024), dK = smem_desc(sK, 16, 1024), dV = smem_desc(sV, KBLK, 1024);
             auto issue_qk = [&](int buf, int s) {
+                const uint64_t b0 = dK + (uint64_t)((s * KV_BYTES) >> 4);
+                const uint32_t d = tmem + buf * kTwBN;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
-                    mma_ss(tmem + buf * kTwBN, smem_desc(sQ + (ks >> 2) * QBLK + (ks & 3) * 32, 16, 1024),
-                           smem_desc(sK + s * KV_BYTES + (ks >> 2) * KBLK + (ks & 3) * 32, 16, 1024), IDESC_QK,
-                           ks > 0 ? 1u : 0u);
+                    mma_ss_e(d, dQ + (uint64_t)(((ks >> 2) * QBLK + (ks & 3) * 32) >> 4),
+                           b0 + (uint64_t)(((ks >> 2) * KBLK + (ks & 3) * 32) >> 4), IDESC_QK, ks > 0 ? 1u : 0u);
                 }
             };
             auto issue_pv = [&](int buf, int s, bool accumulate) {
+                const uint64_t b0 = dV + (uint64_t)((s * KV_BYTES) >> 4);
+                const uint32_t p0 = tmem + buf * kTwBN;
+                mma_ts_e(tmem + O_COL0, p0, b0, IDESC_PV, accumulate ? 1u : 0u);
 #pragma unroll
-                for (int ks = 0; ks < kTwBN / 16; ++ks) {
-                    mma_ts(tmem + O_COL0, tmem + buf * kTwBN + ks * 8,
-                           smem_desc(sV + s * KV_BYTES + ks * 16 * 128, KBLK, 1024), IDESC_PV,
-                           (accumulate || ks > 0) ? 1u : 0u);
-                }
+                for (int ks = 1; ks < kTwBN / 16; ++ks)
+                    mma_ts_e(tmem + O_COL0, p0 + ks * 8, b0 + (uint64_t)((ks * 16 * 128) >> 4), IDESC_PV, 1u);
             };
-            bool ok = mbar_wait(q_full, 0, abortp);
-            if (ok) ok = mbar_wait(k_full(0), 0, abortp);
+            bool ok = mbar_wait_warp(q_full, 0, abortp);
+            if (ok) ok = mbar_wait_warp(k_full(0), 0, abortp);
             if (ok) {
                 fence_after_sync();
                 issue_qk(0, 0);
-                mma_commit(s_full(0));
-                mma_commit(k_empty(0));
+                mma_commit_e(s_full(0));
+                mma_commit_e(k_empty(0));
             }
             for (int j = lo; ok && j < hi; ++j) {
                 const int n = j - lo, s = n & 1;
                 if (j + 1 < hi) {
-                    if (!(ok = mbar_wait(k_full(s ^ 1), ((n + 1) >> 1) & 1, abortp))) break;
+                    if (!(ok = mbar_wait_warp(k_full(s ^ 1), ((n + 1) >> 1) & 1, abortp))) break;
                     fence_after_sync();
                     issue_qk((n + 1) & 1, s ^ 1);
-                    mma_commit(s_full((n + 1) & 1));
-                    mma_commit(k_empty(s ^ 1));
+                    mma_commit_e(s_full((n + 1) & 1));
+                    mma_commit_e(k_empty(s ^ 1));
                 }
-                if (!(ok = mbar_wait(v_full(s), (n >> 1) & 1, abortp))) break;
-                if (!(ok = mbar_wait(p_full, n & 1, abortp))) break;
+                if (!(ok = mbar_wait_warp(v_full(s), (n >> 1) & 1, abortp))) break;
+                if (!(ok = mbar_wait_warp(p_full, n & 1, abortp))) break;
                 fence_after_sync();
                 issue_pv(n & 1, s, n > 0);
-                mma_commit(pv_done);
-                mma_commit(v_empty(s));
-                if (j == hi - 1) mma_commit(o_final);
+                mma_commit_e(pv_done);
+                mma_commit_e(v_empty(s));
+                if (j == hi - 1) mma_commit_e(o_final);
             }
         }
     } else if (warp < 4) {

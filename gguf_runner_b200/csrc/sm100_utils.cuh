@@ -100,17 +100,53 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
         : "memory");
 }
 
+// Warp-uniform issue: every lane of the issuing warp runs the loop (so the descriptors live in
+// uniform registers and cost no per-lane work) and one elected lane executes the instruction. With a
+// single divergent thread issuing, each tcgen05.mma took ~128 cycles to get out while the other warps
+// kept the ALU / MUFU pipes busy; issued this way it takes the 64 cycles the tensor core needs.
+__device__ __forceinline__ void mma_ss_e(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "elect.sync _|q, 0xffffffff;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void mma_ts_e(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "elect.sync _|q, 0xffffffff;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit_e(uint32_t bar) {
+    asm volatile(
+        "{\n\t.reg .pred q;\n\t"
+        "elect.sync _|q, 0xffffffff;\n\t"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+        ::"r"(bar)
+        : "memory");
+}
+// bounded wait by a whole warp; the result is the same on every lane
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    const bool ok = mbar_wait(bar, parity, abort_flag);
+    return __all_sync(0xffffffffu, ok);
+}
+
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-// Warpgroup-wide register re-allocation: the control warps give registers up, the softmax warps take them.
-// 128 * 40 + 256 * 232 = 64512 registers: the 384-thread launch allocation (168 each) exactly, leaving
-// the rest of the 64 K file untouched. A split that needs the whole file (64 / 224) never completed
-// its setmaxnreg.inc on B200 and the kernel hung.
-__device__ __forceinline__ void reg_dec40() { asm volatile("setmaxnreg.dec.sync.aligned.u32 40;"); }
-__device__ __forceinline__ void reg_inc232() { asm volatile("setmaxnreg.inc.sync.aligned.u32 232;"); }
+// Warpgroup-wide register re-allocation in a 384-thread CTA launched with 168 registers per thread:
+// the control warpgroup shrinks to 56, which frees (168 - 56) * 128 = 14336 registers, exactly what the
+// two softmax warpgroups need to grow to 224 ((224 - 168) * 256). setmaxnreg.inc blocks until the pool
+// holds enough registers: a 64 / 224 split frees only 13312, never completes, and hung the kernel.
+__device__ __forceinline__ void reg_release() { asm volatile("setmaxnreg.dec.sync.aligned.u32 56;"); }
+__device__ __forceinline__ void reg_acquire() { asm volatile("setmaxnreg.inc.sync.aligned.u32 224;"); }
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
