@@ -297,11 +297,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
             for (int cidx = 0; cidx < 4; ++cidx)
 #pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    mxa = fmaxf(mxa, __uint_as_float(sr[cidx][i]));
-                    mxb = fmaxf(mxb, __uint_as_float(sr[cidx][i + 1]));
-                    mxc = fmaxf(mxc, __uint_as_float(sr[cidx][i + 2]));
-                    mxd = fmaxf(mxd, __uint_as_float(sr[cidx][i + 3]));
+                for (int i = 0; i < 32; i += 8) {
+                    mxa = max3(mxa, __uint_as_float(sr[cidx][i]), __uint_as_float(sr[cidx][i + 1]));
+                    mxb = max3(mxb, __uint_as_float(sr[cidx][i + 2]), __uint_as_float(sr[cidx][i + 3]));
+                    mxc = max3(mxc, __uint_as_float(sr[cidx][i + 4]), __uint_as_float(sr[cidx][i + 5]));
+                    mxd = max3(mxd, __uint_as_float(sr[cidx][i + 6]), __uint_as_float(sr[cidx][i + 7]));
                 }
             const float mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
             TRACE_ADD(ts_max);
@@ -327,20 +327,22 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             TRACE_ADD(ts_resc);
             const float mref = (m_used == -INFINITY) ? 0.0f : m_used;
             const float neg = -mref * c;
-            float ps0 = 0.0f, ps1 = 0.0f, ps2 = 0.0f, ps3 = 0.0f;
+            // p = 2^(s * c - m * c): one packed FMA per two scores, sums kept as packed pairs
+            const uint64_t c2 = pack_f32x2(c, c), neg2 = pack_f32x2(neg, neg);
+            uint64_t sum_a = 0ull, sum_b = 0ull;  // bit pattern of (0.0f, 0.0f)
 #pragma unroll
             for (int cidx = 0; cidx < 4; ++cidx) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 16; i += 2) {
-                    const float p0 = ex2(fmaf(__uint_as_float(sr[cidx][2 * i]), c, neg));
-                    const float p1 = ex2(fmaf(__uint_as_float(sr[cidx][2 * i + 1]), c, neg));
-                    const float p2 = ex2(fmaf(__uint_as_float(sr[cidx][2 * i + 2]), c, neg));
-                    const float p3 = ex2(fmaf(__uint_as_float(sr[cidx][2 * i + 3]), c, neg));
-                    ps0 += p0;
-                    ps1 += p1;
-                    ps2 += p2;
-                    ps3 += p3;
+                    const uint64_t ta = fma_f32x2(pack_f32x2(__uint_as_float(sr[cidx][2 * i]), __uint_as_float(sr[cidx][2 * i + 1])), c2, neg2);
+                    const uint64_t tb = fma_f32x2(pack_f32x2(__uint_as_float(sr[cidx][2 * i + 2]), __uint_as_float(sr[cidx][2 * i + 3])), c2, neg2);
+                    float x0, x1, x2, x3;
+                    unpack_f32x2(ta, x0, x1);
+                    unpack_f32x2(tb, x2, x3);
+                    const float p0 = ex2(x0), p1 = ex2(x1), p2 = ex2(x2), p3 = ex2(x3);
+                    sum_a = add_f32x2(sum_a, pack_f32x2(p0, p1));
+                    sum_b = add_f32x2(sum_b, pack_f32x2(p2, p3));
                     __nv_bfloat162 pa = __floats2bfloat162_rn(p0, p1);
                     __nv_bfloat162 pb = __floats2bfloat162_rn(p2, p3);
                     pk[i] = *reinterpret_cast<uint32_t*>(&pa);
@@ -348,8 +350,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 }
                 tmem_st16(tS + cidx * 16, pk);
             }
-            const float psum = (ps0 + ps1) + (ps2 + ps3);
-            l += psum;
+            {
+                float s0, s1;
+                unpack_f32x2(add_f32x2(sum_a, sum_b), s0, s1);
+                l += s0 + s1;
+            }
             tmem_wait_st();
             fence_before_sync();
             mbar_arrive(p_full(t));
