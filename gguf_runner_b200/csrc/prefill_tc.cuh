@@ -327,7 +327,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             TRACE_ADD(ts_resc);
             const float mref = (m_used == -INFINITY) ? 0.0f : m_used;
             const float neg = -mref * c;
-            // p = 2^(s * c - m * c): one packed FMA per two scores, sums kept as packed pairs
+            // p = 2^(s * c - m * c): one packed FMA per two scores, sums kept as packed pairs. Two variants were
+            // measured and dropped: ex2.approx.f16x2 (half-precision pairs) made this phase slower, and writing
+            // P as f16 against a bf16 V is an illegal instruction (A and B of one MMA share the 16-bit type).
             const uint64_t c2 = pack_f32x2(c, c), neg2 = pack_f32x2(neg, neg);
             uint64_t sum_a = 0ull, sum_b = 0ull;  // bit pattern of (0.0f, 0.0f)
 #pragma unroll
