@@ -56,6 +56,7 @@ class _Config(C.Structure):
         ("shard_mode", C.c_int32), ("shard_pos_begin", C.c_int32), ("shard_pos_count", C.c_int32),
         ("n_ranks", C.c_int32), ("rank", C.c_int32),
         ("decode_impl", C.c_int32), ("prefill_impl", C.c_int32), ("max_splits", C.c_int32),
+        ("decode_fusion", C.c_int32),
     ]
 
 
@@ -179,6 +180,7 @@ class AttnConfig:
     decode_impl: int = IMPL_AUTO
     prefill_impl: int = IMPL_AUTO
     max_splits: int = 0
+    decode_fusion: int = 0
 
     @property
     def q_dim(self) -> int:
@@ -195,7 +197,7 @@ class AttnConfig:
                      "rope_theta", "rope_theta_swa", "rope_scale_global", "rope_scale_local", "rope_style",
                      "rope_layout", "swa_theta_on_window_layers", "swa_pattern", "scale_mode", "softmax_mode",
                      "kv_format", "image_mode", "device", "shard_mode", "shard_pos_begin", "shard_pos_count",
-                     "n_ranks", "rank", "decode_impl", "prefill_impl", "max_splits"):
+                     "n_ranks", "rank", "decode_impl", "prefill_impl", "max_splits", "decode_fusion"):
             setattr(c, name, getattr(self, name))
         for i in range(4):
             c.rope_sections[i] = int(self.rope_sections[i])

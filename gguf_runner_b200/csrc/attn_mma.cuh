@@ -372,6 +372,8 @@ __global__ void __launch_bounds__(kTmaWarps * 32) attn_mma_tma_decode_kernel(con
     }
     __syncthreads();
     volatile int* abortp = &s_abort;
+    const float* qsrc = a.q + ((int64_t)item * Hq + (int64_t)kvh * G) * D;
+    if (a.fused.enabled) qsrc = fused_rope_prologue(a, item, kvh, seq, pos, pos >= s0 && pos < s1, smem);
 
     auto issue = [&](int tile_idx, int stage) {
         // one lane: K and V rows [key, key + 16) of this KV head, 64 columns per box
@@ -391,8 +393,8 @@ __global__ void __launch_bounds__(kTmaWarps * 32) attn_mma_tma_decode_kernel(con
         uint32_t qf[KS][4];
         {
             const int r0 = g0 + gq, r1 = g0 + gq + 8;
-            const float* q0 = a.q + ((int64_t)item * Hq + (int64_t)kvh * G + r0) * D;
-            const float* q1 = a.q + ((int64_t)item * Hq + (int64_t)kvh * G + r1) * D;
+            const float* q0 = qsrc + (int64_t)r0 * D;
+            const float* q1 = qsrc + (int64_t)r1 * D;
             const bool v0 = r0 < G, v1 = r1 < G;
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) {

@@ -14,11 +14,24 @@
 #pragma once
 
 #include "common.cuh"
+#include "rope_append.cuh"
 
 namespace ggr {
 
 constexpr int kSimtTK = 16;      // keys per pipeline stage of one warp
 constexpr int kSimtWarps = 4;
+
+// Decode fusion: the attention kernel itself rotates q (every CTA, for its own query heads) and the
+// CTA whose key range holds the new position rotates k and appends the k / v row slice of its KV head
+// before it starts streaming, so a decode step is one launch per layer instead of two.
+struct FusedRope {
+    int enabled;
+    RopeParams rope;
+    const float* q_in;  // [items][q_dim] f32, before RoPE
+    const float* k_in;  // [items][kv_dim]
+    const float* v_in;  // [items][kv_dim]
+    int smem_off;       // byte offset of the fusion scratch inside dynamic shared memory
+};
 
 struct AttnArgs {
     KvView kv;
@@ -35,7 +48,128 @@ struct AttnArgs {
     int shard_count;      // positions held locally
     int stage_bytes;      // bytes of one ring stage of one warp
     int* err;             // raised when a bounded wait runs out (kernels that wait on mbarriers)
+    FusedRope fused;
 };
+
+inline size_t fused_rope_smem_bytes(const KvView& kv, int rope_half) {
+    return (size_t)(2 * rope_half + kv.G * kv.D + 2 * kv.kv_dim + 32) * sizeof(float);
+}
+
+// Returns the rotated (and pre-scaled) query heads of this CTA's KV head in shared memory.
+// `owner` is CTA-uniform: this CTA's key range holds `pos`, so it appends the row first.
+__device__ __forceinline__ const float* fused_rope_prologue(const AttnArgs& a, int item, int kvh, int seq, int pos,
+                                                            bool owner, unsigned char* smem_base) {
+    const RopeParams& rp = a.fused.rope;
+    const int D = a.kv.D, G = a.kv.G, Hq = a.kv.Hq, kv_dim = a.kv.kv_dim, half = rp.rope_half;
+    const int tid = threadIdx.x, nt = blockDim.x;
+    float* cs = reinterpret_cast<float*>(smem_base + a.fused.smem_off);
+    float* sn = cs + half;
+    float* qs = sn + half;
+    float* krow = qs + G * D;
+    float* vrow = krow + kv_dim;
+    float* red = vrow + kv_dim;
+    for (int i = tid; i < half; i += nt) {
+        const int axis = rope_axis(rp.layout, i, rp.sections);
+        int coord = pos;
+        if (rp.has_plan) coord = pos < rp.plan_len ? rp.plan[pos * 3 + axis] : rp.next_text + (pos - rp.plan_len);
+        const float val = __fmul_rn(__fmul_rn((float)coord, rp.freqs[i]), rp.fscale);
+        float sv, cv;
+        sincosf(val, &sv, &cv);
+        cs[i] = cv;
+        sn[i] = sv;
+    }
+    __syncthreads();
+    const int64_t qb = ((int64_t)item * Hq + (int64_t)kvh * G) * D;
+    for (int idx = tid; idx < G * D; idx += nt) {
+        const int g = idx / D, i = idx - g * D;
+        float r = rope_elem(a.fused.q_in, qb + (int64_t)g * D, i, D, rp, cs, sn, 0);
+        if (rp.do_prescale) r = __fmul_rn(r, rp.q_prescale);
+        qs[idx] = r;
+    }
+    if (owner) {
+        const int64_t kb = (int64_t)item * kv_dim;
+        const bool whole = a.kv.fmt == KV_Q8_ROW;  // the row scale spans all KV heads
+        const int e0 = whole ? 0 : kvh * D, e1 = whole ? kv_dim : (kvh + 1) * D;
+        for (int idx = e0 + tid; idx < e1; idx += nt) {
+            const int h = idx / D, i = idx - h * D;
+            krow[idx] = rope_elem(a.fused.k_in, kb + (int64_t)h * D, i, D, rp, cs, sn, 0);
+            vrow[idx] = a.fused.v_in[kb + idx];
+        }
+        __syncthreads();
+        const int64_t r = a.kv.row(seq, a.layer, pos);
+        const int64_t off = r * kv_dim + (int64_t)kvh * D;
+        const float* kh = krow + kvh * D;
+        const float* vh = vrow + kvh * D;
+        if (a.kv.fmt == KV_F32) {
+            float* kc = reinterpret_cast<float*>(a.kv.k) + off;
+            float* vc = reinterpret_cast<float*>(a.kv.v) + off;
+            for (int i = tid; i < D; i += nt) {
+                kc[i] = kh[i];
+                vc[i] = vh[i];
+            }
+        } else if (a.kv.fmt == KV_BF16) {
+            __nv_bfloat16* kc = reinterpret_cast<__nv_bfloat16*>(a.kv.k) + off;
+            __nv_bfloat16* vc = reinterpret_cast<__nv_bfloat16*>(a.kv.v) + off;
+            for (int i = tid; i < D; i += nt) {
+                kc[i] = __float2bfloat16_rn(kh[i]);
+                vc[i] = __float2bfloat16_rn(vh[i]);
+            }
+        } else if (a.kv.fmt == KV_Q8_ROW) {
+            float mk = 0.0f, mv = 0.0f;
+            for (int idx = tid; idx < kv_dim; idx += nt) {
+                mk = fmaxf(mk, fabsf(krow[idx]));
+                mv = fmaxf(mv, fabsf(vrow[idx]));
+            }
+            mk = warp_max(mk);
+            mv = warp_max(mv);
+            if ((tid & 31) == 0) {
+                red[tid >> 5] = mk;
+                red[16 + (tid >> 5)] = mv;
+            }
+            __syncthreads();
+            mk = 0.0f;
+            mv = 0.0f;
+            for (int w = 0; w < (nt >> 5); ++w) {
+                mk = fmaxf(mk, red[w]);
+                mv = fmaxf(mv, red[16 + w]);
+            }
+            const float invk = mk == 0.0f ? 0.0f : __fdiv_rn(127.0f, mk);
+            const float invv = mv == 0.0f ? 0.0f : __fdiv_rn(127.0f, mv);
+            int8_t* kc = reinterpret_cast<int8_t*>(a.kv.k) + off;
+            int8_t* vc = reinterpret_cast<int8_t*>(a.kv.v) + off;
+            for (int i = tid; i < D; i += nt) {
+                kc[i] = mk == 0.0f ? (int8_t)0 : q8_code(kh[i], invk);
+                vc[i] = mv == 0.0f ? (int8_t)0 : q8_code(vh[i], invv);
+            }
+            if (tid == 0) {  // every KV head's owner CTA writes the same two values
+                a.kv.ks[r] = mk == 0.0f ? 1.0f : __fdiv_rn(mk, 127.0f);
+                a.kv.vs[r] = mv == 0.0f ? 1.0f : __fdiv_rn(mv, 127.0f);
+            }
+        } else {  // KV_Q8_BLOCK32: the blocks of this head
+            const int nb = kv_dim / 32, nbh = D / 32;
+            int8_t* kc = reinterpret_cast<int8_t*>(a.kv.k) + off;
+            int8_t* vc = reinterpret_cast<int8_t*>(a.kv.v) + off;
+            const int lane = tid & 31, warp = tid >> 5, nwp = nt >> 5;
+            for (int b = warp; b < nbh; b += nwp) {
+                const float xk = kh[b * 32 + lane], xv = vh[b * 32 + lane];
+                const float mk = warp_max(fabsf(xk)), mv = warp_max(fabsf(xv));
+                const float invk = mk == 0.0f ? 0.0f : __fdiv_rn(127.0f, mk);
+                const float invv = mv == 0.0f ? 0.0f : __fdiv_rn(127.0f, mv);
+                kc[b * 32 + lane] = mk == 0.0f ? (int8_t)0 : q8_code(xk, invk);
+                vc[b * 32 + lane] = mv == 0.0f ? (int8_t)0 : q8_code(xv, invv);
+                if (lane == 0) {
+                    a.kv.ks[r * nb + kvh * nbh + b] = mk == 0.0f ? 1.0f : __fdiv_rn(mk, 127.0f);
+                    a.kv.vs[r * nb + kvh * nbh + b] = mv == 0.0f ? 1.0f : __fdiv_rn(mv, 127.0f);
+                }
+            }
+        }
+        __threadfence();
+    }
+    __syncthreads();
+    // the appended row is read back through cp.async / TMA by this CTA
+    if (owner) asm volatile("fence.proxy.async;" ::: "memory");
+    return qs;
+}
 
 // Writes one head's merged state: the final output row, a (o / l, m, l)
 // partial for cross-rank merging, or nothing when a later stage will.
@@ -261,6 +395,9 @@ __global__ void __launch_bounds__(kSimtWarps * 32) attn_simt_kernel(AttnArgs a) 
     const bool active = j < chunks;
     const int nsh = FMT == KV_Q8_ROW ? 1 : (FMT == KV_Q8_BLOCK32 ? D / 32 : 0);
 
+    const float* qsrc = a.q + ((int64_t)item * Hq + (int64_t)kvh * G) * D;
+    if (a.fused.enabled) qsrc = fused_rope_prologue(a, item, kvh, seq, pos, pos >= s0 && pos < s1, smem);
+
     unsigned char* ring = smem + (size_t)warp * NST * a.stage_bytes;
     const int n_tiles_total = k1 > k0 ? (k1 - k0 + kSimtTK - 1) / kSimtTK : 0;
     // this warp's tiles: warp, warp + W, ...
@@ -273,7 +410,7 @@ __global__ void __launch_bounds__(kSimtWarps * 32) attn_simt_kernel(AttnArgs a) 
             m[g] = -INFINITY;
             l[g] = 0.0f;
             const bool hv = g0 + g < G;
-            const float* qh = a.q + ((int64_t)item * Hq + (int64_t)kvh * G + g0 + g) * D;
+            const float* qh = qsrc + (int64_t)(g0 + g) * D;
 #pragma unroll
             for (int p = 0; p < 8; ++p) {
                 acc[g][p] = 0.0f;

@@ -370,8 +370,17 @@ bool use_mma_decode(const ggr_attn_ctx* c) {
 }
 
 // Attention over the cache for `items` (already rotated q at q_dev).
+// When `raw` is given (decode), q_dev is scratch for the rotated queries: the kernels rotate q and
+// append the k / v row themselves if the fusion scratch fits in shared memory, otherwise the
+// rope/append kernel runs first.
+struct RawDecodeInputs {
+    const float* q;
+    const float* k;
+    const float* v;
+};
+
 int launch_attention(ggr_attn_ctx* c, int layer, const Items& items, int t_max, const float* q_dev, float* out_dev,
-                     float* partial_dev, bool allow_mma) {
+                     float* partial_dev, bool allow_mma, const RawDecodeInputs* raw = nullptr) {
     AttnArgs a{};
     a.kv = c->kv;
     a.items = items;
@@ -397,6 +406,25 @@ int launch_attention(ggr_attn_ctx* c, int layer, const Items& items, int t_max, 
     }
     a.stage_bytes = p.stage_bytes;
     a.err = c->d_err;
+    if (raw) {
+        const size_t fb = fused_rope_smem_bytes(c->kv, c->rope_half);
+        const size_t base = (std::max(smem, p.smem) + 15) & ~(size_t)15;
+        const bool kernel_ok = !mma || tma;  // the cp.async-fed tensor-core kernel has no fused prologue
+        if (c->cfg.decode_fusion == 0 && kernel_ok && base + fb + 4096 <= (size_t)c->smem_optin) {
+            a.fused.enabled = 1;
+            a.fused.rope = rope_params(c, layer);
+            a.fused.q_in = raw->q;
+            a.fused.k_in = raw->k;
+            a.fused.v_in = raw->v;
+            a.fused.smem_off = (int)base;
+            smem = base + fb;
+            p.smem = base + fb;
+        } else {
+            int rc = launch_rope_append(c, layer, items, RF_ROTATE | RF_WRITE_Q | RF_APPEND, 0, raw->q, raw->k, raw->v,
+                                        const_cast<float*>(q_dev), nullptr, nullptr);
+            if (rc) return rc;
+        }
+    }
 
     const double bytes_per_key = 2.0 * c->D * c->kv.elem_bytes;
     const double cta_rate = tma ? 65e9 : 40e9;
@@ -408,6 +436,12 @@ int launch_attention(ggr_attn_ctx* c, int layer, const Items& items, int t_max, 
     const size_t merge_smem = n_split > 1 ? ((size_t)c->G * n_split + 2 * c->G) * sizeof(float) : 0;
     smem = std::max(smem, merge_smem);
     p.smem = std::max(p.smem, merge_smem);
+    if (a.fused.enabled && merge_smem > (size_t)a.fused.smem_off) {
+        // tiny rings: keep the fusion scratch behind the merge area
+        const size_t fb = fused_rope_smem_bytes(c->kv, c->rope_half);
+        a.fused.smem_off = (int)((merge_smem + 15) & ~(size_t)15);
+        smem = p.smem = (size_t)a.fused.smem_off + fb;
+    }
     if (n_split > 1) {
         int rc = ensure(c, &c->d_part, &c->part_cap, (size_t)items.n * c->kv.Hq * n_split * (c->D + 2));
         if (rc) return rc;
@@ -496,12 +530,11 @@ int decode_common(ggr_attn_ctx* c, int layer, const int32_t* pos, int B, const f
         const float* kc = reinterpret_cast<const float*>(dk) + (size_t)b0 * c->kv_dim;
         const float* vc = reinterpret_cast<const float*>(dv) + (size_t)b0 * c->kv_dim;
         float* qr = c->d_qrot + (size_t)b0 * c->q_dim;
-        rc = launch_rope_append(c, layer, it, RF_ROTATE | RF_WRITE_Q | RF_APPEND, 0, qc, kc, vc, qr, nullptr, nullptr);
-        if (rc) return rc;
         const int t_max = t_max_of(c, layer, pos + b0, n);
         float* oc = partial ? nullptr : dout + (size_t)b0 * c->q_dim;
         float* pc = partial ? dout + (size_t)b0 * c->kv.Hq * (c->D + 2) : nullptr;
-        rc = launch_attention(c, layer, it, t_max, qr, oc, pc, true);
+        const RawDecodeInputs raw{qc, kc, vc};
+        rc = launch_attention(c, layer, it, t_max, qr, oc, pc, true, &raw);
         if (rc) return rc;
     }
     if (ptr_kind == GGR_PTR_HOST) {

@@ -88,6 +88,8 @@ typedef struct ggr_attn_config {
     int32_t decode_impl;  /* GGR_IMPL_*: kernel family for decode, AUTO picks by shape */
     int32_t prefill_impl; /* GGR_IMPL_*: kernel family for prefill */
     int32_t max_splits;   /* 0 = automatic split-KV factor */
+    int32_t decode_fusion; /* 0 = decode rotates q and appends k/v inside the attention kernel (one launch per
+                              layer) where the shape allows; 1 = separate rope/append launch */
 } ggr_attn_config;
 
 /* Fills *cfg with the reference's defaults (theta 5e5, swa theta 1e4,

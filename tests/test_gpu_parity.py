@@ -403,3 +403,37 @@ def test_invalid_arguments_return_errors():
         with pytest.raises(GgrError):
             ctx.set_media_blocks([(2, 5), (6, 2)], 12)  # overlapping blocks
         ctx.decode(0, [0], z, kz, kz)  # the context is still usable
+
+
+# ---- decode fusion: one launch per layer gives the same rows and outputs as rope/append + attention ---------
+
+@pytest.mark.parametrize("kv_format", [KV_F32, KV_BF16, KV_Q8_ROW, KV_Q8_BLOCK32])
+@pytest.mark.parametrize("n_heads,n_kv_heads,head_dim", [(8, 4, 64), (32, 4, 128), (4, 4, 32)])
+def test_fused_decode_equals_separate_kernels(kv_format, n_heads, n_kv_heads, head_dim):
+    import dataclasses
+    cfg = AttnConfig(n_layers=2, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim, seq_len=700, max_batch=3,
+                     rope_theta=1e6, kv_format=kv_format, layer_windows=[0, 300])
+    rng = np.random.default_rng(31)
+    with g.AttnContext(cfg) as fused, g.AttnContext(dataclasses.replace(cfg, decode_fusion=1)) as plain:
+        ora = Oracle(cfg, threads=THREADS)
+        lens = [650, 129, 1]
+        for b, n in enumerate(lens):
+            q, k, v = rand(rng, n, cfg.q_dim), rand(rng, n, cfg.kv_dim), rand(rng, n, cfg.kv_dim)
+            for c in (fused, plain):
+                c.prefill(1, 0, q, k, v, seq=b)
+            ora.prefill(1, 0, q, k, v, seq=b)
+        launches_f, launches_p = fused.launch_count, plain.launch_count
+        for step in range(3):
+            pos = [n + step for n in lens]
+            q, k, v = rand(rng, 3, cfg.q_dim), rand(rng, 3, cfg.kv_dim), rand(rng, 3, cfg.kv_dim)
+            a = fused.decode(1, pos, q, k, v)
+            b_ = plain.decode(1, pos, q, k, v)
+            want = ora.decode(1, pos, q, k, v)
+            assert np.max(np.abs(a - b_)) <= 1e-5
+            assert np.max(np.abs(a - want)) <= TOL[kv_format]
+            for s_, p_ in enumerate(pos):
+                fk, fv = fused.kv_read_row(1, p_, seq=s_)
+                pk, pv = plain.kv_read_row(1, p_, seq=s_)
+                assert np.array_equal(fk, pk) and np.array_equal(fv, pv)
+        assert fused.launch_count - launches_f == 3       # one launch per step
+        assert plain.launch_count - launches_p == 6       # rope/append + attention
