@@ -71,6 +71,8 @@ EXPORTED_SYMBOLS = [
     "ggr_attn_kv_export", "ggr_attn_kv_import", "ggr_attn_kv_read_row", "ggr_attn_launch_count",
     "ggr_attn_set_kernel_timing", "ggr_attn_kernel_time", "ggr_attn_kv_device_ptrs",
     "ggr_attn_attention_tokens_static", "ggr_attn_last_split_count",
+    "ggr_attn_exchange_create", "ggr_attn_exchange_connect", "ggr_attn_decode_exchange",
+    "ggr_attn_exchange_send", "ggr_attn_exchange_receive",
     "ggr_rope_plan_new", "ggr_rope_plan_free", "ggr_rope_plan_append_text", "ggr_rope_plan_append_grid",
     "ggr_rope_plan_len", "ggr_rope_plan_next_text", "ggr_rope_plan_at", "ggr_rope_plan_export",
     "ggr_rope_axis", "ggr_media_plan_validate", "ggr_media_chunk_end", "ggr_gemma_layer_windows",
@@ -121,6 +123,11 @@ def lib() -> C.CDLL:
     L.ggr_attn_launch_count.restype = i64
     L.ggr_attn_last_split_count.argtypes = [vp]
     L.ggr_attn_attention_tokens_static.argtypes = [vp, i32, vp, i32, vp, vp]
+    L.ggr_attn_exchange_create.argtypes = [vp, i32, C.POINTER(vp), vp]
+    L.ggr_attn_exchange_connect.argtypes = [vp, vp, vp]
+    L.ggr_attn_decode_exchange.argtypes = [vp, i32, vp, i32, vp, vp, vp, vp, i32]
+    L.ggr_attn_exchange_send.argtypes = [vp, i32, vp, i32, vp, vp, vp, i32]
+    L.ggr_attn_exchange_receive.argtypes = [vp, i32, vp, i32]
     L.ggr_attn_set_kernel_timing.argtypes = [vp, i32]
     L.ggr_attn_kernel_time.argtypes = [vp, i32, C.POINTER(C.c_double), C.POINTER(i64), i32]
     L.ggr_attn_kv_device_ptrs.argtypes = [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp),
@@ -354,6 +361,48 @@ class AttnContext:
         self._check(self._L.ggr_attn_decode_partial(self._h, layer, C.c_void_p(pos.ctypes.data), B, qp, kp, vp, pp,
                                                      kind))
         return partial
+
+    def exchange_create(self, max_B: int):
+        """Allocates the local receive buffer of the fused shard exchange; returns (device address, 64-byte IPC handle)."""
+        base = C.c_void_p()
+        handle = (C.c_ubyte * 64)()
+        self._check(self._L.ggr_attn_exchange_create(self._h, max_B, C.byref(base), handle))
+        return base.value, bytes(handle)
+
+    def exchange_connect(self, ipc_handles=None, same_process_ptrs=None):
+        """ipc_handles: list of n_ranks 64-byte handles (other processes); same_process_ptrs: list of device addresses."""
+        hbuf = None
+        if ipc_handles is not None:
+            hbuf = (C.c_ubyte * (64 * len(ipc_handles)))(*b"".join(ipc_handles))
+        pbuf = None
+        if same_process_ptrs is not None:
+            pbuf = (C.c_void_p * len(same_process_ptrs))(*[C.c_void_p(p) for p in same_process_ptrs])
+        self._check(self._L.ggr_attn_exchange_connect(self._h, hbuf, pbuf))
+
+    def decode_exchange(self, layer: int, pos, q, k, v, out=None):
+        pos = np.ascontiguousarray(np.asarray(pos, dtype=np.int32).reshape(-1))
+        B = pos.shape[0]
+        if out is None:
+            out = self._out_like(q, (B, self.config.q_dim))
+        self._follow_torch_stream(q)
+        (qp, kind), (kp, _), (vp, _), (op, _) = _ptr(q), _ptr(k), _ptr(v), _ptr(out)
+        self._check(self._L.ggr_attn_decode_exchange(self._h, layer, C.c_void_p(pos.ctypes.data), B, qp, kp, vp, op, kind))
+        return out
+
+    def exchange_send(self, layer: int, pos, q, k, v):
+        pos = np.ascontiguousarray(np.asarray(pos, dtype=np.int32).reshape(-1))
+        self._follow_torch_stream(q)
+        (qp, kind), (kp, _), (vp, _) = _ptr(q), _ptr(k), _ptr(v)
+        self._check(self._L.ggr_attn_exchange_send(self._h, layer, C.c_void_p(pos.ctypes.data), pos.shape[0], qp, kp, vp,
+                                                    kind))
+
+    def exchange_receive(self, B: int, like, out=None):
+        if out is None:
+            out = self._out_like(like, (B, self.config.q_dim))
+        self._follow_torch_stream(like)
+        (op, kind) = _ptr(out)
+        self._check(self._L.ggr_attn_exchange_receive(self._h, B, op, kind))
+        return out
 
     def combine_partials(self, parts, out=None):
         n_parts, B = parts.shape[0], parts.shape[1]

@@ -33,6 +33,21 @@ struct FusedRope {
     int smem_off;       // byte offset of the fusion scratch inside dynamic shared memory
 };
 
+// Fused exchange of KV-sequence shards: instead of handing its partial states to a collective, the
+// decode kernel stores them straight into the receive slot every rank keeps for this rank (peer memory
+// over NVLink, plain stores), and the last (token, kv head) group to finish raises this rank's flag on
+// every peer. No TMA and no multicast are involved; waits on the flags are bounded.
+constexpr int kMaxPeers = 8;
+struct PeerExchange {
+    int enabled;
+    int n_ranks, rank;
+    float* slot[kMaxPeers];    // rank r's receive slot for this rank's states: [B][Hq][D + 2]
+    int* flag[kMaxPeers];      // rank r's flag word for this rank
+    int epoch;                 // value the flags take when this step's states are complete
+    unsigned* done_counter;    // local count of finished (token, kv head) groups, zero between launches
+    int groups_total;
+};
+
 struct AttnArgs {
     KvView kv;
     Items items;
@@ -49,6 +64,7 @@ struct AttnArgs {
     int stage_bytes;      // bytes of one ring stage of one warp
     int* err;             // raised when a bounded wait runs out (kernels that wait on mbarriers)
     FusedRope fused;
+    PeerExchange px;
 };
 
 inline size_t fused_rope_smem_bytes(const KvView& kv, int rope_half) {
@@ -176,7 +192,18 @@ __device__ __forceinline__ const float* fused_rope_prologue(const AttnArgs& a, i
 __device__ __forceinline__ void store_final(const AttnArgs& a, int item, int h, int d, float o, float ms, float ls) {
     const int D = a.kv.D, Hq = a.kv.Hq;
     const float inv = ls > 0.0f ? 1.0f / ls : 0.0f;
-    if (a.partial_out) {
+    if (a.px.enabled) {
+        const int64_t o_idx = ((int64_t)item * Hq + h) * (D + 2);
+        const float val = o * inv;
+        for (int r = 0; r < a.px.n_ranks; ++r) {
+            float* po = a.px.slot[r] + o_idx;
+            po[d] = val;
+            if (d == 0) {
+                po[D] = ms;
+                po[D + 1] = ls;
+            }
+        }
+    } else if (a.partial_out) {
         float* po = a.partial_out + ((int64_t)item * Hq + h) * (D + 2);
         po[d] = o * inv;
         if (d == 0) {
@@ -219,11 +246,32 @@ __device__ __forceinline__ void cta_merge_store(const AttnArgs& a, const float* 
     }
 }
 
+// Called by the CTA that stored the final states of a (token, kv head) group. When every group of the
+// launch has finished, this rank's flag is raised on all peers (system-scope release after the stores).
+__device__ __forceinline__ void peer_group_done(const AttnArgs& a) {
+    if (!a.px.enabled) return;
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned prev = atomicAdd(a.px.done_counter, 1u);
+        if (prev == (unsigned)a.px.groups_total - 1u) {
+            __threadfence_system();
+            for (int r = 0; r < a.px.n_ranks; ++r) {
+                asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(a.px.flag[r]), "r"(a.px.epoch) : "memory");
+            }
+            *a.px.done_counter = 0u;  // ready for the next launch
+        }
+    }
+}
+
 // The last CTA of a (token, kv head) to arrive (atomic ticket) merges the
 // per-split states from the scratch buffer and resets the ticket. `wsm` is
 // shared memory for G * n_split weights (the drained ring is reused).
 __device__ __forceinline__ void split_merge_store(const AttnArgs& a, int item, int kvh, int* s_last, float* wsm) {
-    if (a.n_split == 1) return;
+    if (a.n_split == 1) {
+        peer_group_done(a);
+        return;
+    }
     const int D = a.kv.D, G = a.kv.G, Hq = a.kv.Hq, NS = a.n_split;
     __threadfence();
     __syncthreads();
@@ -275,6 +323,7 @@ __device__ __forceinline__ void split_merge_store(const AttnArgs& a, int item, i
         store_final(a, item, kvh * G + g, d, (o0 + o1) + (o2 + o3), lsum[G + g], lsum[g]);
     }
     if (threadIdx.x == 0) a.counters[item * a.kv.Hkv + kvh] = 0u;  // ready for the next launch
+    peer_group_done(a);
 }
 
 // f32 view of the 8 elements lane j owns in a cache row slice held in shared
@@ -552,6 +601,43 @@ __global__ void combine_partials_kernel(const float* parts, int n_parts, int ite
             ls += f;
         }
         out[((int64_t)item * Hq + h) * D + d] = ls > 0.0f ? o / ls : 0.0f;
+    }
+}
+
+// Merge of the states every rank stored into this rank's receive slots. One lane per CTA first waits
+// (bounded) until all flags carry this step's epoch; the states are read around L1, which may still
+// hold the lines of an earlier step.
+__global__ void combine_exchange_kernel(const float* parts, const int* flags, int epoch, int n_parts, int64_t part_stride,
+                                        int Hq, int D, float* out, int* err) {
+    __shared__ int s_ok;
+    const int h = blockIdx.x, item = blockIdx.y;
+    if (threadIdx.x == 0) {
+        int ok = 1;
+        for (int r = 0; r < n_parts; ++r) {
+            int seen = 0;
+            for (uint32_t it = 0; it < (1u << 22); ++it) {
+                asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(flags + r) : "memory");
+                if (seen >= epoch) break;
+                __nanosleep(100);
+            }
+            if (seen < epoch) ok = 0;
+        }
+        s_ok = ok;
+        if (!ok && err) atomicExch(err, 1);
+    }
+    __syncthreads();
+    const float* base = parts + ((int64_t)item * Hq + h) * (D + 2);
+    float ms = -INFINITY;
+    for (int r = 0; r < n_parts; ++r) ms = fmaxf(ms, __ldcg(base + r * part_stride + D));
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float o = 0.0f, ls = 0.0f;
+        for (int r = 0; r < n_parts; ++r) {
+            const float mw = __ldcg(base + r * part_stride + D), lw = __ldcg(base + r * part_stride + D + 1);
+            const float f = (mw == -INFINITY) ? 0.0f : lw * exp2f(mw - ms);
+            o += f * __ldcg(base + r * part_stride + d);
+            ls += f;
+        }
+        out[((int64_t)item * Hq + h) * D + d] = (s_ok && ls > 0.0f) ? o / ls : 0.0f;
     }
 }
 

@@ -63,6 +63,15 @@ struct ggr_attn_ctx {
     // error word the kernels raise when a bounded wait runs out (mapped pinned host memory)
     int* h_err = nullptr;
     int* d_err = nullptr;
+    // fused exchange of KV-sequence shards: local receive buffer (flags, then two parities of
+    // [n_ranks][max_B][Hq][D + 2] floats), the peers' buffers, step counter
+    unsigned char* x_local = nullptr;
+    unsigned char* x_peer[kMaxPeers] = {};
+    bool x_opened[kMaxPeers] = {};
+    int x_max_b = 0;
+    int x_epoch = 0;
+    bool x_connected = false;
+    unsigned* d_done = nullptr;
     // copy streams and events of the pipelined host-buffer prefill
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
     std::vector<cudaEvent_t> ev_in, ev_done;
@@ -380,7 +389,8 @@ struct RawDecodeInputs {
 };
 
 int launch_attention(ggr_attn_ctx* c, int layer, const Items& items, int t_max, const float* q_dev, float* out_dev,
-                     float* partial_dev, bool allow_mma, const RawDecodeInputs* raw = nullptr) {
+                     float* partial_dev, bool allow_mma, const RawDecodeInputs* raw = nullptr,
+                     const PeerExchange* px = nullptr) {
     AttnArgs a{};
     a.kv = c->kv;
     a.items = items;
@@ -391,6 +401,7 @@ int launch_attention(ggr_attn_ctx* c, int layer, const Items& items, int t_max, 
     a.out = out_dev;
     a.partial_out = partial_dev;
     a.shard_count = c->shard_count;
+    if (px) a.px = *px;
 
     const bool mma = allow_mma && use_mma_decode(c);
     const bool tma = mma && c->have_tmaps16 && c->cfg.decode_impl != GGR_IMPL_MMA;
@@ -881,6 +892,10 @@ void ggr_attn_destroy(ggr_attn_ctx* c) {
     cudaFree(c->d_part);
     cudaFree(c->d_counters);
     for (auto* p : c->d_stage) cudaFree(p);
+    for (int r = 0; r < kMaxPeers; ++r)
+        if (c->x_opened[r]) cudaIpcCloseMemHandle(c->x_peer[r]);
+    cudaFree(c->x_local);
+    cudaFree(c->d_done);
     if (c->h_err) cudaFreeHost(c->h_err);
     for (auto e : c->ev_in) cudaEventDestroy(e);
     for (auto e : c->ev_done) cudaEventDestroy(e);
@@ -1353,3 +1368,163 @@ extern "C" int ggr_attn_attention_tokens_static(ggr_attn_ctx* c, int32_t layer, 
 // diagnostic builds only: device buffer of 32 int64 cycle counters written by CTA 0 of the prefill kernel
 extern "C" void ggr_attn_debug_set_trace(long long* device_ptr) { g_tc_trace = device_ptr; }
 #endif
+
+// ---- fused exchange of KV-sequence shards -----------------------------------------------------------
+
+namespace {
+size_t x_slot_floats(const ggr_attn_ctx* c) { return (size_t)c->x_max_b * c->kv.Hq * (c->D + 2); }
+size_t x_flag_bytes() { return 256; }
+size_t x_total_bytes(const ggr_attn_ctx* c) {
+    return x_flag_bytes() + 2 * (size_t)c->cfg.n_ranks * x_slot_floats(c) * sizeof(float);
+}
+}  // namespace
+
+extern "C" int ggr_attn_exchange_create(ggr_attn_ctx* c, int32_t max_B, void** local_base, unsigned char* ipc_handle) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    if (c->cfg.shard_mode != GGR_SHARD_KV_SEQUENCE) return fail(c, GGR_ERR_INVALID, "the exchange belongs to a KV-sequence shard");
+    if (c->cfg.n_ranks < 1 || c->cfg.n_ranks > kMaxPeers || c->cfg.rank < 0 || c->cfg.rank >= c->cfg.n_ranks)
+        return fail(c, GGR_ERR_INVALID, "the exchange supports 1 to 8 ranks");
+    if (max_B <= 0 || max_B > c->cfg.max_batch || max_B > kMaxArgItems) return fail(c, GGR_ERR_RANGE, "exchange batch out of range");
+    if (c->x_local) return fail(c, GGR_ERR_INVALID, "the exchange buffer already exists");
+    c->x_max_b = max_B;
+    const size_t bytes = x_total_bytes(c);
+    if (cudaMalloc((void**)&c->x_local, bytes) != cudaSuccess || cudaMalloc((void**)&c->d_done, sizeof(unsigned)) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(c, GGR_ERR_ALLOC, "unable to allocate the exchange buffer");
+    }
+    CUDA_TRY(c, cudaMemset(c->x_local, 0, bytes));
+    CUDA_TRY(c, cudaMemset(c->d_done, 0, sizeof(unsigned)));
+    c->x_peer[c->cfg.rank] = c->x_local;
+    if (local_base) *local_base = c->x_local;
+    if (ipc_handle) {
+        cudaIpcMemHandle_t h;
+        CUDA_TRY(c, cudaIpcGetMemHandle(&h, c->x_local));
+        static_assert(sizeof(h) == 64, "IPC handle size");
+        std::memcpy(ipc_handle, &h, 64);
+    }
+    return GGR_OK;
+}
+
+extern "C" int ggr_attn_exchange_connect(ggr_attn_ctx* c, const unsigned char* ipc_handles, void* const* same_process_ptrs) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    if (!c->x_local) return fail(c, GGR_ERR_INVALID, "create the exchange buffer first");
+    if (!ipc_handles && !same_process_ptrs) return fail(c, GGR_ERR_INVALID, "no peer buffers given");
+    for (int r = 0; r < c->cfg.n_ranks; ++r) {
+        if (r == c->cfg.rank) continue;
+        if (same_process_ptrs && same_process_ptrs[r]) {
+            c->x_peer[r] = static_cast<unsigned char*>(same_process_ptrs[r]);
+            continue;
+        }
+        if (!ipc_handles) return fail(c, GGR_ERR_INVALID, "missing peer buffer");
+        cudaIpcMemHandle_t h;
+        std::memcpy(&h, ipc_handles + (size_t)r * 64, 64);
+        void* p = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) return fail(c, GGR_ERR_COMM, std::string("cudaIpcOpenMemHandle: ") + cudaGetErrorString(e));
+        c->x_peer[r] = static_cast<unsigned char*>(p);
+        c->x_opened[r] = true;
+    }
+    c->x_connected = true;
+    return GGR_OK;
+}
+
+namespace {
+
+// send half: fused decode over the local slab, states stored into every rank's receive slot, flag raised
+int exchange_send(ggr_attn_ctx* c, int layer, const int32_t* pos, int B, const float* q, const float* k, const float* v,
+                  int ptr_kind) {
+    int rc = check_layer(c, layer);
+    if (rc) return rc;
+    if (!c->x_connected) return fail(c, GGR_ERR_INVALID, "connect the exchange buffers first");
+    if (B <= 0 || B > c->x_max_b) return fail(c, GGR_ERR_RANGE, "batch larger than the exchange buffer");
+    if (!pos || !q || !k || !v) return fail(c, GGR_ERR_INVALID, "null buffer");
+    for (int b = 0; b < B; ++b)
+        if (pos[b] < 0 || pos[b] >= c->cfg.seq_len) return fail(c, GGR_ERR_RANGE, "position outside the cache");
+    const size_t qb = (size_t)B * c->q_dim * sizeof(float), kb = (size_t)B * c->kv_dim * sizeof(float);
+    const void *dq, *dk, *dv;
+    if ((rc = stage_in(c, 0, q, qb, ptr_kind, &dq))) return rc;
+    if ((rc = stage_in(c, 1, k, kb, ptr_kind, &dk))) return rc;
+    if ((rc = stage_in(c, 2, v, kb, ptr_kind, &dv))) return rc;
+    if ((rc = ensure(c, &c->d_qrot, &c->qrot_cap, (size_t)B * c->q_dim))) return rc;
+    const int n = c->cfg.n_ranks, me = c->cfg.rank;
+    const int epoch = ++c->x_epoch;
+    const size_t slot = x_slot_floats(c), parity_off = (size_t)(epoch & 1) * n * slot;
+    PeerExchange px{};
+    px.enabled = 1;
+    px.n_ranks = n;
+    px.rank = me;
+    px.epoch = epoch;
+    px.done_counter = c->d_done;
+    px.groups_total = B * c->kv.Hkv;
+    for (int r = 0; r < n; ++r) {
+        px.slot[r] = reinterpret_cast<float*>(c->x_peer[r] + x_flag_bytes()) + parity_off + (size_t)me * slot;
+        px.flag[r] = reinterpret_cast<int*>(c->x_peer[r]) + me;
+    }
+    Items it{};
+    it.mode = 0;
+    it.seq0 = 0;
+    it.n = B;
+    for (int i = 0; i < B; ++i) it.pos[i] = pos[i];
+    const RawDecodeInputs raw{static_cast<const float*>(dq), static_cast<const float*>(dk), static_cast<const float*>(dv)};
+    return launch_attention(c, layer, it, t_max_of(c, layer, pos, B), c->d_qrot, nullptr, nullptr, true, &raw, &px);
+}
+
+// receive half: bounded wait for every rank's flag of the current step, then the merge
+int exchange_receive(ggr_attn_ctx* c, int B, float* out, int ptr_kind) {
+    if (!c->x_connected || c->x_epoch == 0) return fail(c, GGR_ERR_INVALID, "nothing was sent on this exchange yet");
+    if (B <= 0 || B > c->x_max_b || !out) return fail(c, GGR_ERR_INVALID, "invalid receive arguments");
+    const size_t qb = (size_t)B * c->q_dim * sizeof(float);
+    float* dout = out;
+    int rc;
+    if (ptr_kind == GGR_PTR_HOST) {
+        if ((rc = ensure(c, &c->d_stage[3], &c->stage_cap[3], qb))) return rc;
+        dout = reinterpret_cast<float*>(c->d_stage[3]);
+    }
+    const int n = c->cfg.n_ranks, epoch = c->x_epoch;
+    const size_t slot = x_slot_floats(c), parity_off = (size_t)(epoch & 1) * n * slot;
+    {
+        LaunchTimer t(c, 2);
+        combine_exchange_kernel<<<dim3(c->kv.Hq, B), 128, 0, c->stream>>>(
+            reinterpret_cast<const float*>(c->x_local + x_flag_bytes()) + parity_off, reinterpret_cast<const int*>(c->x_local),
+            epoch, n, (int64_t)slot, c->kv.Hq, c->D, dout, c->d_err);
+    }
+    CUDA_TRY(c, cudaGetLastError());
+    c->launches++;
+    if (ptr_kind == GGR_PTR_HOST) {
+        CUDA_TRY(c, cudaMemcpyAsync(out, dout, qb, cudaMemcpyDeviceToHost, c->stream));
+        CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+        if (c->h_err && *c->h_err) {
+            *c->h_err = 0;
+            return fail(c, GGR_ERR_TIMEOUT, "a peer's partial states did not arrive in time");
+        }
+    }
+    return GGR_OK;
+}
+
+}  // namespace
+
+extern "C" int ggr_attn_exchange_send(ggr_attn_ctx* c, int32_t layer, const int32_t* pos, int32_t B, const float* q,
+                                      const float* k, const float* v, int32_t ptr_kind) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    int rc = exchange_send(c, layer, pos, B, q, k, v, ptr_kind);
+    if (rc == GGR_OK && ptr_kind == GGR_PTR_HOST) CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    return rc;
+}
+
+extern "C" int ggr_attn_exchange_receive(ggr_attn_ctx* c, int32_t B, float* out, int32_t ptr_kind) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    return exchange_receive(c, B, out, ptr_kind);
+}
+
+extern "C" int ggr_attn_decode_exchange(ggr_attn_ctx* c, int32_t layer, const int32_t* pos, int32_t B, const float* q,
+                                        const float* k, const float* v, float* out, int32_t ptr_kind) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    int rc = exchange_send(c, layer, pos, B, q, k, v, ptr_kind);
+    if (rc) return rc;
+    return exchange_receive(c, B, out, ptr_kind);
+}

@@ -190,6 +190,34 @@ int ggr_attn_decode_partial(ggr_attn_ctx* ctx, int32_t layer, const int32_t* pos
 int ggr_attn_combine_partials(ggr_attn_ctx* ctx, const float* parts, int32_t n_parts, int32_t B, float* out,
                               int32_t ptr_kind);
 
+/*
+ * Fused exchange for KV-sequence shards (no counterpart in the reference). Instead of all-gathering
+ * the partial states with a collective, the decode kernel stores this rank's states directly into the
+ * receive buffer every rank keeps (peer memory over NVLink, plain stores) and raises a flag there; a
+ * second kernel waits, bounded, for all ranks' flags and merges. One call replaces
+ * ggr_attn_decode_partial + all-gather + ggr_attn_combine_partials.
+ *
+ * ggr_attn_exchange_create allocates the local receive buffer for up to max_B sequences (uses the
+ * context's n_ranks / rank, at most 8 ranks) and returns its device address and its 64-byte CUDA IPC
+ * handle. ggr_attn_exchange_connect takes all ranks' handles ([n_ranks][64] bytes, gathered by the
+ * host, e.g. with torch.distributed.all_gather) or, for ranks living in one process, their device
+ * addresses. Every rank must make the same sequence of ggr_attn_decode_exchange calls. A rank whose
+ * peers do not deliver within the bound gets GGR_ERR_TIMEOUT (after a host-pointer call, or from
+ * ggr_attn_synchronize).
+ */
+int ggr_attn_exchange_create(ggr_attn_ctx* ctx, int32_t max_B, void** local_base, unsigned char* ipc_handle);
+int ggr_attn_exchange_connect(ggr_attn_ctx* ctx, const unsigned char* ipc_handles, void* const* same_process_ptrs);
+int ggr_attn_decode_exchange(ggr_attn_ctx* ctx, int32_t layer, const int32_t* pos, int32_t B, const float* q,
+                             const float* k, const float* v, float* out, int32_t ptr_kind);
+/* The two halves of ggr_attn_decode_exchange on their own: send = fused decode over the local slab with
+ * the states stored to all ranks; receive = bounded wait for all ranks' states of the latest step, then
+ * the merge. Ranks that share one GPU (several shards in one process) must finish every send before
+ * any receive is issued, because a waiting kernel and the kernel it waits for must not depend on being
+ * co-scheduled on one GPU. */
+int ggr_attn_exchange_send(ggr_attn_ctx* ctx, int32_t layer, const int32_t* pos, int32_t B, const float* q,
+                           const float* k, const float* v, int32_t ptr_kind);
+int ggr_attn_exchange_receive(ggr_attn_ctx* ctx, int32_t B, float* out, int32_t ptr_kind);
+
 /* Rows [row0, row0 + nrows) of one layer of one sequence in the reference's
  * Q8 row layout (int8 codes [nrows][kv_dim] and one f32 scale per row), the
  * layout its prefill cache serialises (src/app/prefill_cache.rs:214-249) and

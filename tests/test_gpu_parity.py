@@ -437,3 +437,34 @@ def test_fused_decode_equals_separate_kernels(kv_format, n_heads, n_kv_heads, he
                 assert np.array_equal(fk, pk) and np.array_equal(fv, pv)
         assert fused.launch_count - launches_f == 3       # one launch per step
         assert plain.launch_count - launches_p == 6       # rope/append + attention
+
+
+# ---- fused shard exchange (peer stores + flags), ranks emulated as contexts of one process -----------------
+
+@pytest.mark.parametrize("n_ranks,n_heads,n_kv_heads", [(2, 10, 2), (4, 8, 8)])
+def test_fused_exchange_equals_gather_and_combine(n_ranks, n_heads, n_kv_heads):
+    T, B = 600, 3
+    base = AttnConfig(n_layers=1, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=128, seq_len=T, max_batch=B,
+                      rope_theta=1e6, kv_format=KV_BF16)
+    from gguf_runner_b200 import sharding
+    ora = Oracle(base, threads=THREADS)
+    ranks = [g.AttnContext(sharding.sequence_shard_config(base, r, n_ranks)) for r in range(n_ranks)]
+    bufs = [c.exchange_create(B) for c in ranks]
+    for c in ranks:
+        c.exchange_connect(same_process_ptrs=[b[0] for b in bufs])
+    rng = np.random.default_rng(41)
+    lens = [T - 3, 310, 7]
+    for step in range(max(lens) + 3):
+        pos = [min(step, n + 2) for n in lens]
+        q, k, v = rand(rng, B, base.q_dim), rand(rng, B, base.kv_dim), rand(rng, B, base.kv_dim)
+        want = ora.decode(0, pos, q, k, v)
+        # every rank sends (host buffers: each send is complete on return), then every rank receives
+        for c in ranks:
+            c.exchange_send(0, pos, q, k, v)
+        outs = [c.exchange_receive(B, q) for c in ranks]
+        if step in (0, 5, 200, 400, max(lens) + 2):
+            for o in outs:
+                assert np.max(np.abs(o - want)) <= 2e-2, step
+            assert all(np.array_equal(outs[0], o) for o in outs[1:])
+    for c in ranks:
+        c.close()
