@@ -72,7 +72,7 @@ EXPORTED_SYMBOLS = [
     "ggr_attn_set_kernel_timing", "ggr_attn_kernel_time", "ggr_attn_kv_device_ptrs",
     "ggr_attn_attention_tokens_static", "ggr_attn_last_split_count",
     "ggr_attn_exchange_create", "ggr_attn_exchange_connect", "ggr_attn_decode_exchange",
-    "ggr_attn_exchange_send", "ggr_attn_exchange_receive",
+    "ggr_attn_exchange_send", "ggr_attn_exchange_receive", "ggr_attn_set_layer_fixups",
     "ggr_rope_plan_new", "ggr_rope_plan_free", "ggr_rope_plan_append_text", "ggr_rope_plan_append_grid",
     "ggr_rope_plan_len", "ggr_rope_plan_next_text", "ggr_rope_plan_at", "ggr_rope_plan_export",
     "ggr_rope_axis", "ggr_media_plan_validate", "ggr_media_chunk_end", "ggr_gemma_layer_windows",
@@ -128,6 +128,7 @@ def lib() -> C.CDLL:
     L.ggr_attn_decode_exchange.argtypes = [vp, i32, vp, i32, vp, vp, vp, vp, i32]
     L.ggr_attn_exchange_send.argtypes = [vp, i32, vp, i32, vp, vp, vp, i32]
     L.ggr_attn_exchange_receive.argtypes = [vp, i32, vp, i32]
+    L.ggr_attn_set_layer_fixups.argtypes = [vp, i32, vp, vp, vp, vp, vp, C.c_float]
     L.ggr_attn_set_kernel_timing.argtypes = [vp, i32]
     L.ggr_attn_kernel_time.argtypes = [vp, i32, C.POINTER(C.c_double), C.POINTER(i64), i32]
     L.ggr_attn_kv_device_ptrs.argtypes = [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp),
@@ -304,6 +305,15 @@ class AttnContext:
         arr = np.ascontiguousarray(np.array(list(blocks), dtype=np.int32).reshape(-1, 2))
         self._check(self._L.ggr_attn_set_media_blocks(self._h, C.c_void_p(arr.ctypes.data), arr.shape[0],
                                                        prompt_tokens))
+
+    def set_layer_fixups(self, layer: int, q_bias=None, k_bias=None, v_bias=None, q_norm=None, k_norm=None,
+                         eps: float = 1e-6):
+        """Qwen2 biases and per-head RMS QK-norm weights of one layer (qkv_bias_and_norm,
+        src/engine/runtime/inference.rs:2535-2572); None clears."""
+        arrs = [None if a is None else np.ascontiguousarray(a, dtype=np.float32)
+                for a in (q_bias, k_bias, v_bias, q_norm, k_norm)]
+        ptrs = [None if a is None else C.c_void_p(a.ctypes.data) for a in arrs]
+        self._check(self._L.ggr_attn_set_layer_fixups(self._h, layer, *ptrs, eps))
 
     def visible_keys(self, layer: int, pos: int) -> range:
         s, e = C.c_int32(), C.c_int32()

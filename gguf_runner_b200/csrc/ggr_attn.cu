@@ -63,6 +63,15 @@ struct ggr_attn_ctx {
     // error word the kernels raise when a bounded wait runs out (mapped pinned host memory)
     int* h_err = nullptr;
     int* d_err = nullptr;
+    // per-layer pre-attention fixups (device arrays, null = absent) and their f32 scratch rows
+    struct LayerFixups {
+        float *q_bias = nullptr, *k_bias = nullptr, *v_bias = nullptr, *q_norm = nullptr, *k_norm = nullptr;
+        float eps = 1e-6f;
+        bool any() const { return q_bias || q_norm; }
+    };
+    std::vector<LayerFixups> fixups;
+    float* d_fix[3] = {nullptr, nullptr, nullptr};
+    size_t fix_cap[3] = {0, 0, 0};
     // fused exchange of KV-sequence shards: local receive buffer (flags, then two parities of
     // [n_ranks][max_B][Hq][D + 2] floats), the peers' buffers, step counter
     unsigned char* x_local = nullptr;
@@ -213,6 +222,56 @@ int ensure_copy_streams(ggr_attn_ctx* c, int n_pieces) {
         c->ev_in.push_back(a);
         c->ev_done.push_back(b);
     }
+    return GGR_OK;
+}
+
+// Applies the layer's bias / QK-norm fixups to n rows of q/k/v (device memory, element type es bytes)
+// and redirects the pointers to the f32 scratch rows. No-op for layers without fixups.
+int apply_fixups(ggr_attn_ctx* c, int layer, int n, const void** q, const void** k, const void** v, int* in_bf16) {
+    if ((size_t)layer >= c->fixups.size() || !c->fixups[layer].any()) return GGR_OK;
+    const auto& f = c->fixups[layer];
+    int rc;
+    if ((rc = ensure(c, &c->d_fix[0], &c->fix_cap[0], (size_t)n * c->q_dim))) return rc;
+    if ((rc = ensure(c, &c->d_fix[1], &c->fix_cap[1], (size_t)n * c->kv_dim))) return rc;
+    if ((rc = ensure(c, &c->d_fix[2], &c->fix_cap[2], (size_t)n * c->kv_dim))) return rc;
+    FixupArgs a{};
+    a.q = *q;
+    a.k = *k;
+    a.v = *v;
+    a.in_bf16 = *in_bf16;
+    a.q_bias = f.q_bias;
+    a.k_bias = f.k_bias;
+    a.v_bias = f.v_bias;
+    a.q_norm = f.q_norm;
+    a.k_norm = f.k_norm;
+    a.eps = f.eps > 0.0f ? f.eps : 1e-5f;  // src/engine/runtime/inference.rs:2539-2543
+    a.Hq = c->kv.Hq;
+    a.Hkv = c->kv.Hkv;
+    a.D = c->D;
+    a.q_out = c->d_fix[0];
+    a.k_out = c->d_fix[1];
+    a.v_out = c->d_fix[2];
+    for (int i0 = 0; i0 < n; i0 += 65535) {
+        const int cnt = std::min(65535, n - i0);
+        FixupArgs b = a;
+        const size_t es = *in_bf16 ? 2 : 4;
+        b.q = static_cast<const unsigned char*>(a.q) + (size_t)i0 * c->q_dim * es;
+        b.k = static_cast<const unsigned char*>(a.k) + (size_t)i0 * c->kv_dim * es;
+        b.v = static_cast<const unsigned char*>(a.v) + (size_t)i0 * c->kv_dim * es;
+        b.q_out = a.q_out + (size_t)i0 * c->q_dim;
+        b.k_out = a.k_out + (size_t)i0 * c->kv_dim;
+        b.v_out = a.v_out + (size_t)i0 * c->kv_dim;
+        {
+            LaunchTimer t(c, 1);
+            qkv_fixup_kernel<<<cnt, 256, 0, c->stream>>>(b);
+        }
+        CUDA_TRY(c, cudaGetLastError());
+        c->launches++;
+    }
+    *q = c->d_fix[0];
+    *k = c->d_fix[1];
+    *v = c->d_fix[2];
+    *in_bf16 = 0;
     return GGR_OK;
 }
 
@@ -529,6 +588,8 @@ int decode_common(ggr_attn_ctx* c, int layer, const int32_t* pos, int B, const f
         dout = reinterpret_cast<float*>(c->d_stage[3]);
     }
     if ((rc = ensure(c, &c->d_qrot, &c->qrot_cap, (size_t)B * c->q_dim))) return rc;
+    int in_bf16 = 0;
+    if ((rc = apply_fixups(c, layer, B, &dq, &dk, &dv, &in_bf16))) return rc;
 
     for (int b0 = 0; b0 < B; b0 += kMaxArgItems) {
         const int n = std::min(kMaxArgItems, B - b0);
@@ -616,10 +677,15 @@ int prefill_common(ggr_attn_ctx* c, int layer, int seq, int base_pos, int m, con
             it.seq0 = seq;
             it.base_pos = base_pos + j0;
             it.n = cnt;
-            int r = launch_rope_append(c, layer, it, RF_ROTATE | RF_WRITE_Q | RF_APPEND, in_dtype == GGR_DTYPE_BF16,
-                                       dq + (size_t)j0 * c->q_dim * es, dk + (size_t)j0 * c->kv_dim * es,
-                                       dv + (size_t)j0 * c->kv_dim * es, tc ? nullptr : c->d_qrot + (size_t)j0 * c->q_dim,
-                                       tc ? c->d_qrot_h + (size_t)j0 * c->q_dim : nullptr, nullptr);
+            const void* fq = dq + (size_t)j0 * c->q_dim * es;
+            const void* fk = dk + (size_t)j0 * c->kv_dim * es;
+            const void* fv = dv + (size_t)j0 * c->kv_dim * es;
+            int in_bf16 = in_dtype == GGR_DTYPE_BF16;
+            int r = apply_fixups(c, layer, cnt, &fq, &fk, &fv, &in_bf16);
+            if (r) return r;
+            r = launch_rope_append(c, layer, it, RF_ROTATE | RF_WRITE_Q | RF_APPEND, in_bf16, fq, fk, fv,
+                                   tc ? nullptr : c->d_qrot + (size_t)j0 * c->q_dim,
+                                   tc ? c->d_qrot_h + (size_t)j0 * c->q_dim : nullptr, nullptr);
             if (r) return r;
         }
         return GGR_OK;
@@ -896,6 +962,9 @@ void ggr_attn_destroy(ggr_attn_ctx* c) {
         if (c->x_opened[r]) cudaIpcCloseMemHandle(c->x_peer[r]);
     cudaFree(c->x_local);
     cudaFree(c->d_done);
+    for (auto* p : c->d_fix) cudaFree(p);
+    for (auto& f : c->fixups)
+        for (float* p : {f.q_bias, f.k_bias, f.v_bias, f.q_norm, f.k_norm}) cudaFree(p);
     if (c->h_err) cudaFreeHost(c->h_err);
     for (auto e : c->ev_in) cudaEventDestroy(e);
     for (auto e : c->ev_done) cudaEventDestroy(e);
@@ -1448,6 +1517,8 @@ int exchange_send(ggr_attn_ctx* c, int layer, const int32_t* pos, int B, const f
     if ((rc = stage_in(c, 1, k, kb, ptr_kind, &dk))) return rc;
     if ((rc = stage_in(c, 2, v, kb, ptr_kind, &dv))) return rc;
     if ((rc = ensure(c, &c->d_qrot, &c->qrot_cap, (size_t)B * c->q_dim))) return rc;
+    int in_bf16 = 0;
+    if ((rc = apply_fixups(c, layer, B, &dq, &dk, &dv, &in_bf16))) return rc;
     const int n = c->cfg.n_ranks, me = c->cfg.rank;
     const int epoch = ++c->x_epoch;
     const size_t slot = x_slot_floats(c), parity_off = (size_t)(epoch & 1) * n * slot;
@@ -1527,4 +1598,37 @@ extern "C" int ggr_attn_decode_exchange(ggr_attn_ctx* c, int32_t layer, const in
     int rc = exchange_send(c, layer, pos, B, q, k, v, ptr_kind);
     if (rc) return rc;
     return exchange_receive(c, B, out, ptr_kind);
+}
+
+// ---- per-layer pre-attention fixups ----------------------------------------------------------------------
+
+extern "C" int ggr_attn_set_layer_fixups(ggr_attn_ctx* c, int32_t layer, const float* q_bias, const float* k_bias,
+                                         const float* v_bias, const float* q_norm, const float* k_norm, float eps) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    int rc = check_layer(c, layer);
+    if (rc) return rc;
+    if ((q_bias || k_bias || v_bias) && !(q_bias && k_bias && v_bias))
+        return fail(c, GGR_ERR_INVALID, "q, k and v biases come together");
+    if ((q_norm || k_norm) && !(q_norm && k_norm)) return fail(c, GGR_ERR_INVALID, "q and k norm weights come together");
+    CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    c->fixups.resize(c->cfg.n_layers);
+    auto& f = c->fixups[layer];
+    for (float** p : {&f.q_bias, &f.k_bias, &f.v_bias, &f.q_norm, &f.k_norm}) {
+        cudaFree(*p);
+        *p = nullptr;
+    }
+    auto upload = [&](float** dst, const float* src, size_t n) -> int {
+        if (!src) return GGR_OK;
+        if (cudaMalloc((void**)dst, n * sizeof(float)) != cudaSuccess) return fail(c, GGR_ERR_ALLOC, "unable to allocate fixups");
+        CUDA_TRY(c, cudaMemcpy(*dst, src, n * sizeof(float), cudaMemcpyHostToDevice));
+        return GGR_OK;
+    };
+    if ((rc = upload(&f.q_bias, q_bias, c->q_dim))) return rc;
+    if ((rc = upload(&f.k_bias, k_bias, c->kv_dim))) return rc;
+    if ((rc = upload(&f.v_bias, v_bias, c->kv_dim))) return rc;
+    if ((rc = upload(&f.q_norm, q_norm, c->D))) return rc;
+    if ((rc = upload(&f.k_norm, k_norm, c->D))) return rc;
+    f.eps = eps;
+    return GGR_OK;
 }

@@ -524,4 +524,58 @@ __global__ void __launch_bounds__(256) rope_append_vec_kernel(RopeAppendArgs a) 
     }
 }
 
+// ---- pre-attention fixups: Qwen2 biases and per-head RMS QK-norm --------------------------------------
+// Device counterpart of qkv_bias_and_norm (src/engine/runtime/inference.rs:2535-2572) and
+// rmsnorm_per_head_gemma_inplace (src/engine/kernels/math.rs:164-184): q/k/v (+ bias), then
+// x = weight * (x / sqrt(mean(x^2) + eps)) per head of q and k. One CTA per token, one warp per head;
+// results go to f32 scratch rows that the rope/append (or fused decode) kernels then read.
+struct FixupArgs {
+    const void* q;
+    const void* k;
+    const void* v;
+    int in_bf16;
+    const float* q_bias;  // [q_dim] or null
+    const float* k_bias;  // [kv_dim]
+    const float* v_bias;  // [kv_dim]
+    const float* q_norm;  // [D] or null
+    const float* k_norm;  // [D]
+    float eps;
+    int Hq, Hkv, D;
+    float* q_out;
+    float* k_out;
+    float* v_out;
+};
+
+__global__ void __launch_bounds__(256) qkv_fixup_kernel(FixupArgs a) {
+    const int item = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int D = a.D, q_dim = a.Hq * D, kv_dim = a.Hkv * D;
+    for (int hh = warp; hh < a.Hq + a.Hkv; hh += nw) {
+        const bool is_q = hh < a.Hq;
+        const int h = is_q ? hh : hh - a.Hq;
+        const int64_t base = (int64_t)item * (is_q ? q_dim : kv_dim) + (int64_t)h * D;
+        const void* src = is_q ? a.q : a.k;
+        const float* bias = is_q ? a.q_bias : a.k_bias;
+        const float* w = is_q ? a.q_norm : a.k_norm;
+        float* dst = (is_q ? a.q_out : a.k_out) + base;
+        float ss = 0.0f;
+        for (int j = lane; j < D; j += 32) {
+            float x = load_in(src, base + j, a.in_bf16);
+            if (bias) x = __fadd_rn(x, bias[h * D + j]);
+            dst[j] = x;
+            ss = fmaf(x, x, ss);
+        }
+        if (w) {
+            ss = warp_sum(ss);
+            const float inv = 1.0f / sqrtf(ss / (float)D + a.eps);
+            __syncwarp();
+            for (int j = lane; j < D; j += 32) dst[j] = __fmul_rn(w[j], __fmul_rn(inv, dst[j]));
+        }
+    }
+    for (int idx = threadIdx.x; idx < kv_dim; idx += blockDim.x) {
+        float x = load_in(a.v, (int64_t)item * kv_dim + idx, a.in_bf16);
+        if (a.v_bias) x = __fadd_rn(x, a.v_bias[idx]);
+        a.v_out[(int64_t)item * kv_dim + idx] = x;
+    }
+}
+
 }  // namespace ggr

@@ -130,6 +130,17 @@ int ggr_attn_set_media_blocks(ggr_attn_ctx* ctx, const int32_t* start_len, int32
 int ggr_attn_visible_keys(const ggr_attn_ctx* ctx, int32_t layer, int32_t pos, int32_t* start, int32_t* end);
 
 /*
+ * Per-layer pre-attention fixups, applied to q/k/v before RoPE inside ggr_attn_decode, ggr_attn_prefill,
+ * ggr_attn_prefill_block and the shard exchange: Qwen2 q/k/v bias add and the per-head RMS norm of q and k
+ * (Qwen3, Gemma3). Replaces qkv_bias_and_norm (src/engine/runtime/inference.rs:2535-2572) and
+ * rmsnorm_per_head_gemma_inplace (src/engine/kernels/math.rs:164-184). Host arrays: biases [q_dim] /
+ * [kv_dim] / [kv_dim] (all three or none), norm weights [head_dim] each (both or none); null clears.
+ * eps <= 0 selects 1e-5 like the reference.
+ */
+int ggr_attn_set_layer_fixups(ggr_attn_ctx* ctx, int32_t layer, const float* q_bias, const float* k_bias,
+                              const float* v_bias, const float* q_norm, const float* k_norm, float eps);
+
+/*
  * Fused decode step: for each of B sequences, rope(q, k) + append(k, v) at
  * pos[b] + attention over the visible cache rows. Replaces the three calls at
  * src/engine/runtime/inference.rs:3499-3507 (apply_rope_qk :1817,

@@ -141,6 +141,9 @@ struct ora_ctx {
     ora_plan plan;
     std::vector<Block> blocks;
     int64_t prompt_tokens = 0;
+    // per-layer fixups (empty = absent)
+    std::vector<std::vector<float>> q_bias, k_bias, v_bias, q_norm, k_norm;
+    float norm_eps = 1e-6f;
     // scratch: att rows per head (src/engine/runtime/inference.rs:1611-1614)
     std::vector<float> att;
 };
@@ -432,6 +435,35 @@ void attention_head(ora_ctx* s, int seq, int l, int h, int64_t vs, int64_t ve, c
     }
 }
 
+// src/engine/kernels/math.rs:164-184
+void rmsnorm_per_head(float* x, const float* weight, int n_heads, int head_size, float eps) {
+    for (int h = 0; h < n_heads; ++h) {
+        float* p = x + (size_t)h * head_size;
+        float ss = 0.0f;
+        for (int j = 0; j < head_size; ++j) ss += p[j] * p[j];
+        ss /= (float)head_size;
+        ss += eps;
+        ss = 1.0f / sqrtf(ss);
+        for (int j = 0; j < head_size; ++j) p[j] = weight[j] * (ss * p[j]);
+    }
+}
+
+// src/engine/runtime/inference.rs:2535-2572
+void qkv_bias_and_norm(const ora_ctx* s, int l, float* q, float* k, float* v) {
+    if ((size_t)l < s->q_bias.size() && !s->q_bias[l].empty()) {
+        for (int i = 0; i < s->q_dim; ++i) q[i] += s->q_bias[l][i];
+        for (int i = 0; i < s->kv_dim; ++i) {
+            k[i] += s->k_bias[l][i];
+            v[i] += s->v_bias[l][i];
+        }
+    }
+    if ((size_t)l < s->q_norm.size() && !s->q_norm[l].empty() && !s->k_norm[l].empty()) {
+        const float eps = s->norm_eps > 0.0f ? s->norm_eps : 1e-5f;
+        rmsnorm_per_head(q, s->q_norm[l].data(), s->c.n_heads, s->D, eps);
+        rmsnorm_per_head(k, s->k_norm[l].data(), s->c.n_kv_heads, s->D, eps);
+    }
+}
+
 void attention_token(ora_ctx* s, int seq, int l, int64_t pos, const float* q, float* out) {
     int64_t vs, ve;
     visible_keys(s, l, pos, &vs, &ve);
@@ -604,6 +636,32 @@ int64_t ora_media_chunk_end(const int64_t* sl, int32_t n, int64_t prompt_tokens,
     return end;
 }
 
+int ora_set_layer_fixups(ora_ctx* s, int32_t layer, const float* q_bias, const float* k_bias, const float* v_bias,
+                         const float* q_norm, const float* k_norm, float eps) {
+    if (layer < 0 || layer >= s->c.n_layers) return -1;
+    const size_t L = (size_t)s->c.n_layers;
+    for (auto* vec : {&s->q_bias, &s->k_bias, &s->v_bias, &s->q_norm, &s->k_norm}) vec->resize(L);
+    s->q_bias[layer].clear();
+    s->k_bias[layer].clear();
+    s->v_bias[layer].clear();
+    s->q_norm[layer].clear();
+    s->k_norm[layer].clear();
+    if (q_bias && k_bias && v_bias) {
+        s->q_bias[layer].assign(q_bias, q_bias + s->q_dim);
+        s->k_bias[layer].assign(k_bias, k_bias + s->kv_dim);
+        s->v_bias[layer].assign(v_bias, v_bias + s->kv_dim);
+    }
+    if (q_norm && k_norm) {
+        s->q_norm[layer].assign(q_norm, q_norm + s->D);
+        s->k_norm[layer].assign(k_norm, k_norm + s->D);
+    }
+    s->norm_eps = eps;
+    return 0;
+}
+void ora_qkv_bias_and_norm(ora_ctx* ctx, int32_t layer, float* q, float* k, float* v) {
+    qkv_bias_and_norm(ctx, layer, q, k, v);
+}
+
 void ora_rope_angles(ora_ctx* ctx, int32_t layer, int32_t pos, float* c, float* s) {
     rope_angles(ctx, layer, pos, c, s);
 }
@@ -626,12 +684,14 @@ void ora_visible_keys(ora_ctx* ctx, int32_t layer, int32_t pos, int32_t* start, 
 // call site src/engine/runtime/inference.rs:3499-3507, once per sequence
 void ora_decode(ora_ctx* ctx, int32_t layer, const int32_t* pos, int32_t B, const float* q, const float* k,
                 const float* v, float* out) {
-    std::vector<float> qb(ctx->q_dim), kb(ctx->kv_dim);
+    std::vector<float> qb(ctx->q_dim), kb(ctx->kv_dim), vb(ctx->kv_dim);
     for (int b = 0; b < B; ++b) {
         std::memcpy(qb.data(), q + (size_t)b * ctx->q_dim, sizeof(float) * ctx->q_dim);
         std::memcpy(kb.data(), k + (size_t)b * ctx->kv_dim, sizeof(float) * ctx->kv_dim);
+        std::memcpy(vb.data(), v + (size_t)b * ctx->kv_dim, sizeof(float) * ctx->kv_dim);
+        qkv_bias_and_norm(ctx, layer, qb.data(), kb.data(), vb.data());
         apply_rope(ctx, layer, pos[b], qb.data(), kb.data());
-        kv_write(ctx, b, layer, pos[b], kb.data(), v + (size_t)b * ctx->kv_dim);
+        kv_write(ctx, b, layer, pos[b], kb.data(), vb.data());
         attention_token(ctx, b, layer, pos[b], qb.data(), out + (size_t)b * ctx->q_dim);
     }
 }
@@ -639,13 +699,15 @@ void ora_decode(ora_ctx* ctx, int32_t layer, const int32_t* pos, int32_t B, cons
 // call site src/engine/runtime/inference.rs:2981-3017 (attention part)
 void ora_prefill(ora_ctx* ctx, int32_t layer, int32_t seq, int32_t base_pos, int32_t m, const float* q,
                  const float* k, const float* v, float* out) {
-    std::vector<float> qb(ctx->q_dim), kb(ctx->kv_dim);
+    std::vector<float> qb(ctx->q_dim), kb(ctx->kv_dim), vb(ctx->kv_dim);
     for (int i = 0; i < m; ++i) {
         int pos = base_pos + i;
         std::memcpy(qb.data(), q + (size_t)i * ctx->q_dim, sizeof(float) * ctx->q_dim);
         std::memcpy(kb.data(), k + (size_t)i * ctx->kv_dim, sizeof(float) * ctx->kv_dim);
+        std::memcpy(vb.data(), v + (size_t)i * ctx->kv_dim, sizeof(float) * ctx->kv_dim);
+        qkv_bias_and_norm(ctx, layer, qb.data(), kb.data(), vb.data());
         apply_rope(ctx, layer, pos, qb.data(), kb.data());
-        kv_write(ctx, seq, layer, pos, kb.data(), v + (size_t)i * ctx->kv_dim);
+        kv_write(ctx, seq, layer, pos, kb.data(), vb.data());
         attention_token(ctx, seq, layer, pos, qb.data(), out + (size_t)i * ctx->q_dim);
     }
 }
@@ -653,13 +715,15 @@ void ora_prefill(ora_ctx* ctx, int32_t layer, int32_t seq, int32_t base_pos, int
 // call site src/engine/runtime/media_prefill.rs:87-118 (attention part)
 void ora_prefill_block(ora_ctx* ctx, int32_t layer, int32_t seq, int32_t base_pos, int32_t m, const float* q,
                        const float* k, const float* v, float* out) {
-    std::vector<float> queries((size_t)m * ctx->q_dim), kb(ctx->kv_dim);
+    std::vector<float> queries((size_t)m * ctx->q_dim), kb(ctx->kv_dim), vb(ctx->kv_dim);
     std::memcpy(queries.data(), q, sizeof(float) * (size_t)m * ctx->q_dim);
     for (int i = 0; i < m; ++i) {
         int pos = base_pos + i;
         std::memcpy(kb.data(), k + (size_t)i * ctx->kv_dim, sizeof(float) * ctx->kv_dim);
+        std::memcpy(vb.data(), v + (size_t)i * ctx->kv_dim, sizeof(float) * ctx->kv_dim);
+        qkv_bias_and_norm(ctx, layer, queries.data() + (size_t)i * ctx->q_dim, kb.data(), vb.data());
         apply_rope(ctx, layer, pos, queries.data() + (size_t)i * ctx->q_dim, kb.data());
-        kv_write(ctx, seq, layer, pos, kb.data(), v + (size_t)i * ctx->kv_dim);
+        kv_write(ctx, seq, layer, pos, kb.data(), vb.data());
     }
     for (int i = 0; i < m; ++i)
         attention_token(ctx, seq, layer, base_pos + i, queries.data() + (size_t)i * ctx->q_dim,

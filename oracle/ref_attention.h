@@ -51,6 +51,12 @@ int ora_threads_available(void);
 int ora_set_position_plan(ora_ctx* ctx, const int32_t* thw, int32_t n, int32_t next_text_pos);
 int ora_set_media_blocks(ora_ctx* ctx, const int32_t* start_len, int32_t n, int32_t prompt_tokens);
 
+/* per-layer pre-attention fixups (null = absent): Qwen2 biases and per-head RMS QK-norm,
+ * applied to q/k/v before RoPE by the call-site compositions below */
+int ora_set_layer_fixups(ora_ctx* ctx, int32_t layer, const float* q_bias, const float* k_bias, const float* v_bias,
+                         const float* q_norm, const float* k_norm, float eps);
+void ora_qkv_bias_and_norm(ora_ctx* ctx, int32_t layer, float* q, float* k, float* v);
+
 /* the three reference functions, with explicit buffers instead of RunState */
 void ora_rope_angles(ora_ctx* ctx, int32_t layer, int32_t pos, float* cos_out, float* sin_out);
 void ora_apply_rope_qk(ora_ctx* ctx, int32_t layer, int32_t pos, float* q, float* k);

@@ -49,6 +49,9 @@ def lib() -> C.CDLL:
     L.ora_set_threads.restype = None
     L.ora_set_position_plan.argtypes = [vp, vp, i32, i32]
     L.ora_set_media_blocks.argtypes = [vp, vp, i32, i32]
+    L.ora_set_layer_fixups.argtypes = [vp, i32, vp, vp, vp, vp, vp, C.c_float]
+    L.ora_qkv_bias_and_norm.argtypes = [vp, i32, vp, vp, vp]
+    L.ora_qkv_bias_and_norm.restype = None
     L.ora_rope_angles.argtypes = [vp, i32, i32, vp, vp]
     L.ora_rope_angles.restype = None
     L.ora_apply_rope_qk.argtypes = [vp, i32, i32, vp, vp]
@@ -181,6 +184,13 @@ class Oracle:
         arr = np.ascontiguousarray(np.asarray(blocks, dtype=np.int32).reshape(-1, 2))
         if self.L.ora_set_media_blocks(self.h, _p(arr), arr.shape[0], prompt_tokens) != 0:
             raise ValueError("invalid blocks")
+
+    def set_layer_fixups(self, layer, q_bias=None, k_bias=None, v_bias=None, q_norm=None, k_norm=None, eps=1e-6):
+        arrs = [None if a is None else _f32(a) for a in (q_bias, k_bias, v_bias, q_norm, k_norm)]
+        self._fix = arrs
+        ptrs = [None if a is None else _p(a) for a in arrs]
+        if self.L.ora_set_layer_fixups(self.h, layer, *ptrs, eps) != 0:
+            raise ValueError("bad layer")
 
     def rope_angles(self, layer, pos):
         half = (self.cfg.rope_dim or self.cfg.head_dim) // 2

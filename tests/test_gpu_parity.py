@@ -468,3 +468,30 @@ def test_fused_exchange_equals_gather_and_combine(n_ranks, n_heads, n_kv_heads):
             assert all(np.array_equal(outs[0], o) for o in outs[1:])
     for c in ranks:
         c.close()
+
+
+# ---- pre-attention fixups: Qwen2 biases and per-head RMS QK-norm (qkv_bias_and_norm) ----------------------
+
+@pytest.mark.parametrize("kv_format,with_bias,with_norm", [(KV_F32, True, True), (KV_BF16, False, True),
+                                                           (KV_Q8_ROW, True, False), (KV_BF16, True, True)])
+def test_bias_and_qk_norm_fixups_match_oracle(kv_format, with_bias, with_norm):
+    cfg = AttnConfig(n_layers=2, n_heads=8, n_kv_heads=2, head_dim=128, seq_len=400, rope_theta=1e6, kv_format=kv_format)
+    ctx, ora = make(cfg)
+    rng = np.random.default_rng(51)
+    kw = {}
+    if with_bias:
+        kw.update(q_bias=rand(rng, cfg.q_dim) * 0.5, k_bias=rand(rng, cfg.kv_dim) * 0.5, v_bias=rand(rng, cfg.kv_dim) * 0.5)
+    if with_norm:
+        kw.update(q_norm=1.0 + 0.1 * rand(rng, cfg.head_dim), k_norm=1.0 + 0.1 * rand(rng, cfg.head_dim))
+    ctx.set_layer_fixups(1, eps=1e-6, **kw)
+    ora.set_layer_fixups(1, eps=1e-6, **kw)
+    tol = TOL[kv_format]
+    q, k, v = rand(rng, 300, cfg.q_dim), rand(rng, 300, cfg.kv_dim), rand(rng, 300, cfg.kv_dim)
+    assert np.max(np.abs(ctx.prefill(1, 0, q, k, v) - ora.prefill(1, 0, q, k, v))) <= tol
+    for pos in (300, 301):
+        q, k, v = rand(rng, 1, cfg.q_dim), rand(rng, 1, cfg.kv_dim), rand(rng, 1, cfg.kv_dim)
+        assert np.max(np.abs(ctx.decode(1, [pos], q, k, v) - ora.decode(1, [pos], q, k, v))) <= tol
+    # a layer without fixups is untouched
+    q, k, v = rand(rng, 50, cfg.q_dim), rand(rng, 50, cfg.kv_dim), rand(rng, 50, cfg.kv_dim)
+    assert np.max(np.abs(ctx.prefill(0, 0, q, k, v) - ora.prefill(0, 0, q, k, v))) <= tol
+    ctx.close()
