@@ -13,7 +13,9 @@
 //                (cp.async.bulk.tensor, 128-byte swizzle, mbarrier complete_tx)
 //   warp 9       MMA issuer: S_t = Q_t K^T and O_t += P_t V with tcgen05.mma,
 //                accumulators in TMEM (S0 S1 O0 O1 = 512 columns); P_t is read
-//                straight from TMEM where the softmax wrote it over S_t
+//                straight from TMEM where the softmax wrote it over S_t, in two
+//                64-key halves so that P V starts before the softmax has finished
+//                the tile
 //   warps 0-3    softmax of query tile 0 (one thread per query row)
 //   warps 4-7    softmax of query tile 1
 // The two query tiles ping-pong: while one tile's softmax runs on the CUDA
@@ -45,9 +47,35 @@ struct PrefillTcArgs {
 #endif
 };
 
+// cycle-trace hooks of diagnostic builds (-DGGR_TC_TRACE); empty otherwise
+#ifdef GGR_TC_TRACE
+#define TRACE_ADD(var) do { long long now_ = clock64(); var += now_ - tr_x; tr_x = now_; } while (0)
+#define TRACE_MARK() tr_x = clock64()
+// absolute time stamps of four mid-kernel steps: slot layout [step - 16][24]
+#define TRACE_EVT(step, slot) do { if (blockIdx.x == 0 && a.trace && (threadIdx.x & 31) == 0 && (step) >= 16 && (step) < 20) \
+        a.trace[32 + ((step) - 16) * 24 + (slot)] = clock64(); } while (0)
+#else
+#define TRACE_EVT(step, slot)
+#define TRACE_ADD(var)
+#define TRACE_MARK()
+#endif
+
 constexpr int kTcBM = 128;       // query rows per tile
 constexpr int kTcBN = 128;       // keys per tile
 constexpr int kTcThreads = 384;  // 8 softmax warps + a control warpgroup (producer, MMA issuer, 2 idle)
+// Which of every four 4-score groups compute their second score pair with ex2_poly_x2 instead of the MUFU
+// unit: bit g set = group g. 0x5 moves a quarter of all exponentials to the FMA pipe.
+#ifndef GGR_EXP_POLY_MASK
+#define GGR_EXP_POLY_MASK 0x5
+#endif
+constexpr int kExpPolyMask = GGR_EXP_POLY_MASK;
+// registers per thread after the split: control warpgroup (producer, MMA issuer) / softmax warpgroups
+#ifndef GGR_TC_CTRL_REGS
+#define GGR_TC_CTRL_REGS 88
+#define GGR_TC_SOFTMAX_REGS 208
+#endif
+constexpr int kTcCtrlRegs = GGR_TC_CTRL_REGS, kTcSoftmaxRegs = GGR_TC_SOFTMAX_REGS;
+static_assert(tc::RegSplitOk<kTcCtrlRegs, kTcSoftmaxRegs>::value, "setmaxnreg split would never complete");
 
 
 template <int D>
@@ -61,7 +89,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     constexpr uint32_t O_COL0 = 256;                // S0 at 0, S1 at 128, O tiles from 256
 
     extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t bars[16];
+    __shared__ __align__(8) uint64_t bars[18];
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
 
@@ -78,8 +106,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     auto v_full = [&](int s) { return bar0 + 8u * (5 + s); };
     auto v_empty = [&](int s) { return bar0 + 8u * (7 + s); };
     auto s_full = [&](int t) { return bar0 + 8u * (9 + t); };
-    auto p_full = [&](int t) { return bar0 + 8u * (11 + t); };
-    auto o_final = [&](int t) { return bar0 + 8u * (13 + t); };
+    auto p_half = [&](int t, int half) { return bar0 + 8u * (11 + 2 * t + half); };  // P_t keys 0-63 / 64-127 stored
+    auto o_final = [&](int t) { return bar0 + 8u * (15 + t); };
 
     // which query rows and head
     const int Hq = a.kv.Hq, G = a.kv.G;
@@ -122,7 +150,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             mbar_init(v_full(s), 1);
             mbar_init(v_empty(s), 1);
             mbar_init(s_full(s), 1);
-            mbar_init(p_full(s), kTcBM);
+            mbar_init(p_half(s, 0), kTcBM);
+            mbar_init(p_half(s, 1), kTcBM);
             mbar_init(o_final(s), 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -140,7 +169,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
     if (warp >= 8) {
       // control warpgroup: gives registers up; warps 10 and 11 have no role
-      reg_release();
+      reg_release<kTcCtrlRegs>();
       if (warp == 8) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
@@ -167,12 +196,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
       } else if (warp == 9) {
         // ---------------- MMA issuer ----------------
+        // One issuer serves both query tiles in turn. That order is what keeps the tiles in anti-phase (one
+        // tile's softmax runs while the tensor core works for the other tile): with one issuer warp per tile
+        // both tiles fell into step on the shared K / V stages, their softmaxes competed for the MUFU unit
+        // and the kernel was slower.
         if (hi > lo) {  // the whole warp runs the loop, one elected lane issues
             constexpr uint32_t IDESC_QK = idesc_bf16(kTcBN, 0);
             constexpr uint32_t IDESC_PV = idesc_bf16(D, 1);
             // Descriptors are built once; an MMA adds its byte offset (in 16-byte units) to the start
             // address field, so the issue loop is a few integer adds per instruction. (Rebuilding the
-            // 64-bit descriptors per MMA under the 40-register cap made every issue cost ~110 cycles.)
+            // 64-bit descriptors per MMA under the register cap made every issue cost ~110 cycles.)
             const uint64_t dQ = smem_desc(sQ, 16, 1024), dK = smem_desc(sK, 16, 1024);
             const uint64_t dV = smem_desc(sV, BLK_BYTES, 1024);
             auto issue_qk = [&](int t, int s) {
@@ -185,26 +218,24 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                     mma_ss_e(d, a0 + off, b0 + off, IDESC_QK, ks > 0 ? 1u : 0u);
                 }
             };
-            auto issue_pv = [&](int t, int s, bool accumulate) {
-                // O_t += P_t V: P from TMEM (two bf16 per column), V MN-major, 16 keys per instruction
+            auto issue_pv_half = [&](int t, int s, int half, bool accumulate) {
+                // O_t += P_t V over 64 keys: P from TMEM (two bf16 per column), V MN-major, 16 keys per instruction
                 const uint64_t b0 = dV + (uint64_t)((s * TILE_BYTES) >> 4);
                 const uint32_t d = tmem + O_COL0 + t * D, p0 = tmem + t * 128;
-                mma_ts_e(d, p0, b0, IDESC_PV, accumulate ? 1u : 0u);
 #pragma unroll
-                for (int ks = 1; ks < kTcBN / 16; ++ks) mma_ts_e(d, p0 + ks * 8, b0 + (uint64_t)((ks * 16 * 128) >> 4), IDESC_PV, 1u);
+                for (int kk = 0; kk < kTcBN / 32; ++kk) {
+                    const int ks = half * (kTcBN / 32) + kk;
+                    mma_ts_e(d, p0 + ks * 8, b0 + (uint64_t)((ks * 16 * 128) >> 4), IDESC_PV, (accumulate || ks > 0) ? 1u : 0u);
+                }
             };
 #ifdef GGR_TC_TRACE
             long long tr_v = 0, tr_p0 = 0, tr_p1 = 0, tr_k = 0, tr_issue = 0, tr_issue_qk = 0, tr_t0 = clock64(), tr_x;
-#define TRACE_ADD(var) do { long long now_ = clock64(); var += now_ - tr_x; tr_x = now_; } while (0)
-#define TRACE_MARK() tr_x = clock64()
-#else
-#define TRACE_ADD(var)
-#define TRACE_MARK()
 #endif
             bool ok = mbar_wait_warp(q_full, 0, abortp);
             if (ok) ok = mbar_wait_warp(k_full(0), 0, abortp);
             if (ok) {
                 fence_after_sync();
+#pragma unroll
                 for (int t = 0; t < 2; ++t)
                     if (active(t, lo)) {
                         issue_qk(t, 0);
@@ -218,15 +249,23 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 TRACE_MARK();
                 if (!(ok = mbar_wait_warp(v_full(s), (n >> 1) & 1, abortp))) break;
                 TRACE_ADD(tr_v);
+                TRACE_EVT(n, 6);
                 bool next_k_ready = false;
-                for (int t = 0; t < 2 && ok; ++t) {
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
                     if (active(t, j)) {
-                        if (!(ok = mbar_wait_warp(p_full(t), (j - lo_t[t]) & 1, abortp))) break;
+                        const uint32_t ph = (j - lo_t[t]) & 1;
+                        if (!(ok = mbar_wait_warp(p_half(t, 0), ph, abortp))) break;
                         if (t == 0) { TRACE_ADD(tr_p0); } else { TRACE_ADD(tr_p1); }
+                        TRACE_EVT(n, t * 3);
                         fence_after_sync();
-                        issue_pv(t, s, j > lo_t[t]);
+                        issue_pv_half(t, s, 0, j > lo_t[t]);
+                        if (!(ok = mbar_wait_warp(p_half(t, 1), ph, abortp))) break;
+                        fence_after_sync();
+                        issue_pv_half(t, s, 1, true);
                         if (j == hi_t[t] - 1) mma_commit_e(o_final(t));
                         TRACE_ADD(tr_issue);
+                        TRACE_EVT(n, t * 3 + 1);
                     }
                     if (has_next && active(t, j + 1)) {
                         if (!next_k_ready) {
@@ -238,6 +277,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                         issue_qk(t, s ^ 1);
                         mma_commit_e(s_full(t));
                         TRACE_ADD(tr_issue_qk);
+                        TRACE_EVT(n, t * 3 + 2);
                     }
                 }
                 if (!ok) break;
@@ -254,7 +294,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       }
     } else {
         // ---------------- softmax warps: one thread per query row ----------------
-        reg_acquire();
+        reg_acquire<kTcSoftmaxRegs>();
         const int t = warp >> 2;
         const int row = (warp & 3) * 32 + lane;
         const int qi = q_row0 + t * kTcBM + row;
@@ -277,12 +317,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             TRACE_MARK();
             if (!(ok = mbar_wait(s_full(t), k & 1, abortp))) break;
             TRACE_ADD(ts_wait);
+            if ((warp & 3) == 0) TRACE_EVT(j - lo, 8 + t * 8);
             fence_after_sync();
             uint32_t sr[4][32];
 #pragma unroll
             for (int cidx = 0; cidx < 4; ++cidx) tmem_ld32(tS + cidx * 32, sr[cidx]);
             tmem_wait_ld();
             TRACE_ADD(ts_ld);
+            if ((warp & 3) == 0) TRACE_EVT(j - lo, 9 + t * 8);
             const int key0 = j * kTcBN;
             if (key0 < vs || key0 + kTcBN > ve) {
 #pragma unroll
@@ -305,6 +347,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 }
             const float mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
             TRACE_ADD(ts_max);
+            if ((warp & 3) == 0) TRACE_EVT(j - lo, 10 + t * 8);
             // lazy rescale of the running output
             const bool need = mx > m_used + thr;
             float alpha = 1.0f;
@@ -325,6 +368,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             }
             l *= alpha;
             TRACE_ADD(ts_resc);
+            if ((warp & 3) == 0) TRACE_EVT(j - lo, 11 + t * 8);
             const float mref = (m_used == -INFINITY) ? 0.0f : m_used;
             const float neg = -mref * c;
             // p = 2^(s * c - m * c): one packed FMA per two scores, sums kept as packed pairs. Two variants were
@@ -339,10 +383,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 for (int i = 0; i < 16; i += 2) {
                     const uint64_t ta = fma_f32x2(pack_f32x2(__uint_as_float(sr[cidx][2 * i]), __uint_as_float(sr[cidx][2 * i + 1])), c2, neg2);
                     const uint64_t tb = fma_f32x2(pack_f32x2(__uint_as_float(sr[cidx][2 * i + 2]), __uint_as_float(sr[cidx][2 * i + 3])), c2, neg2);
-                    float x0, x1, x2, x3;
+                    float x0, x1, p2, p3;
                     unpack_f32x2(ta, x0, x1);
-                    unpack_f32x2(tb, x2, x3);
-                    const float p0 = ex2(x0), p1 = ex2(x1), p2 = ex2(x2), p3 = ex2(x3);
+                    const float p0 = ex2(x0), p1 = ex2(x1);
+                    if (kExpPolyMask & (1 << ((i >> 1) & 3))) {
+                        ex2_poly_x2(tb, p2, p3);
+                    } else {
+                        float x2, x3;
+                        unpack_f32x2(tb, x2, x3);
+                        p2 = ex2(x2);
+                        p3 = ex2(x3);
+                    }
                     sum_a = add_f32x2(sum_a, pack_f32x2(p0, p1));
                     sum_b = add_f32x2(sum_b, pack_f32x2(p2, p3));
                     __nv_bfloat162 pa = __floats2bfloat162_rn(p0, p1);
@@ -351,6 +402,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                     pk[i + 1] = *reinterpret_cast<uint32_t*>(&pb);
                 }
                 tmem_st16(tS + cidx * 16, pk);
+                if (cidx == 1) {
+                    // keys 0-63 of P_t are in TMEM: their half of P V starts while the other half is computed
+                    tmem_wait_st();
+                    fence_before_sync();
+                    mbar_arrive(p_half(t, 0));
+                }
             }
             {
                 float s0, s1;
@@ -359,8 +416,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             }
             tmem_wait_st();
             fence_before_sync();
-            mbar_arrive(p_full(t));
+            mbar_arrive(p_half(t, 1));
             TRACE_ADD(ts_exp);
+            if ((warp & 3) == 0) TRACE_EVT(j - lo, 12 + t * 8);
         }
 #ifdef GGR_TC_TRACE
         if (blockIdx.x == 0 && a.trace && (tid & 127) == 0) {

@@ -139,6 +139,9 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 for (int ks = 1; ks < kTwBN / 16; ++ks)
                     mma_ts_e(tmem + O_COL0, p0 + ks * 8, b0 + (uint64_t)((ks * 16 * 128) >> 4), IDESC_PV, 1u);
             };
+#ifdef GGR_TC_TRACE
+            long long tr_v = 0, tr_p0 = 0, tr_k = 0, tr_issue = 0, tr_issue_qk = 0, tr_t0 = clock64(), tr_x;
+#endif
             bool ok = mbar_wait_warp(q_full, 0, abortp);
             if (ok) ok = mbar_wait_warp(k_full(0), 0, abortp);
             if (ok) {
@@ -149,21 +152,33 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             }
             for (int j = lo; ok && j < hi; ++j) {
                 const int n = j - lo, s = n & 1;
+                TRACE_MARK();
                 if (j + 1 < hi) {
                     if (!(ok = mbar_wait_warp(k_full(s ^ 1), ((n + 1) >> 1) & 1, abortp))) break;
+                    TRACE_ADD(tr_k);
                     fence_after_sync();
                     issue_qk((n + 1) & 1, s ^ 1);
                     mma_commit_e(s_full((n + 1) & 1));
                     mma_commit_e(k_empty(s ^ 1));
+                    TRACE_ADD(tr_issue_qk);
                 }
                 if (!(ok = mbar_wait_warp(v_full(s), (n >> 1) & 1, abortp))) break;
+                TRACE_ADD(tr_v);
                 if (!(ok = mbar_wait_warp(p_full, n & 1, abortp))) break;
+                TRACE_ADD(tr_p0);
                 fence_after_sync();
                 issue_pv(n & 1, s, n > 0);
                 mma_commit_e(pv_done);
                 mma_commit_e(v_empty(s));
                 if (j == hi - 1) mma_commit_e(o_final);
+                TRACE_ADD(tr_issue);
             }
+#ifdef GGR_TC_TRACE
+            if (blockIdx.x == 0 && a.trace) {
+                a.trace[0] = clock64() - tr_t0; a.trace[1] = tr_v; a.trace[2] = tr_p0; a.trace[3] = 0;
+                a.trace[4] = tr_k; a.trace[5] = tr_issue; a.trace[6] = hi - lo; a.trace[7] = tr_issue_qk;
+            }
+#endif
         }
     } else if (warp < 4) {
         // ---------------- softmax: one thread per query row ----------------
@@ -178,15 +193,21 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         const float thr = 8.0f / c;
         float m_used = -INFINITY, l = 0.0f;
         bool ok = true;
+#ifdef GGR_TC_TRACE
+        long long ts_wait = 0, ts_ld = 0, ts_max = 0, ts_resc = 0, ts_exp = 0, ts_t0 = clock64(), tr_x;
+#endif
         for (int j = lo; j < hi; ++j) {
             const int n = j - lo, buf = n & 1;
             const uint32_t tS = tmem + lane_addr + buf * kTwBN;
+            TRACE_MARK();
             if (!(ok = mbar_wait(s_full(buf), (n >> 1) & 1, abortp))) break;
+            TRACE_ADD(ts_wait);
             fence_after_sync();
             uint32_t sr[2][32];
             tmem_ld32(tS, sr[0]);
             tmem_ld32(tS + 32, sr[1]);
             tmem_wait_ld();
+            TRACE_ADD(ts_ld);
             const int key0 = j * kTwBN;
             if (key0 < vs || key0 + kTwBN > ve) {
 #pragma unroll
@@ -208,6 +229,7 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                     mxd = max3(mxd, __uint_as_float(sr[cidx][i + 6]), __uint_as_float(sr[cidx][i + 7]));
                 }
             const float mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
+            TRACE_ADD(ts_max);
             const bool need = mx > m_used + thr;
             float alpha = 1.0f;
             if (need) {
@@ -231,6 +253,7 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 }
             }
             l *= alpha;
+            TRACE_ADD(ts_resc);
             const float mref = (m_used == -INFINITY) ? 0.0f : m_used;
             const float neg = -mref * c;
             // p = 2^(s * c - m * c): one packed FMA per two scores, sums kept as packed pairs
@@ -243,10 +266,17 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 for (int i = 0; i < 16; i += 2) {
                     const uint64_t ta = fma_f32x2(pack_f32x2(__uint_as_float(sr[cidx][2 * i]), __uint_as_float(sr[cidx][2 * i + 1])), c2, neg2);
                     const uint64_t tb = fma_f32x2(pack_f32x2(__uint_as_float(sr[cidx][2 * i + 2]), __uint_as_float(sr[cidx][2 * i + 3])), c2, neg2);
-                    float x0, x1, x2, x3;
+                    float x0, x1, p2, p3;
                     unpack_f32x2(ta, x0, x1);
-                    unpack_f32x2(tb, x2, x3);
-                    const float p0 = ex2(x0), p1 = ex2(x1), p2 = ex2(x2), p3 = ex2(x3);
+                    const float p0 = ex2(x0), p1 = ex2(x1);
+                    if (kExpPolyMask & (1 << ((i >> 1) & 3))) {
+                        ex2_poly_x2(tb, p2, p3);
+                    } else {
+                        float x2, x3;
+                        unpack_f32x2(tb, x2, x3);
+                        p2 = ex2(x2);
+                        p3 = ex2(x3);
+                    }
                     sum_a = add_f32x2(sum_a, pack_f32x2(p0, p1));
                     sum_b = add_f32x2(sum_b, pack_f32x2(p2, p3));
                     __nv_bfloat162 pa = __floats2bfloat162_rn(p0, p1);
@@ -264,7 +294,14 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             tmem_wait_st();
             fence_before_sync();
             mbar_arrive(p_full);
+            TRACE_ADD(ts_exp);
         }
+#ifdef GGR_TC_TRACE
+        if (blockIdx.x == 0 && a.trace && tid == 0) {
+            long long* o = a.trace + 8;
+            o[0] = clock64() - ts_t0; o[1] = ts_wait; o[2] = ts_ld; o[3] = ts_max; o[4] = ts_resc; o[5] = ts_exp; o[6] = hi - lo;
+        }
+#endif
         if (ok && hi > lo) ok = mbar_wait(o_final, 0, abortp);
         if (ok && hi > lo) {
             fence_after_sync();

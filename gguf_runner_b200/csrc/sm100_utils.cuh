@@ -166,12 +166,47 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// 2^x of a packed pair on the FMA and integer pipes, without the MUFU unit (which a flash-attention softmax
+// saturates: 16 ex2 per clock per SM is exactly the rate at which the tensor cores consume 128 x 128 tiles).
+// x = n + f with n = round(x), |f| <= 0.5: adding 1.5 * 2^23 leaves n in the low mantissa bits of the sum;
+// 2^f is a cubic minimax polynomial (relative error 7.5e-5, far inside the bf16 rounding of P); n is then
+// added into the exponent field. Needs x <= 127; x below -125 is clamped, so a masked score (-inf) gives
+// 2^-125 instead of 0, which no sum of at most 2^31 terms can see.
+__device__ __forceinline__ void ex2_poly_x2(uint64_t x2, float& p0, float& p1) {
+    float x0, x1;
+    unpack_f32x2(x2, x0, x1);
+    x0 = fmaxf(x0, -125.0f);
+    x1 = fmaxf(x1, -125.0f);
+    const uint64_t xc = pack_f32x2(x0, x1);
+    const uint64_t r = add_f32x2(xc, pack_f32x2(12582912.0f, 12582912.0f));
+    const uint64_t fl = add_f32x2(r, pack_f32x2(-12582912.0f, -12582912.0f));
+    const uint64_t f = fma_f32x2(fl, pack_f32x2(-1.0f, -1.0f), xc);
+    uint64_t p = fma_f32x2(f, pack_f32x2(0.0551716685f, 0.0551716685f), pack_f32x2(0.24261114f, 0.24261114f));
+    p = fma_f32x2(p, f, pack_f32x2(0.693260968f, 0.693260968f));
+    p = fma_f32x2(p, f, pack_f32x2(0.999928057f, 0.999928057f));
+    float q0, q1, r0, r1;
+    unpack_f32x2(p, q0, q1);
+    unpack_f32x2(r, r0, r1);
+    p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(r0) << 23));
+    p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(r1) << 23));
+}
+
 // Warpgroup-wide register re-allocation in a 384-thread CTA launched with 168 registers per thread:
-// the control warpgroup shrinks to 56, which frees (168 - 56) * 128 = 14336 registers, exactly what the
-// two softmax warpgroups need to grow to 224 ((224 - 168) * 256). setmaxnreg.inc blocks until the pool
-// holds enough registers: a 64 / 224 split frees only 13312, never completes, and hung the kernel.
-__device__ __forceinline__ void reg_release() { asm volatile("setmaxnreg.dec.sync.aligned.u32 56;"); }
-__device__ __forceinline__ void reg_acquire() { asm volatile("setmaxnreg.inc.sync.aligned.u32 224;"); }
+// the control warpgroup shrinks to DEC, which frees (168 - DEC) * 128 registers; the two softmax
+// warpgroups grow to INC and need (INC - 168) * 256. setmaxnreg.inc blocks until the pool holds enough
+// registers, and only registers given back by setmaxnreg.dec count: a 64 / 224 split frees 13312 of the
+// 14336 needed, never completes, and hung the kernel. Legal pairs: 56 / 224, 72 / 216, 88 / 208.
+template <int DEC>
+__device__ __forceinline__ void reg_release() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(DEC)); }
+template <int INC>
+__device__ __forceinline__ void reg_acquire() {
+    static_assert(INC % 8 == 0 && INC <= 224, "register count");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(INC));
+}
+template <int DEC, int INC>
+struct RegSplitOk {
+    static constexpr bool value = DEC % 8 == 0 && INC % 8 == 0 && (168 - DEC) * 128 >= (INC - 168) * 256;
+};
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
