@@ -63,6 +63,7 @@ struct ggr_attn_ctx {
     // error word the kernels raise when a bounded wait runs out (mapped pinned host memory)
     int* h_err = nullptr;
     int* d_err = nullptr;
+    int* d_sched = nullptr;  // work counters of the persistent prefill kernel (rewound by the kernel itself)
     // per-layer pre-attention fixups (device arrays, null = absent) and their f32 scratch rows
     struct LayerFixups {
         float *q_bias = nullptr, *k_bias = nullptr, *v_bias = nullptr, *q_norm = nullptr, *k_norm = nullptr;
@@ -704,6 +705,7 @@ int prefill_common(ggr_attn_ctx* c, int layer, int seq, int base_pos, int m, con
             a.out = dout + (size_t)i0 * c->q_dim;
             a.score_scale = (c->cfg.scale_mode == GGR_SCALE_SCORE ? c->attn_scale : 1.0f) * kLog2e;
             a.err = c->d_err;
+            a.sched = c->d_sched;
 #ifdef GGR_TC_TRACE
             a.trace = g_tc_trace;
 #endif
@@ -923,6 +925,11 @@ int ggr_attn_create(const ggr_attn_config* cfg, ggr_attn_ctx** out) {
         return cleanup(GGR_ERR_ALLOC, "unable to allocate the error word");
     }
     *c->h_err = 0;
+    if (cudaMalloc((void**)&c->d_sched, 2 * sizeof(int)) != cudaSuccess) {
+        cudaGetLastError();
+        return cleanup(GGR_ERR_ALLOC, "unable to allocate the prefill work counters");
+    }
+    cudaMemsetAsync(c->d_sched, 0, 2 * sizeof(int), c->stream);
     if (prefill_tc_shape_ok(kv.fmt, c->D) && rows < ((size_t)1 << 31)) {
         c->have_tmaps = make_tmap_bf16(&c->tmK, kv.k, (uint64_t)c->kv_dim, (uint64_t)rows) &&
                         make_tmap_bf16(&c->tmV, kv.v, (uint64_t)c->kv_dim, (uint64_t)rows);
@@ -966,6 +973,7 @@ void ggr_attn_destroy(ggr_attn_ctx* c) {
     for (auto& f : c->fixups)
         for (float* p : {f.q_bias, f.k_bias, f.v_bias, f.q_norm, f.k_norm}) cudaFree(p);
     if (c->h_err) cudaFreeHost(c->h_err);
+    if (c->d_sched) cudaFree(c->d_sched);
     for (auto e : c->ev_in) cudaEventDestroy(e);
     for (auto e : c->ev_done) cudaEventDestroy(e);
     if (c->copy_in) cudaStreamDestroy(c->copy_in);

@@ -6,8 +6,10 @@
 //   warp 5       MMA issuer: S[b] = Q K^T (N = 64) into one of two S buffers, O += P V (N = 256)
 //   warps 0-3    softmax, one thread per query row
 // TMEM columns: S0 0-63, S1 64-127, O 128-383. The score tile of step j+1 is computed while the
-// softmax of step j runs; because QK(j+1) is issued before PV(j), the softmax waits for PV(j-1)
-// (pv_done) before it may rescale O.
+// softmax of step j runs. Because QK(j+1) is issued before PV(j), O is still being written when the
+// softmax of step j+1 starts: a step that has to rescale O waits for PV(j) (pv_done) first, every other
+// step only observes that barrier after its exponentials, where the wait is normally over. P is
+// published in two 32-key halves so that P V starts under the second half of the softmax.
 // Shared memory: Q 64 KB + 2 x 32 KB K + 2 x 32 KB V = 192 KB. Every wait is bounded.
 #pragma once
 
@@ -35,11 +37,12 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     constexpr uint32_t O_COL0 = 128;
 
     extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t bars[16];
+    __shared__ __align__(8) uint64_t bars[16];  // 15 used
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // the warp index goes through a broadcast so that the compiler knows the role branches are warp-uniform
+    const int tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sQ = smem_base;
     const uint32_t sK = sQ + Q_BYTES;        // [2 stages][KV_BYTES]
@@ -52,7 +55,8 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     auto v_full = [&](int s) { return bar0 + 8u * (5 + s); };
     auto v_empty = [&](int s) { return bar0 + 8u * (7 + s); };
     auto s_full = [&](int b) { return bar0 + 8u * (9 + b); };
-    const uint32_t p_full = bar0 + 8u * 11, pv_done = bar0 + 8u * 12, o_final = bar0 + 8u * 13;
+    auto p_half = [&](int half) { return bar0 + 8u * (11 + half); };  // P keys 0-31 / 32-63 stored
+    const uint32_t pv_done = bar0 + 8u * 13, o_final = bar0 + 8u * 14;
 
     const int Hq = a.kv.Hq, G = a.kv.G;
     const int n_tiles = (a.m + kTcBM - 1) / kTcBM;
@@ -81,7 +85,8 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             mbar_init(v_empty(s), 1);
             mbar_init(s_full(s), 1);
         }
-        mbar_init(p_full, kTcBM);
+        mbar_init(p_half(0), kTcBM);
+        mbar_init(p_half(1), kTcBM);
         mbar_init(pv_done, 1);
         mbar_init(o_final, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -122,6 +127,7 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             constexpr uint32_t IDESC_QK = idesc_bf16(kTwBN, 0);
             constexpr uint32_t IDESC_PV = idesc_bf16(D, 1);
             const uint64_t dQ = smem_desc(sQ, 16, 1024), dK = smem_desc(sK, 16, 1024), dV = smem_desc(sV, KBLK, 1024);
+            const uint32_t tmem = __shfl_sync(0xffffffffu, s_tmem_base, 0);  // shadows the CTA-wide copy: provably uniform
             auto issue_qk = [&](int buf, int s) {
                 const uint64_t b0 = dK + (uint64_t)((s * KV_BYTES) >> 4);
                 const uint32_t d = tmem + buf * kTwBN;
@@ -131,13 +137,14 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                            b0 + (uint64_t)(((ks >> 2) * KBLK + (ks & 3) * 32) >> 4), IDESC_QK, ks > 0 ? 1u : 0u);
                 }
             };
-            auto issue_pv = [&](int buf, int s, bool accumulate) {
+            auto issue_pv_half = [&](int buf, int s, int half, bool accumulate) {
                 const uint64_t b0 = dV + (uint64_t)((s * KV_BYTES) >> 4);
                 const uint32_t p0 = tmem + buf * kTwBN;
-                mma_ts_e(tmem + O_COL0, p0, b0, IDESC_PV, accumulate ? 1u : 0u);
 #pragma unroll
-                for (int ks = 1; ks < kTwBN / 16; ++ks)
-                    mma_ts_e(tmem + O_COL0, p0 + ks * 8, b0 + (uint64_t)((ks * 16 * 128) >> 4), IDESC_PV, 1u);
+                for (int kk = 0; kk < kTwBN / 32; ++kk) {
+                    const int ks = half * (kTwBN / 32) + kk;
+                    mma_ts_e(tmem + O_COL0, p0 + ks * 8, b0 + (uint64_t)((ks * 16 * 128) >> 4), IDESC_PV, (accumulate || ks > 0) ? 1u : 0u);
+                }
             };
 #ifdef GGR_TC_TRACE
             long long tr_v = 0, tr_p0 = 0, tr_k = 0, tr_issue = 0, tr_issue_qk = 0, tr_t0 = clock64(), tr_x;
@@ -164,10 +171,13 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 }
                 if (!(ok = mbar_wait_warp(v_full(s), (n >> 1) & 1, abortp))) break;
                 TRACE_ADD(tr_v);
-                if (!(ok = mbar_wait_warp(p_full, n & 1, abortp))) break;
+                if (!(ok = mbar_wait_warp(p_half(0), n & 1, abortp))) break;
                 TRACE_ADD(tr_p0);
                 fence_after_sync();
-                issue_pv(n & 1, s, n > 0);
+                issue_pv_half(n & 1, s, 0, n > 0);
+                if (!(ok = mbar_wait_warp(p_half(1), n & 1, abortp))) break;
+                fence_after_sync();
+                issue_pv_half(n & 1, s, 1, true);
                 mma_commit_e(pv_done);
                 mma_commit_e(v_empty(s));
                 if (j == hi - 1) mma_commit_e(o_final);
@@ -236,20 +246,21 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 alpha = ex2((m_used - mx) * c);
                 m_used = mx;
             }
-            if (n > 0) {
-                // O must be quiet before it is rescaled: PV(j-1) was issued after QK(j)
+            // O must be quiet before it is rescaled: PV(j-1) was issued after QK(j). A step that rescales waits
+            // for it here; the others only keep track of the barrier's phase, after their exponentials, where
+            // the wait is normally over already.
+            const bool rescale_now = n > 0 && __any_sync(0xffffffffu, need);
+            if (rescale_now) {
                 if (!(ok = mbar_wait(pv_done, (n - 1) & 1, abortp))) break;
                 fence_after_sync();
-                if (__any_sync(0xffffffffu, need)) {
 #pragma unroll
-                    for (int cidx = 0; cidx < D / 32; ++cidx) {
-                        uint32_t orow[32];
-                        tmem_ld32(tO + cidx * 32, orow);
-                        tmem_wait_ld();
+                for (int cidx = 0; cidx < D / 32; ++cidx) {
+                    uint32_t orow[32];
+                    tmem_ld32(tO + cidx * 32, orow);
+                    tmem_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
-                        tmem_st32(tO + cidx * 32, orow);
-                    }
+                    for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
+                    tmem_st32(tO + cidx * 32, orow);
                 }
             }
             l *= alpha;
@@ -285,6 +296,12 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                     pk[i + 1] = *reinterpret_cast<uint32_t*>(&pb);
                 }
                 tmem_st16(tS + cidx * 16, pk);
+                if (cidx == 0) {
+                    // keys 0-31 of P are in TMEM: their half of P V starts while the other half is computed
+                    tmem_wait_st();
+                    fence_before_sync();
+                    mbar_arrive(p_half(0));
+                }
             }
             {
                 float s0, s1;
@@ -293,7 +310,8 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             }
             tmem_wait_st();
             fence_before_sync();
-            mbar_arrive(p_full);
+            mbar_arrive(p_half(1));
+            if (n > 0 && !rescale_now && !(ok = mbar_wait(pv_done, (n - 1) & 1, abortp))) break;
             TRACE_ADD(ts_exp);
         }
 #ifdef GGR_TC_TRACE

@@ -495,3 +495,27 @@ def test_bias_and_qk_norm_fixups_match_oracle(kv_format, with_bias, with_norm):
     q, k, v = rand(rng, 50, cfg.q_dim), rand(rng, 50, cfg.kv_dim), rand(rng, 50, cfg.kv_dim)
     assert np.max(np.abs(ctx.prefill(0, 0, q, k, v) - ora.prefill(0, 0, q, k, v))) <= tol
     ctx.close()
+
+
+@pytest.mark.parametrize("head_dim,m,window", [(64, 1400, 0), (128, 1280, 0), (128, 1400, 300)])
+def test_prefill_more_work_items_than_sms(head_dim, m, window):
+    """Device-pointer prefill with 200-240 query-tile pairs in one launch: the persistent kernel hands items out
+    from its work counter, a ragged last pair has no second tile, and the counter must be back at zero for the
+    next launch (second layer, then a second chunk on top of the first)."""
+    import torch
+    cfg = AttnConfig(n_layers=2, n_heads=40, n_kv_heads=8, head_dim=head_dim, seq_len=2048, rope_theta=5e5,
+                     kv_format=KV_BF16, layer_windows=[window, window] if window else [])
+    rng = np.random.default_rng(m + head_dim)
+    ctx, ora = make(cfg)
+    worst = 0.0
+    for layer in (0, 1):
+        pos = 0
+        for n in (m, 300):
+            q, k, v = rand(rng, n, cfg.q_dim), rand(rng, n, cfg.kv_dim), rand(rng, n, cfg.kv_dim)
+            got = ctx.prefill(layer, pos, torch.from_numpy(q).cuda(), torch.from_numpy(k).cuda(),
+                              torch.from_numpy(v).cuda()).cpu().numpy()
+            want = ora.prefill(layer, pos, q, k, v)
+            worst = max(worst, float(np.max(np.abs(got - want))))
+            pos += n
+    assert worst <= TOL[KV_BF16], f"max abs err {worst}"
+    ctx.close()
