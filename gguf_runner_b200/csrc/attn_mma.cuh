@@ -105,7 +105,9 @@ __global__ void __launch_bounds__(kMmaWarps * 32) attn_mma_decode_kernel(AttnArg
 
     const int G = a.kv.G, Hq = a.kv.Hq;
     const int split = blockIdx.x, kvh = blockIdx.y, item = blockIdx.z;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // the warp index goes through a broadcast so that the compiler knows everything derived from it (key range,
+    // ring addresses, TMA coordinates) is warp-uniform
+    const int tid = threadIdx.x, lane = tid & 31, warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
     const int gq = lane >> 2, tq = lane & 3;  // row group and position in the quad
 
     int seq, pos;
@@ -343,7 +345,9 @@ __global__ void __launch_bounds__(kTmaWarps * 32) attn_mma_tma_decode_kernel(con
 
     const int G = a.kv.G, Hq = a.kv.Hq;
     const int split = blockIdx.x, kvh = blockIdx.y, item = blockIdx.z;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // the warp index goes through a broadcast so that the compiler knows everything derived from it (key range,
+    // ring addresses, TMA coordinates) is warp-uniform
+    const int tid = threadIdx.x, lane = tid & 31, warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
     const int gq = lane >> 2, tq = lane & 3;
 
     int seq, pos;

@@ -416,7 +416,9 @@ __global__ void __launch_bounds__(kSimtWarps * 32) attn_simt_kernel(AttnArgs a) 
 
     const int D = a.kv.D, G = a.kv.G, Hq = a.kv.Hq;
     const int split = blockIdx.x, kvh = blockIdx.y, item = blockIdx.z;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // the warp index goes through a broadcast so that the compiler knows everything derived from it (key range,
+    // ring addresses, TMA coordinates) is warp-uniform
+    const int tid = threadIdx.x, lane = tid & 31, warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
     const int nw = blockDim.x >> 5;  // 1, 2 or 4 warps, each with its own ring
     const int rowbytes = D * a.kv.elem_bytes;
 
