@@ -38,7 +38,7 @@ inline MmaPlan mma_plan(int D, int smem_optin) {
     if ((size_t)kMmaWarps * nst * stage > (size_t)200 * 1024) nst = 2;
     p.nst = nst;
     size_t ring = (size_t)kMmaWarps * nst * stage;
-    size_t merge = (size_t)kMmaWarps * 16 * (D + 2) * sizeof(float) + 64;
+    size_t merge = (size_t)kMmaWarps * 16 * (D + 2) * sizeof(float) + 256;
     p.smem = ring > merge ? ring : merge;
     p.ctas_per_sm = (int)((size_t)(smem_optin + 1024) / (p.smem + 4096));
     if (p.ctas_per_sm < 1) p.ctas_per_sm = 1;
@@ -317,7 +317,7 @@ inline MmaPlan mma_tma_plan(int D, int smem_optin) {
     const int stage = 2 * kTmaTK * D * 2;
     p.nst = kTmaNST;
     size_t ring = (size_t)kTmaWarps * kTmaNST * stage;
-    size_t merge = (size_t)kTmaWarps * 16 * (D + 2) * sizeof(float) + 64;
+    size_t merge = (size_t)kTmaWarps * 16 * (D + 8 + 2) * sizeof(float) + 256;
     p.smem = (ring > merge ? ring : merge) + 1024;  // slack to align the ring to the swizzle atom
     p.ctas_per_sm = (int)((size_t)(smem_optin + 1024) / (p.smem + 4096));
     if (p.ctas_per_sm < 1) p.ctas_per_sm = 1;
@@ -369,6 +369,19 @@ __global__ void __launch_bounds__(kTmaWarps * 32) attn_mma_tma_decode_kernel(con
     const int n_tiles_total = k1 > k0 ? (k1 - k0 + kTmaTK - 1) / kTmaTK : 0;
     const int my_tiles = n_tiles_total > warp ? (n_tiles_total - warp + kTmaWarps - 1) / kTmaWarps : 0;
 
+#ifdef GGR_TC_TRACE
+    auto stamp = [&](int k) {
+        if (tid == 0 && a.trace) {
+            long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            a.trace[((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + k] = t;
+        }
+    };
+#define DECODE_STAMP(k) stamp(k)
+#else
+#define DECODE_STAMP(k)
+#endif
+    DECODE_STAMP(0);
     if (tid == 0) s_abort = 0;
     if (lane == 0) {
         for (int s = 0; s < NST; ++s) mbar_init(smem_u32(&s_full[warp][s]), 1);
@@ -376,8 +389,6 @@ __global__ void __launch_bounds__(kTmaWarps * 32) attn_mma_tma_decode_kernel(con
     }
     __syncthreads();
     volatile int* abortp = &s_abort;
-    const float* qsrc = a.q + ((int64_t)item * Hq + (int64_t)kvh * G) * D;
-    if (a.fused.enabled) qsrc = fused_rope_prologue(a, item, kvh, seq, pos, pos >= s0 && pos < s1, smem);
 
     auto issue = [&](int tile_idx, int stage) {
         // one lane: K and V rows [key, key + 16) of this KV head, 64 columns per box
@@ -391,6 +402,22 @@ __global__ void __launch_bounds__(kTmaWarps * 32) attn_mma_tma_decode_kernel(con
             tma_load_2d(dst + MAT_BYTES + b * BLK_BYTES, &tmV, kvh * D + b * 64, y, bar);
         }
     };
+
+    // The first tiles are requested before the fused prologue (they do not depend on the query), so the
+    // rotation of q and the append hide behind their latency. The one exception is the warp of the owner CTA
+    // whose first tiles would hold the row that the prologue is about to append.
+    const bool owner = a.fused.enabled && pos >= s0 && pos < s1;
+    bool prefetched = true;
+    if (owner) {
+        const int tile_pos = (pos - s0) / kTmaTK;
+        if (tile_pos % kTmaWarps == warp && tile_pos / kTmaWarps < NST - 1) prefetched = false;
+    }
+    if (prefetched && lane == 0) {
+        for (int s = 0; s < NST - 1 && s < my_tiles; ++s) issue(s, s);
+    }
+    const float* qsrc = a.q + ((int64_t)item * Hq + (int64_t)kvh * G) * D;
+    if (a.fused.enabled) qsrc = fused_rope_prologue(a, item, kvh, seq, pos, owner, smem);
+    DECODE_STAMP(1);
 
     uint32_t use_count = 0;  // tiles consumed so far by this warp over all head groups (barrier phases)
     for (int g0 = 0; g0 < G; g0 += 16) {
@@ -418,7 +445,7 @@ __global__ void __launch_bounds__(kTmaWarps * 32) attn_mma_tma_decode_kernel(con
         for (int nt = 0; nt < NT; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
         float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-        if (lane == 0) {
+        if (lane == 0 && !(g0 == 0 && prefetched)) {
             for (int s = 0; s < NST - 1 && s < my_tiles; ++s) issue(s, (int)((use_count + s) % NST));
         }
         bool ok = true;
@@ -517,14 +544,18 @@ __global__ void __launch_bounds__(kTmaWarps * 32) attn_mma_tma_decode_kernel(con
             for (int i = 0; i < 500; ++i) __nanosleep(1000);  // let copies in flight land
         }
         __syncthreads();  // all rings drained: reuse shared memory as the merge area
-        float* wacc = reinterpret_cast<float*>(smem_al);  // [W][16][D]
-        float* wm = wacc + kTmaWarps * 16 * D;
+        DECODE_STAMP(2);
+        // rows are padded by 8 floats: the eight row groups of a warp then hit different banks
+        constexpr int LD = D + 8;
+        float* wacc = reinterpret_cast<float*>(smem_al);  // [W][16][LD]
+        float* wm = wacc + kTmaWarps * 16 * LD;
         float* wl = wm + kTmaWarps * 16;
+        const bool row0_used = g0 + gq < G, row1_used = g0 + gq + 8 < G;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
             const int d = nt * 8 + tq * 2;
-            *reinterpret_cast<float2*>(&wacc[(warp * 16 + gq) * D + d]) = make_float2(o[nt][0], o[nt][1]);
-            *reinterpret_cast<float2*>(&wacc[(warp * 16 + gq + 8) * D + d]) = make_float2(o[nt][2], o[nt][3]);
+            if (row0_used) *reinterpret_cast<float2*>(&wacc[(warp * 16 + gq) * LD + d]) = make_float2(o[nt][0], o[nt][1]);
+            if (row1_used) *reinterpret_cast<float2*>(&wacc[(warp * 16 + gq + 8) * LD + d]) = make_float2(o[nt][2], o[nt][3]);
         }
         if (tq == 0) {
             wm[warp * 16 + gq] = m0;
@@ -533,11 +564,13 @@ __global__ void __launch_bounds__(kTmaWarps * 32) attn_mma_tma_decode_kernel(con
             wl[warp * 16 + gq + 8] = l1;
         }
         __syncthreads();
-        cta_merge_store(a, wacc, wm, wl, kTmaWarps, 16, g0, min(16, G - g0), item, kvh, split);
+        cta_merge_store(a, wacc, wm, wl, kTmaWarps, 16, g0, min(16, G - g0), item, kvh, split, LD);
         __syncthreads();
     }
     if (tid == 0 && s_abort && a.err) atomicExch(a.err, 1);
+    DECODE_STAMP(3);
     split_merge_store(a, item, kvh, &s_last, reinterpret_cast<float*>(smem_al));
+    DECODE_STAMP(4);
 }
 
 template <int D>

@@ -65,6 +65,9 @@ struct AttnArgs {
     int* err;             // raised when a bounded wait runs out (kernels that wait on mbarriers)
     FusedRope fused;
     PeerExchange px;
+#ifdef GGR_TC_TRACE
+    long long* trace;     // per-CTA phase time stamps (diagnostic builds only)
+#endif
 };
 
 inline size_t fused_rope_smem_bytes(const KvView& kv, int rope_half) {
@@ -84,6 +87,30 @@ __device__ __forceinline__ const float* fused_rope_prologue(const AttnArgs& a, i
     float* krow = qs + G * D;
     float* vrow = krow + kv_dim;
     float* red = vrow + kv_dim;
+    // The raw q (and, in the owner CTA, k / v) values travel to shared memory with cp.async while the angles
+    // are computed, so the prologue costs one round trip to memory instead of two; the rotation then works
+    // pairwise in place, with the same separately rounded products as rope_elem.
+    const int64_t qb = ((int64_t)item * Hq + (int64_t)kvh * G) * D;
+    const int64_t kb = (int64_t)item * kv_dim;
+    const bool whole = a.kv.fmt == KV_Q8_ROW;  // the row scale spans all KV heads
+    const int e0 = whole ? 0 : kvh * D, e1 = whole ? kv_dim : (kvh + 1) * D;
+    {
+        const bool al16 = ((reinterpret_cast<uintptr_t>(a.fused.q_in) | reinterpret_cast<uintptr_t>(a.fused.k_in) |
+                            reinterpret_cast<uintptr_t>(a.fused.v_in)) & 15) == 0 && (half & 3) == 0;
+        auto stage = [&](float* dst, const float* src, int n) {
+            if (al16) {
+                for (int i = tid * 4; i < n; i += nt * 4) cp_async_16(smem_u32(dst + i), src + i, 16);
+            } else {
+                for (int i = tid; i < n; i += nt) cp_async_4(smem_u32(dst + i), src + i, 4);
+            }
+        };
+        stage(qs, a.fused.q_in + qb, G * D);
+        if (owner) {
+            stage(krow + e0, a.fused.k_in + kb + e0, e1 - e0);
+            stage(vrow + e0, a.fused.v_in + kb + e0, e1 - e0);
+        }
+        cp_async_commit();
+    }
     for (int i = tid; i < half; i += nt) {
         const int axis = rope_axis(rp.layout, i, rp.sections);
         int coord = pos;
@@ -94,23 +121,34 @@ __device__ __forceinline__ const float* fused_rope_prologue(const AttnArgs& a, i
         cs[i] = cv;
         sn[i] = sv;
     }
+    cp_async_wait<0>();
     __syncthreads();
-    const int64_t qb = ((int64_t)item * Hq + (int64_t)kvh * G) * D;
-    for (int idx = tid; idx < G * D; idx += nt) {
-        const int g = idx / D, i = idx - g * D;
-        float r = rope_elem(a.fused.q_in, qb + (int64_t)g * D, i, D, rp, cs, sn, 0);
-        if (rp.do_prescale) r = __fmul_rn(r, rp.q_prescale);
-        qs[idx] = r;
-    }
-    if (owner) {
-        const int64_t kb = (int64_t)item * kv_dim;
-        const bool whole = a.kv.fmt == KV_Q8_ROW;  // the row scale spans all KV heads
-        const int e0 = whole ? 0 : kvh * D, e1 = whole ? kv_dim : (kvh + 1) * D;
-        for (int idx = e0 + tid; idx < e1; idx += nt) {
-            const int h = idx / D, i = idx - h * D;
-            krow[idx] = rope_elem(a.fused.k_in, kb + (int64_t)h * D, i, D, rp, cs, sn, 0);
-            vrow[idx] = a.fused.v_in[kb + idx];
+    auto rotate_heads = [&](float* x, int n_heads, bool prescale) {
+        for (int p = tid; p < n_heads * half; p += nt) {
+            const int g = p / half, j = p - g * half;
+            const int i0 = rp.style == 0 ? j : 2 * j, i1 = rp.style == 0 ? j + half : 2 * j + 1;
+            float* xh = x + g * D;
+            const float v0 = xh[i0], v1 = xh[i1];
+            float r0 = __fsub_rn(__fmul_rn(v0, cs[j]), __fmul_rn(v1, sn[j]));
+            float r1 = __fadd_rn(__fmul_rn(v0, sn[j]), __fmul_rn(v1, cs[j]));
+            if (prescale) {
+                r0 = __fmul_rn(r0, rp.q_prescale);
+                r1 = __fmul_rn(r1, rp.q_prescale);
+            }
+            xh[i0] = r0;
+            xh[i1] = r1;
         }
+        if (prescale) {
+            const int tail = D - rp.rope_dim;  // elements beyond the rotated span are only scaled
+            for (int p = tid; p < n_heads * tail; p += nt) {
+                const int g = p / tail, i = rp.rope_dim + (p - g * tail);
+                x[g * D + i] = __fmul_rn(x[g * D + i], rp.q_prescale);
+            }
+        }
+    };
+    rotate_heads(qs, G, rp.do_prescale != 0);
+    if (owner) {
+        rotate_heads(krow + e0, (e1 - e0) / D, false);
         __syncthreads();
         const int64_t r = a.kv.row(seq, a.layer, pos);
         const int64_t off = r * kv_dim + (int64_t)kvh * D;
@@ -218,20 +256,32 @@ __device__ __forceinline__ void store_final(const AttnArgs& a, int item, int h, 
 // Merges the per-warp online-softmax states of a CTA (wacc [nw][RS][D] un-normalised,
 // wm / wl [nw][RS]) for heads g0 .. g0+gn-1 of this KV head and stores them: final
 // when the launch has one split, else into the split scratch.
-__device__ __forceinline__ void cta_merge_store(const AttnArgs& a, const float* wacc, const float* wm, const float* wl,
-                                                int nw, int RS, int g0, int gn, int item, int kvh, int split) {
+__device__ __forceinline__ void cta_merge_store(const AttnArgs& a, const float* wacc, float* wm, float* wl, int nw,
+                                                int RS, int g0, int gn, int item, int kvh, int split, int ld = 0) {
+    if (ld == 0) ld = a.kv.D;  // row stride of wacc (the tensor-core kernels pad it against bank conflicts)
     const int D = a.kv.D, G = a.kv.G, Hq = a.kv.Hq;
-    for (int idx = threadIdx.x; idx < gn * D; idx += blockDim.x) {
-        const int g = idx / D, d = idx - g * D;
+    // one thread per head turns the warps' maxima into weights once (wm <- 2^(m_w - max), wl[g] <- merged l,
+    // wx[g] <- max), so the per-element loop below is a plain weighted sum
+    float* wx = wl + nw * RS;
+    for (int g = threadIdx.x; g < gn; g += blockDim.x) {
         float ms = -INFINITY;
         for (int w = 0; w < nw; ++w) ms = fmaxf(ms, wm[w * RS + g]);
-        float o = 0.0f, ls = 0.0f;
+        float ls = 0.0f;
         for (int w = 0; w < nw; ++w) {
             const float mw = wm[w * RS + g];
             const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - ms);
-            o += f * wacc[(w * RS + g) * D + d];
             ls += f * wl[w * RS + g];
+            wm[w * RS + g] = f;
         }
+        wl[g] = ls;
+        wx[g] = ms;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < gn * D; idx += blockDim.x) {
+        const int g = idx / D, d = idx - g * D;
+        float o = 0.0f;
+        for (int w = 0; w < nw; ++w) o = fmaf(wm[w * RS + g], wacc[(w * RS + g) * ld + d], o);
+        const float ms = wx[g], ls = wl[g];
         const int h = kvh * G + g0 + g;
         if (a.n_split == 1) {
             store_final(a, item, h, d, o, ms, ls);
@@ -283,44 +333,49 @@ __device__ __forceinline__ void split_merge_store(const AttnArgs& a, int item, i
     if (!*s_last) return;
     __threadfence();
     const float* base = a.part + ((int64_t)item * Hq + (int64_t)kvh * G) * NS * (D + 2);
-    // pass 1: one weight per (head, split): w = 2^(m_s - max m); all loads independent
-    for (int idx = threadIdx.x; idx < G * NS; idx += blockDim.x)
-        wsm[idx] = __ldcg(base + (int64_t)idx * (D + 2) + D);
-    __syncthreads();
-    float* lsum = wsm + G * NS;  // [G] merged l
-    for (int g = threadIdx.x; g < G; g += blockDim.x) {
+    // One warp per head; this CTA runs alone at the end of the launch, so everything is arranged for few
+    // dependent round trips to L2: (m, l) of all splits in one lane-strided batch of 8-byte loads, then the
+    // split outputs in batches of 32 independent 8-byte loads per lane (rows of D + 2 floats are 8-byte aligned).
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    for (int g = warp; g < G; g += nwarp) {
+        const float* hb = base + (int64_t)g * NS * (D + 2);
+        float* w = wsm + (size_t)g * 2 * NS;  // [NS] weights, [NS] l
         float ms = -INFINITY;
-        for (int sidx = 0; sidx < NS; ++sidx) ms = fmaxf(ms, wsm[g * NS + sidx]);
+        for (int sidx = lane; sidx < NS; sidx += 32) {
+            const float2 ml = __ldcg(reinterpret_cast<const float2*>(hb + (int64_t)sidx * (D + 2) + D));
+            w[sidx] = ml.x;
+            w[NS + sidx] = ml.y;
+            ms = fmaxf(ms, ml.x);
+        }
+        ms = warp_max(ms);
         float ls = 0.0f;
-        for (int sidx = 0; sidx < NS; ++sidx) {
-            const float mw = wsm[g * NS + sidx];
+        for (int sidx = lane; sidx < NS; sidx += 32) {
+            const float mw = w[sidx];
             const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - ms);
-            wsm[g * NS + sidx] = f;
-            ls += f * __ldcg(base + (int64_t)(g * NS + sidx) * (D + 2) + D + 1);
+            w[sidx] = f;
+            ls += f * w[NS + sidx];
         }
-        lsum[g] = ls;
-        lsum[G + g] = ms;
-    }
-    __syncthreads();
-    // pass 2: weighted sum of the split outputs, four independent loads in flight per thread
-    for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
-        const int g = idx / D, d = idx - g * D;
-        const float* pp = base + (int64_t)g * NS * (D + 2) + d;
-        const float* w = wsm + g * NS;
-        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
-        int sidx = 0;
-        for (; sidx + 4 <= NS; sidx += 4) {
-            const float x0 = __ldcg(pp + (int64_t)(sidx + 0) * (D + 2));
-            const float x1 = __ldcg(pp + (int64_t)(sidx + 1) * (D + 2));
-            const float x2 = __ldcg(pp + (int64_t)(sidx + 2) * (D + 2));
-            const float x3 = __ldcg(pp + (int64_t)(sidx + 3) * (D + 2));
-            o0 = fmaf(w[sidx], x0, o0);
-            o1 = fmaf(w[sidx + 1], x1, o1);
-            o2 = fmaf(w[sidx + 2], x2, o2);
-            o3 = fmaf(w[sidx + 3], x3, o3);
+        ls = warp_sum(ls);
+        __syncwarp();
+        for (int d0 = 2 * lane; d0 < D; d0 += 64) {
+            const float* pp = hb + d0;
+            float ox = 0.0f, oy = 0.0f;
+            for (int s0 = 0; s0 < NS; s0 += 32) {
+                float2 x[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    x[i] = s0 + i < NS ? __ldcg(reinterpret_cast<const float2*>(pp + (int64_t)(s0 + i) * (D + 2)))
+                                       : make_float2(0.0f, 0.0f);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float f = s0 + i < NS ? w[s0 + i] : 0.0f;
+                    ox = fmaf(f, x[i].x, ox);
+                    oy = fmaf(f, x[i].y, oy);
+                }
+            }
+            store_final(a, item, kvh * G + g, d0, ox, ms, ls);
+            store_final(a, item, kvh * G + g, d0 + 1, oy, ms, ls);
         }
-        for (; sidx < NS; ++sidx) o0 = fmaf(w[sidx], __ldcg(pp + (int64_t)sidx * (D + 2)), o0);
-        store_final(a, item, kvh * G + g, d, (o0 + o1) + (o2 + o3), lsum[G + g], lsum[g]);
     }
     if (threadIdx.x == 0) a.counters[item * a.kv.Hkv + kvh] = 0u;  // ready for the next launch
     peer_group_done(a);
@@ -446,13 +501,30 @@ __global__ void __launch_bounds__(kSimtWarps * 32) attn_simt_kernel(AttnArgs a) 
     const bool active = j < chunks;
     const int nsh = FMT == KV_Q8_ROW ? 1 : (FMT == KV_Q8_BLOCK32 ? D / 32 : 0);
 
-    const float* qsrc = a.q + ((int64_t)item * Hq + (int64_t)kvh * G) * D;
-    if (a.fused.enabled) qsrc = fused_rope_prologue(a, item, kvh, seq, pos, pos >= s0 && pos < s1, smem);
-
     unsigned char* ring = smem + (size_t)warp * NST * a.stage_bytes;
     const int n_tiles_total = k1 > k0 ? (k1 - k0 + kSimtTK - 1) / kSimtTK : 0;
     // this warp's tiles: warp, warp + W, ...
     const int my_tiles = n_tiles_total > warp ? (n_tiles_total - warp + nw - 1) / nw : 0;
+
+    // The first tiles are requested before the fused prologue (they do not depend on the query), so the
+    // rotation of q and the append hide behind their latency. The one exception is the warp of the owner CTA
+    // whose first tiles would hold the row that the prologue is about to append.
+    const bool owner = a.fused.enabled && pos >= s0 && pos < s1;
+    bool prefetched = true;
+    if (owner) {
+        const int tile_pos = (pos - s0) / kSimtTK;
+        if (tile_pos % nw == warp && tile_pos / nw < NST - 1) prefetched = false;
+    }
+    if (prefetched) {
+#pragma unroll
+        for (int s = 0; s < NST - 1; ++s) {
+            if (s < my_tiles)
+                issue_tile<FMT>(a, ring + (size_t)s * a.stage_bytes, row0, k0 + (warp + s * nw) * kSimtTK, k1, kvh, lane);
+            cp_async_commit();
+        }
+    }
+    const float* qsrc = a.q + ((int64_t)item * Hq + (int64_t)kvh * G) * D;
+    if (a.fused.enabled) qsrc = fused_rope_prologue(a, item, kvh, seq, pos, owner, smem);
 
     for (int g0 = 0; g0 < G; g0 += GH) {
         float qreg[GH][8], acc[GH][8], m[GH], l[GH];
@@ -470,12 +542,14 @@ __global__ void __launch_bounds__(kSimtWarps * 32) attn_simt_kernel(AttnArgs a) 
         }
 
         // prologue: NST - 1 tiles in flight
+        if (!(g0 == 0 && prefetched)) {
 #pragma unroll
-        for (int s = 0; s < NST - 1; ++s) {
-            if (s < my_tiles)
-                issue_tile<FMT>(a, ring + (size_t)s * a.stage_bytes, row0, k0 + (warp + s * nw) * kSimtTK, k1,
-                                kvh, lane);
-            cp_async_commit();
+            for (int s = 0; s < NST - 1; ++s) {
+                if (s < my_tiles)
+                    issue_tile<FMT>(a, ring + (size_t)s * a.stage_bytes, row0, k0 + (warp + s * nw) * kSimtTK, k1,
+                                    kvh, lane);
+                cp_async_commit();
+            }
         }
 
         for (int it = 0; it < my_tiles; ++it) {

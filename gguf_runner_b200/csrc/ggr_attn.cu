@@ -349,7 +349,7 @@ SimtPlan simt_plan(const ggr_attn_ctx* c) {
     p.nw = nw;
     p.nst = std::max(nst, 2);
     size_t ring = (size_t)p.nw * p.nst * stage;
-    size_t merge = (size_t)p.nw * gh * (c->D + 2) * sizeof(float) + 64;
+    size_t merge = (size_t)p.nw * gh * (c->D + 2) * sizeof(float) + 256;
     p.smem = std::max(ring, merge);
     p.ctas_per_sm = std::max(1, std::min(8, (int)((size_t)(c->smem_optin + 1024) / (p.smem + 4096))));
     return p;
@@ -504,7 +504,7 @@ int launch_attention(ggr_attn_ctx* c, int layer, const Items& items, int t_max, 
     a.n_split = n_split;
     c->last_splits = n_split;
     // the split merge stages one weight per (head, split) in shared memory
-    const size_t merge_smem = n_split > 1 ? ((size_t)c->G * n_split + 2 * c->G) * sizeof(float) : 0;
+    const size_t merge_smem = n_split > 1 ? ((size_t)2 * c->G * n_split + 2 * c->G) * sizeof(float) : 0;
     smem = std::max(smem, merge_smem);
     p.smem = std::max(p.smem, merge_smem);
     if (a.fused.enabled && merge_smem > (size_t)a.fused.smem_off) {
@@ -525,6 +525,9 @@ int launch_attention(ggr_attn_ctx* c, int layer, const Items& items, int t_max, 
         a.counters = c->d_counters;
     }
     dim3 grid(n_split, c->kv.Hkv, items.n);
+#ifdef GGR_TC_TRACE
+    a.trace = g_tc_trace;
+#endif
     if (mma) {
         int rc;
         {
@@ -1417,7 +1420,7 @@ extern "C" int ggr_attn_attention_tokens_static(ggr_attn_ctx* c, int32_t layer, 
     a.n_split = choose_splits((int64_t)c->kv.Hkv * B, (int64_t)c->sm_count * ctas_per_sm, t_max, min_keys, fit,
                               2.0 * c->D * c->kv.elem_bytes, tma ? 65e9 : 40e9);
     c->last_splits = a.n_split;
-    const size_t merge_smem = a.n_split > 1 ? ((size_t)c->G * a.n_split + 2 * c->G) * sizeof(float) : 0;
+    const size_t merge_smem = a.n_split > 1 ? ((size_t)2 * c->G * a.n_split + 2 * c->G) * sizeof(float) : 0;
     smem = std::max(smem, merge_smem);
     p.smem = std::max(p.smem, merge_smem);
     if (a.n_split > 1) {
