@@ -22,7 +22,7 @@ _LIB = None
 
 PTR_HOST, PTR_DEVICE = 0, 1
 DTYPE_F32, DTYPE_BF16 = 0, 1
-KV_F32, KV_BF16, KV_Q8_ROW, KV_Q8_BLOCK32 = 0, 1, 2, 3
+KV_F32, KV_BF16, KV_Q8_ROW, KV_Q8_BLOCK32, KV_TURBO = 0, 1, 2, 3, 4
 ROPE_NEOX, ROPE_ADJACENT = 0, 1
 ROPE_SEQUENTIAL, ROPE_INTERLEAVED = 0, 1
 SCALE_SCORE, SCALE_Q_PRESCALED = 0, 1
@@ -30,7 +30,7 @@ IMAGE_CAUSAL, IMAGE_BIDIRECTIONAL = 0, 1
 SHARD_NONE, SHARD_KV_SEQUENCE = 0, 2
 IMPL_AUTO, IMPL_SIMT, IMPL_MMA, IMPL_TCGEN05 = 0, 1, 2, 3
 
-KV_FORMATS = {"f32": KV_F32, "bf16": KV_BF16, "q8_row": KV_Q8_ROW, "q8_block32": KV_Q8_BLOCK32}
+KV_FORMATS = {"f32": KV_F32, "bf16": KV_BF16, "q8_row": KV_Q8_ROW, "q8_block32": KV_Q8_BLOCK32, "turbo": KV_TURBO}
 
 
 class GgrError(RuntimeError):

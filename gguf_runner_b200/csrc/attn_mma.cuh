@@ -369,18 +369,6 @@ __global__ void __launch_bounds__(kTmaWarps * 32) attn_mma_tma_decode_kernel(con
     const int n_tiles_total = k1 > k0 ? (k1 - k0 + kTmaTK - 1) / kTmaTK : 0;
     const int my_tiles = n_tiles_total > warp ? (n_tiles_total - warp + kTmaWarps - 1) / kTmaWarps : 0;
 
-#ifdef GGR_TC_TRACE
-    auto stamp = [&](int k) {
-        if (tid == 0 && a.trace) {
-            long long t;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-            a.trace[((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + k] = t;
-        }
-    };
-#define DECODE_STAMP(k) stamp(k)
-#else
-#define DECODE_STAMP(k)
-#endif
     DECODE_STAMP(0);
     if (tid == 0) s_abort = 0;
     if (lane == 0) {

@@ -70,6 +70,20 @@ struct AttnArgs {
 #endif
 };
 
+// phase time stamps of diagnostic builds: slot k of this CTA's row in a.trace
+#ifdef GGR_TC_TRACE
+#define DECODE_STAMP(k)                                                                                      \
+    do {                                                                                                     \
+        if (threadIdx.x == 0 && a.trace) {                                                                   \
+            long long t_;                                                                                    \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                           \
+            a.trace[((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + (k)] = t_;        \
+        }                                                                                                    \
+    } while (0)
+#else
+#define DECODE_STAMP(k)
+#endif
+
 inline size_t fused_rope_smem_bytes(const KvView& kv, int rope_half) {
     return (size_t)(2 * rope_half + kv.G * kv.D + 2 * kv.kv_dim + 32) * sizeof(float);
 }
@@ -331,15 +345,30 @@ __device__ __forceinline__ void split_merge_store(const AttnArgs& a, int item, i
     }
     __syncthreads();
     if (!*s_last) return;
+    DECODE_STAMP(5);
     __threadfence();
     const float* base = a.part + ((int64_t)item * Hq + (int64_t)kvh * G) * NS * (D + 2);
-    // One warp per head; this CTA runs alone at the end of the launch, so everything is arranged for few
-    // dependent round trips to L2: (m, l) of all splits in one lane-strided batch of 8-byte loads, then the
-    // split outputs in batches of 32 independent 8-byte loads per lane (rows of D + 2 floats are 8-byte aligned).
+    // One warp per head; this CTA runs alone at the end of the launch and a round trip to the states that other
+    // SMs just wrote costs about 1.4 us, so everything is arranged for few dependent round trips: (m, l) of all
+    // splits in one lane-strided batch of 8-byte loads, the split outputs in batches of 16 or 32 independent
+    // 8-byte loads per lane (rows of D + 2 floats are 8-byte aligned).
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     for (int g = warp; g < G; g += nwarp) {
         const float* hb = base + (int64_t)g * NS * (D + 2);
         float* w = wsm + (size_t)g * 2 * NS;  // [NS] weights, [NS] l
+        // head_dim 128 (two 64-float spans per lane): the outputs of the first 16 splits are requested before
+        // the (m, l) pairs, so both travel in the same round trip; 16 splits or fewer need no second one
+        float2 xa[16], xb[16];
+        const bool fast = D == 128;
+        if (fast) {
+            const float* pp = hb + 2 * lane;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const bool in = i < NS;
+                xa[i] = in ? __ldcg(reinterpret_cast<const float2*>(pp + (int64_t)i * (D + 2))) : make_float2(0.0f, 0.0f);
+                xb[i] = in ? __ldcg(reinterpret_cast<const float2*>(pp + (int64_t)i * (D + 2) + 64)) : make_float2(0.0f, 0.0f);
+            }
+        }
         float ms = -INFINITY;
         for (int sidx = lane; sidx < NS; sidx += 32) {
             const float2 ml = __ldcg(reinterpret_cast<const float2*>(hb + (int64_t)sidx * (D + 2) + D));
@@ -357,20 +386,50 @@ __device__ __forceinline__ void split_merge_store(const AttnArgs& a, int item, i
         }
         ls = warp_sum(ls);
         __syncwarp();
+        DECODE_STAMP(6);
+        if (fast) {
+            const float* pp = hb + 2 * lane;
+            float ax = 0.0f, ay = 0.0f, bx = 0.0f, by = 0.0f;
+            for (int s0 = 0; s0 < NS; s0 += 16) {
+                if (s0 > 0) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const bool in = s0 + i < NS;
+                        xa[i] = in ? __ldcg(reinterpret_cast<const float2*>(pp + (int64_t)(s0 + i) * (D + 2)))
+                                   : make_float2(0.0f, 0.0f);
+                        xb[i] = in ? __ldcg(reinterpret_cast<const float2*>(pp + (int64_t)(s0 + i) * (D + 2) + 64))
+                                   : make_float2(0.0f, 0.0f);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float f = s0 + i < NS ? w[s0 + i] : 0.0f;
+                    ax = fmaf(f, xa[i].x, ax);
+                    ay = fmaf(f, xa[i].y, ay);
+                    bx = fmaf(f, xb[i].x, bx);
+                    by = fmaf(f, xb[i].y, by);
+                }
+            }
+            const int h = kvh * G + g;
+            store_final(a, item, h, 2 * lane, ax, ms, ls);
+            store_final(a, item, h, 2 * lane + 1, ay, ms, ls);
+            store_final(a, item, h, 2 * lane + 64, bx, ms, ls);
+            store_final(a, item, h, 2 * lane + 65, by, ms, ls);
+            continue;
+        }
         for (int d0 = 2 * lane; d0 < D; d0 += 64) {
             const float* pp = hb + d0;
             float ox = 0.0f, oy = 0.0f;
-            for (int s0 = 0; s0 < NS; s0 += 32) {
-                float2 x[32];
+            for (int s0 = 0; s0 < NS; s0 += 16) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    x[i] = s0 + i < NS ? __ldcg(reinterpret_cast<const float2*>(pp + (int64_t)(s0 + i) * (D + 2)))
-                                       : make_float2(0.0f, 0.0f);
+                for (int i = 0; i < 16; ++i)
+                    xa[i] = s0 + i < NS ? __ldcg(reinterpret_cast<const float2*>(pp + (int64_t)(s0 + i) * (D + 2)))
+                                        : make_float2(0.0f, 0.0f);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
+                for (int i = 0; i < 16; ++i) {
                     const float f = s0 + i < NS ? w[s0 + i] : 0.0f;
-                    ox = fmaf(f, x[i].x, ox);
-                    oy = fmaf(f, x[i].y, oy);
+                    ox = fmaf(f, xa[i].x, ox);
+                    oy = fmaf(f, xa[i].y, oy);
                 }
             }
             store_final(a, item, kvh * G + g, d0, ox, ms, ls);
@@ -476,6 +535,7 @@ __global__ void __launch_bounds__(kSimtWarps * 32) attn_simt_kernel(AttnArgs a) 
     const int tid = threadIdx.x, lane = tid & 31, warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
     const int nw = blockDim.x >> 5;  // 1, 2 or 4 warps, each with its own ring
     const int rowbytes = D * a.kv.elem_bytes;
+    DECODE_STAMP(0);
 
     int seq, pos;
     a.items.get(item, seq, pos);
@@ -525,6 +585,7 @@ __global__ void __launch_bounds__(kSimtWarps * 32) attn_simt_kernel(AttnArgs a) 
     }
     const float* qsrc = a.q + ((int64_t)item * Hq + (int64_t)kvh * G) * D;
     if (a.fused.enabled) qsrc = fused_rope_prologue(a, item, kvh, seq, pos, owner, smem);
+    DECODE_STAMP(1);
 
     for (int g0 = 0; g0 < G; g0 += GH) {
         float qreg[GH][8], acc[GH][8], m[GH], l[GH];
@@ -636,6 +697,7 @@ __global__ void __launch_bounds__(kSimtWarps * 32) attn_simt_kernel(AttnArgs a) 
             }
         }
         __syncthreads();  // every warp is done with its ring; reuse it as the merge area
+        DECODE_STAMP(2);
         float* wacc = reinterpret_cast<float*>(smem);            // [W][GH][D]
         float* wm = wacc + nw * GH * D;                           // [W][GH]
         float* wl = wm + nw * GH;                                 // [W][GH]
@@ -658,7 +720,9 @@ __global__ void __launch_bounds__(kSimtWarps * 32) attn_simt_kernel(AttnArgs a) 
         __syncthreads();  // merge area is free again before the next head group refills the ring
     }
 
+    DECODE_STAMP(3);
     split_merge_store(a, item, kvh, &s_last, reinterpret_cast<float*>(smem));
+    DECODE_STAMP(4);
 }
 
 // Merges n_parts partial states [n_parts][items][Hq][D + 2] (o / l, m, l) into out.

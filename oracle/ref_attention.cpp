@@ -136,6 +136,10 @@ struct ora_ctx {
     std::vector<uint16_t> kh, vh;
     std::vector<int8_t> kq, vq;
     std::vector<float> ks, vs;
+    // TurboQuant storage (kv_format 4): 2-bit codes, residual sign bits, sigma (ks / vs) and residual norm per
+    // (row, kv head), and the sign tables of the four transforms
+    std::vector<uint8_t> kt_base, vt_base, kt_sign, vt_sign, turbo_signs;
+    std::vector<float> k_rnorm, v_rnorm;
     // plans
     bool has_plan = false;
     ora_plan plan;
@@ -250,6 +254,160 @@ inline size_t row_index(const ora_ctx* s, int seq, int l, int64_t pos) {
     return ((size_t)seq * s->c.n_layers + l) * (size_t)s->c.seq_len + (size_t)pos;
 }
 
+// ---- TurboQuant cache format (src/engine/runtime/inference.rs:349-1334, scalar branches) ----------------
+
+const float kTurboCentroids[4] = {-1.510417f, -0.45278f, 0.45278f, 1.510417f};  // :349
+const float kTurboThreshold = 0.9815985f;                                       // :350-351
+const uint64_t kTurboSalts[4] = {0x9E3779B97F4A7C15ull, 0xC2B2AE3D27D4EB4Full, 0x165667B19E3779F9ull,
+                                 0xD6E8FEB86659FD93ull};  // rot_pre, rot_post, res_pre, res_post (:352-355)
+
+// :673-679
+inline uint64_t splitmix64(uint64_t x) {
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+
+inline int turbo_sign_bytes(int D) { return (D + 7) / 8; }
+
+// :370-395: bit = 1 means multiply by -1; layout [slot][layer][kv_head][bytes]
+void turbo_build_sign_table(ora_ctx* s) {
+    const int L = s->c.n_layers, H = s->c.n_kv_heads, D = s->D, bytes = turbo_sign_bytes(D);
+    s->turbo_signs.assign((size_t)4 * L * H * bytes, 0);
+    const size_t stride = (size_t)L * H * bytes;
+    for (int slot = 0; slot < 4; ++slot)
+        for (int l = 0; l < L; ++l)
+            for (int h = 0; h < H; ++h) {
+                uint64_t seed = splitmix64(((uint64_t)l << 32) ^ (uint64_t)h ^ kTurboSalts[slot]);
+                uint8_t* bits = &s->turbo_signs[slot * stride + ((size_t)l * H + h) * bytes];
+                for (int i = 0; i < D; ++i)
+                    if (splitmix64(seed ^ (uint64_t)i) & 1) bits[i / 8] |= (uint8_t)(1u << (i & 7));
+            }
+}
+
+inline const uint8_t* turbo_sign_slot(const ora_ctx* s, int slot, int l, int kvh) {
+    const int bytes = turbo_sign_bytes(s->D);
+    const size_t stride = (size_t)s->c.n_layers * s->c.n_kv_heads * bytes;
+    return &s->turbo_signs[slot * stride + ((size_t)l * s->c.n_kv_heads + kvh) * bytes];
+}
+
+// :441-456 scalar tail
+inline void turbo_apply_signs(float* v, int n, const uint8_t* bits) {
+    for (int i = 0; i < n; ++i)
+        if ((bits[i / 8] >> (i & 7)) & 1) v[i] = -v[i];
+}
+
+// :681-701 and :822-833: skipped when n is not a power of two
+inline void turbo_fwht(float* v, int n) {
+    if (n <= 0 || (n & (n - 1)) != 0) return;
+    for (int width = 1; width < n; width *= 2)
+        for (int base = 0; base < n; base += 2 * width)
+            for (int i = 0; i < width; ++i) {
+                float a = v[base + i], b = v[base + i + width];
+                v[base + i] = a + b;
+                v[base + i + width] = a - b;
+            }
+    float scale = 1.0f / sqrtf((float)n);
+    for (int i = 0; i < n; ++i) v[i] *= scale;
+}
+
+// :595-605
+inline void turbo_transform(float* v, int n, const uint8_t* first, const uint8_t* second) {
+    turbo_apply_signs(v, n, first);
+    turbo_fwht(v, n);
+    turbo_apply_signs(v, n, second);
+}
+
+// src/engine/kernels/math.rs:467-473
+inline float l2_norm(const float* x, int n) {
+    float ss = 0.0f;
+    for (int i = 0; i < n; ++i) ss += x[i] * x[i];
+    return sqrtf(ss);
+}
+
+// :835-845
+inline int turbo_code(float x) {
+    if (x < -kTurboThreshold) return 0;
+    if (x < 0.0f) return 1;
+    if (x < kTurboThreshold) return 2;
+    return 3;
+}
+
+inline int get_q2(const uint8_t* src, size_t e) { return (src[e / 4] >> ((e & 3) * 2)) & 3; }
+inline void set_q2(uint8_t* dst, size_t e, int code) {
+    const int sh = (int)(e & 3) * 2;
+    dst[e / 4] = (uint8_t)((dst[e / 4] & ~(3u << sh)) | ((unsigned)code << sh));
+}
+inline bool get_bit(const uint8_t* src, size_t e) { return (src[e / 8] >> (e & 7)) & 1; }
+inline void set_bit(uint8_t* dst, size_t e, bool on) {
+    if (on) dst[e / 8] |= (uint8_t)(1u << (e & 7));
+    else dst[e / 8] &= (uint8_t)~(1u << (e & 7));
+}
+
+// :885-952: one head of one row
+void turbo_quantize_head(const ora_ctx* s, const float* src, int l, int kvh, uint8_t* base, uint8_t* sign,
+                         size_t elem_offset, float* scale_out, float* rnorm_out) {
+    const int D = s->D;
+    std::vector<float> rot(src, src + D), res(D);
+    turbo_transform(rot.data(), D, turbo_sign_slot(s, 0, l, kvh), turbo_sign_slot(s, 1, l, kvh));
+    float sigma = l2_norm(rot.data(), D) / sqrtf((float)D);
+    *scale_out = sigma;
+    if (sigma == 0.0f) {
+        *rnorm_out = 0.0f;
+        for (int i = 0; i < D; ++i) {
+            set_q2(base, elem_offset + i, 0);
+            set_bit(sign, elem_offset + i, true);
+        }
+        return;
+    }
+    float inv_sigma = 1.0f / sigma;
+    for (int i = 0; i < D; ++i) {
+        int code = turbo_code(rot[i] * inv_sigma);
+        res[i] = rot[i] - kTurboCentroids[code] * sigma;
+        set_q2(base, elem_offset + i, code);
+    }
+    float gamma = l2_norm(res.data(), D);
+    *rnorm_out = gamma;
+    if (gamma == 0.0f) {
+        for (int i = 0; i < D; ++i) set_bit(sign, elem_offset + i, true);
+        return;
+    }
+    for (int i = 0; i < D; ++i) res[i] /= gamma;
+    turbo_transform(res.data(), D, turbo_sign_slot(s, 2, l, kvh), turbo_sign_slot(s, 3, l, kvh));
+    for (int i = 0; i < D; ++i) set_bit(sign, elem_offset + i, res[i] >= 0.0f);
+}
+
+// :975-982
+inline float turbo_residual_scale(int D, float rnorm) {
+    if (rnorm == 0.0f) return 0.0f;
+    return rnorm * sqrtf(1.57079632679489661923f / (float)D);
+}
+
+// :1246-1269
+inline float turbo_dot(const ora_ctx* s, const float* qr, const float* qp, const uint8_t* base, const uint8_t* sign,
+                       size_t off, float scale, float rnorm) {
+    const int D = s->D;
+    float acc = 0.0f;
+    if (scale != 0.0f)
+        for (int i = 0; i < D; ++i) acc += qr[i] * (kTurboCentroids[get_q2(base, off + i)] * scale);
+    float rs = turbo_residual_scale(D, rnorm);
+    if (rs != 0.0f)
+        for (int i = 0; i < D; ++i) acc += get_bit(sign, off + i) ? rs * qp[i] : -rs * qp[i];
+    return acc;
+}
+
+// :1284-1306
+inline void turbo_axpy(const ora_ctx* s, float* base_acc, float* res_acc, float a, const uint8_t* base,
+                       const uint8_t* sign, size_t off, float scale, float rnorm) {
+    const int D = s->D;
+    if (scale != 0.0f)
+        for (int i = 0; i < D; ++i) base_acc[i] += a * kTurboCentroids[get_q2(base, off + i)] * scale;
+    float rs = a * turbo_residual_scale(D, rnorm);
+    if (rs != 0.0f)
+        for (int i = 0; i < D; ++i) res_acc[i] += get_bit(sign, off + i) ? rs : -rs;
+}
+
 // src/engine/runtime/inference.rs:1877-1918
 void kv_write(ora_ctx* s, int seq, int l, int64_t pos, const float* k, const float* v) {
     size_t r = row_index(s, seq, l, pos);
@@ -277,6 +435,15 @@ void kv_write(ora_ctx* s, int seq, int l, int64_t pos, const float* k, const flo
             }
             break;
         }
+        case 4:  // :1919-1963
+            for (int h = 0; h < s->c.n_kv_heads; ++h) {
+                size_t aux = r * s->c.n_kv_heads + h, eo = off + (size_t)h * s->D;
+                turbo_quantize_head(s, k + (size_t)h * s->D, l, h, s->kt_base.data(), s->kt_sign.data(), eo, &s->ks[aux],
+                                    &s->k_rnorm[aux]);
+                turbo_quantize_head(s, v + (size_t)h * s->D, l, h, s->vt_base.data(), s->vt_sign.data(), eo, &s->vs[aux],
+                                    &s->v_rnorm[aux]);
+            }
+            break;
     }
 }
 
@@ -386,10 +553,81 @@ void softmax_scalar(float* x, int64_t size) {
     for (int64_t i = 0; i < size; ++i) x[i] *= inv;
 }
 
+// The TurboQuant arm of attention_token (src/engine/runtime/inference.rs:2301-2527): the query is rotated and
+// projected once per head (:954-968), scores and value sums read the packed codes, and the two accumulators go
+// through the inverse transforms at the end (:1323-1334).
+void attention_head_turbo(ora_ctx* s, int seq, int l, int h, int64_t vs, int64_t ve, const float* q, float* out,
+                          float* att) {
+    const int D = s->D, Hkv = s->c.n_kv_heads;
+    const int kvh = h / s->G;
+    float* xb = out + (size_t)h * D;
+    const uint8_t* rot_pre = turbo_sign_slot(s, 0, l, kvh);
+    const uint8_t* rot_post = turbo_sign_slot(s, 1, l, kvh);
+    const uint8_t* res_pre = turbo_sign_slot(s, 2, l, kvh);
+    const uint8_t* res_post = turbo_sign_slot(s, 3, l, kvh);
+    std::vector<float> qr(q + (size_t)h * D, q + (size_t)(h + 1) * D), qp, res(D, 0.0f);
+    turbo_transform(qr.data(), D, rot_pre, rot_post);
+    qp = qr;
+    turbo_transform(qp.data(), D, res_pre, res_post);
+    const bool apply_scale = s->c.scale_mode == 0;
+    const size_t base = row_index(s, seq, l, 0);
+    auto score_at = [&](int64_t t) {
+        size_t r = base + t, aux = r * Hkv + kvh, off = r * s->kv_dim + (size_t)kvh * D;
+        float sc = turbo_dot(s, qr.data(), qp.data(), s->kt_base.data(), s->kt_sign.data(), off, s->ks[aux], s->k_rnorm[aux]);
+        if (apply_scale) sc *= s->attn_scale;
+        return sc;
+    };
+    auto value_at = [&](int64_t t, float a) {
+        size_t r = base + t, aux = r * Hkv + kvh, off = r * s->kv_dim + (size_t)kvh * D;
+        turbo_axpy(s, xb, res.data(), a, s->vt_base.data(), s->vt_sign.data(), off, s->vs[aux], s->v_rnorm[aux]);
+    };
+    for (int i = 0; i < D; ++i) xb[i] = 0.0f;
+    if (s->c.softmax_mode == 1) {
+        float max_score = -std::numeric_limits<float>::infinity(), score_sum = 0.0f;
+        for (int64_t t = vs; t < ve; ++t) {
+            float score = score_at(t);
+            if (score > max_score) {
+                if (score_sum > 0.0f) {
+                    float rescale = expf(max_score - score);
+                    for (int i = 0; i < D; ++i) {
+                        xb[i] *= rescale;
+                        res[i] *= rescale;
+                    }
+                    score_sum *= rescale;
+                }
+                max_score = score;
+            }
+            float w = expf(score - max_score);
+            score_sum += w;
+            value_at(t, w);
+        }
+        if (score_sum > 0.0f) {
+            float inv = 1.0f / score_sum;
+            for (int i = 0; i < D; ++i) {
+                xb[i] *= inv;
+                res[i] *= inv;
+            }
+        }
+    } else {
+        int64_t n = ve - vs;
+        for (int64_t t = 0; t < n; ++t) att[t] = score_at(vs + t);
+        softmax_scalar(att, n);
+        for (int64_t t = 0; t < n; ++t) value_at(vs + t, att[t]);
+    }
+    // :1323-1334
+    turbo_transform(res.data(), D, res_post, res_pre);
+    for (int i = 0; i < D; ++i) xb[i] += res[i];
+    turbo_transform(xb, D, rot_post, rot_pre);
+}
+
 // src/engine/runtime/inference.rs:2286-2529 (serial branch; the rayon branch
 // :2002-2283 does the same arithmetic per head on worker threads)
 void attention_head(ora_ctx* s, int seq, int l, int h, int64_t vs, int64_t ve, const float* q, float* out,
                     float* att) {
+    if (s->c.kv_format == 4) {
+        attention_head_turbo(s, seq, l, h, vs, ve, q, out, att);
+        return;
+    }
     const int D = s->D;
     const float* qh = q + (size_t)h * D;
     int kvh = h / s->G;
@@ -552,6 +790,19 @@ int ora_create(const ora_config* cfg, ora_ctx** out, const char** err) {
             s->ks.assign(rows * (size_t)std::max(1, s->kv_dim / 32), 0.0f);
             s->vs.assign(rows * (size_t)std::max(1, s->kv_dim / 32), 0.0f);
             break;
+        case 4: {
+            size_t aux = rows * (size_t)cfg->n_kv_heads;
+            s->kt_base.assign((elems + 3) / 4, 0);
+            s->vt_base.assign((elems + 3) / 4, 0);
+            s->kt_sign.assign((elems + 7) / 8, 0);
+            s->vt_sign.assign((elems + 7) / 8, 0);
+            s->ks.assign(aux, 0.0f);
+            s->vs.assign(aux, 0.0f);
+            s->k_rnorm.assign(aux, 0.0f);
+            s->v_rnorm.assign(aux, 0.0f);
+            turbo_build_sign_table(s);
+            break;
+        }
         default:
             delete s;
             *err = e_shape;
@@ -754,6 +1005,32 @@ void ora_kv_read_row(ora_ctx* s, int32_t seq, int32_t layer, int32_t pos, float*
             }
         }
     }
+}
+
+// raw TurboQuant row: codes (kv_dim / 4 bytes), sign bits (kv_dim / 8 bytes), sigma and residual norm per kv head
+int ora_kv_read_turbo(ora_ctx* s, int32_t seq, int32_t layer, int32_t pos, uint8_t* k_base, uint8_t* v_base,
+                      uint8_t* k_sign, uint8_t* v_sign, float* k_scale, float* v_scale, float* k_rnorm, float* v_rnorm) {
+    if (s->c.kv_format != 4 || s->kv_dim % 8 != 0) return -1;
+    size_t r = row_index(s, seq, layer, pos), off = r * s->kv_dim;
+    std::memcpy(k_base, &s->kt_base[off / 4], s->kv_dim / 4);
+    std::memcpy(v_base, &s->vt_base[off / 4], s->kv_dim / 4);
+    std::memcpy(k_sign, &s->kt_sign[off / 8], s->kv_dim / 8);
+    std::memcpy(v_sign, &s->vt_sign[off / 8], s->kv_dim / 8);
+    for (int h = 0; h < s->c.n_kv_heads; ++h) {
+        size_t aux = r * s->c.n_kv_heads + h;
+        k_scale[h] = s->ks[aux];
+        v_scale[h] = s->vs[aux];
+        k_rnorm[h] = s->k_rnorm[aux];
+        v_rnorm[h] = s->v_rnorm[aux];
+    }
+    return 0;
+}
+
+// the transform of the reference's property tests (:4546-4566): signs of slot `first`, FWHT, signs of slot `second`
+int ora_turbo_transform(ora_ctx* s, int32_t layer, int32_t kv_head, int32_t first_slot, int32_t second_slot, float* values) {
+    if (s->c.kv_format != 4 || first_slot < 0 || first_slot > 3 || second_slot < 0 || second_slot > 3) return -1;
+    turbo_transform(values, s->D, turbo_sign_slot(s, first_slot, layer, kv_head), turbo_sign_slot(s, second_slot, layer, kv_head));
+    return 0;
 }
 
 int ora_kv_read_q8(ora_ctx* s, int32_t seq, int32_t layer, int32_t pos, int8_t* k_q, int8_t* v_q, float* k_scale,

@@ -34,7 +34,7 @@ typedef struct ora_config {
     int32_t swa_pattern;  /* layer-kind fallback when layer_windows is empty */
     int32_t scale_mode;   /* 0 = score *= 1/sqrt(D), 1 = q pre-scaled after RoPE */
     int32_t softmax_mode; /* 0 = two-pass, 1 = online */
-    int32_t kv_format;    /* 0 f32, 1 bf16, 2 q8 row scale, 3 q8 block-32 scales */
+    int32_t kv_format;    /* 0 f32, 1 bf16, 2 q8 row scale, 3 q8 block-32 scales, 4 TurboQuant (2 + 1 bit) */
     int32_t image_mode;   /* 0 causal, 1 bidirectional image blocks */
     int32_t n_layer_windows;
     const int32_t* layer_windows; /* n_layer_windows entries, 0 = global */
@@ -77,6 +77,11 @@ void ora_prefill_block(ora_ctx* ctx, int32_t layer, int32_t seq, int32_t base_po
 void ora_kv_read_row(ora_ctx* ctx, int32_t seq, int32_t layer, int32_t pos, float* k_out, float* v_out);
 int ora_kv_read_q8(ora_ctx* ctx, int32_t seq, int32_t layer, int32_t pos, int8_t* k_q, int8_t* v_q,
                    float* k_scale, float* v_scale);
+
+int ora_kv_read_turbo(ora_ctx* ctx, int32_t seq, int32_t layer, int32_t pos, uint8_t* k_base, uint8_t* v_base,
+                      uint8_t* k_sign, uint8_t* v_sign, float* k_scale, float* v_scale, float* k_rnorm, float* v_rnorm);
+int ora_turbo_transform(ora_ctx* ctx, int32_t layer, int32_t kv_head, int32_t first_slot, int32_t second_slot,
+                        float* values);
 
 /* host-side planners restated from the reference, for known-answer tests */
 typedef struct ora_plan ora_plan;

@@ -71,6 +71,10 @@ def lib() -> C.CDLL:
     L.ora_kv_read_row.argtypes = [vp, i32, i32, i32, vp, vp]
     L.ora_kv_read_row.restype = None
     L.ora_kv_read_q8.argtypes = [vp, i32, i32, i32, vp, vp, vp, vp]
+    L.ora_kv_read_turbo.argtypes = [vp, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp]
+    L.ora_kv_read_turbo.restype = C.c_int
+    L.ora_turbo_transform.argtypes = [vp, i32, i32, i32, i32, vp]
+    L.ora_turbo_transform.restype = C.c_int
     L.ora_plan_new.restype = vp
     L.ora_plan_free.argtypes = [vp]
     L.ora_plan_free.restype = None
@@ -247,6 +251,24 @@ class Oracle:
         if self.L.ora_kv_read_q8(self.h, seq, layer, pos, _p(kq), _p(vq), _p(ks), _p(vs)) != 0:
             raise ValueError("not a q8 cache")
         return kq, vq, ks, vs
+
+    def kv_read_turbo(self, layer, pos, seq=0):
+        """Raw TurboQuant row: dict of codes, sign bits and the per-head sigma / residual norm of K and V."""
+        kd, H = self.kv_dim, self.cfg.n_kv_heads
+        out = {"k_base": np.empty(kd // 4, np.uint8), "v_base": np.empty(kd // 4, np.uint8),
+               "k_sign": np.empty(kd // 8, np.uint8), "v_sign": np.empty(kd // 8, np.uint8),
+               "k_scale": np.empty(H, np.float32), "v_scale": np.empty(H, np.float32),
+               "k_rnorm": np.empty(H, np.float32), "v_rnorm": np.empty(H, np.float32)}
+        order = ("k_base", "v_base", "k_sign", "v_sign", "k_scale", "v_scale", "k_rnorm", "v_rnorm")
+        if self.L.ora_kv_read_turbo(self.h, seq, layer, pos, *[_p(out[n]) for n in order]) != 0:
+            raise ValueError("not a TurboQuant cache")
+        return out
+
+    def turbo_transform(self, layer, kv_head, first_slot, second_slot, values):
+        v = np.ascontiguousarray(values, dtype=np.float32).copy()
+        if self.L.ora_turbo_transform(self.h, layer, kv_head, first_slot, second_slot, _p(v)) != 0:
+            raise ValueError("not a TurboQuant cache")
+        return v
 
 
 def bf16_round(a: np.ndarray) -> np.ndarray:
