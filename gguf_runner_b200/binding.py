@@ -68,7 +68,7 @@ EXPORTED_SYMBOLS = [
     "ggr_attn_decode", "ggr_attn_prefill", "ggr_attn_prefill_block",
     "ggr_attn_apply_rope_qk", "ggr_attn_kv_write_token", "ggr_attn_attention_token",
     "ggr_attn_decode_partial", "ggr_attn_combine_partials",
-    "ggr_attn_kv_export", "ggr_attn_kv_import", "ggr_attn_kv_read_row", "ggr_attn_launch_count",
+    "ggr_attn_kv_export", "ggr_attn_kv_import", "ggr_attn_kv_read_row", "ggr_attn_kv_read_turbo", "ggr_attn_launch_count",
     "ggr_attn_set_kernel_timing", "ggr_attn_kernel_time", "ggr_attn_kv_device_ptrs",
     "ggr_attn_attention_tokens_static", "ggr_attn_last_split_count",
     "ggr_attn_exchange_create", "ggr_attn_exchange_connect", "ggr_attn_decode_exchange",
@@ -119,6 +119,8 @@ def lib() -> C.CDLL:
     L.ggr_attn_kv_export.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp]
     L.ggr_attn_kv_import.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp]
     L.ggr_attn_kv_read_row.argtypes = [vp, i32, i32, i32, vp, vp]
+    L.ggr_attn_kv_read_turbo.argtypes = [vp, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp]
+    L.ggr_attn_kv_read_turbo.restype = C.c_int
     L.ggr_attn_launch_count.argtypes = [vp]
     L.ggr_attn_launch_count.restype = i64
     L.ggr_attn_last_split_count.argtypes = [vp]
@@ -484,6 +486,18 @@ class AttnContext:
         self._check(self._L.ggr_attn_kv_read_row(self._h, seq, layer, pos, C.c_void_p(k.ctypes.data),
                                                   C.c_void_p(v.ctypes.data)))
         return k, v
+
+    def kv_read_turbo(self, layer: int, pos: int, seq: int = 0):
+        """Raw TurboQuant row (src/engine/runtime/inference.rs:1919-1963): codes, sign bits, sigma and residual norm."""
+        kd, H = self.config.kv_dim, self.config.n_kv_heads
+        out = {"k_base": np.empty(kd // 4, np.uint8), "v_base": np.empty(kd // 4, np.uint8),
+               "k_sign": np.empty(kd // 8, np.uint8), "v_sign": np.empty(kd // 8, np.uint8),
+               "k_scale": np.empty(H, np.float32), "v_scale": np.empty(H, np.float32),
+               "k_rnorm": np.empty(H, np.float32), "v_rnorm": np.empty(H, np.float32)}
+        order = ("k_base", "v_base", "k_sign", "v_sign", "k_scale", "v_scale", "k_rnorm", "v_rnorm")
+        self._check(self._L.ggr_attn_kv_read_turbo(self._h, seq, layer, pos,
+                                                    *[C.c_void_p(out[n].ctypes.data) for n in order]))
+        return out
 
     def kv_export(self, layer: int, row0: int, nrows: int, seq: int = 0):
         kd = self.config.kv_dim

@@ -9,7 +9,7 @@
 
 namespace ggr {
 
-enum KvFormat : int { KV_F32 = 0, KV_BF16 = 1, KV_Q8_ROW = 2, KV_Q8_BLOCK32 = 3 };
+enum KvFormat : int { KV_F32 = 0, KV_BF16 = 1, KV_Q8_ROW = 2, KV_Q8_BLOCK32 = 3, KV_TURBO = 4 };
 
 constexpr int kMaxArgItems = 128;  // positions carried inside the kernel arguments
 constexpr float kLog2e = 1.4426950408889634f;
@@ -20,8 +20,15 @@ constexpr float kLog2e = 1.4426950408889634f;
 struct KvView {
     void* k;
     void* v;
-    float* ks;  // q8 scales: one per row (Q8_ROW) or kv_dim/32 per row (Q8_BLOCK32)
+    float* ks;  // q8 scales: one per row (Q8_ROW) or kv_dim/32 per row (Q8_BLOCK32); TurboQuant: sigma per (row, kv head)
     float* vs;
+    // TurboQuant only (k / v then hold the packed 2-bit codes): residual sign bits, residual norms per
+    // (row, kv head), and the sign tables of the four transforms [slot][layer][kv_head][D / 8]
+    unsigned char* k_sign;
+    unsigned char* v_sign;
+    float* k_rn;
+    float* v_rn;
+    const unsigned char* turbo_signs;
     int fmt;
     int D, kv_dim, Hkv, Hq, G;
     int n_layers;

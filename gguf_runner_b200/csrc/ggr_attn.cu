@@ -15,6 +15,7 @@
 #include "../../include/ggr_attn.h"
 #include "attn_mma.cuh"
 #include "attn_simt.cuh"
+#include "attn_turbo.cuh"
 #include "common.cuh"
 #include "prefill_tc.cuh"
 #include "prefill_tc_wide.cuh"
@@ -41,6 +42,9 @@ struct ggr_attn_ctx {
     float* d_qrot = nullptr;
     __nv_bfloat16* d_qrot_h = nullptr;
     size_t qrot_cap = 0, qrot_h_cap = 0;
+    float* d_krot = nullptr;  // rotated keys on their way into a TurboQuant cache
+    size_t krot_cap = 0;
+    unsigned char* d_turbo_signs = nullptr;
     float* d_part = nullptr;
     size_t part_cap = 0;
     unsigned* d_counters = nullptr;
@@ -90,6 +94,9 @@ struct ggr_attn_ctx {
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> ev[3];
     size_t ev_used[3] = {0, 0, 0};
 };
+
+// defined in host_plan.cpp
+std::vector<unsigned char> ggr_turbo_sign_table(int n_layers, int n_kv_heads, int head_dim);
 
 namespace {
 
@@ -299,13 +306,33 @@ int launch_rope_append(ggr_attn_ctx* c, int layer, const Items& items, int flags
     a.q_out_h = q_out_h;
     a.k_out = k_out;
     a.shard_count = c->shard_count;
+    // TurboQuant: the rope kernel leaves the rotated keys in a scratch buffer and a second kernel quantises
+    // them and the values head by head
+    const bool turbo = c->kv.fmt == KV_TURBO;
+    const bool turbo_append = turbo && (flags & RF_APPEND);
+    const float* turbo_k = nullptr;
+    bool skip_rope = false;
+    if (turbo_append) {
+        if (flags == RF_APPEND && !in_bf16) {
+            turbo_k = static_cast<const float*>(k);  // already rotated f32 keys: nothing for the rope kernel to do
+            skip_rope = true;
+        } else {
+            int rc = ensure(c, &c->d_krot, &c->krot_cap, (size_t)items.n * c->kv_dim);
+            if (rc) return rc;
+            a.flags = (flags & ~RF_APPEND) | RF_WRITE_K;
+            a.k_out = c->d_krot;
+            turbo_k = c->d_krot;
+        }
+    }
     size_t smem = (size_t)(2 * c->rope_half + 2 * c->kv_dim + 16) * sizeof(float);
     if (smem > 48 * 1024) {
         CUDA_TRY(c, cudaFuncSetAttribute(rope_append_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     }
-    {
+    if (!skip_rope) {
         LaunchTimer t(c, 1);
-        if (rope_append_fast_ok(a))
+        if (turbo)
+            rope_append_kernel<<<items.n, 256, smem, c->stream>>>(a);
+        else if (rope_append_fast_ok(a))
             rope_append_bf16_kernel<<<items.n, 256, 0, c->stream>>>(a);
         else if (rope_append_vec_ok(a) && smem + 16 <= 48 * 1024 && in_bf16)
             rope_append_vec_kernel<__nv_bfloat16><<<items.n, 256, smem + 16, c->stream>>>(a);
@@ -315,7 +342,23 @@ int launch_rope_append(ggr_attn_ctx* c, int layer, const Items& items, int flags
             rope_append_kernel<<<items.n, 256, smem, c->stream>>>(a);
     }
     CUDA_TRY(c, cudaGetLastError());
-    c->launches++;
+    if (!skip_rope) c->launches++;
+    if (turbo_append) {
+        TurboAppendArgs t{};
+        t.kv = c->kv;
+        t.items = items;
+        t.layer = layer;
+        t.k_rot = turbo_k;
+        t.v = v;
+        t.v_bf16 = in_bf16;
+        t.shard_count = c->shard_count;
+        {
+            LaunchTimer lt(c, 1);
+            turbo_append_kernel<<<dim3(items.n, c->kv.Hkv), 64, (size_t)4 * c->D * sizeof(float), c->stream>>>(t);
+        }
+        CUDA_TRY(c, cudaGetLastError());
+        c->launches++;
+    }
     return GGR_OK;
 }
 
@@ -462,6 +505,46 @@ int launch_attention(ggr_attn_ctx* c, int layer, const Items& items, int t_max, 
     a.partial_out = partial_dev;
     a.shard_count = c->shard_count;
     if (px) a.px = *px;
+    a.err = c->d_err;
+
+    if (c->kv.fmt == KV_TURBO) {
+        // TurboQuant cache: rope + quantising append as separate launches, then the CUDA-core attention kernel.
+        // Splits fill the GPU about four CTAs deep (the kernel is bound by arithmetic, not by HBM).
+        if (raw) {
+            int rc = launch_rope_append(c, layer, items, RF_ROTATE | RF_WRITE_Q | RF_APPEND, 0, raw->q, raw->k, raw->v,
+                                        const_cast<float*>(q_dev), nullptr, nullptr);
+            if (rc) return rc;
+        }
+        const int64_t base_ctas = (int64_t)c->kv.Hkv * items.n;
+        int n_split = (int)std::max<int64_t>(1, ((int64_t)4 * c->sm_count + base_ctas - 1) / base_ctas);
+        n_split = std::min(n_split, std::max(1, t_max / (4 * kTurboGroups)));
+        n_split = std::min(n_split, 64);
+        if (c->cfg.max_splits > 0) n_split = std::min(n_split, c->cfg.max_splits);
+        a.n_split = n_split;
+        c->last_splits = n_split;
+        if (n_split > 1) {
+            int rc = ensure(c, &c->d_part, &c->part_cap, (size_t)items.n * c->kv.Hq * n_split * (c->D + 2));
+            if (rc) return rc;
+            const size_t before = c->counters_cap;
+            rc = ensure(c, &c->d_counters, &c->counters_cap, (size_t)items.n * c->kv.Hkv);
+            if (rc) return rc;
+            if (c->counters_cap != before)
+                CUDA_TRY(c, cudaMemsetAsync(c->d_counters, 0, c->counters_cap * sizeof(unsigned), c->stream));
+            a.part = c->d_part;
+            a.counters = c->d_counters;
+        }
+        const size_t smem = turbo_attn_smem_floats(c->D, c->G, turbo_heads_per_pass(c->G, c->D), n_split) * sizeof(float);
+        if (smem + 1024 > (size_t)c->smem_optin)
+            return fail(c, GGR_ERR_UNSUPPORTED, "TurboQuant attention: too many query heads per KV head for shared memory");
+        int e;
+        {
+            LaunchTimer t(c, 0);
+            e = launch_turbo_attention(a, dim3(n_split, c->kv.Hkv, items.n), smem, c->smem_optin, c->cfg.device, c->stream);
+        }
+        if (e != 0) return fail(c, GGR_ERR_CUDA, std::string("TurboQuant attention launch: ") + cudaGetErrorString((cudaError_t)e));
+        c->launches++;
+        return GGR_OK;
+    }
 
     const bool mma = allow_mma && use_mma_decode(c);
     const bool tma = mma && c->have_tmaps16 && c->cfg.decode_impl != GGR_IMPL_MMA;
@@ -825,7 +908,9 @@ int ggr_attn_create(const ggr_attn_config* cfg, ggr_attn_ctx** out) {
         return bad(GGR_ERR_INVALID, "invalid attention shape");
     if (cfg->head_dim % 8 != 0 || cfg->head_dim > 256)
         return bad(GGR_ERR_UNSUPPORTED, "head_dim must be a multiple of 8 and at most 256");
-    if (cfg->kv_format < GGR_KV_F32 || cfg->kv_format > GGR_KV_Q8_BLOCK32) return bad(GGR_ERR_INVALID, "unknown kv_format");
+    if (cfg->kv_format < GGR_KV_F32 || cfg->kv_format > GGR_KV_TURBO) return bad(GGR_ERR_INVALID, "unknown kv_format");
+    if (cfg->kv_format == GGR_KV_TURBO && cfg->head_dim != 64 && cfg->head_dim != 128 && cfg->head_dim != 256)
+        return bad(GGR_ERR_UNSUPPORTED, "the TurboQuant cache is built for head_dim 64, 128 or 256");
     if (cfg->kv_format == GGR_KV_Q8_BLOCK32 && cfg->head_dim % 32 != 0)
         return bad(GGR_ERR_UNSUPPORTED, "q8 block scales need head_dim to be a multiple of 32");
     int rope_dim = cfg->rope_dim > 0 ? cfg->rope_dim : cfg->head_dim;
@@ -902,8 +987,11 @@ int ggr_attn_create(const ggr_attn_config* cfg, ggr_attn_ctx** out) {
     kv.pos_begin = shard_begin;
     kv.elem_bytes = elem_bytes_of(cfg->kv_format);
     kv.n_scales = cfg->kv_format == GGR_KV_Q8_ROW ? 1 : (cfg->kv_format == GGR_KV_Q8_BLOCK32 ? c->kv_dim / 32 : 0);
+    const bool turbo = cfg->kv_format == GGR_KV_TURBO;
+    if (turbo) kv.n_scales = cfg->n_kv_heads;  // sigma per (row, kv head): src/engine/runtime/inference.rs:1717
     const size_t rows = (size_t)cfg->max_batch * cfg->n_layers * shard_count;
-    const size_t bytes = rows * c->kv_dim * kv.elem_bytes;
+    // TurboQuant: 2 bits per element in k / v, 1 bit per element in k_sign / v_sign (:1658-1662)
+    const size_t bytes = turbo ? (rows * c->kv_dim + 3) / 4 : rows * c->kv_dim * kv.elem_bytes;
     char buf[160];
     if (cudaMalloc(&kv.k, bytes) != cudaSuccess || cudaMalloc(&kv.v, bytes) != cudaSuccess) {
         cudaGetLastError();
@@ -921,6 +1009,28 @@ int ggr_attn_create(const ggr_attn_config* cfg, ggr_attn_ctx** out) {
         }
         cudaMemsetAsync(kv.ks, 0, sb, c->stream);
         cudaMemsetAsync(kv.vs, 0, sb, c->stream);
+    }
+    if (turbo) {
+        const size_t sign_bytes = (rows * c->kv_dim + 7) / 8, aux = rows * cfg->n_kv_heads * sizeof(float);
+        if (cudaMalloc((void**)&kv.k_sign, sign_bytes) != cudaSuccess || cudaMalloc((void**)&kv.v_sign, sign_bytes) != cudaSuccess ||
+            cudaMalloc((void**)&kv.k_rn, aux) != cudaSuccess || cudaMalloc((void**)&kv.v_rn, aux) != cudaSuccess) {
+            cudaGetLastError();
+            return cleanup(GGR_ERR_ALLOC, "unable to allocate the TurboQuant sign and norm buffers");
+        }
+        cudaMemsetAsync(kv.k_sign, 0, sign_bytes, c->stream);
+        cudaMemsetAsync(kv.v_sign, 0, sign_bytes, c->stream);
+        cudaMemsetAsync(kv.k_rn, 0, aux, c->stream);
+        cudaMemsetAsync(kv.v_rn, 0, aux, c->stream);
+        // sign tables of the four transforms (:370-395): bit 1 = negate, [slot][layer][kv_head][D / 8]
+        const std::vector<unsigned char> table = ggr_turbo_sign_table(cfg->n_layers, cfg->n_kv_heads, c->D);
+        if (cudaMalloc((void**)&c->d_turbo_signs, table.size()) != cudaSuccess) {
+            cudaGetLastError();
+            return cleanup(GGR_ERR_ALLOC, "unable to allocate the TurboQuant sign tables");
+        }
+        if (cudaMemcpyAsync(c->d_turbo_signs, table.data(), table.size(), cudaMemcpyHostToDevice, c->stream) != cudaSuccess ||
+            cudaStreamSynchronize(c->stream) != cudaSuccess)
+            return cleanup(GGR_ERR_CUDA, "unable to upload the TurboQuant sign tables");
+        kv.turbo_signs = c->d_turbo_signs;
     }
     if (cudaHostAlloc((void**)&c->h_err, sizeof(int), cudaHostAllocMapped) != cudaSuccess ||
         cudaHostGetDevicePointer((void**)&c->d_err, c->h_err, 0) != cudaSuccess) {
@@ -959,6 +1069,12 @@ void ggr_attn_destroy(ggr_attn_ctx* c) {
     cudaFree(c->kv.v);
     cudaFree(c->kv.ks);
     cudaFree(c->kv.vs);
+    cudaFree(c->kv.k_sign);
+    cudaFree(c->kv.v_sign);
+    cudaFree(c->kv.k_rn);
+    cudaFree(c->kv.v_rn);
+    cudaFree(c->d_turbo_signs);
+    cudaFree(c->d_krot);
     cudaFree(c->d_freqs);
     cudaFree(c->d_freqs_swa);
     cudaFree(c->d_plan);
@@ -1282,6 +1398,8 @@ int ggr_attn_kv_read_row(ggr_attn_ctx* c, int32_t seq, int32_t layer, int32_t po
     DeviceGuard guard(c->cfg.device);
     int rc = kv_rows_check(c, layer, seq, pos, 1);
     if (rc) return rc;
+    if (c->kv.fmt == KV_TURBO)
+        return fail(c, GGR_ERR_UNSUPPORTED, "a TurboQuant row has no element-wise decoding: read it with ggr_attn_kv_read_turbo");
     CUDA_TRY(c, cudaStreamSynchronize(c->stream));
     const int64_t r = c->kv.row(seq, layer, pos);
     const int n = c->kv_dim, eb = c->kv.elem_bytes;
@@ -1316,6 +1434,30 @@ int ggr_attn_kv_read_row(ggr_attn_ctx* c, int32_t seq, int32_t layer, int32_t po
                 break;
         }
     }
+    return GGR_OK;
+}
+
+int ggr_attn_kv_read_turbo(ggr_attn_ctx* c, int32_t seq, int32_t layer, int32_t pos, uint8_t* k_base, uint8_t* v_base,
+                           uint8_t* k_sign, uint8_t* v_sign, float* k_scale, float* v_scale, float* k_rnorm,
+                           float* v_rnorm) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    int rc = kv_rows_check(c, layer, seq, pos, 1);
+    if (rc) return rc;
+    if (c->kv.fmt != KV_TURBO) return fail(c, GGR_ERR_UNSUPPORTED, "the cache is not in the TurboQuant format");
+    if (!k_base || !v_base || !k_sign || !v_sign || !k_scale || !v_scale || !k_rnorm || !v_rnorm)
+        return fail(c, GGR_ERR_INVALID, "null buffer");
+    CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    const int64_t r = c->kv.row(seq, layer, pos);
+    const size_t n = (size_t)c->kv_dim, h = (size_t)c->kv.Hkv;
+    CUDA_TRY(c, cudaMemcpy(k_base, (unsigned char*)c->kv.k + r * n / 4, n / 4, cudaMemcpyDeviceToHost));
+    CUDA_TRY(c, cudaMemcpy(v_base, (unsigned char*)c->kv.v + r * n / 4, n / 4, cudaMemcpyDeviceToHost));
+    CUDA_TRY(c, cudaMemcpy(k_sign, c->kv.k_sign + r * n / 8, n / 8, cudaMemcpyDeviceToHost));
+    CUDA_TRY(c, cudaMemcpy(v_sign, c->kv.v_sign + r * n / 8, n / 8, cudaMemcpyDeviceToHost));
+    CUDA_TRY(c, cudaMemcpy(k_scale, c->kv.ks + r * h, h * sizeof(float), cudaMemcpyDeviceToHost));
+    CUDA_TRY(c, cudaMemcpy(v_scale, c->kv.vs + r * h, h * sizeof(float), cudaMemcpyDeviceToHost));
+    CUDA_TRY(c, cudaMemcpy(k_rnorm, c->kv.k_rn + r * h, h * sizeof(float), cudaMemcpyDeviceToHost));
+    CUDA_TRY(c, cudaMemcpy(v_rnorm, c->kv.v_rn + r * h, h * sizeof(float), cudaMemcpyDeviceToHost));
     return GGR_OK;
 }
 
@@ -1369,6 +1511,7 @@ extern "C" int ggr_attn_attention_tokens_static(ggr_attn_ctx* c, int32_t layer, 
     if (rc) return rc;
     if (!pos || !q_dev || !out_dev) return fail(c, GGR_ERR_INVALID, "null buffer");
     if (c->cfg.shard_mode != GGR_SHARD_NONE) return fail(c, GGR_ERR_UNSUPPORTED, "not available on a KV-sequence shard");
+    if (c->kv.fmt == KV_TURBO) return fail(c, GGR_ERR_UNSUPPORTED, "not available for the TurboQuant cache format");
     if (B <= 0 || B > c->cfg.max_batch) return fail(c, GGR_ERR_RANGE, "batch larger than max_batch");
     if (B > kMaxArgItems) return fail(c, GGR_ERR_RANGE, "the allocation-free entry point takes at most 128 sequences per call");
     for (int b = 0; b < B; ++b)

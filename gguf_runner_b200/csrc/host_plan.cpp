@@ -133,3 +133,33 @@ int ggr_gemma_layer_windows(int32_t n_layers, int32_t window, int32_t period, in
 }
 
 }  // extern "C"
+
+// ---- TurboQuant transform signs (src/engine/runtime/inference.rs:370-395, splitmix64 :673-679) ----
+
+namespace {
+inline uint64_t turbo_splitmix64(uint64_t x) {
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+}  // namespace
+
+// Sign bits of the four transforms {rot_pre, rot_post, res_pre, res_post} for every (layer, kv head):
+// layout [slot][layer][kv_head][ceil(D / 8)], element i is negated iff its bit (LSB first) is set.
+std::vector<unsigned char> ggr_turbo_sign_table(int n_layers, int n_kv_heads, int head_dim) {
+    static const uint64_t salts[4] = {0x9E3779B97F4A7C15ull, 0xC2B2AE3D27D4EB4Full, 0x165667B19E3779F9ull,
+                                      0xD6E8FEB86659FD93ull};
+    const size_t bytes = (size_t)(head_dim + 7) / 8, stride = (size_t)n_layers * n_kv_heads * bytes;
+    std::vector<unsigned char> table(4 * stride, 0);
+    for (int slot = 0; slot < 4; ++slot)
+        for (int l = 0; l < n_layers; ++l)
+            for (int h = 0; h < n_kv_heads; ++h) {
+                const uint64_t seed = turbo_splitmix64(((uint64_t)l << 32) ^ (uint64_t)h ^ salts[slot]);
+                unsigned char* bits = &table[slot * stride + ((size_t)l * n_kv_heads + h) * bytes];
+                for (int i = 0; i < head_dim; ++i)
+                    if (turbo_splitmix64(seed ^ (uint64_t)i) & 1) bits[i / 8] |= (unsigned char)(1u << (i & 7));
+            }
+    return table;
+}
+

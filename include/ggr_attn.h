@@ -43,7 +43,10 @@ typedef enum ggr_status {
 
 enum { GGR_PTR_HOST = 0, GGR_PTR_DEVICE = 1 };
 enum { GGR_DTYPE_F32 = 0, GGR_DTYPE_BF16 = 1 };
-enum { GGR_KV_F32 = 0, GGR_KV_BF16 = 1, GGR_KV_Q8_ROW = 2, GGR_KV_Q8_BLOCK32 = 3 };
+/* GGR_KV_TURBO is the reference's default cache (KvCacheFormat::Turbo, src/engine/runtime/inference.rs:1634):
+ * 2-bit codes of the rotated head plus one sign bit of the projected residual per element, sigma and residual
+ * norm per (row, kv head); head_dim 64, 128 or 256 */
+enum { GGR_KV_F32 = 0, GGR_KV_BF16 = 1, GGR_KV_Q8_ROW = 2, GGR_KV_Q8_BLOCK32 = 3, GGR_KV_TURBO = 4 };
 enum { GGR_ROPE_NEOX = 0, GGR_ROPE_ADJACENT = 1 };
 enum { GGR_ROPE_SEQUENTIAL = 0, GGR_ROPE_INTERLEAVED = 1 };
 enum { GGR_SCALE_SCORE = 0, GGR_SCALE_Q_PRESCALED = 1 };
@@ -239,6 +242,12 @@ int ggr_attn_kv_import(ggr_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t ro
                        const int8_t* k_q8, const int8_t* v_q8, const float* k_scale, const float* v_scale);
 /* Dequantised f32 view of one cache row (any format), for tests. Host buffers. */
 int ggr_attn_kv_read_row(ggr_attn_ctx* ctx, int32_t seq, int32_t layer, int32_t pos, float* k_out, float* v_out);
+/* Raw TurboQuant row in the reference's layout (src/engine/runtime/inference.rs:1919-1963): 2-bit codes
+ * (kv_dim / 4 bytes, four per byte, LSB first), residual sign bits (kv_dim / 8 bytes), sigma and residual norm
+ * per kv head, for K and for V. Host buffers; only for kv_format GGR_KV_TURBO. */
+int ggr_attn_kv_read_turbo(ggr_attn_ctx* ctx, int32_t seq, int32_t layer, int32_t pos, uint8_t* k_base, uint8_t* v_base,
+                           uint8_t* k_sign, uint8_t* v_sign, float* k_scale, float* v_scale, float* k_rnorm,
+                           float* v_rnorm);
 
 /*
  * Allocation-free variant of ggr_attn_attention_token for B sequences (no

@@ -9,13 +9,13 @@ import pytest
 import gguf_runner_b200 as g
 from gguf_runner_b200 import presets
 from gguf_runner_b200.binding import (AttnConfig, GgrError, IMPL_AUTO, IMPL_MMA, IMPL_SIMT, KV_BF16, KV_F32, KV_Q8_BLOCK32,
-                                      KV_Q8_ROW, ROPE_ADJACENT, ROPE_INTERLEAVED, ROPE_NEOX, SCALE_Q_PRESCALED,
+                                      KV_Q8_ROW, KV_TURBO, ROPE_ADJACENT, ROPE_INTERLEAVED, ROPE_NEOX, SCALE_Q_PRESCALED,
                                       SHARD_KV_SEQUENCE)
 from tests.oracle_binding import Oracle, bf16_bits, bf16_round
 
 pytestmark = pytest.mark.gpu
 
-TOL = {KV_F32: 1e-3, KV_Q8_ROW: 1e-3, KV_Q8_BLOCK32: 1e-3, KV_BF16: 2e-2}
+TOL = {KV_F32: 1e-3, KV_Q8_ROW: 1e-3, KV_Q8_BLOCK32: 1e-3, KV_BF16: 2e-2, KV_TURBO: 1e-3}
 THREADS = 8
 
 
@@ -518,4 +518,68 @@ def test_prefill_more_work_items_than_sms(head_dim, m, window):
             worst = max(worst, float(np.max(np.abs(got - want))))
             pos += n
     assert worst <= TOL[KV_BF16], f"max abs err {worst}"
+    ctx.close()
+
+
+# ---- TurboQuant cache (src/engine/runtime/inference.rs:885-982, :1246-1334) ----
+
+@pytest.mark.parametrize("head_dim,n_heads,n_kv_heads,style", [(64, 4, 2, ROPE_NEOX), (128, 8, 2, ROPE_ADJACENT),
+                                                                (256, 4, 4, ROPE_NEOX)])
+def test_turboquant_append_is_bit_exact(head_dim, n_heads, n_kv_heads, style):
+    """Codes, sign bits, sigma and residual norm of appended rows equal the oracle's bit for bit wherever the inputs
+    are bit-identical: every V row, and the K row of the granular write (already rotated keys). A zero row takes the
+    sigma == 0 arm."""
+    cfg = AttnConfig(n_layers=2, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim, seq_len=64, rope_theta=1e6,
+                     rope_style=style, kv_format=KV_TURBO)
+    rng = np.random.default_rng(head_dim)
+    ctx, ora = make(cfg)
+    m = 20
+    q, k, v = rand(rng, m, cfg.q_dim), rand(rng, m, cfg.kv_dim), rand(rng, m, cfg.kv_dim)
+    k[3] = 0.0
+    v[5] = 0.0
+    ctx.prefill(1, 0, q, k, v)
+    ora.prefill(1, 0, q, k, v)
+    q1, k1, v1 = rand(rng, 1, cfg.q_dim), rand(rng, 1, cfg.kv_dim), rand(rng, 1, cfg.kv_dim)
+    ctx.decode(1, [m], q1, k1, v1)
+    ora.decode(1, [m], q1, k1, v1)
+    kr = rand(rng, cfg.kv_dim)
+    ctx.kv_write_token(1, m + 1, kr, v1[0])
+    ora.kv_write_token(1, m + 1, kr, v1[0])
+    for pos in range(m + 2):
+        got, want = ctx.kv_read_turbo(1, pos), ora.kv_read_turbo(1, pos)
+        for name in want:
+            if name.startswith("v_") or pos == m + 1:
+                assert np.array_equal(got[name], want[name]), (pos, name)
+        # keys written through prefill / decode were rotated on the device, whose sincosf may differ from the host's
+        # cosf / sinf in the last bit: norms agree to rounding and at most a few elements sit on the other side
+        # of a threshold
+        np.testing.assert_allclose(got["k_scale"], want["k_scale"], rtol=2e-6)
+        np.testing.assert_allclose(got["k_rnorm"], want["k_rnorm"], rtol=2e-5)
+        flipped = np.unpackbits(got["k_base"] ^ want["k_base"]).sum() + np.unpackbits(got["k_sign"] ^ want["k_sign"]).sum()
+        assert flipped <= 4, (pos, int(flipped))
+    ctx.close()
+
+
+@pytest.mark.parametrize("head_dim,n_heads,n_kv_heads", [(64, 8, 2), (128, 8, 8), (128, 12, 4), (256, 4, 2)])
+@pytest.mark.parametrize("window", [0, 24])
+def test_turboquant_prefill_and_decode_match_oracle(head_dim, n_heads, n_kv_heads, window):
+    cfg = AttnConfig(n_layers=1, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim, seq_len=400, rope_theta=1e6,
+                     rope_style=ROPE_NEOX, kv_format=KV_TURBO, layer_windows=[window] if window else [])
+    check_prefill_then_decode(cfg, m=150, steps=3, seed=head_dim + window, chunk=64)
+
+
+def test_turboquant_long_decode_uses_splits_and_batches():
+    cfg = AttnConfig(n_layers=1, n_heads=8, n_kv_heads=2, head_dim=128, seq_len=3000, max_batch=3, rope_theta=1e6,
+                     rope_style=ROPE_NEOX, kv_format=KV_TURBO)
+    rng = np.random.default_rng(5)
+    ctx, ora = make(cfg)
+    for seq, n in enumerate((2500, 1200, 40)):
+        q, k, v = rand(rng, n, cfg.q_dim), rand(rng, n, cfg.kv_dim), rand(rng, n, cfg.kv_dim)
+        ctx.prefill(0, 0, q, k, v, seq=seq)
+        ora.prefill(0, 0, q, k, v, seq=seq)
+    q, k, v = rand(rng, 3, cfg.q_dim), rand(rng, 3, cfg.kv_dim), rand(rng, 3, cfg.kv_dim)
+    got = ctx.decode(0, [2500, 1200, 40], q, k, v)
+    want = ora.decode(0, [2500, 1200, 40], q, k, v)
+    assert ctx.last_split_count > 1
+    assert np.max(np.abs(got - want)) <= TOL[KV_TURBO]
     ctx.close()

@@ -269,3 +269,100 @@ def test_bf16_rounding_helpers_agree():
     L = oracle_lib()
     want = np.array([L.ora_bf16_to_f32(L.ora_f32_to_bf16(float(v))) for v in x], np.float32)
     assert np.array_equal(bf16_round(x), want)
+
+
+# ---- TurboQuant cache format (src/engine/runtime/inference.rs:349-1334) ----
+
+def _splitmix64(x):
+    m = (1 << 64) - 1
+    x = (x + 0x9E3779B97F4A7C15) & m
+    x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & m
+    x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & m
+    return x ^ (x >> 31)
+
+
+def _turbo_oracle(head_dim, n_layers=3, n_kv_heads=8, **kw):
+    cfg = AttnConfig(n_layers=n_layers, n_heads=n_kv_heads, n_kv_heads=n_kv_heads, head_dim=head_dim, seq_len=8,
+                     rope_dim=head_dim, rope_theta=1e6, rope_style=ROPE_NEOX, kv_format=4, **kw)
+    return Oracle(cfg), cfg
+
+
+# inference.rs:4546-4556: forward then inverse rotation restores the vector (power-of-two head: FWHT included)
+def test_turboquant_transform_is_self_inverse_for_power_of_two_heads():
+    ora, _ = _turbo_oracle(8)
+    values = np.array([0.25, -0.5, 1.0, -1.5, 0.75, 0.125, -0.25, 0.5], np.float32)
+    fwd = ora.turbo_transform(2, 3, 0, 1, values)
+    assert np.max(np.abs(fwd - values)) > 1e-3
+    back = ora.turbo_transform(2, 3, 1, 0, fwd)
+    assert np.max(np.abs(back - values)) < 1e-5
+
+
+# inference.rs:4558-4566: a head that is not a power of two skips the FWHT (only the sign flips remain)
+def test_turboquant_transform_is_self_inverse_for_non_power_of_two_heads():
+    ora, _ = _turbo_oracle(6, n_layers=2, n_kv_heads=8)
+    values = np.array([0.25, -0.5, 1.0, -1.5, 0.75, 0.125], np.float32)
+    fwd = ora.turbo_transform(1, 7, 2, 3, values)
+    assert np.array_equal(np.abs(fwd), np.abs(values))
+    back = ora.turbo_transform(1, 7, 3, 2, fwd)
+    assert np.max(np.abs(back - values)) < 1e-6
+
+
+# inference.rs:370-395 and :4292-4304: element i is negated iff splitmix64(seed ^ i) & 1, seed from (layer, head, salt)
+def test_turboquant_sign_pattern_follows_splitmix64():
+    ora, _ = _turbo_oracle(6, n_layers=2, n_kv_heads=8)
+    salts = [0x9E3779B97F4A7C15, 0xC2B2AE3D27D4EB4F, 0x165667B19E3779F9, 0xD6E8FEB86659FD93]
+    ones = np.ones(6, np.float32)
+    for layer, head in ((0, 0), (1, 7)):
+        for a, b in ((0, 1), (2, 3)):
+            got = ora.turbo_transform(layer, head, a, b, ones)  # no FWHT at length 6: product of both sign vectors
+            want = np.ones(6, np.float32)
+            for slot in (a, b):
+                seed = _splitmix64(((layer << 32) ^ head ^ salts[slot]) & ((1 << 64) - 1))
+                want *= np.array([-1.0 if _splitmix64(seed ^ i) & 1 else 1.0 for i in range(6)], np.float32)
+            assert np.array_equal(got, want)
+
+
+# inference.rs:885-952: codes follow the +-0.9815985 / 0 thresholds of r / sigma, zero rows store zero codes, all
+# sign bits set and zero norms; codes are packed four per byte, LSB first (:853-855, :4535-4545)
+def test_turboquant_write_codes_and_zero_row():
+    ora, cfg = _turbo_oracle(16, n_layers=1, n_kv_heads=2)
+    rng = np.random.default_rng(3)
+    k = rng.standard_normal(32).astype(np.float32)
+    v = np.zeros(32, np.float32)
+    ora.kv_write_token(0, 0, k, v)
+    row = ora.kv_read_turbo(0, 0)
+    assert not row["v_base"].any() and (row["v_sign"] == 0xFF).all()
+    assert (row["v_scale"] == 0).all() and (row["v_rnorm"] == 0).all()
+    centroids = np.array([-1.510417, -0.45278, 0.45278, 1.510417], np.float32)
+    for h in range(2):
+        r = ora.turbo_transform(0, h, 0, 1, k[h * 16:(h + 1) * 16])
+        sigma = np.float32(np.sqrt(np.sum(r.astype(np.float32) ** 2, dtype=np.float32)) / np.float32(4.0))
+        assert abs(row["k_scale"][h] - sigma) <= 1e-6 * sigma
+        codes = [(row["k_base"][(h * 16 + i) // 4] >> (((h * 16 + i) & 3) * 2)) & 3 for i in range(16)]
+        x = r / row["k_scale"][h]
+        want = [0 if t < -0.9815985 else 1 if t < 0 else 2 if t < 0.9815985 else 3 for t in x]
+        assert codes == want
+        resid = r - centroids[codes] * row["k_scale"][h]
+        gamma = np.sqrt(np.sum(resid.astype(np.float64) ** 2))
+        assert abs(row["k_rnorm"][h] - gamma) < 1e-5
+        proj = ora.turbo_transform(0, h, 2, 3, (resid / row["k_rnorm"][h]).astype(np.float32))
+        bits = [(row["k_sign"][(h * 16 + i) // 8] >> ((h * 16 + i) & 7)) & 1 for i in range(16)]
+        assert bits == [1 if p >= 0 else 0 for p in proj]
+
+
+# the format is lossy by design: its attention output stays close to the f32 cache's, and the online and two-pass
+# arms (:2320-2429, :2430-2527) agree with each other
+def test_turboquant_attention_tracks_f32_attention():
+    rng = np.random.default_rng(11)
+    base = dict(n_layers=1, n_heads=4, n_kv_heads=2, head_dim=64, seq_len=48, rope_dim=0, rope_theta=1e6,
+                rope_style=ROPE_NEOX)
+    m = 48
+    q = rng.standard_normal((m, 256)).astype(np.float32)
+    k = rng.standard_normal((m, 128)).astype(np.float32)
+    v = rng.standard_normal((m, 128)).astype(np.float32)
+    exact = Oracle(AttnConfig(kv_format=0, **base)).prefill(0, 0, q, k, v)
+    two_pass = Oracle(AttnConfig(kv_format=4, softmax_mode=0, **base)).prefill(0, 0, q, k, v)
+    online = Oracle(AttnConfig(kv_format=4, softmax_mode=1, **base)).prefill(0, 0, q, k, v)
+    assert np.max(np.abs(two_pass - online)) < 5e-6
+    err = np.abs(two_pass - exact)
+    assert err.max() < 1.5 and np.sqrt(np.mean(err ** 2)) < 0.35
