@@ -472,6 +472,58 @@ def bench_decode_cfg3(torch, args, local_rank, peaks, B=8):
     return res
 
 
+def bench_decode_turbo(torch, args, local_rank, peaks, B=8):
+    """The config-3 decode shape over a TurboQuant cache (the reference's default format, 3 bits per element)."""
+    import gguf_runner_b200 as g
+    from gguf_runner_b200 import presets
+    from gguf_runner_b200.binding import KV_TURBO
+    T, L = 32768, 8
+    cfg = presets.qwen3_30b_a3b_decode(n_layers=L, seq_len=T, max_batch=B, device=local_rank, kv_format=KV_TURBO)
+    ctx = g.AttnContext(cfg)
+    # synthetic cache content: random codes, sigma in (0.5, 1.5); sign bits and residual norms stay zero
+    kp, vp, ksp, vsp, nbytes = ctx.kv_device_ptrs()
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1006)
+    for ptr in (kp, vp):
+        flat = torch.as_tensor(RawCuda(ptr, nbytes), device="cuda").view(torch.uint8)
+        flat.copy_(torch.randint(0, 256, (flat.numel(),), generator=gen, device="cuda", dtype=torch.uint8))
+    n_aux = B * L * T * cfg.n_kv_heads
+    for ptr in (ksp, vsp):
+        flat = torch.as_tensor(RawCuda(ptr, n_aux * 4), device="cuda").view(torch.float32)
+        flat.copy_(torch.rand(n_aux, generator=gen, device="cuda") + 0.5)
+    q = torch.randn(L, B, cfg.q_dim, generator=gen, device="cuda")
+    k = torch.randn(L, B, cfg.kv_dim, generator=gen, device="cuda")
+    v = torch.randn(L, B, cfg.kv_dim, generator=gen, device="cuda")
+    out = torch.empty(L, B, cfg.q_dim, device="cuda")
+    pos = [T - 1] * B
+
+    def step():
+        for l in range(L):
+            ctx.decode(l, pos, q[l], k[l], v[l], out=out[l])
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    ctx.set_kernel_timing(True)
+    for _ in range(max(3, args.steps)):
+        step()
+    torch.cuda.synchronize()
+    attn_ms, attn_n = ctx.kernel_time(0)
+    rope_ms, rope_n = ctx.kernel_time(1)
+    # per key and kv head: codes D/4 + sign bits D/8 bytes and two floats, for K and for V
+    bytes_per_launch = B * T * cfg.n_kv_heads * (cfg.head_dim * 3 // 8 + 8) * 2
+    achieved = bytes_per_launch / (attn_ms / attn_n * 1e-3) / 1e9
+    res = {"workload": f"config-3 decode shape over a TurboQuant cache: 32 q / 4 kv heads, T=32768, B={B}, {L} layers resident",
+           "attention_ms_per_layer": attn_ms / attn_n, "rope_and_append_ms_per_layer": rope_ms / max(1, rope_n) * 2,
+           "cache_bytes_per_layer": bytes_per_launch, "bf16_cache_bytes_per_layer": B * T * cfg.n_kv_heads * cfg.head_dim * 4,
+           "roofline": {"bound": "hbm", "kernel": "attn_turbo_kernel (CUDA cores, f32)", "achieved": achieved,
+                        "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                        "note": "arithmetic-bound on the CUDA cores: 4*G*D lane operations per key"}}
+    ctx.close()
+    torch.cuda.empty_cache()
+    return res
+
+
 def bench_decode_seq_split(torch, dist, args, rank, world, local_rank, peaks):
     """Qwen2.5-14B-shaped long-context decode (configs[4]): T=131072, B=16, the KV sequence split into one
     contiguous slab per rank; partial (o, m, l) all-gathered with NCCL and merged on every rank."""
@@ -625,6 +677,7 @@ def run_ours(args):
                 extras["decode_sweep"] = [bench_decode_cfg3(torch, args, local_rank, peaks, B=b) for b in (1, 32)]
                 extras["prefill_chunked_gemma"] = bench_prefill_gemma(torch, args, local_rank, peaks)
                 extras["decode_small_f32"] = bench_decode_cfg1(torch, args, local_rank, peaks)
+                extras["decode_turboquant"] = bench_decode_turbo(torch, args, local_rank, peaks, B=args.decode_batch)
         else:
             extras["decode_seq_split"] = bench_decode_seq_split(torch, dist, args, rank, world, local_rank, peaks)
 

@@ -1161,8 +1161,10 @@ int ggr_attn_kv_device_ptrs(ggr_attn_ctx* c, void** k, void** v, float** k_scale
     if (v) *v = c->kv.v;
     if (k_scale) *k_scale = c->kv.ks;
     if (v_scale) *v_scale = c->kv.vs;
-    if (array_bytes)
-        *array_bytes = (uint64_t)c->cfg.max_batch * c->cfg.n_layers * c->shard_count * c->kv_dim * c->kv.elem_bytes;
+    if (array_bytes) {
+        const uint64_t elems = (uint64_t)c->cfg.max_batch * c->cfg.n_layers * c->shard_count * c->kv_dim;
+        *array_bytes = c->kv.fmt == KV_TURBO ? (elems + 3) / 4 : elems * c->kv.elem_bytes;  // TurboQuant: the code arrays
+    }
     return GGR_OK;
 }
 
