@@ -16,6 +16,7 @@
 #include "attn_mma.cuh"
 #include "attn_simt.cuh"
 #include "attn_turbo.cuh"
+#include "attn_turbo_mma.cuh"
 #include "common.cuh"
 #include "prefill_tc.cuh"
 #include "prefill_tc_wide.cuh"
@@ -516,8 +517,13 @@ int launch_attention(ggr_attn_ctx* c, int layer, const Items& items, int t_max, 
             if (rc) return rc;
         }
         const int64_t base_ctas = (int64_t)c->kv.Hkv * items.n;
-        int n_split = (int)std::max<int64_t>(1, ((int64_t)4 * c->sm_count + base_ctas - 1) / base_ctas);
-        n_split = std::min(n_split, std::max(1, t_max / (4 * kTurboGroups)));
+        // tensor-core kernel (head_dim 128, at most 16 query heads per KV head): one 8-warp CTA per SM, splits fill
+        // the SMs once; the CUDA-core kernel otherwise (and when decode_impl asks for it): four CTAs per SM deep
+        const bool tc = allow_mma && turbo_mma_supported(c->D, c->G) && c->cfg.decode_impl != GGR_IMPL_SIMT;
+        const int per_cta_keys = tc ? 2 * kTmWarps * kTmTK : 4 * kTurboGroups;
+        int n_split = (int)std::max<int64_t>(1, ((int64_t)(tc ? 1 : 4) * c->sm_count + base_ctas - 1) / base_ctas);
+        if (tc && base_ctas * n_split > c->sm_count && n_split > 1) --n_split;  // stay within one wave
+        n_split = std::min(n_split, std::max(1, t_max / per_cta_keys));
         n_split = std::min(n_split, 64);
         if (c->cfg.max_splits > 0) n_split = std::min(n_split, c->cfg.max_splits);
         a.n_split = n_split;
@@ -533,11 +539,16 @@ int launch_attention(ggr_attn_ctx* c, int layer, const Items& items, int t_max, 
             a.part = c->d_part;
             a.counters = c->d_counters;
         }
-        const size_t smem = turbo_attn_smem_floats(c->D, c->G, turbo_heads_per_pass(c->G, c->D), n_split) * sizeof(float);
-        if (smem + 1024 > (size_t)c->smem_optin)
-            return fail(c, GGR_ERR_UNSUPPORTED, "TurboQuant attention: too many query heads per KV head for shared memory");
         int e;
-        {
+        if (tc) {
+            const size_t smem = turbo_mma_smem_bytes(c->G, n_split);
+            a.stage_bytes = (int)turbo_mma_prep_offset(c->G, n_split);
+            LaunchTimer t(c, 0);
+            e = launch_turbo_mma(a, dim3(n_split, c->kv.Hkv, items.n), smem, c->smem_optin, c->cfg.device, c->stream);
+        } else {
+            const size_t smem = turbo_attn_smem_floats(c->D, c->G, turbo_heads_per_pass(c->G, c->D), n_split) * sizeof(float);
+            if (smem + 1024 > (size_t)c->smem_optin)
+                return fail(c, GGR_ERR_UNSUPPORTED, "TurboQuant attention: too many query heads per KV head for shared memory");
             LaunchTimer t(c, 0);
             e = launch_turbo_attention(a, dim3(n_split, c->kv.Hkv, items.n), smem, c->smem_optin, c->cfg.device, c->stream);
         }

@@ -562,10 +562,15 @@ def test_turboquant_append_is_bit_exact(head_dim, n_heads, n_kv_heads, style):
 
 @pytest.mark.parametrize("head_dim,n_heads,n_kv_heads", [(64, 8, 2), (128, 8, 8), (128, 12, 4), (256, 4, 2)])
 @pytest.mark.parametrize("window", [0, 24])
-def test_turboquant_prefill_and_decode_match_oracle(head_dim, n_heads, n_kv_heads, window):
+@pytest.mark.parametrize("impl", [IMPL_AUTO, IMPL_SIMT])
+def test_turboquant_prefill_and_decode_match_oracle(head_dim, n_heads, n_kv_heads, window, impl):
+    """Prefill rows and CUDA-core decode compute in f32 (1e-3); head_dim 128 decode runs on the tensor cores by
+    default, with bf16 queries, centroids and probabilities (the bf16 tolerance, 2e-2)."""
     cfg = AttnConfig(n_layers=1, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim, seq_len=400, rope_theta=1e6,
-                     rope_style=ROPE_NEOX, kv_format=KV_TURBO, layer_windows=[window] if window else [])
-    check_prefill_then_decode(cfg, m=150, steps=3, seed=head_dim + window, chunk=64)
+                     rope_style=ROPE_NEOX, kv_format=KV_TURBO, layer_windows=[window] if window else [],
+                     decode_impl=impl)
+    tol = TOL[KV_BF16] if (head_dim == 128 and impl == IMPL_AUTO) else TOL[KV_TURBO]
+    check_prefill_then_decode(cfg, m=150, steps=3, seed=head_dim + window, chunk=64, tol=tol)
 
 
 def test_turboquant_long_decode_uses_splits_and_batches():
@@ -581,5 +586,30 @@ def test_turboquant_long_decode_uses_splits_and_batches():
     got = ctx.decode(0, [2500, 1200, 40], q, k, v)
     want = ora.decode(0, [2500, 1200, 40], q, k, v)
     assert ctx.last_split_count > 1
-    assert np.max(np.abs(got - want)) <= TOL[KV_TURBO]
+    err = float(np.max(np.abs(got - want)))
+    assert err <= TOL[KV_BF16], err  # tensor-core decode: bf16 queries, centroids and probabilities
     ctx.close()
+
+
+def test_turboquant_tensor_core_decode_at_full_grouping():
+    """16 query heads per KV head (all rows of the MMA tile in use), a key range that is no multiple of the tile,
+    several sequences with different lengths; compared with the oracle and with the CUDA-core kernel."""
+    base = dict(n_layers=1, n_heads=32, n_kv_heads=2, head_dim=128, seq_len=1500, max_batch=2, rope_theta=1e6,
+                rope_style=ROPE_NEOX, kv_format=KV_TURBO)
+    rng = np.random.default_rng(9)
+    lens = (1237, 333)
+    ctx, ora = make(AttnConfig(**base))
+    ref = g.AttnContext(AttnConfig(decode_impl=IMPL_SIMT, **base))
+    for seq, n in enumerate(lens):
+        q, k, v = rand(rng, n, 32 * 128), rand(rng, n, 256), rand(rng, n, 256)
+        for c in (ctx, ref):
+            c.prefill(0, 0, q, k, v, seq=seq)
+        ora.prefill(0, 0, q, k, v, seq=seq)
+    q, k, v = rand(rng, 2, 32 * 128), rand(rng, 2, 256), rand(rng, 2, 256)
+    got = ctx.decode(0, list(lens), q, k, v)
+    exact = ref.decode(0, list(lens), q, k, v)
+    want = ora.decode(0, list(lens), q, k, v)
+    assert np.max(np.abs(exact - want)) <= TOL[KV_TURBO]
+    assert np.max(np.abs(got - want)) <= TOL[KV_BF16]
+    ctx.close()
+    ref.close()
