@@ -647,6 +647,19 @@ def run_small_case(args):
         for _ in range(3):
             for l in range(2):
                 out = ctx.decode(l, [T - 1] * B, q, k, v)
+    elif args.case == "decode_turbo_small":
+        # two layers of the config-3 decode shape over a TurboQuant cache: T=32768, B=8 (0.25 GB on the device);
+        # the cache keeps its zero rows (timing of the tensor-core kernel does not depend on the code values)
+        from gguf_runner_b200.binding import KV_TURBO
+        B, T = 8, 32768
+        cfg = presets.qwen3_30b_a3b_decode(n_layers=2, seq_len=T, max_batch=B, kv_format=KV_TURBO)
+        ctx = g.AttnContext(cfg)
+        q = torch.randn(B, cfg.q_dim, generator=gen, device="cuda")
+        k = torch.randn(B, cfg.kv_dim, generator=gen, device="cuda")
+        v = torch.randn(B, cfg.kv_dim, generator=gen, device="cuda")
+        for _ in range(3):
+            for l in range(2):
+                out = ctx.decode(l, [T - 1] * B, q, k, v)
     else:
         raise SystemExit(f"unknown case {args.case}")
     torch.cuda.synchronize()
@@ -714,7 +727,7 @@ def main():
     ap.add_argument("--decode-batch", type=int, default=8)
     ap.add_argument("--all-configs", action="store_true", help="also run configs[0], configs[2] at B=1/32 and configs[3]")
     ap.add_argument("--cpu-stride", type=int, default=16)
-    ap.add_argument("--case", default=None, help="run a small profiling case (prefill_small, decode_small) and exit")
+    ap.add_argument("--case", default=None, help="run a small profiling case (prefill_small, decode_small, decode_turbo_small) and exit")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

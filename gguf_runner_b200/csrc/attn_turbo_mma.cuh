@@ -76,10 +76,23 @@ __device__ __forceinline__ void turbo_mma_issue(const AttnArgs& a, unsigned char
     }
 }
 
-// expands 64 codes (16 bytes) and 64 sign bits (8 bytes) of one key half into bf16 chunks of the two tiles
+// Two bf16 centroids from two 2-bit codes (n = c0 | c1 << 2) with one byte permute: the table registers hold the
+// high and the low bytes of bf16(-1.510417, -0.45278, 0.45278, 1.510417) = 0xBFC1, 0xBEE8, 0x3EE8, 0x3FC1.
+__device__ __forceinline__ uint32_t turbo_centroid_pair(uint32_t n) {
+    const uint32_t sel = (n & 3u) * 0x11u + (n >> 2) * 0x1100u + 0x0404u;  // bytes: lo[c0], hi[c0], lo[c1], hi[c1]
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(0x3F3EBEBFu), "r"(0xC1E8E8C1u), "r"(sel));
+    return r;
+}
+// Two bf16 values +1 / -1 from two sign bits (1 = positive)
+__device__ __forceinline__ uint32_t turbo_sign_pair(uint32_t x) {
+    return 0xBF80BF80u ^ ((x & 1u) << 15) ^ ((x & 2u) << 30);
+}
+
+// expands 64 codes (16 bytes) and 64 sign bits (8 bytes) of one key half into bf16 chunks of the two tiles;
+// shared memory only sees the 16-byte stores (the lookups are register arithmetic)
 __device__ __forceinline__ void turbo_mma_expand(const unsigned char* codes, const unsigned char* signs, unsigned char* ctile,
-                                                 unsigned char* stile, int key, int half, const uint32_t* lut_c,
-                                                 const uint32_t* lut_s) {
+                                                 unsigned char* stile, int key, int half) {
     const uint4 cw = *reinterpret_cast<const uint4*>(codes);
     const uint2 sw = *reinterpret_cast<const uint2*>(signs);
     const uint32_t cwords[4] = {cw.x, cw.y, cw.z, cw.w};
@@ -89,14 +102,14 @@ __device__ __forceinline__ void turbo_mma_expand(const unsigned char* codes, con
         const uint32_t w = (cwords[j >> 1] >> ((j & 1) * 16)) & 0xffffu;
         const uint32_t sb = (swords[j >> 2] >> ((j & 3) * 8)) & 0xffu;
         uint4 cv, sv;
-        cv.x = lut_c[w & 15];
-        cv.y = lut_c[(w >> 4) & 15];
-        cv.z = lut_c[(w >> 8) & 15];
-        cv.w = lut_c[(w >> 12) & 15];
-        sv.x = lut_s[sb & 3];
-        sv.y = lut_s[(sb >> 2) & 3];
-        sv.z = lut_s[(sb >> 4) & 3];
-        sv.w = lut_s[(sb >> 6) & 3];
+        cv.x = turbo_centroid_pair(w & 15);
+        cv.y = turbo_centroid_pair((w >> 4) & 15);
+        cv.z = turbo_centroid_pair((w >> 8) & 15);
+        cv.w = turbo_centroid_pair(w >> 12);
+        sv.x = turbo_sign_pair(sb & 3);
+        sv.y = turbo_sign_pair((sb >> 2) & 3);
+        sv.z = turbo_sign_pair((sb >> 4) & 3);
+        sv.w = turbo_sign_pair(sb >> 6);
         const int off = key * (kTmD * 2) + (((half * 8 + j) ^ (key & 7)) << 4);
         *reinterpret_cast<uint4*>(ctile + off) = cv;
         *reinterpret_cast<uint4*>(stile + off) = sv;
@@ -106,8 +119,6 @@ __device__ __forceinline__ void turbo_mma_expand(const unsigned char* codes, con
 __global__ void __launch_bounds__(kTmWarps * 32) attn_turbo_mma_kernel(AttnArgs a) {
     extern __shared__ __align__(16) unsigned char tsm8[];
     __shared__ int s_last;
-    __shared__ uint32_t lut_c[16];  // two codes -> two bf16 centroids
-    __shared__ uint32_t lut_s[4];   // two sign bits -> two bf16 +-1
     constexpr int D = kTmD, KS = D / 16, NT = D / 8, rowbytes = D * 2;
     const int G = a.kv.G, Hq = a.kv.Hq;
     const int split = blockIdx.x, kvh = blockIdx.y, item = blockIdx.z;
@@ -143,11 +154,6 @@ __global__ void __launch_bounds__(kTmWarps * 32) attn_turbo_mma_kernel(AttnArgs 
 #pragma unroll
     for (int s = 0; s < kTmNST - 1; ++s) issue(s);
 
-    if (tid < 16) {
-        const uint32_t cb[4] = {0xBFC1u, 0xBEE8u, 0x3EE8u, 0x3FC1u};  // bf16(-1.510417, -0.45278, 0.45278, 1.510417)
-        lut_c[tid] = cb[tid & 3] | (cb[(tid >> 2) & 3] << 16);
-        if (tid < 4) lut_s[tid] = ((tid & 1) ? 0x3F80u : 0xBF80u) | (((tid & 2) ? 0x3F80u : 0xBF80u) << 16);
-    }
     // query preparation (:954-968): q_r = T(q; rot_pre, rot_post), q_p = T(q_r; res_pre, res_post)
     const unsigned char* rot_pre = turbo_sign_slot(a.kv, 0, a.layer, kvh);
     const unsigned char* rot_post = turbo_sign_slot(a.kv, 1, a.layer, kvh);
@@ -197,12 +203,13 @@ __global__ void __launch_bounds__(kTmWarps * 32) attn_turbo_mma_kernel(AttnArgs 
         const float* scal = reinterpret_cast<const float*>(raw + 2 * (kTmTK * D / 4) + 2 * (kTmTK * D / 8));
         const int key0 = k0 + (warp + it * kTmWarps) * kTmTK;
         {
-            const int key = lane >> 1, half = lane & 1;
+            // eight consecutive lanes expand eight different keys: their 16-byte stores then fall into different banks
+            const int key = lane & 15, half = lane >> 4;
             turbo_mma_expand(raw + key * 32 + half * 16, raw + 2 * (kTmTK * D / 4) + key * 16 + half * 8, tiles,
-                             tiles + kTmTileBytes, key, half, lut_c, lut_s);
+                             tiles + kTmTileBytes, key, half);
             turbo_mma_expand(raw + kTmTK * D / 4 + key * 32 + half * 16,
                              raw + 2 * (kTmTK * D / 4) + kTmTK * D / 8 + key * 16 + half * 8, tiles + 2 * kTmTileBytes,
-                             tiles + 3 * kTmTileBytes, key, half, lut_c, lut_s);
+                             tiles + 3 * kTmTileBytes, key, half);
         }
         __syncwarp();
 
