@@ -521,11 +521,25 @@ int launch_attention(ggr_attn_ctx* c, int layer, const Items& items, int t_max, 
         // the SMs once; the CUDA-core kernel otherwise (and when decode_impl asks for it): four CTAs per SM deep
         const bool tc = allow_mma && turbo_mma_supported(c->D, c->G) && c->cfg.decode_impl != GGR_IMPL_SIMT;
         const int per_cta_keys = tc ? 2 * kTmWarps * kTmTK : 4 * kTurboGroups;
-        int n_split = (int)std::max<int64_t>(1, ((int64_t)(tc ? 1 : 4) * c->sm_count + base_ctas - 1) / base_ctas);
-        if (tc && base_ctas * n_split > c->sm_count && n_split > 1) --n_split;  // stay within one wave
-        n_split = std::min(n_split, std::max(1, t_max / per_cta_keys));
-        n_split = std::min(n_split, 64);
-        if (c->cfg.max_splits > 0) n_split = std::min(n_split, c->cfg.max_splits);
+        int limit = std::min(64, std::max(1, t_max / per_cta_keys));
+        if (c->cfg.max_splits > 0) limit = std::min(limit, c->cfg.max_splits);
+        int n_split = (int)std::max<int64_t>(1, ((int64_t)4 * c->sm_count + base_ctas - 1) / base_ctas);
+        if (tc) {
+            // the kernel is bound by its own arithmetic (expanding the codes), so what matters is that the last
+            // wave is full: the smallest split count whose CTAs fill at least 95 % of their waves, else the fullest
+            double best_eff = -1.0;
+            n_split = 1;
+            for (int n = 1; n <= limit; ++n) {
+                const int64_t ctas = base_ctas * n, waves = (ctas + c->sm_count - 1) / c->sm_count;
+                const double eff = (double)ctas / (double)(waves * c->sm_count);
+                if (eff > best_eff + 1e-9) {
+                    best_eff = eff;
+                    n_split = n;
+                }
+                if (eff >= 0.95) break;
+            }
+        }
+        n_split = std::min(n_split, limit);
         a.n_split = n_split;
         c->last_splits = n_split;
         if (n_split > 1) {
