@@ -76,17 +76,38 @@ __device__ __forceinline__ void turbo_mma_issue(const AttnArgs& a, unsigned char
     }
 }
 
-// Two bf16 centroids from two 2-bit codes (n = c0 | c1 << 2) with one byte permute: the table registers hold the
-// high and the low bytes of bf16(-1.510417, -0.45278, 0.45278, 1.510417) = 0xBFC1, 0xBEE8, 0x3EE8, 0x3FC1.
-__device__ __forceinline__ uint32_t turbo_centroid_pair(uint32_t n) {
-    const uint32_t sel = (n & 3u) * 0x11u + (n >> 2) * 0x1100u + 0x0404u;  // bytes: lo[c0], hi[c0], lo[c1], hi[c1]
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     uint32_t r;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(0x3F3EBEBFu), "r"(0xC1E8E8C1u), "r"(sel));
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
     return r;
 }
-// Two bf16 values +1 / -1 from two sign bits (1 = positive)
-__device__ __forceinline__ uint32_t turbo_sign_pair(uint32_t x) {
-    return 0xBF80BF80u ^ ((x & 1u) << 15) ^ ((x & 2u) << 30);
+
+// Eight 2-bit codes (16 bits) -> eight bf16 centroids (four words). The codes are first spread into the eight
+// nibbles of a word; four nibbles at a time then select the high and the low bytes of
+// bf16(-1.510417, -0.45278, 0.45278, 1.510417) = 0xBFC1, 0xBEE8, 0x3EE8, 0x3FC1 from two table registers, and two
+// more permutes interleave them.
+__device__ __forceinline__ uint4 turbo_centroids8(uint32_t w) {
+    uint32_t x = w;
+    x = (x | (x << 8)) & 0x00FF00FFu;
+    x = (x | (x << 4)) & 0x0F0F0F0Fu;
+    x = (x | (x << 2)) & 0x33333333u;
+    const uint32_t hi_tab = 0x3F3EBEBFu, lo_tab = 0xC1E8E8C1u;
+    const uint32_t s0 = x & 0xFFFFu, s1 = x >> 16;
+    const uint32_t hi0 = prmt(hi_tab, lo_tab, s0), lo0 = prmt(hi_tab, lo_tab, s0 | 0x4444u);
+    const uint32_t hi1 = prmt(hi_tab, lo_tab, s1), lo1 = prmt(hi_tab, lo_tab, s1 | 0x4444u);
+    return make_uint4(prmt(lo0, hi0, 0x5140u), prmt(lo0, hi0, 0x7362u), prmt(lo1, hi1, 0x5140u), prmt(lo1, hi1, 0x7362u));
+}
+
+// Eight sign bits (1 = positive) -> eight bf16 values +1 / -1: bits spread into nibbles select 0xBF or 0x3F as
+// the high byte, the low byte is 0x80.
+__device__ __forceinline__ uint4 turbo_signs8(uint32_t sb) {
+    uint32_t x = sb;
+    x = (x | (x << 12)) & 0x000F000Fu;
+    x = (x | (x << 6)) & 0x03030303u;
+    x = (x | (x << 3)) & 0x11111111u;
+    const uint32_t h0 = prmt(0x00003FBFu, 0u, x & 0xFFFFu), h1 = prmt(0x00003FBFu, 0u, x >> 16);
+    const uint32_t c80 = 0x80808080u;
+    return make_uint4(prmt(h0, c80, 0x1404u), prmt(h0, c80, 0x3424u), prmt(h1, c80, 0x1404u), prmt(h1, c80, 0x3424u));
 }
 
 // expands 64 codes (16 bytes) and 64 sign bits (8 bytes) of one key half into bf16 chunks of the two tiles;
@@ -97,22 +118,14 @@ __device__ __forceinline__ void turbo_mma_expand(const unsigned char* codes, con
     const uint2 sw = *reinterpret_cast<const uint2*>(signs);
     const uint32_t cwords[4] = {cw.x, cw.y, cw.z, cw.w};
     const uint32_t swords[2] = {sw.x, sw.y};
+    const int row_off = key * (kTmD * 2), sw7 = key & 7;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {  // chunk j: elements half * 64 + 8 j .. + 7
         const uint32_t w = (cwords[j >> 1] >> ((j & 1) * 16)) & 0xffffu;
         const uint32_t sb = (swords[j >> 2] >> ((j & 3) * 8)) & 0xffu;
-        uint4 cv, sv;
-        cv.x = turbo_centroid_pair(w & 15);
-        cv.y = turbo_centroid_pair((w >> 4) & 15);
-        cv.z = turbo_centroid_pair((w >> 8) & 15);
-        cv.w = turbo_centroid_pair(w >> 12);
-        sv.x = turbo_sign_pair(sb & 3);
-        sv.y = turbo_sign_pair((sb >> 2) & 3);
-        sv.z = turbo_sign_pair((sb >> 4) & 3);
-        sv.w = turbo_sign_pair(sb >> 6);
-        const int off = key * (kTmD * 2) + (((half * 8 + j) ^ (key & 7)) << 4);
-        *reinterpret_cast<uint4*>(ctile + off) = cv;
-        *reinterpret_cast<uint4*>(stile + off) = sv;
+        const int off = row_off + (((half * 8 + j) ^ sw7) << 4);
+        *reinterpret_cast<uint4*>(ctile + off) = turbo_centroids8(w);
+        *reinterpret_cast<uint4*>(stile + off) = turbo_signs8(sb);
     }
 }
 
