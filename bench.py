@@ -269,7 +269,11 @@ def bench_prefill(torch, dist, args, rank, world, local_rank, peaks):
     # a kernel timed inside a seconds-long step: compare with the sustained cuBLAS figure
     peak = peaks["bf16_tflops_sustained"]
     roofline = {"bound": "tensor", "kernel": "prefill attention (one launch per layer)", "achieved": achieved,
-                "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this shape in the committed ncu capture
+                # (profiles/prefill_tc_kernel_llama3_8b_S4096.md): 50.5 MB + 15.2 MB; the kernel is bound by the tensor
+                # cores and the MUFU unit, its traffic is the q / K / V minimum plus the part of the output that left L2
+                "traffic": 65.7e6, "traffic_unit": "bytes per launch (ncu capture of the same shape)",
                 "peak_source": peaks["source"] + " (sustained cuBLAS bf16)",
                 "flops_per_launch": flops_per_launch, "avg_launch_ms": attn_ms / attn_n,
                 "rope_append_avg_ms": rope_ms / max(1, rope_n)}
@@ -466,7 +470,10 @@ def bench_decode_cfg3(torch, args, local_rank, peaks, B=8):
            "roofline": {"bound": "hbm", "kernel": "split-KV decode attention", "achieved": achieved,
                         "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                         "bytes_per_launch": bytes_per_launch, "avg_launch_ms": attn_ms / attn_n,
-                        "peak_source": peaks["source"], "traffic": None}}
+                        "peak_source": peaks["source"],
+                        # B = 8 capture (profiles/attn_mma_tma_decode_kernel_qwen3_30b_T32768_B8.md): 537.1 MB read +
+                        # 4.3 MB written for 536.9 MB of cache; other batch sizes scale with B
+                        "traffic": 541.4e6 * B / 8, "traffic_unit": "bytes per launch (ncu capture at B=8, scaled by B)"}}
     ctx.close()
     torch.cuda.empty_cache()
     return res
