@@ -89,7 +89,8 @@ typedef struct ggr_attn_config {
     int32_t shard_mode, shard_pos_begin, shard_pos_count;
     int32_t n_ranks, rank;
     int32_t decode_impl;  /* GGR_IMPL_*: kernel family for decode, AUTO picks by shape */
-    int32_t prefill_impl; /* GGR_IMPL_*: kernel family for prefill */
+    int32_t prefill_impl; /* GGR_IMPL_*: kernel family for prefill (TurboQuant cache: GGR_IMPL_MMA moves prefill rows to
+                             the tensor-core kernel, bf16-class error; default is the f32 kernel) */
     int32_t max_splits;   /* 0 = automatic split-KV factor */
     int32_t decode_fusion; /* 0 = decode rotates q and appends k/v inside the attention kernel (one launch per
                               layer) where the shape allows; 1 = separate rope/append launch */

@@ -613,3 +613,19 @@ def test_turboquant_tensor_core_decode_at_full_grouping():
     assert np.max(np.abs(got - want)) <= TOL[KV_BF16]
     ctx.close()
     ref.close()
+
+
+def test_turboquant_prefill_on_tensor_cores_is_opt_in():
+    """prefill_impl = MMA sends TurboQuant prefill rows through the tensor-core kernel (bf16 tolerance); the default
+    keeps them on the f32 kernel (1e-3)."""
+    base = dict(n_layers=1, n_heads=16, n_kv_heads=4, head_dim=128, seq_len=600, rope_theta=1e6, rope_style=ROPE_NEOX,
+                kv_format=KV_TURBO)
+    rng = np.random.default_rng(21)
+    q, k, v = rand(rng, 500, 16 * 128), rand(rng, 500, 512), rand(rng, 500, 512)
+    want = Oracle(AttnConfig(**base), threads=THREADS).prefill(0, 0, q, k, v)
+    exact = g.AttnContext(AttnConfig(**base))
+    fast = g.AttnContext(AttnConfig(prefill_impl=IMPL_MMA, **base))
+    assert np.max(np.abs(exact.prefill(0, 0, q, k, v) - want)) <= TOL[KV_TURBO]
+    assert np.max(np.abs(fast.prefill(0, 0, q, k, v) - want)) <= TOL[KV_BF16]
+    exact.close()
+    fast.close()
