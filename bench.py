@@ -1,20 +1,23 @@
 #!/usr/bin/env python
 """Benchmark of the attention path on B200.
 
-Default workload (the one the JSON line reports): Llama-3-8B-shaped causal
-prefill attention (config 2 of BASELINE.json): 32 layers, 32 query / 8 KV heads,
-head_dim 128, one sequence of 4096 tokens, bf16 q/k/v, RoPE + append + causal
-GQA attention per layer, f32 output. A step is one pass over all 32 layers.
-With N GPUs every rank processes its own sequence (independent sequences,
-no data-path collective): weak scaling.
+Headline workload (the fields of the JSON line): Llama-3-8B-shaped causal prefill attention
+(BASELINE.json configs[1]): 32 layers, 32 query / 8 KV heads, head_dim 128, one sequence of 4096
+tokens, bf16 q/k/v, RoPE + append + causal GQA attention per layer, f32 output. A step is one pass
+over all 32 layers. With N GPUs every rank processes its own sequence (independent sequences, no
+data-path collective): weak scaling.
 
-Extra objects in the same line: `decode` (Qwen3-30B-A3B-shaped split-KV decode,
-config 3, achieved HBM GB/s) at N=1 and `decode_seq_split` (Qwen2.5-14B-shaped
-long-context decode, config 5, KV sequence split over the ranks with an NCCL
-all-gather of the partial softmax states) at N>1.
+The same line carries one object per remaining BASELINE.json config, each with its own roofline:
+  decode_small_f32       configs[0]  Qwen3-0.6B-shaped decode, f32 cache (+ CPU baseline, + host-buffer e2e)
+  decode / decode_sweep  configs[2]  Qwen3-30B-A3B-shaped decode at B = 8 / B = 1, 32, 64
+  prefill_chunked_gemma  configs[3]  Gemma-3-4B-shaped chunked prefill, head_dim 256
+  decode_seq_split       configs[4]  Qwen2.5-14B-shaped long-context decode, KV sequence split over the
+                                     ranks (also at N = 1), with `decode_scaling`
+  decode_head_shard      configs[2]  at B = 32 / 64 with the KV heads split over the ranks (N > 1)
+  decode_turboquant      configs[2]  shape over the reference's default 3-bit cache
 
-`--impl reference` times the CPU restatement of the reference's attention
-(oracle/) on the host cores for the same workload, on a bounded sample.
+`--impl reference` times the CPU restatement of the reference's attention (oracle/) on the host
+cores for the headline workload, on a bounded sample.
 """
 from __future__ import annotations
 
@@ -112,19 +115,19 @@ def visible_pairs_causal(S: int) -> int:
     return S * (S + 1) // 2
 
 
-# ---- CPU reference arm --------------------------------------------------------------------------------
+# ---- CPU legs (the oracle: a restatement of the reference's scalar CPU attention) ------------------------
 
-def cpu_prefill_sample(stride: int = 16, threads: int = 0):
+def cpu_prefill_sample(stride: int = 16, threads: int = 0, native: bool = True):
     """Times the oracle (the reference's per-token CPU attention) on every `stride`-th query
     position of one Llama-3-8B-shaped layer over a fully populated Q8 cache, and scales by the
-    visible (query, key) pairs to a whole layer. Returns (tokens/s for the 32-layer pass, info)."""
+    visible (query, key) pairs to a whole layer. Returns (one_pass, scale, info, oracle)."""
     from gguf_runner_b200 import presets
     from gguf_runner_b200.binding import KV_Q8_ROW
     from tests.oracle_binding import Oracle, lib as oracle_lib
 
     cores = threads or oracle_lib().ora_threads_available()
     cfg = presets.llama3_8b_prefill(n_layers=1, seq_len=S_PREFILL, kv_format=KV_Q8_ROW)
-    ora = Oracle(cfg, threads=cores)
+    ora = Oracle(cfg, threads=cores, native=native)
     rng = np.random.default_rng(1002)
     k = rng.standard_normal((S_PREFILL, cfg.kv_dim)).astype(np.float32)
     v = rng.standard_normal((S_PREFILL, cfg.kv_dim)).astype(np.float32)
@@ -148,30 +151,93 @@ def cpu_prefill_sample(stride: int = 16, threads: int = 0):
 
     pairs_sample = sum(p + 1 for p in positions)
     scale = visible_pairs_causal(S_PREFILL) / pairs_sample
-    info = {"cores": cores, "kind": "port",
+    build = "-O3 -march=native (built on this host)" if native else "-O2, strict IEEE (the parity build)"
+    info = {"cores": cores, "kind": "port", "build": build,
             "sample": f"one layer, every {stride}th query position of S={S_PREFILL} ({len(positions)} tokens) over a "
                       f"populated q8_row cache; layer time = sample time x {scale:.2f} (visible-pair ratio), "
                       f"x {N_LAYERS_PREFILL} layers"}
     return one_pass, scale, info, ora
 
 
+def cpu_prefill_baseline(stride: int, reps: int = 1):
+    """tokens/s of the 32-layer prefill pass on the host cores, native and strict builds."""
+    out = {}
+    for native in (True, False):
+        one_pass, scale, info, ora = cpu_prefill_sample(stride=stride, native=native)
+        one_pass()
+        t = min(one_pass() for _ in range(max(1, reps)))
+        out["native" if native else "strict"] = (S_PREFILL / (t * scale * N_LAYERS_PREFILL), info)
+        ora.close()
+    value, info = out["native"]
+    return dict(info, value=value, unit="tokens/s", value_parity_build=out["strict"][0])
+
+
+def cpu_decode_cfg1():
+    """configs[0] on the host cores, full size: 28 layers, T = 2048, one new token per step, q8_row cache (the
+    reference's closest-to-lossless format); all cores and one thread, native and strict builds."""
+    from gguf_runner_b200 import presets
+    from gguf_runner_b200.binding import KV_Q8_ROW
+    from tests.oracle_binding import Oracle, lib as oracle_lib
+    T, L = 2048, 28
+    cores = oracle_lib().ora_threads_available()
+    cfg = presets.qwen3_0p6b_decode(n_layers=L, seq_len=T, kv_format=KV_Q8_ROW)
+    rng = np.random.default_rng(1001)
+    q = rng.standard_normal((L, 1, cfg.q_dim)).astype(np.float32)
+    k = rng.standard_normal((L, 1, cfg.kv_dim)).astype(np.float32)
+    v = rng.standard_normal((L, 1, cfg.kv_dim)).astype(np.float32)
+    res = {}
+    for native in (True, False):
+        ora = Oracle(cfg, threads=cores, native=native)
+        qd = np.zeros(cfg.q_dim, np.float32)
+        for l in range(L):
+            rows = rng.standard_normal((T - 1, 2, cfg.kv_dim)).astype(np.float32)
+            for pos in range(T - 1):
+                kr = rows[pos, 0].copy()
+                ora.apply_rope_qk(l, pos, qd.copy(), kr)
+                ora.kv_write_token(l, pos, kr, rows[pos, 1])
+
+        def step():
+            t0 = time.perf_counter()
+            for l in range(L):
+                ora.decode(l, [T - 1], q[l], k[l], v[l])
+            return time.perf_counter() - t0
+
+        for threads in (cores, 1):
+            ora.set_threads(threads)
+            step()
+            t = min(step() for _ in range(5))
+            res[("native" if native else "strict", threads)] = 1.0 / t
+        ora.close()
+    return {"value": res[("native", cores)], "unit": "tokens/s", "cores": cores, "kind": "port",
+            "build": "-O3 -march=native (built on this host)",
+            "value_one_thread": res[("native", 1)],
+            "value_parity_build": res[("strict", cores)], "value_parity_build_one_thread": res[("strict", 1)],
+            "sample": "full size: all 28 layers, 2048 cached positions, q8_row cache, best of 5 steps"}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    one_pass, scale, info, _ora = cpu_prefill_sample(stride=args.cpu_stride)
-    for _ in range(args.warmup):
-        one_pass()
-    times = [one_pass() for _ in range(args.steps)]
-    t = float(np.mean(times))
+    results = {}
+    for native in (True, False):
+        one_pass, scale, info, ora = cpu_prefill_sample(stride=args.cpu_stride, native=native)
+        for _ in range(args.warmup if native else 1):
+            one_pass()
+        times = [one_pass() for _ in range(args.steps if native else 1)]
+        results[native] = (float(np.mean(times)), scale, info)
+        ora.close()
+    t, scale, info = results[True]
     step_s = t * scale * N_LAYERS_PREFILL
     value = S_PREFILL / step_s
+    strict_value = S_PREFILL / (results[False][0] * scale * N_LAYERS_PREFILL)
     line = {
         "impl": "reference", "metric": "prefill attention tokens/s", "value": value, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args.gpus),
-        "cpu_baseline": dict(info, value=value, unit="tokens/s"),
+        "cpu_baseline": dict(info, value=value, unit="tokens/s", value_parity_build=strict_value,
+                             note="ms_per_step is extrapolated from the sample: each timed step runs the sample only"),
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -183,20 +249,16 @@ def workload_config(n_gpus: int):
                         "heads, head_dim 128, batch 1, S=4096, bf16 q/k/v, adjacent-pair RoPE theta 5e5, f32 out",
             "sequences": n_gpus, "seq_len": S_PREFILL, "layers": N_LAYERS_PREFILL,
             "parallelism": f"{n_gpus} independent sequences, one per GPU" if n_gpus > 1 else "single GPU",
-            "l2": "each step streams 1.6 GB of q/k/v, 0.5 GB of cache and 2.1 GB of output per GPU, far above the 126 MB L2"}
+            "l2": "each step streams 1.6 GB of q/k/v, 0.5 GB of cache and 2.1 GB of output per GPU, far above the 126 MB L2",
+            "timing": "value: K steps between CUDA events with no per-launch instrumentation; roofline: the same K steps "
+                      "repeated with an event pair around every launch"}
 
 
 # ---- GPU arm ---------------------------------------------------------------------------------------------
 
-class RawCuda:
-    """Lets torch view device memory owned by the library (__cuda_array_interface__)."""
-
-    def __init__(self, ptr, nbytes):
-        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
-
-
 def fill_cache_random(torch, ctx, seed):
     """Fills a bf16 / f32 cache with N(0,1) values (synthetic stand-in for appended rows)."""
+    from gguf_runner_b200.binding import RawCuda
     k, v, _, _, nbytes = ctx.kv_device_ptrs()
     dt = torch.bfloat16 if ctx.config.kv_format == 1 else torch.float32
     gen = torch.Generator(device="cuda")
@@ -207,6 +269,53 @@ def fill_cache_random(torch, ctx, seed):
         for i in range(0, flat.numel(), step):
             n = min(step, flat.numel() - i)
             flat[i:i + n] = torch.randn(n, generator=gen, device="cuda", dtype=torch.float32).to(dt)
+
+
+def timed_steps(torch, fn, steps, warmup=3, sync=None):
+    """Milliseconds per call of fn over `steps` calls (CUDA events on the current stream, after warm-up)."""
+    for _ in range(warmup):
+        fn()
+    (sync or torch.cuda.synchronize)()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    (sync or torch.cuda.synchronize)()
+    return e0.elapsed_time(e1) / steps
+
+
+def instrumented(torch, ctx, fn, steps):
+    """Runs fn `steps` times with an event pair around every launch; returns {kind: (ms per launch, launches per step)}."""
+    ctx.set_kernel_timing(True)
+    for _ in range(steps):
+        fn()
+    torch.cuda.synchronize()
+    out = {}
+    for kind in (0, 1, 2):
+        ms, n = ctx.kernel_time(kind)
+        out[kind] = (ms / n if n else 0.0, n / steps)
+    ctx.set_kernel_timing(False)
+    return out
+
+
+def tensor_roofline(peaks, flops, ms, **extra):
+    achieved = flops / (ms * 1e-3) / 1e12
+    r = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+         "frac": achieved / peaks["bf16_tflops"], "frac_of_sustained_peak": achieved / peaks["bf16_tflops_sustained"],
+         "peak_sustained": peaks["bf16_tflops_sustained"],
+         "peak_source": peaks["source"] + " (cuBLAS bf16: burst figure in `peak`, seconds-long loop in `peak_sustained`; "
+                        "the timed regions here last well under a second, so `frac` uses the burst figure)"}
+    r.update(extra)
+    return r
+
+
+def hbm_roofline(peaks, nbytes, ms, **extra):
+    achieved = nbytes / (ms * 1e-3) / 1e9
+    r = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+         "peak_source": peaks["source"] + " (copy bandwidth)"}
+    r.update(extra)
+    return r
 
 
 def bench_prefill(torch, dist, args, rank, world, local_rank, peaks):
@@ -243,7 +352,6 @@ def bench_prefill(torch, dist, args, rank, world, local_rank, peaks):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    ctx.set_kernel_timing(True)
     launches0 = ctx.launch_count
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -252,11 +360,12 @@ def bench_prefill(torch, dist, args, rank, world, local_rank, peaks):
     e1.record()
     sync_all()
     elapsed_ms = e0.elapsed_time(e1)
-    attn_ms, attn_n = ctx.kernel_time(0)
-    rope_ms, rope_n = ctx.kernel_time(1)
-    ctx.set_kernel_timing(False)
-    clocks = sampler.stop() if rank == 0 else None
     launches = ctx.launch_count - launches0
+    # the same K steps again with an event pair around every launch: kernel durations for the roofline
+    t0 = time.perf_counter()
+    per_kind = instrumented(torch, ctx, step, args.steps)
+    instrumented_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    clocks = sampler.stop() if rank == 0 else None
     if world > 1:
         t = torch.tensor([elapsed_ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -265,18 +374,19 @@ def bench_prefill(torch, dist, args, rank, world, local_rank, peaks):
     value = world * S / (ms_per_step * 1e-3)
 
     flops_per_launch = 4.0 * cfg.n_heads * cfg.head_dim * visible_pairs_causal(S)
-    achieved = flops_per_launch / (attn_ms / attn_n * 1e-3) / 1e12
-    # a kernel timed inside a seconds-long step: compare with the sustained cuBLAS figure
-    peak = peaks["bf16_tflops_sustained"]
-    roofline = {"bound": "tensor", "kernel": "prefill attention (one launch per layer)", "achieved": achieved,
-                "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this shape in the committed ncu capture
-                # (profiles/prefill_tc_kernel_llama3_8b_S4096.md): 50.5 MB + 15.2 MB; the kernel is bound by the tensor
-                # cores and the MUFU unit, its traffic is the q / K / V minimum plus the part of the output that left L2
-                "traffic": 65.7e6, "traffic_unit": "bytes per launch (ncu capture of the same shape)",
-                "peak_source": peaks["source"] + " (sustained cuBLAS bf16)",
-                "flops_per_launch": flops_per_launch, "avg_launch_ms": attn_ms / attn_n,
-                "rope_append_avg_ms": rope_ms / max(1, rope_n)}
+    attn_ms, attn_per_step = per_kind[0]
+    rope_ms, rope_per_step = per_kind[1]
+    roofline = tensor_roofline(
+        peaks, flops_per_launch, attn_ms, kernel="prefill attention (one launch per layer)",
+        # DRAM bytes of one launch of this shape, read + write, taken from an ncu capture of the same kernel and shape
+        # (not measured by this run): the kernel is bound by the tensor cores and the MUFU unit, its traffic is the
+        # q / K / V minimum plus the part of the output that left L2
+        traffic=65.7e6, traffic_unit="bytes per launch",
+        traffic_source="constant: dram__bytes_read.sum + dram__bytes_write.sum of an ncu capture of this kernel at this shape",
+        flops_per_launch=flops_per_launch, avg_launch_ms=attn_ms, launches_per_step=attn_per_step,
+        rope_append_avg_ms=rope_ms, rope_append_launches_per_step=rope_per_step,
+        step_frac=(flops_per_launch * L) / (ms_per_step * 1e-3) / 1e12 / peaks["bf16_tflops"],
+        ms_per_step_instrumented=instrumented_ms)
 
     # end to end through the C ABI with host buffers (pinned): H2D of q/k/v and D2H of out inside the timed region
     hq = [torch.empty(S, cfg.q_dim, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
@@ -308,7 +418,8 @@ def bench_prefill(torch, dist, args, rank, world, local_rank, peaks):
     h2d = L * (S * cfg.q_dim + 2 * S * cfg.kv_dim) * 2
     d2h = L * S * cfg.q_dim * 4
     e2e = {"value": world * S / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-           "ms_per_step": e2e_s * 1e3}
+           "ms_per_step": e2e_s * 1e3,
+           "call": "ggr_attn_prefill(GGR_PTR_HOST) per layer from pinned host buffers; bound by the f32 output crossing PCIe"}
     ctx.close()
     del q, k, v, out
     torch.cuda.empty_cache()
@@ -336,35 +447,27 @@ def bench_prefill_gemma(torch, args, local_rank, peaks):
             for l in range(L):
                 ctx.prefill(l, c0, q, k, v, out=out)
 
-    step()
-    torch.cuda.synchronize()
-    ctx.set_kernel_timing(True)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    step()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
-    attn_ms, attn_n = ctx.kernel_time(0)
-    ctx.set_kernel_timing(False)
+    ms = timed_steps(torch, step, 1, warmup=1)
+    per_kind = instrumented(torch, ctx, step, 1)
+    attn_ms_total = per_kind[0][0] * per_kind[0][1]
     pairs_global = S * (S + 1) // 2
     w = 1024
     pairs_local = sum(min(p + 1, w) for p in range(S))
     flops = 4.0 * cfg.n_heads * cfg.head_dim * (5 * pairs_global + 29 * pairs_local)
-    achieved = flops / (attn_ms * 1e-3) / 1e12
     res = {"workload": "Gemma-3-4B-shaped chunked prefill (configs[3]): 34 layers (29 with window 1024, 5 global), 8 q / "
                        "4 kv heads, head_dim 256, context 32768 in 2048-token chunks, bf16",
            "tokens_per_s": S / (ms * 1e-3), "ms_per_pass": ms,
-           "roofline": {"bound": "tensor", "kernel": "prefill attention, head_dim 256 (all launches of the pass)",
-                        "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
-                        "frac": achieved / peaks["bf16_tflops_sustained"], "flops_per_pass": flops,
-                        "attention_ms_per_pass": attn_ms, "launches": attn_n, "peak_source": peaks["source"]}}
+           "roofline": tensor_roofline(peaks, flops, attn_ms_total,
+                                       kernel="prefill attention, head_dim 256 (all launches of the pass)",
+                                       flops_per_pass=flops, attention_ms_per_pass=attn_ms_total,
+                                       launches=per_kind[0][1], rope_append_ms_per_pass=per_kind[1][0] * per_kind[1][1],
+                                       pass_frac=flops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"], traffic=None)}
     ctx.close()
     torch.cuda.empty_cache()
     return res
 
 
-def bench_decode_cfg1(torch, args, local_rank, peaks):
+def bench_decode_cfg1(torch, args, local_rank, peaks, with_cpu):
     """Qwen3-0.6B-shaped decode (configs[0]): 28 layers, 16 q / 8 kv heads, T=2048, batch 1, f32 cache.
     16.8 MB per layer is ~2.6 us of HBM time, below a kernel launch: the step is launch-bound, so the
     28-layer step is timed both as plain launches and replayed from a CUDA graph."""
@@ -387,20 +490,9 @@ def bench_decode_cfg1(torch, args, local_rank, peaks):
         for l in range(L):
             ctx.decode(l, pos, q[l], k[l], v[l], out=out[l])
 
-    def timed(fn, reps):
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(reps):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / reps
-
-    plain_ms = timed(step, 20)
-    graph_ms = None
+    plain_ms = timed_steps(torch, step, 20)
+    per_kind = instrumented(torch, ctx, step, 5)
+    graph_ms, graph_err = None, None
     try:
         side = torch.cuda.Stream()
         with torch.cuda.stream(side):
@@ -410,70 +502,85 @@ def bench_decode_cfg1(torch, args, local_rank, peaks):
             with torch.cuda.graph(graph, stream=side):
                 step()
         torch.cuda.synchronize()
-        graph_ms = timed(graph.replay, 50)
+        graph_ms = timed_steps(torch, graph.replay, 50)
     except Exception as e:  # capture is an optimisation of the host loop, not part of the path
-        graph_ms = None
         graph_err = repr(e)[:200]
-    bytes_per_step = L * T * cfg.kv_dim * 4 * 2
+    bytes_per_layer = T * cfg.kv_dim * 4 * 2
     best = min(x for x in (plain_ms, graph_ms) if x)
+    # drop-in call: what the unmodified engine would issue per layer and token (host f32 buffers, pageable)
+    hq, hk, hv = (x.cpu().numpy() for x in (q, k, v))
+    hout = np.empty((1, cfg.q_dim), np.float32)
+
+    def host_step():
+        for l in range(L):
+            ctx.decode(l, pos, hq[l], hk[l], hv[l], out=hout)
+
+    for _ in range(3):
+        host_step()
+    t0 = time.perf_counter()
+    for _ in range(20):
+        host_step()
+    host_s = (time.perf_counter() - t0) / 20
     res = {"workload": "Qwen3-0.6B-shaped decode (configs[0]): 28 layers, 16 q / 8 kv heads, T=2048, batch 1, f32 cache",
            "ms_per_step_plain_launches": plain_ms, "ms_per_step_cuda_graph": graph_ms,
-           "tokens_per_s": 1.0 / (best * 1e-3),
-           "roofline": {"bound": "hbm", "achieved": bytes_per_step / (best * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
-                        "unit": "GB/s", "frac": bytes_per_step / (best * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                        "bytes_per_step": bytes_per_step, "note": "whole 28-layer step (launch-bound), not one kernel"}}
+           "tokens_per_s": 1.0 / (best * 1e-3), "split_count": ctx.last_split_count,
+           "roofline": hbm_roofline(peaks, bytes_per_layer, per_kind[0][0], kernel="split-KV decode attention (one launch per layer)",
+                                    bytes_per_launch=bytes_per_layer, avg_launch_ms=per_kind[0][0],
+                                    step_frac=L * bytes_per_layer / (best * 1e-3) / 1e9 / peaks["hbm_gbs"], traffic=None,
+                                    note="`frac` is the kernel alone; `step_frac` the whole 28-layer step, which is "
+                                         "bound by launch latency (2.6 us of HBM time per layer)"),
+           "e2e": {"value": 1.0 / host_s, "unit": "tokens/s", "ms_per_step": host_s * 1e3,
+                   "h2d_bytes_per_step": L * (cfg.q_dim + 2 * cfg.kv_dim) * 4, "d2h_bytes_per_step": L * cfg.q_dim * 4,
+                   "call": "ggr_attn_decode(GGR_PTR_HOST) per layer from pageable host f32 buffers (one pinned staging "
+                           "copy in, one out, one stream synchronisation per call)"}}
     if graph_ms is None:
         res["cuda_graph_error"] = graph_err
     ctx.close()
     torch.cuda.empty_cache()
+    if with_cpu:
+        res["cpu_baseline"] = cpu_decode_cfg1()
     return res
 
 
-def bench_decode_cfg3(torch, args, local_rank, peaks, B=8):
-    """Qwen3-30B-A3B-shaped decode: 48 layers, 32 q / 4 kv heads, T=32768, bf16 cache, one new token per step."""
+def bench_decode_cfg3(torch, args, local_rank, peaks, B=8, n_res=None):
+    """Qwen3-30B-A3B-shaped decode: 48 layers, 32 q / 4 kv heads, T=32768, bf16 cache, one new token per step.
+    With n_res < 48 only n_res layers are resident and the 48 launches of a step cycle through them (each
+    layer holds gigabytes, so the L2 cannot help)."""
     import gguf_runner_b200 as g
     from gguf_runner_b200 import presets
     T, L = 32768, 48
-    cfg = presets.qwen3_30b_a3b_decode(n_layers=L, seq_len=T, max_batch=B, device=local_rank)
+    n_res = n_res or L
+    cfg = presets.qwen3_30b_a3b_decode(n_layers=n_res, seq_len=T, max_batch=B, device=local_rank)
     ctx = g.AttnContext(cfg)
     fill_cache_random(torch, ctx, 1003)
     gen = torch.Generator(device="cuda")
     gen.manual_seed(2003)
-    q = torch.randn(L, B, cfg.q_dim, generator=gen, device="cuda")
-    k = torch.randn(L, B, cfg.kv_dim, generator=gen, device="cuda")
-    v = torch.randn(L, B, cfg.kv_dim, generator=gen, device="cuda")
-    out = torch.empty(L, B, cfg.q_dim, device="cuda")
+    q = torch.randn(n_res, B, cfg.q_dim, generator=gen, device="cuda")
+    k = torch.randn(n_res, B, cfg.kv_dim, generator=gen, device="cuda")
+    v = torch.randn(n_res, B, cfg.kv_dim, generator=gen, device="cuda")
+    out = torch.empty(n_res, B, cfg.q_dim, device="cuda")
     pos = [T - 1] * B
 
     def step():
         for l in range(L):
-            ctx.decode(l, pos, q[l], k[l], v[l], out=out[l])
+            r = l % n_res
+            ctx.decode(r, pos, q[r], k[r], v[r], out=out[r])
 
-    for _ in range(max(3, args.warmup)):
-        step()
-    torch.cuda.synchronize()
-    ctx.set_kernel_timing(True)
     steps = max(3, args.steps)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        step()
-    e1.record()
-    torch.cuda.synchronize()
-    ms_per_step = e0.elapsed_time(e1) / steps
-    attn_ms, attn_n = ctx.kernel_time(0)
-    ctx.set_kernel_timing(False)
+    ms_per_step = timed_steps(torch, step, steps, warmup=max(3, args.warmup))
+    per_kind = instrumented(torch, ctx, step, steps)
     bytes_per_launch = B * T * cfg.n_kv_heads * cfg.head_dim * 2 * 2  # K and V, bf16
-    achieved = bytes_per_launch / (attn_ms / attn_n * 1e-3) / 1e9
-    res = {"workload": f"Qwen3-30B-A3B-shaped decode (configs[2]): 48 layers, 32 q / 4 kv heads, T=32768, B={B}, bf16 cache",
-           "tokens_per_s": B / (ms_per_step * 1e-3), "ms_per_step": ms_per_step,
-           "roofline": {"bound": "hbm", "kernel": "split-KV decode attention", "achieved": achieved,
-                        "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                        "bytes_per_launch": bytes_per_launch, "avg_launch_ms": attn_ms / attn_n,
-                        "peak_source": peaks["source"],
-                        # B = 8 capture (profiles/attn_mma_tma_decode_kernel_qwen3_30b_T32768_B8.md): 537.1 MB read +
-                        # 4.3 MB written for 536.9 MB of cache; other batch sizes scale with B
-                        "traffic": 541.4e6 * B / 8, "traffic_unit": "bytes per launch (ncu capture at B=8, scaled by B)"}}
+    resident = "all 48 layers resident" if n_res == L else f"{n_res} layers resident, cycled by the 48 launches of a step"
+    res = {"workload": f"Qwen3-30B-A3B-shaped decode (configs[2]): 48 layers, 32 q / 4 kv heads, T=32768, B={B}, bf16 cache, {resident}",
+           "tokens_per_s": B / (ms_per_step * 1e-3), "ms_per_step": ms_per_step, "split_count": ctx.last_split_count,
+           "roofline": hbm_roofline(peaks, bytes_per_launch, per_kind[0][0], kernel="split-KV decode attention",
+                                    bytes_per_launch=bytes_per_launch, avg_launch_ms=per_kind[0][0],
+                                    step_frac=L * bytes_per_launch / (ms_per_step * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                    # every cache byte is read exactly once, so the traffic of another batch size is
+                                    # the B = 8 capture scaled by B
+                                    traffic=541.4e6 * B / 8, traffic_unit="bytes per launch",
+                                    traffic_source="constant: ncu capture of this kernel at B=8 (537.1 MB read + 4.3 MB "
+                                                   "written for 536.9 MB of cache), scaled by B")}
     ctx.close()
     torch.cuda.empty_cache()
     return res
@@ -483,7 +590,7 @@ def bench_decode_turbo(torch, args, local_rank, peaks, B=8):
     """The config-3 decode shape over a TurboQuant cache (the reference's default format, 3 bits per element)."""
     import gguf_runner_b200 as g
     from gguf_runner_b200 import presets
-    from gguf_runner_b200.binding import KV_TURBO
+    from gguf_runner_b200.binding import KV_TURBO, RawCuda
     T, L = 32768, 8
     cfg = presets.qwen3_30b_a3b_decode(n_layers=L, seq_len=T, max_batch=B, device=local_rank, kv_format=KV_TURBO)
     ctx = g.AttnContext(cfg)
@@ -508,32 +615,24 @@ def bench_decode_turbo(torch, args, local_rank, peaks, B=8):
         for l in range(L):
             ctx.decode(l, pos, q[l], k[l], v[l], out=out[l])
 
-    for _ in range(3):
-        step()
-    torch.cuda.synchronize()
-    ctx.set_kernel_timing(True)
-    for _ in range(max(3, args.steps)):
-        step()
-    torch.cuda.synchronize()
-    attn_ms, attn_n = ctx.kernel_time(0)
-    rope_ms, rope_n = ctx.kernel_time(1)
+    ms_per_step = timed_steps(torch, step, max(3, args.steps))
+    per_kind = instrumented(torch, ctx, step, max(3, args.steps))
     # per key and kv head: codes D/4 + sign bits D/8 bytes and two floats, for K and for V
     bytes_per_launch = B * T * cfg.n_kv_heads * (cfg.head_dim * 3 // 8 + 8) * 2
-    achieved = bytes_per_launch / (attn_ms / attn_n * 1e-3) / 1e9
     res = {"workload": f"config-3 decode shape over a TurboQuant cache: 32 q / 4 kv heads, T=32768, B={B}, {L} layers resident",
-           "attention_ms_per_layer": attn_ms / attn_n, "rope_and_append_ms_per_layer": rope_ms / max(1, rope_n) * 2,
+           "ms_per_layer": ms_per_step / L, "attention_ms_per_layer": per_kind[0][0],
+           "rope_and_append_ms_per_layer": per_kind[1][0] * per_kind[1][1] / L,
            "cache_bytes_per_layer": bytes_per_launch, "bf16_cache_bytes_per_layer": B * T * cfg.n_kv_heads * cfg.head_dim * 4,
-           "roofline": {"bound": "hbm", "kernel": "attn_turbo_kernel (CUDA cores, f32)", "achieved": achieved,
-                        "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                        "note": "arithmetic-bound on the CUDA cores: 4*G*D lane operations per key"}}
+           "roofline": hbm_roofline(peaks, bytes_per_launch, per_kind[0][0], kernel="attn_turbo_mma_kernel", traffic=None,
+                                    note="bound by expanding the 3-bit codes (ALU and shared memory), not by HBM")}
     ctx.close()
     torch.cuda.empty_cache()
     return res
 
 
-def bench_decode_seq_split(torch, dist, args, rank, world, local_rank, peaks):
-    """Qwen2.5-14B-shaped long-context decode (configs[4]): T=131072, B=16, the KV sequence split into one
-    contiguous slab per rank; partial (o, m, l) all-gathered with NCCL and merged on every rank."""
+def seq_split_run(torch, dist, args, world, rank, local_rank, peaks, use_nccl):
+    """One measurement of configs[4] with the KV sequence split over `world` ranks (world = 1: the whole
+    sequence on this GPU, same kernels and exchange)."""
     import gguf_runner_b200 as g
     from gguf_runner_b200 import presets
     from gguf_runner_b200.binding import SHARD_KV_SEQUENCE
@@ -555,46 +654,46 @@ def bench_decode_seq_split(torch, dist, args, rank, world, local_rank, peaks):
     gathered = torch.empty(world, B, cfg.n_heads, cfg.head_dim + 2, device="cuda")
     out = torch.empty(B, cfg.q_dim, device="cuda")
     pos = [T - 1] * B
+    multi = world > 1
 
     def step_nccl():
         for l in range(L):
             r = l % n_res
-            ctx.decode_partial(r, pos, q[r], k[r], v[r], partial=part)
-            dist.all_gather_into_tensor(gathered, part)
+            if multi:
+                ctx.decode_partial(r, pos, q[r], k[r], v[r], partial=part)
+                dist.all_gather_into_tensor(gathered, part)
+            else:
+                ctx.decode_partial(r, pos, q[r], k[r], v[r], partial=gathered[0])
             ctx.combine_partials(gathered, out=out)
 
     # fused exchange: the decode kernel stores its states into the peers' receive buffers itself
     _base, handle = ctx.exchange_create(B)
-    handles = [None] * world
-    dist.all_gather_object(handles, handle)
-    ctx.exchange_connect(ipc_handles=handles)
-    dist.barrier()
+    if multi:
+        handles = [None] * world
+        dist.all_gather_object(handles, handle)
+        ctx.exchange_connect(ipc_handles=handles)
+        dist.barrier()
+    else:
+        ctx.exchange_connect(same_process_ptrs=[_base])
 
     def step_fused():
         for l in range(L):
             r = l % n_res
             ctx.decode_exchange(r, pos, q[r], k[r], v[r], out=out)
 
+    def sync():
+        torch.cuda.synchronize()
+        if multi:
+            dist.barrier()
+            torch.cuda.synchronize()
+
     def timed(step):
-        for _ in range(max(3, args.warmup)):
-            step()
-        torch.cuda.synchronize()
-        dist.barrier()
-        torch.cuda.synchronize()
-        ctx.set_kernel_timing(True)
-        steps = max(3, args.steps)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            step()
-        e1.record()
-        torch.cuda.synchronize()
-        dist.barrier()
-        t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        attn_ms, attn_n = ctx.kernel_time(0)
-        ctx.set_kernel_timing(False)
-        return float(t.item()) / steps, attn_ms / attn_n
+        ms = timed_steps(torch, step, max(3, args.steps), warmup=max(3, args.warmup), sync=sync)
+        if multi:
+            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
 
     # both variants must agree before either is timed
     step_nccl()
@@ -602,22 +701,107 @@ def bench_decode_seq_split(torch, dist, args, rank, world, local_rank, peaks):
     step_fused()
     torch.cuda.synchronize()
     agree = float((out - ref).abs().max().item())
-    nccl_ms, _ = timed(step_nccl)
-    ms_per_step, launch_ms = timed(step_fused)
+    nccl_ms = timed(step_nccl) if use_nccl else None
+    ms_per_step = timed(step_fused)
+    sync()
+    per_kind = instrumented(torch, ctx, step_fused, max(3, args.steps))
     ctx.synchronize()
-    bytes_per_launch = per_layer_bytes
-    achieved = bytes_per_launch / (launch_ms * 1e-3) / 1e9
+    sync()
+    res = {"world": world, "per": per, "n_res": n_res, "ms_per_step": ms_per_step, "nccl_ms": nccl_ms, "agree": agree,
+           "launch_ms": per_kind[0][0], "merge_ms_per_step": per_kind[2][0] * per_kind[2][1],
+           "bytes_per_launch": per_layer_bytes, "exchange_bytes": B * cfg.n_heads * (cfg.head_dim + 2) * 4,
+           "split_count": ctx.last_split_count}
+    ctx.close()
+    del q, k, v
+    torch.cuda.empty_cache()
+    return res
+
+
+def bench_decode_seq_split(torch, dist, args, rank, world, local_rank, peaks):
+    """Qwen2.5-14B-shaped long-context decode (configs[4]): T=131072, B=16, the KV sequence split into one
+    contiguous slab per rank; partial (o, m, l) exchanged by the decode kernel itself (peer stores + flags) or
+    all-gathered with NCCL, merged on every rank. Strong scaling: the work is fixed, so the N = 1 point (the whole
+    sequence on one GPU) is measured in the same run on rank 0 as the anchor of the efficiency figure."""
+    B, L = 16, 48
+    n1 = None
+    if world > 1:
+        if rank == 0:
+            n1 = seq_split_run(torch, None, args, 1, 0, local_rank, peaks, use_nccl=False)
+        dist.barrier()
+        torch.cuda.synchronize()
+    r = seq_split_run(torch, dist, args, world, rank, local_rank, peaks, use_nccl=True)
+    if world == 1:
+        n1 = r
+    tok = B / (r["ms_per_step"] * 1e-3)
+    per_gpu = hbm_roofline(peaks, r["bytes_per_launch"], r["launch_ms"], bytes_per_launch=r["bytes_per_launch"],
+                           avg_launch_ms=r["launch_ms"],
+                           step_frac=L * r["bytes_per_launch"] / (r["ms_per_step"] * 1e-3) / 1e9 / peaks["hbm_gbs"])
     res = {"workload": f"Qwen2.5-14B-shaped decode (configs[4]): 48 layers, 40 q / 8 kv heads, T=131072, B=16, bf16 cache, "
-                       f"KV sequence split over {world} GPUs ({per} positions each), {n_res} resident layers cycled",
-           "tokens_per_s": B / (ms_per_step * 1e-3), "ms_per_step": ms_per_step,
+                       f"KV sequence split over {world} GPU(s) ({r['per']} positions each), {r['n_res']} resident layers cycled",
+           "tokens_per_s": tok, "ms_per_step": r["ms_per_step"], "split_count": r["split_count"],
            "exchange": "fused: the decode kernel stores (o/l, m, l) into every rank's receive buffer over NVLink and "
                        "raises a flag; a bounded-wait kernel merges",
-           "tokens_per_s_nccl_all_gather": B / (nccl_ms * 1e-3), "ms_per_step_nccl_all_gather": nccl_ms,
-           "max_abs_diff_fused_vs_nccl": agree,
-           "per_gpu_roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                "frac": achieved / peaks["hbm_gbs"], "bytes_per_launch": bytes_per_launch,
-                                "avg_launch_ms": launch_ms},
-           "exchange_bytes_per_layer_per_gpu": B * cfg.n_heads * (cfg.head_dim + 2) * 4}
+           "tokens_per_s_nccl_all_gather": B / (r["nccl_ms"] * 1e-3), "ms_per_step_nccl_all_gather": r["nccl_ms"],
+           "max_abs_diff_fused_vs_nccl": r["agree"], "per_gpu_roofline": per_gpu,
+           "exchange_bytes_per_layer_per_gpu": r["exchange_bytes"]}
+    scaling = None
+    if rank == 0 and n1 is not None:
+        tok1 = B / (n1["ms_per_step"] * 1e-3)
+        scaling = {"n": world, "tokens_per_s": tok, "tokens_per_s_n1": tok1, "efficiency_vs_n1": tok / (world * tok1),
+                   "per_gpu_frac": per_gpu["frac"], "per_gpu_step_frac": per_gpu["step_frac"],
+                   "merge_ms_per_step": r["merge_ms_per_step"], "scaling": "strong (fixed T=131072, B=16)",
+                   "n1_anchor": "measured in this run on rank 0 with the whole sequence on one GPU"}
+    return res, scaling
+
+
+def bench_decode_head_shard(torch, dist, args, rank, world, local_rank, peaks, B):
+    """configs[2] at a large batch with the KV heads split over the ranks (no collective: every rank's output is
+    its own slice of q_dim). With more ranks than KV heads (8 > 4) the batch is split as well."""
+    import gguf_runner_b200 as g
+    from gguf_runner_b200 import presets, sharding
+    T, L = 32768, 48
+    base = presets.qwen3_30b_a3b_decode(n_layers=1, seq_len=T, max_batch=B, device=local_rank)
+    head_groups = min(world, base.n_kv_heads)
+    batch_groups = world // head_groups
+    hr, br = rank % head_groups, rank // head_groups
+    Bl = B // batch_groups
+    per_layer_bytes = Bl * T * (base.n_kv_heads // head_groups) * 128 * 2 * 2
+    n_res = int(max(1, min(L, (60 << 30) // per_layer_bytes)))
+    import dataclasses
+    cfg, _qs, _ks = sharding.head_shard_config(dataclasses.replace(base, n_layers=n_res, max_batch=Bl), hr, head_groups)
+    ctx = g.AttnContext(cfg)
+    fill_cache_random(torch, ctx, 1103 + rank)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(2103 + rank)
+    q = torch.randn(n_res, Bl, cfg.q_dim, generator=gen, device="cuda")
+    k = torch.randn(n_res, Bl, cfg.kv_dim, generator=gen, device="cuda")
+    v = torch.randn(n_res, Bl, cfg.kv_dim, generator=gen, device="cuda")
+    out = torch.empty(n_res, Bl, cfg.q_dim, device="cuda")
+    pos = [T - 1] * Bl
+
+    def step():
+        for l in range(L):
+            r = l % n_res
+            ctx.decode(r, pos, q[r], k[r], v[r], out=out[r])
+
+    def sync():
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    ms = timed_steps(torch, step, max(3, args.steps), warmup=max(3, args.warmup), sync=sync)
+    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    per_kind = instrumented(torch, ctx, step, max(3, args.steps))
+    sync()
+    res = {"workload": f"Qwen3-30B-A3B-shaped decode (configs[2]) at B={B}, T=32768: KV heads split over {head_groups} rank(s)"
+                       f"{', batch over ' + str(batch_groups) if batch_groups > 1 else ''}; {cfg.n_kv_heads} kv head(s) and "
+                       f"{Bl} sequences per GPU, {n_res} resident layers cycled, no collective",
+           "tokens_per_s": B / (ms * 1e-3), "ms_per_step": ms,
+           "per_gpu_roofline": hbm_roofline(peaks, per_layer_bytes, per_kind[0][0], bytes_per_launch=per_layer_bytes,
+                                            avg_launch_ms=per_kind[0][0],
+                                            step_frac=L * per_layer_bytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"])}
     ctx.close()
     torch.cuda.empty_cache()
     return res
@@ -642,9 +826,19 @@ def run_small_case(args):
         for _ in range(3):
             for l in range(2):
                 out = ctx.prefill(l, 0, q, k, v)
-    elif args.case == "decode_small":
-        # two Qwen3-30B-A3B-shaped layers: T=32768, B=8, bf16 cache (1 GB on the device)
-        B, T = 8, 32768
+    elif args.case == "prefill_gemma_small":
+        # two Gemma-3-4B-shaped layers (one window, one global): 8192 positions in 2048-token chunks (0.1 GB)
+        cfg = presets.gemma3_4b_prefill(n_layers=6, seq_len=8192)
+        ctx = g.AttnContext(cfg)
+        q = torch.randn(2048, cfg.q_dim, generator=gen, device="cuda").to(torch.bfloat16)
+        k = torch.randn(2048, cfg.kv_dim, generator=gen, device="cuda").to(torch.bfloat16)
+        v = torch.randn(2048, cfg.kv_dim, generator=gen, device="cuda").to(torch.bfloat16)
+        for c0 in range(0, 8192, 2048):
+            for l in (4, 5):
+                out = ctx.prefill(l, c0, q, k, v)
+    elif args.case in ("decode_small", "decode_b1_small"):
+        # two Qwen3-30B-A3B-shaped layers: T=32768, B=8 (1 GB on the device) or B=1 (0.13 GB)
+        B, T = (8 if args.case == "decode_small" else 1), 32768
         cfg = presets.qwen3_30b_a3b_decode(n_layers=2, seq_len=T, max_batch=B)
         ctx = g.AttnContext(cfg)
         fill_cache_random(torch, ctx, 3)
@@ -654,6 +848,18 @@ def run_small_case(args):
         for _ in range(3):
             for l in range(2):
                 out = ctx.decode(l, [T - 1] * B, q, k, v)
+    elif args.case == "decode_cfg1_small":
+        # the Qwen3-0.6B-shaped decode (f32 cache, T=2048), all 28 layers (0.47 GB on the device)
+        from gguf_runner_b200.binding import KV_F32
+        cfg = presets.qwen3_0p6b_decode(n_layers=28, seq_len=2048, kv_format=KV_F32)
+        ctx = g.AttnContext(cfg)
+        fill_cache_random(torch, ctx, 3)
+        q = torch.randn(1, cfg.q_dim, generator=gen, device="cuda")
+        k = torch.randn(1, cfg.kv_dim, generator=gen, device="cuda")
+        v = torch.randn(1, cfg.kv_dim, generator=gen, device="cuda")
+        for _ in range(2):
+            for l in range(28):
+                out = ctx.decode(l, [2047], q, k, v)
     elif args.case == "decode_turbo_small":
         # two layers of the config-3 decode shape over a TurboQuant cache: T=32768, B=8 (0.25 GB on the device);
         # the cache keeps its zero rows (timing of the tensor-core kernel does not depend on the code values)
@@ -687,26 +893,27 @@ def run_ours(args):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     peaks = measured_peaks()
+    with_cpu = rank == 0 and world == 1 and not args.no_cpu
 
     value, ms_per_step, roofline, e2e, clocks, launches = bench_prefill(torch, dist, args, rank, world, local_rank, peaks)
     extras = {}
     if not args.no_extras:
         if world == 1:
             extras["decode"] = bench_decode_cfg3(torch, args, local_rank, peaks, B=args.decode_batch)
-            if args.all_configs:
-                extras["decode_sweep"] = [bench_decode_cfg3(torch, args, local_rank, peaks, B=b) for b in (1, 32)]
-                extras["prefill_chunked_gemma"] = bench_prefill_gemma(torch, args, local_rank, peaks)
-                extras["decode_small_f32"] = bench_decode_cfg1(torch, args, local_rank, peaks)
-                extras["decode_turboquant"] = bench_decode_turbo(torch, args, local_rank, peaks, B=args.decode_batch)
-        else:
-            extras["decode_seq_split"] = bench_decode_seq_split(torch, dist, args, rank, world, local_rank, peaks)
+            extras["decode_sweep"] = [bench_decode_cfg3(torch, args, local_rank, peaks, B=1),
+                                      bench_decode_cfg3(torch, args, local_rank, peaks, B=32, n_res=12),
+                                      bench_decode_cfg3(torch, args, local_rank, peaks, B=64, n_res=8)]
+            extras["prefill_chunked_gemma"] = bench_prefill_gemma(torch, args, local_rank, peaks)
+            extras["decode_small_f32"] = bench_decode_cfg1(torch, args, local_rank, peaks, with_cpu)
+            extras["decode_turboquant"] = bench_decode_turbo(torch, args, local_rank, peaks, B=args.decode_batch)
+        seq, scaling = bench_decode_seq_split(torch, dist, args, rank, world, local_rank, peaks)
+        extras["decode_seq_split"] = seq
+        extras["decode_scaling"] = scaling
+        if world > 1:
+            extras["decode_head_shard"] = [bench_decode_head_shard(torch, dist, args, rank, world, local_rank, peaks, B=b)
+                                           for b in (32, 64)]
 
-    cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu:
-        one_pass, scale, info, _ora = cpu_prefill_sample(stride=args.cpu_stride)
-        one_pass()
-        t = one_pass()
-        cpu = dict(info, value=S_PREFILL / (t * scale * N_LAYERS_PREFILL), unit="tokens/s")
+    cpu = cpu_prefill_baseline(args.cpu_stride) if with_cpu else None
 
     if rank == 0:
         line = {
@@ -729,12 +936,12 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--no-extras", action="store_true", help="skip the decode extras")
-    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extras", action="store_true", help="headline workload only")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs")
     ap.add_argument("--decode-batch", type=int, default=8)
-    ap.add_argument("--all-configs", action="store_true", help="also run configs[0], configs[2] at B=1/32 and configs[3]")
     ap.add_argument("--cpu-stride", type=int, default=16)
-    ap.add_argument("--case", default=None, help="run a small profiling case (prefill_small, decode_small, decode_turbo_small) and exit")
+    ap.add_argument("--case", default=None, help="run a small profiling case (prefill_small, prefill_gemma_small, decode_small, "
+                                                 "decode_b1_small, decode_cfg1_small, decode_turbo_small) and exit")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

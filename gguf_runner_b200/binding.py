@@ -56,7 +56,7 @@ class _Config(C.Structure):
         ("shard_mode", C.c_int32), ("shard_pos_begin", C.c_int32), ("shard_pos_count", C.c_int32),
         ("n_ranks", C.c_int32), ("rank", C.c_int32),
         ("decode_impl", C.c_int32), ("prefill_impl", C.c_int32), ("max_splits", C.c_int32),
-        ("decode_fusion", C.c_int32),
+        ("decode_fusion", C.c_int32), ("exchange_wait_us", C.c_int32),
     ]
 
 
@@ -73,6 +73,8 @@ EXPORTED_SYMBOLS = [
     "ggr_attn_attention_tokens_static", "ggr_attn_last_split_count",
     "ggr_attn_exchange_create", "ggr_attn_exchange_connect", "ggr_attn_decode_exchange",
     "ggr_attn_exchange_send", "ggr_attn_exchange_receive", "ggr_attn_set_layer_fixups",
+    "ggr_attn_exchange_epoch", "ggr_attn_exchange_resync", "ggr_attn_decode_gated", "ggr_attn_prefill_gated",
+    "ggr_attn_reserve", "ggr_attn_kv_export_turbo", "ggr_attn_kv_import_turbo",
     "ggr_rope_plan_new", "ggr_rope_plan_free", "ggr_rope_plan_append_text", "ggr_rope_plan_append_grid",
     "ggr_rope_plan_len", "ggr_rope_plan_next_text", "ggr_rope_plan_at", "ggr_rope_plan_export",
     "ggr_rope_axis", "ggr_media_plan_validate", "ggr_media_chunk_end", "ggr_gemma_layer_windows",
@@ -131,6 +133,14 @@ def lib() -> C.CDLL:
     L.ggr_attn_exchange_send.argtypes = [vp, i32, vp, i32, vp, vp, vp, i32]
     L.ggr_attn_exchange_receive.argtypes = [vp, i32, vp, i32]
     L.ggr_attn_set_layer_fixups.argtypes = [vp, i32, vp, vp, vp, vp, vp, C.c_float]
+    L.ggr_attn_exchange_epoch.argtypes = [vp]
+    L.ggr_attn_exchange_epoch.restype = i32
+    L.ggr_attn_exchange_resync.argtypes = [vp, i32]
+    L.ggr_attn_decode_gated.argtypes = [vp, i32, vp, i32, vp, vp, vp, vp, i32, vp, i32]
+    L.ggr_attn_prefill_gated.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp, i32, i32, vp, i32]
+    L.ggr_attn_reserve.argtypes = [vp, i32]
+    L.ggr_attn_kv_export_turbo.argtypes = [vp, i32, i32, i32, i32] + [vp] * 8
+    L.ggr_attn_kv_import_turbo.argtypes = [vp, i32, i32, i32, i32] + [vp] * 8
     L.ggr_attn_set_kernel_timing.argtypes = [vp, i32]
     L.ggr_attn_kernel_time.argtypes = [vp, i32, C.POINTER(C.c_double), C.POINTER(i64), i32]
     L.ggr_attn_kv_device_ptrs.argtypes = [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp),
@@ -191,6 +201,7 @@ class AttnConfig:
     prefill_impl: int = IMPL_AUTO
     max_splits: int = 0
     decode_fusion: int = 0
+    exchange_wait_us: int = 0
 
     @property
     def q_dim(self) -> int:
@@ -207,7 +218,8 @@ class AttnConfig:
                      "rope_theta", "rope_theta_swa", "rope_scale_global", "rope_scale_local", "rope_style",
                      "rope_layout", "swa_theta_on_window_layers", "swa_pattern", "scale_mode", "softmax_mode",
                      "kv_format", "image_mode", "device", "shard_mode", "shard_pos_begin", "shard_pos_count",
-                     "n_ranks", "rank", "decode_impl", "prefill_impl", "max_splits", "decode_fusion"):
+                     "n_ranks", "rank", "decode_impl", "prefill_impl", "max_splits", "decode_fusion",
+                     "exchange_wait_us"):
             setattr(c, name, getattr(self, name))
         for i in range(4):
             c.rope_sections[i] = int(self.rope_sections[i])
@@ -215,6 +227,14 @@ class AttnConfig:
         c.n_layer_windows = len(self.layer_windows)
         c.layer_windows = C.cast(windows, C.POINTER(C.c_int32))
         return c, windows
+
+
+class RawCuda:
+    """Lets torch view device memory owned by the library (__cuda_array_interface__), e.g. the cache arrays
+    returned by AttnContext.kv_device_ptrs()."""
+
+    def __init__(self, ptr, nbytes):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
 
 
 def _is_torch(x) -> bool:
@@ -363,6 +383,23 @@ class AttnContext:
         self._check(self._L.ggr_attn_decode(self._h, layer, C.c_void_p(pos.ctypes.data), B, qp, kp, vp, op, kind))
         return out
 
+    def decode_gated(self, layer: int, pos, q, k, v, gate, gate_head_stride: Optional[int] = None, out=None):
+        """decode followed by out *= sigmoid(gate), non-finite -> 0 (src/engine/runtime/inference.rs:3509-3519);
+        gate is f32, head h of batch entry b at gate[(b * n_heads + h) * gate_head_stride]."""
+        pos = np.ascontiguousarray(np.asarray(pos, dtype=np.int32).reshape(-1))
+        B = pos.shape[0]
+        if out is None:
+            out = self._out_like(q, (B, self.config.q_dim))
+        self._follow_torch_stream(q)
+        (qp, kind), (kp, _), (vp, _), (gp, _), (op, _) = _ptr(q), _ptr(k), _ptr(v), _ptr(gate), _ptr(out)
+        self._check(self._L.ggr_attn_decode_gated(self._h, layer, C.c_void_p(pos.ctypes.data), B, qp, kp, vp, gp,
+                                                   gate_head_stride or self.config.head_dim, op, kind))
+        return out
+
+    def reserve(self, B: int):
+        """Pre-allocates all decode scratch for batches of up to B sequences."""
+        self._check(self._L.ggr_attn_reserve(self._h, B))
+
     def decode_partial(self, layer: int, pos, q, k, v, partial=None):
         pos = np.ascontiguousarray(np.asarray(pos, dtype=np.int32).reshape(-1))
         B = pos.shape[0]
@@ -408,6 +445,13 @@ class AttnContext:
         self._check(self._L.ggr_attn_exchange_send(self._h, layer, C.c_void_p(pos.ctypes.data), pos.shape[0], qp, kp, vp,
                                                     kind))
 
+    @property
+    def exchange_epoch(self) -> int:
+        return int(self._L.ggr_attn_exchange_epoch(self._h))
+
+    def exchange_resync(self, epoch: int):
+        self._check(self._L.ggr_attn_exchange_resync(self._h, epoch))
+
     def exchange_receive(self, B: int, like, out=None):
         if out is None:
             out = self._out_like(like, (B, self.config.q_dim))
@@ -442,6 +486,23 @@ class AttnContext:
     def prefill(self, layer: int, base_pos: int, q, k, v, seq: int = 0, out=None):
         """q/k/v: [m, q_dim] / [m, kv_dim], f32, or bf16 (torch.bfloat16 / numpy uint16 bit patterns)."""
         return self._prefill(self._L.ggr_attn_prefill, layer, seq, base_pos, q, k, v, out)
+
+    def prefill_gated(self, layer: int, base_pos: int, q, k, v, gate, gate_head_stride: Optional[int] = None,
+                      seq: int = 0, out=None):
+        """prefill with the output gate of decode_gated; gate has the dtype of q."""
+        m = q.shape[0]
+        if _is_torch(q):
+            import torch
+            in_dtype = DTYPE_BF16 if q.dtype == torch.bfloat16 else DTYPE_F32
+        else:
+            in_dtype = DTYPE_BF16 if q.dtype == np.uint16 else DTYPE_F32
+        if out is None:
+            out = self._out_like(q, (m, self.config.q_dim))
+        self._follow_torch_stream(q)
+        (qp, kind), (kp, _), (vp, _), (gp, _), (op, _) = _ptr(q), _ptr(k), _ptr(v), _ptr(gate), _ptr(out)
+        self._check(self._L.ggr_attn_prefill_gated(self._h, layer, seq, base_pos, m, qp, kp, vp, gp,
+                                                    gate_head_stride or self.config.head_dim, in_dtype, op, kind))
+        return out
 
     def prefill_block(self, layer: int, base_pos: int, q, k, v, seq: int = 0, out=None):
         return self._prefill(self._L.ggr_attn_prefill_block, layer, seq, base_pos, q, k, v, out)
@@ -503,8 +564,9 @@ class AttnContext:
         kd = self.config.kv_dim
         kq = np.empty((nrows, kd), dtype=np.int8)
         vq = np.empty((nrows, kd), dtype=np.int8)
-        ks = np.empty(nrows, dtype=np.float32)
-        vs = np.empty(nrows, dtype=np.float32)
+        scale_shape = (nrows,) if self.config.kv_format == KV_Q8_ROW else (nrows, kd // 32)
+        ks = np.empty(scale_shape, dtype=np.float32)
+        vs = np.empty(scale_shape, dtype=np.float32)
         self._check(self._L.ggr_attn_kv_export(self._h, layer, seq, row0, nrows, C.c_void_p(kq.ctypes.data),
                                                 C.c_void_p(vq.ctypes.data), C.c_void_p(ks.ctypes.data),
                                                 C.c_void_p(vs.ctypes.data)))
@@ -518,6 +580,26 @@ class AttnContext:
         self._check(self._L.ggr_attn_kv_import(self._h, layer, seq, row0, kq.shape[0], C.c_void_p(kq.ctypes.data),
                                                 C.c_void_p(vq.ctypes.data), C.c_void_p(ks.ctypes.data),
                                                 C.c_void_p(vs.ctypes.data)))
+
+
+    _TURBO_SECTIONS = ("k_base", "v_base", "k_sign", "v_sign", "k_scale", "v_scale", "k_rnorm", "v_rnorm")
+
+    def kv_export_turbo(self, layer: int, row0: int, nrows: int, seq: int = 0):
+        """Rows of a TurboQuant cache as the eight sections of the reference's prefill cache
+        (src/app/prefill_cache.rs:16-18)."""
+        kd, H = self.config.kv_dim, self.config.n_kv_heads
+        out = {"k_base": np.empty((nrows, kd // 4), np.uint8), "v_base": np.empty((nrows, kd // 4), np.uint8),
+               "k_sign": np.empty((nrows, kd // 8), np.uint8), "v_sign": np.empty((nrows, kd // 8), np.uint8),
+               "k_scale": np.empty((nrows, H), np.float32), "v_scale": np.empty((nrows, H), np.float32),
+               "k_rnorm": np.empty((nrows, H), np.float32), "v_rnorm": np.empty((nrows, H), np.float32)}
+        self._check(self._L.ggr_attn_kv_export_turbo(self._h, layer, seq, row0, nrows,
+                                                      *[C.c_void_p(out[n].ctypes.data) for n in self._TURBO_SECTIONS]))
+        return out
+
+    def kv_import_turbo(self, layer: int, row0: int, sections, seq: int = 0):
+        arrs = [np.ascontiguousarray(sections[n]) for n in self._TURBO_SECTIONS]
+        self._check(self._L.ggr_attn_kv_import_turbo(self._h, layer, seq, row0, arrs[0].shape[0],
+                                                      *[C.c_void_p(a.ctypes.data) for a in arrs]))
 
 
 class RopePositionPlan:

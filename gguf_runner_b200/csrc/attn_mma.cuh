@@ -276,16 +276,9 @@ __global__ void __launch_bounds__(kMmaWarps * 32) attn_mma_decode_kernel(AttnArg
 
 template <int D, int NST>
 inline int launch_mma_inst(const AttnArgs& a, dim3 grid, size_t smem, int smem_optin, int device, cudaStream_t stream) {
-    static int configured_for = -1;
-    if (configured_for != device) {
-        cudaFuncAttributes fa;
-        cudaError_t e = cudaFuncGetAttributes(&fa, attn_mma_decode_kernel<D, NST>);
-        if (e != cudaSuccess) return (int)e;
-        e = cudaFuncSetAttribute(attn_mma_decode_kernel<D, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 smem_optin - (int)fa.sharedSizeBytes);
-        if (e != cudaSuccess) return (int)e;
-        configured_for = device;
-    }
+    static KernelSmemSetup setup;
+    const cudaError_t se = setup.ensure(attn_mma_decode_kernel<D, NST>, device, smem_optin);
+    if (se != cudaSuccess) return (int)se;
     attn_mma_decode_kernel<D, NST><<<grid, kMmaWarps * 32, smem, stream>>>(a);
     return (int)cudaGetLastError();
 }
@@ -564,16 +557,9 @@ __global__ void __launch_bounds__(kTmaWarps * 32) attn_mma_tma_decode_kernel(con
 template <int D>
 inline int launch_mma_tma_inst(const CUtensorMap& tk, const CUtensorMap& tv, const AttnArgs& a, dim3 grid, size_t smem,
                                int smem_optin, int device, cudaStream_t stream) {
-    static int configured_for = -1;
-    if (configured_for != device) {
-        cudaFuncAttributes fa;
-        cudaError_t e = cudaFuncGetAttributes(&fa, attn_mma_tma_decode_kernel<D>);
-        if (e != cudaSuccess) return (int)e;
-        e = cudaFuncSetAttribute(attn_mma_tma_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 smem_optin - (int)fa.sharedSizeBytes);
-        if (e != cudaSuccess) return (int)e;
-        configured_for = device;
-    }
+    static KernelSmemSetup setup;
+    const cudaError_t se = setup.ensure(attn_mma_tma_decode_kernel<D>, device, smem_optin);
+    if (se != cudaSuccess) return (int)se;
     attn_mma_tma_decode_kernel<D><<<grid, kTmaWarps * 32, smem, stream>>>(tk, tv, a);
     return (int)cudaGetLastError();
 }

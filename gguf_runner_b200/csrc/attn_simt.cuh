@@ -65,6 +65,10 @@ struct AttnArgs {
     int* err;             // raised when a bounded wait runs out (kernels that wait on mbarriers)
     FusedRope fused;
     PeerExchange px;
+    // optional output gate (src/engine/runtime/inference.rs:3509-3519): head h of item i at
+    // gate + (i * Hq + h) * gate_head_stride; final outputs become finite_or_zero(o * sigmoid(gate))
+    const float* gate;
+    int gate_head_stride;
 #ifdef GGR_TC_TRACE
     long long* trace;     // per-CTA phase time stamps (diagnostic builds only)
 #endif
@@ -239,6 +243,13 @@ __device__ __forceinline__ const float* fused_rope_prologue(const AttnArgs& a, i
     return qs;
 }
 
+// sigmoid_mul_inplace + sanitize_finite_inplace of one element (src/engine/kernels/math.rs:399-402, :458-462)
+__device__ __forceinline__ float gated_output(float o, float gate) {
+    const float s = 1.0f / (1.0f + expf(-gate));
+    const float r = o * s;
+    return isfinite(r) ? r : 0.0f;
+}
+
 // Writes one head's merged state: the final output row, a (o / l, m, l)
 // partial for cross-rank merging, or nothing when a later stage will.
 __device__ __forceinline__ void store_final(const AttnArgs& a, int item, int h, int d, float o, float ms, float ls) {
@@ -263,7 +274,9 @@ __device__ __forceinline__ void store_final(const AttnArgs& a, int item, int h, 
             po[D + 1] = ls;
         }
     } else {
-        a.out[((int64_t)item * Hq + h) * D + d] = o * inv;
+        float r = o * inv;
+        if (a.gate) r = gated_output(r, a.gate[((int64_t)item * Hq + h) * a.gate_head_stride + d]);
+        a.out[((int64_t)item * Hq + h) * D + d] = r;
     }
 }
 
@@ -726,7 +739,8 @@ __global__ void __launch_bounds__(kSimtWarps * 32) attn_simt_kernel(AttnArgs a) 
 }
 
 // Merges n_parts partial states [n_parts][items][Hq][D + 2] (o / l, m, l) into out.
-__global__ void combine_partials_kernel(const float* parts, int n_parts, int items, int Hq, int D, float* out) {
+__global__ void combine_partials_kernel(const float* parts, int n_parts, int items, int Hq, int D, float* out,
+                                        const float* gate, int gate_head_stride) {
     const int h = blockIdx.x, item = blockIdx.y;
     const int64_t stride = (int64_t)items * Hq * (D + 2);
     const float* base = parts + ((int64_t)item * Hq + h) * (D + 2);
@@ -740,32 +754,45 @@ __global__ void combine_partials_kernel(const float* parts, int n_parts, int ite
             o += f * base[r * stride + d];
             ls += f;
         }
-        out[((int64_t)item * Hq + h) * D + d] = ls > 0.0f ? o / ls : 0.0f;
+        float r = ls > 0.0f ? o / ls : 0.0f;
+        if (gate) r = gated_output(r, gate[((int64_t)item * Hq + h) * gate_head_stride + d]);
+        out[((int64_t)item * Hq + h) * D + d] = r;
     }
 }
 
 // Merge of the states every rank stored into this rank's receive slots. One lane per CTA first waits
-// (bounded) until all flags carry this step's epoch; the states are read around L1, which may still
-// hold the lines of an earlier step.
+// until all flags carry this step's epoch; the states are read around L1, which may still hold the
+// lines of an earlier step. The wait is bounded twice, by wall time (wait_ns on %globaltimer) and by an
+// iteration count; when it runs out the kernel stores 1 into the error word, writes zeros and returns.
+// A peer may legitimately be one step ahead (it has finished this step and sent the next one into the
+// other parity); a flag further ahead means the ranks' step counters disagree: error word 2, zeros.
 __global__ void combine_exchange_kernel(const float* parts, const int* flags, int epoch, int n_parts, int64_t part_stride,
-                                        int Hq, int D, float* out, int* err) {
+                                        int Hq, int D, float* out, int* err, unsigned long long wait_ns,
+                                        const float* gate, int gate_head_stride) {
     __shared__ int s_ok;
     const int h = blockIdx.x, item = blockIdx.y;
     if (threadIdx.x == 0) {
         int ok = 1;
-        for (int r = 0; r < n_parts; ++r) {
+        unsigned long long t0;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        for (int r = 0; r < n_parts && ok == 1; ++r) {
             int seen = 0;
-            for (uint32_t it = 0; it < (1u << 22); ++it) {
+            for (uint32_t it = 0; it < (1u << 24); ++it) {
                 asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(flags + r) : "memory");
                 if (seen >= epoch) break;
+                unsigned long long now;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                if (now - t0 > wait_ns) break;
                 __nanosleep(100);
             }
             if (seen < epoch) ok = 0;
+            else if (seen > epoch + 1) ok = -1;
         }
         s_ok = ok;
-        if (!ok && err) atomicExch(err, 1);
+        if (ok != 1 && err) atomicExch(err, ok == 0 ? 1 : 2);
     }
     __syncthreads();
+    const bool ok = s_ok == 1;
     const float* base = parts + ((int64_t)item * Hq + h) * (D + 2);
     float ms = -INFINITY;
     for (int r = 0; r < n_parts; ++r) ms = fmaxf(ms, __ldcg(base + r * part_stride + D));
@@ -777,7 +804,9 @@ __global__ void combine_exchange_kernel(const float* parts, const int* flags, in
             o += f * __ldcg(base + r * part_stride + d);
             ls += f;
         }
-        out[((int64_t)item * Hq + h) * D + d] = (s_ok && ls > 0.0f) ? o / ls : 0.0f;
+        float res = (ok && ls > 0.0f) ? o / ls : 0.0f;
+        if (ok && gate) res = gated_output(res, gate[((int64_t)item * Hq + h) * gate_head_stride + d]);
+        out[((int64_t)item * Hq + h) * D + d] = res;
     }
 }
 

@@ -334,16 +334,9 @@ __global__ void __launch_bounds__(kTurboWarps * 32) attn_turbo_kernel(AttnArgs a
 
 template <int D, int GH>
 inline int launch_turbo_inst(const AttnArgs& a, dim3 grid, size_t smem, int smem_optin, int device, cudaStream_t stream) {
-    static int configured_for = -1;
-    if (configured_for != device) {
-        cudaFuncAttributes fa;
-        cudaError_t e = cudaFuncGetAttributes(&fa, attn_turbo_kernel<D, GH>);
-        if (e != cudaSuccess) return (int)e;
-        e = cudaFuncSetAttribute(attn_turbo_kernel<D, GH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 smem_optin - (int)fa.sharedSizeBytes);
-        if (e != cudaSuccess) return (int)e;
-        configured_for = device;
-    }
+    static KernelSmemSetup setup;
+    const cudaError_t se = setup.ensure(attn_turbo_kernel<D, GH>, device, smem_optin);
+    if (se != cudaSuccess) return (int)se;
     attn_turbo_kernel<D, GH><<<grid, kTurboWarps * 32, smem, stream>>>(a);
     return (int)cudaGetLastError();
 }

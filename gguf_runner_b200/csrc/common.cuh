@@ -7,7 +7,38 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+#include <mutex>
+
 namespace ggr {
+
+// Raises a kernel's dynamic shared-memory limit once per device. Contexts are independent and may be
+// driven from different host threads, so the bookkeeping is one atomic bit per device ordinal with a
+// mutex around the slow path. Each launch helper keeps one (function-local static) per kernel instance.
+struct KernelSmemSetup {
+    std::atomic<uint64_t> done{0};
+    std::mutex mu;
+
+    // bytes < 0 selects the device's opt-in maximum minus the kernel's static shared memory
+    template <typename K>
+    cudaError_t ensure(K kernel, int device, int smem_optin, int bytes = -1) {
+        const bool tracked = device >= 0 && device < 64;
+        if (tracked && (done.load(std::memory_order_acquire) >> device) & 1ull) return cudaSuccess;
+        std::lock_guard<std::mutex> lock(mu);
+        if (tracked && (done.load(std::memory_order_relaxed) >> device) & 1ull) return cudaSuccess;
+        int want = bytes;
+        if (want < 0) {
+            cudaFuncAttributes fa;
+            cudaError_t e = cudaFuncGetAttributes(&fa, kernel);
+            if (e != cudaSuccess) return e;
+            want = smem_optin - (int)fa.sharedSizeBytes;
+        }
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, want);
+        if (e != cudaSuccess) return e;
+        if (tracked) done.fetch_or(1ull << device, std::memory_order_release);
+        return cudaSuccess;
+    }
+};
 
 enum KvFormat : int { KV_F32 = 0, KV_BF16 = 1, KV_Q8_ROW = 2, KV_Q8_BLOCK32 = 3, KV_TURBO = 4 };
 

@@ -51,8 +51,17 @@ struct ggr_attn_ctx {
     unsigned* d_counters = nullptr;
     size_t counters_cap = 0;
     // staging for host-pointer calls
-    unsigned char* d_stage[4] = {nullptr, nullptr, nullptr, nullptr};
-    size_t stage_cap[4] = {0, 0, 0, 0};
+    unsigned char* d_stage[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};  // q, k, v, out, gate
+    size_t stage_cap[5] = {0, 0, 0, 0, 0};
+    float* d_gate_f32 = nullptr;  // f32 image of a bf16 gate for the kernels that take f32 gates
+    size_t gate_f32_cap = 0;
+    // pinned host staging of host-pointer decode calls: q | k | v | gate travel as one copy, the output as one
+    unsigned char* h_pin = nullptr;
+    size_t pin_cap = 0;
+    unsigned char* d_pin_in = nullptr;  // device image of the inbound half
+    size_t pin_in_cap = 0;
+    int reserved_batch = 0;     // decode batch the scratch is reserved for (0 = grow on demand)
+    int reserved_splits = 0;    // split-KV factor the reserved partial-state scratch holds per item
     std::string err;
     int64_t launches = 0;
     int last_splits = 0;  // split-KV factor of the most recent attention launch
@@ -86,6 +95,7 @@ struct ggr_attn_ctx {
     int x_max_b = 0;
     int x_epoch = 0;
     bool x_connected = false;
+    unsigned long long x_wait_ns = 1000000000ull;
     unsigned* d_done = nullptr;
     // copy streams and events of the pipelined host-buffer prefill
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
@@ -109,6 +119,17 @@ long long* g_tc_trace = nullptr;
 int fail(ggr_attn_ctx* c, int status, const std::string& msg) {
     if (c) c->err = msg;
     return status;
+}
+
+// maps the error word the kernels raise (1 = a bounded wait ran out, 2 = a peer's flag is ahead of this step)
+int take_device_error(ggr_attn_ctx* c, const char* what) {
+    if (!c->h_err || !*c->h_err) return GGR_OK;
+    const int code = *c->h_err;
+    *c->h_err = 0;
+    if (code == 2)
+        return fail(c, GGR_ERR_COMM, "a peer is more than one step ahead of this rank: resynchronise the exchange "
+                                     "(ggr_attn_exchange_resync)");
+    return fail(c, GGR_ERR_TIMEOUT, what);
 }
 
 #define CUDA_TRY(c, expr)                                                                          \
@@ -136,8 +157,10 @@ int elem_bytes_of(int fmt) { return fmt == GGR_KV_F32 ? 4 : (fmt == GGR_KV_BF16 
 template <typename T>
 int ensure(ggr_attn_ctx* c, T** ptr, size_t* cap, size_t need_elems) {
     if (need_elems <= *cap) return GGR_OK;
-    // earlier launches may still use the old buffer
+    // earlier launches and copies may still use the old buffer
     CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    if (c->copy_in) CUDA_TRY(c, cudaStreamSynchronize(c->copy_in));
+    if (c->copy_out) CUDA_TRY(c, cudaStreamSynchronize(c->copy_out));
     if (*ptr) cudaFree(*ptr);
     *ptr = nullptr;
     *cap = 0;
@@ -401,14 +424,8 @@ SimtPlan simt_plan(const ggr_attn_ctx* c) {
 
 template <int FMT, int GH, int NST>
 int launch_simt_inst(ggr_attn_ctx* c, const AttnArgs& a, dim3 grid, int nw, size_t smem) {
-    static int configured_for = -1;  // device ordinal the attribute was set on
-    if (configured_for != c->cfg.device) {
-        cudaFuncAttributes fa;
-        CUDA_TRY(c, cudaFuncGetAttributes(&fa, attn_simt_kernel<FMT, GH, NST>));
-        CUDA_TRY(c, cudaFuncSetAttribute(attn_simt_kernel<FMT, GH, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         c->smem_optin - (int)fa.sharedSizeBytes));
-        configured_for = c->cfg.device;
-    }
+    static KernelSmemSetup setup;
+    CUDA_TRY(c, setup.ensure(attn_simt_kernel<FMT, GH, NST>, c->cfg.device, c->smem_optin));
     {
         LaunchTimer t(c, 0);
         attn_simt_kernel<FMT, GH, NST><<<grid, nw * 32, smem, c->stream>>>(a);
@@ -482,6 +499,45 @@ bool use_mma_decode(const ggr_attn_ctx* c) {
     return can && c->G >= 3;
 }
 
+// Kernel family and launch geometry of a decode / generic attention launch.
+struct DecodePlan {
+    bool mma, tma;
+    SimtPlan p;
+    size_t smem;
+    int ctas_per_sm, min_keys;
+    double cta_rate;
+};
+
+DecodePlan decode_plan(const ggr_attn_ctx* c, bool allow_mma) {
+    DecodePlan d{};
+    d.mma = allow_mma && use_mma_decode(c);
+    d.tma = d.mma && c->have_tmaps16 && c->cfg.decode_impl != GGR_IMPL_MMA;
+    d.p = simt_plan(c);
+    d.smem = d.p.smem;
+    d.ctas_per_sm = d.p.ctas_per_sm;
+    d.min_keys = d.p.nw * kSimtTK * 2;
+    if (d.mma) {
+        MmaPlan mp = d.tma ? mma_tma_plan(c->D, c->smem_optin) : mma_plan(c->D, c->smem_optin);
+        d.smem = mp.smem;
+        d.ctas_per_sm = mp.ctas_per_sm;
+        d.min_keys = mp.min_keys;
+    }
+    d.cta_rate = d.tma ? 65e9 : 40e9;
+    return d;
+}
+
+int plan_splits(const ggr_attn_ctx* c, const DecodePlan& d, int n_items, int t_max, int max_splits) {
+    return choose_splits((int64_t)c->kv.Hkv * n_items, (int64_t)c->sm_count * d.ctas_per_sm, t_max, d.min_keys, max_splits,
+                         2.0 * c->D * c->kv.elem_bytes, d.cta_rate);
+}
+
+// Output gate of a call (src/engine/runtime/inference.rs:3509-3519); p == nullptr = none.
+struct GateSpec {
+    const void* p;
+    int head_stride;
+    int bf16;
+};
+
 // Attention over the cache for `items` (already rotated q at q_dev).
 // When `raw` is given (decode), q_dev is scratch for the rotated queries: the kernels rotate q and
 // append the k / v row themselves if the fusion scratch fits in shared memory, otherwise the
@@ -494,7 +550,7 @@ struct RawDecodeInputs {
 
 int launch_attention(ggr_attn_ctx* c, int layer, const Items& items, int t_max, const float* q_dev, float* out_dev,
                      float* partial_dev, bool allow_mma, const RawDecodeInputs* raw = nullptr,
-                     const PeerExchange* px = nullptr) {
+                     const PeerExchange* px = nullptr, const GateSpec* gate = nullptr) {
     AttnArgs a{};
     a.kv = c->kv;
     a.items = items;
@@ -507,6 +563,10 @@ int launch_attention(ggr_attn_ctx* c, int layer, const Items& items, int t_max, 
     a.shard_count = c->shard_count;
     if (px) a.px = *px;
     a.err = c->d_err;
+    if (gate && gate->p) {
+        a.gate = static_cast<const float*>(gate->p);  // callers hand f32 gates to this path
+        a.gate_head_stride = gate->head_stride;
+    }
 
     if (c->kv.fmt == KV_TURBO) {
         // TurboQuant cache: rope + quantising append as separate launches, then the CUDA-core attention kernel.
@@ -574,18 +634,10 @@ int launch_attention(ggr_attn_ctx* c, int layer, const Items& items, int t_max, 
         return GGR_OK;
     }
 
-    const bool mma = allow_mma && use_mma_decode(c);
-    const bool tma = mma && c->have_tmaps16 && c->cfg.decode_impl != GGR_IMPL_MMA;
-    SimtPlan p = simt_plan(c);
-    size_t smem = p.smem;
-    int ctas_per_sm = p.ctas_per_sm;
-    int min_keys = p.nw * kSimtTK * 2;
-    if (mma) {
-        MmaPlan mp = tma ? mma_tma_plan(c->D, c->smem_optin) : mma_plan(c->D, c->smem_optin);
-        smem = mp.smem;
-        ctas_per_sm = mp.ctas_per_sm;
-        min_keys = mp.min_keys;
-    }
+    const DecodePlan dp = decode_plan(c, allow_mma);
+    const bool mma = dp.mma, tma = dp.tma;
+    SimtPlan p = dp.p;
+    size_t smem = dp.smem;
     a.stage_bytes = p.stage_bytes;
     a.err = c->d_err;
     if (raw) {
@@ -608,10 +660,16 @@ int launch_attention(ggr_attn_ctx* c, int layer, const Items& items, int t_max, 
         }
     }
 
-    const double bytes_per_key = 2.0 * c->D * c->kv.elem_bytes;
-    const double cta_rate = tma ? 65e9 : 40e9;
-    int n_split = choose_splits((int64_t)c->kv.Hkv * items.n, (int64_t)c->sm_count * ctas_per_sm, t_max, min_keys,
-                                c->cfg.max_splits, bytes_per_key, cta_rate);
+    int n_split = plan_splits(c, dp, items.n, t_max, c->cfg.max_splits);
+    {
+        // with a reservation in place the split count never outgrows the reserved scratch (as long as that
+        // holds two splits): the decode loop then neither allocates nor synchronises for memory
+        const size_t per_split = (size_t)items.n * c->kv.Hq * (c->D + 2);
+        if (c->reserved_batch > 0 && per_split * n_split > c->part_cap) {
+            const int fit = (int)std::min<size_t>(512, c->part_cap / per_split);
+            if (fit >= 2) n_split = std::min(n_split, fit);
+        }
+    }
     a.n_split = n_split;
     c->last_splits = n_split;
     // the split merge stages one weight per (head, split) in shared memory
@@ -678,8 +736,64 @@ int t_max_of(const ggr_attn_ctx* c, int layer, const int32_t* pos, int n) {
     return t;
 }
 
+// Pinned host staging of host-pointer decode calls: the inbound arrays are packed into one pinned buffer and
+// travel in one copy (three pageable copies cost three driver round trips), the result comes back through
+// the same buffer. Layout: [in_bytes inbound][out_bytes outbound].
+int ensure_pinned(ggr_attn_ctx* c, size_t in_bytes, size_t out_bytes) {
+    const size_t need = in_bytes + out_bytes;
+    if (need > c->pin_cap) {
+        CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+        if (c->h_pin) cudaFreeHost(c->h_pin);
+        c->h_pin = nullptr;
+        c->pin_cap = 0;
+        const size_t want = std::max(need, (size_t)4096);
+        if (cudaHostAlloc((void**)&c->h_pin, want, cudaHostAllocDefault) != cudaSuccess) {
+            cudaGetLastError();
+            return fail(c, GGR_ERR_ALLOC, "unable to allocate pinned staging memory");
+        }
+        c->pin_cap = want;
+    }
+    return ensure(c, &c->d_pin_in, &c->pin_in_cap, in_bytes);
+}
+
+// Sizes of the decode scratch for batches of up to B items (see ggr_attn_reserve).
+int reserve_decode(ggr_attn_ctx* c, int B) {
+    int rc;
+    if ((rc = ensure(c, &c->d_qrot, &c->qrot_cap, (size_t)B * c->q_dim))) return rc;
+    int splits = 1;
+    if (c->kv.fmt == KV_TURBO) {
+        splits = c->cfg.max_splits > 0 ? std::min(64, c->cfg.max_splits) : 64;
+        if ((rc = ensure(c, &c->d_krot, &c->krot_cap, (size_t)B * c->kv_dim))) return rc;
+    } else {
+        // the split count is not monotone in the context length: take the largest over a sweep of lengths
+        const DecodePlan dp = decode_plan(c, true);
+        const int chunk = std::min(B, kMaxArgItems);
+        for (int t = c->shard_count; t >= 1; t = t * 3 / 4) {
+            splits = std::max(splits, plan_splits(c, dp, chunk, t, c->cfg.max_splits));
+            if (t == 1) break;
+        }
+    }
+    const int chunk = std::min(B, kMaxArgItems);
+    if (splits > 1) {
+        if ((rc = ensure(c, &c->d_part, &c->part_cap, (size_t)chunk * c->kv.Hq * splits * (c->D + 2)))) return rc;
+        const size_t before = c->counters_cap;
+        if ((rc = ensure(c, &c->d_counters, &c->counters_cap, (size_t)chunk * c->kv.Hkv))) return rc;
+        if (c->counters_cap != before)
+            CUDA_TRY(c, cudaMemsetAsync(c->d_counters, 0, c->counters_cap * sizeof(unsigned), c->stream));
+    }
+    // host-pointer calls: q | k | v | gate inbound (a packed gate spans up to 2 * q_dim per token), out or partial outbound
+    const size_t in_bytes = ((size_t)B * (c->q_dim + 2 * c->kv_dim) + (size_t)B * 2 * c->q_dim) * sizeof(float);
+    const size_t out_bytes = (size_t)B * c->kv.Hq * (c->D + 2) * sizeof(float);
+    if ((rc = ensure_pinned(c, in_bytes, out_bytes))) return rc;
+    if ((rc = ensure(c, &c->d_stage[3], &c->stage_cap[3], out_bytes))) return rc;
+    c->reserved_batch = B;
+    c->reserved_splits = splits;
+    return GGR_OK;
+}
+
 int decode_common(ggr_attn_ctx* c, int layer, const int32_t* pos, int B, const float* q, const float* k,
-                  const float* v, float* out, float* partial, int ptr_kind) {
+                  const float* v, float* out, float* partial, int ptr_kind, const float* gate = nullptr,
+                  int gate_head_stride = 0) {
     if (!c) return GGR_ERR_INVALID;
     DeviceGuard guard(c->cfg.device);
     int rc = check_layer(c, layer);
@@ -690,16 +804,30 @@ int decode_common(ggr_attn_ctx* c, int layer, const int32_t* pos, int B, const f
         if (pos[b] < 0 || pos[b] >= c->cfg.seq_len) return fail(c, GGR_ERR_RANGE, "position outside the cache");
     if (c->cfg.shard_mode != GGR_SHARD_NONE && !partial)
         return fail(c, GGR_ERR_INVALID, "a KV-sequence shard produces partial states: call ggr_attn_decode_partial");
+    if (gate && (partial || gate_head_stride < c->D))
+        return fail(c, GGR_ERR_INVALID, "the output gate needs a final output and a head stride of at least head_dim");
 
     const size_t qb = (size_t)B * c->q_dim * sizeof(float), kb = (size_t)B * c->kv_dim * sizeof(float);
-    const void *dq, *dk, *dv;
-    if ((rc = stage_in(c, 0, q, qb, ptr_kind, &dq))) return rc;
-    if ((rc = stage_in(c, 1, k, kb, ptr_kind, &dk))) return rc;
-    if ((rc = stage_in(c, 2, v, kb, ptr_kind, &dv))) return rc;
+    // elements from the gate pointer to the end of the last head's row
+    const size_t gate_elems = gate ? ((size_t)B * c->kv.Hq - 1) * gate_head_stride + c->D : 0;
+    const size_t gb = gate_elems * sizeof(float);
     const size_t out_elems = partial ? (size_t)B * c->kv.Hq * (c->D + 2) : (size_t)B * c->q_dim;
+    const void *dq = q, *dk = k, *dv = v;
+    const float* dgate = gate;
     float* dout = partial ? partial : out;
     if (ptr_kind == GGR_PTR_HOST) {
+        const size_t in_bytes = qb + 2 * kb + gb;
+        if ((rc = ensure_pinned(c, in_bytes, out_elems * sizeof(float)))) return rc;
         if ((rc = ensure(c, &c->d_stage[3], &c->stage_cap[3], out_elems * sizeof(float)))) return rc;
+        std::memcpy(c->h_pin, q, qb);
+        std::memcpy(c->h_pin + qb, k, kb);
+        std::memcpy(c->h_pin + qb + kb, v, kb);
+        if (gate) std::memcpy(c->h_pin + qb + 2 * kb, gate, gb);
+        CUDA_TRY(c, cudaMemcpyAsync(c->d_pin_in, c->h_pin, in_bytes, cudaMemcpyHostToDevice, c->stream));
+        dq = c->d_pin_in;
+        dk = c->d_pin_in + qb;
+        dv = c->d_pin_in + qb + kb;
+        if (gate) dgate = reinterpret_cast<const float*>(c->d_pin_in + qb + 2 * kb);
         dout = reinterpret_cast<float*>(c->d_stage[3]);
     }
     if ((rc = ensure(c, &c->d_qrot, &c->qrot_cap, (size_t)B * c->q_dim))) return rc;
@@ -721,13 +849,15 @@ int decode_common(ggr_attn_ctx* c, int layer, const int32_t* pos, int B, const f
         float* oc = partial ? nullptr : dout + (size_t)b0 * c->q_dim;
         float* pc = partial ? dout + (size_t)b0 * c->kv.Hq * (c->D + 2) : nullptr;
         const RawDecodeInputs raw{qc, kc, vc};
-        rc = launch_attention(c, layer, it, t_max, qr, oc, pc, true, &raw);
+        GateSpec gs{dgate ? dgate + (size_t)b0 * c->kv.Hq * gate_head_stride : nullptr, gate_head_stride, 0};
+        rc = launch_attention(c, layer, it, t_max, qr, oc, pc, true, &raw, nullptr, &gs);
         if (rc) return rc;
     }
     if (ptr_kind == GGR_PTR_HOST) {
-        CUDA_TRY(c, cudaMemcpyAsync(partial ? partial : out, dout, out_elems * sizeof(float), cudaMemcpyDeviceToHost,
-                                    c->stream));
+        unsigned char* h_out = c->h_pin + (c->pin_cap - out_elems * sizeof(float));
+        CUDA_TRY(c, cudaMemcpyAsync(h_out, dout, out_elems * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
         CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+        std::memcpy(partial ? partial : out, h_out, out_elems * sizeof(float));
         if (c->h_err && *c->h_err) {
             *c->h_err = 0;
             return fail(c, GGR_ERR_TIMEOUT, "a bounded wait inside the decode kernel ran out");
@@ -736,8 +866,14 @@ int decode_common(ggr_attn_ctx* c, int layer, const int32_t* pos, int B, const f
     return GGR_OK;
 }
 
+__global__ void gate_to_f32_kernel(const __nv_bfloat16* src, float* dst, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        dst[i] = __bfloat162float(src[i]);
+}
+
 int prefill_common(ggr_attn_ctx* c, int layer, int seq, int base_pos, int m, const void* q, const void* k,
-                   const void* v, int in_dtype, float* out, int ptr_kind, bool block_mode) {
+                   const void* v, int in_dtype, float* out, int ptr_kind, bool block_mode, const void* gate = nullptr,
+                   int gate_head_stride = 0) {
     if (!c) return GGR_ERR_INVALID;
     DeviceGuard guard(c->cfg.device);
     int rc = check_layer(c, layer);
@@ -759,11 +895,19 @@ int prefill_common(ggr_attn_ctx* c, int layer, int seq, int base_pos, int m, con
                 return fail(c, GGR_ERR_INVALID, "staged prefill must cover whole image blocks");
         }
     }
+    if (gate && gate_head_stride < c->D) return fail(c, GGR_ERR_INVALID, "the gate's head stride must be at least head_dim");
     const size_t es = in_dtype == GGR_DTYPE_BF16 ? 2 : 4;
     const bool host = ptr_kind == GGR_PTR_HOST;
     const unsigned char *dq = static_cast<const unsigned char*>(q), *dk = static_cast<const unsigned char*>(k),
                         *dv = static_cast<const unsigned char*>(v);
+    const unsigned char* dgate = static_cast<const unsigned char*>(gate);
+    const size_t gate_row = (size_t)c->kv.Hq * gate_head_stride;                     // elements per token
+    const size_t gate_elems = gate ? ((size_t)m * c->kv.Hq - 1) * gate_head_stride + c->D : 0;
     float* dout = out;
+    if (host && gate) {
+        if ((rc = ensure(c, &c->d_stage[4], &c->stage_cap[4], gate_elems * es))) return rc;
+        dgate = c->d_stage[4];
+    }
     if (host) {
         if ((rc = ensure(c, &c->d_stage[0], &c->stage_cap[0], (size_t)m * c->q_dim * es))) return rc;
         if ((rc = ensure(c, &c->d_stage[1], &c->stage_cap[1], (size_t)m * c->kv_dim * es))) return rc;
@@ -781,6 +925,9 @@ int prefill_common(ggr_attn_ctx* c, int layer, int seq, int base_pos, int m, con
         return fail(c, GGR_ERR_UNSUPPORTED, "the tensor-core prefill kernels need a bf16 cache and head_dim 64, 128 or 256");
     if ((rc = ensure(c, &c->d_qrot, &c->qrot_cap, tc ? (size_t)1 : (size_t)m * c->q_dim))) return rc;
     if (tc && (rc = ensure(c, &c->d_qrot_h, &c->qrot_h_cap, (size_t)m * c->q_dim))) return rc;
+    // the CUDA-core kernels take f32 gates: a bf16 gate is widened once the rows are on the device
+    const bool widen_gate = gate && !tc && in_dtype == GGR_DTYPE_BF16;
+    if (widen_gate && (rc = ensure(c, &c->d_gate_f32, &c->gate_f32_cap, gate_elems))) return rc;
 
     // rope + append of rows [i0, i0 + n): causality is enforced by the mask, not by write order
     auto append_rows = [&](int i0, int n) -> int {
@@ -820,6 +967,11 @@ int prefill_common(ggr_attn_ctx* c, int layer, int seq, int base_pos, int m, con
             a.score_scale = (c->cfg.scale_mode == GGR_SCALE_SCORE ? c->attn_scale : 1.0f) * kLog2e;
             a.err = c->d_err;
             a.sched = c->d_sched;
+            if (gate) {
+                a.gate = dgate + (size_t)i0 * gate_row * es;
+                a.gate_bf16 = in_dtype == GGR_DTYPE_BF16;
+                a.gate_head_stride = gate_head_stride;
+            }
 #ifdef GGR_TC_TRACE
             a.trace = g_tc_trace;
 #endif
@@ -828,7 +980,7 @@ int prefill_common(ggr_attn_ctx* c, int layer, int seq, int base_pos, int m, con
             {
                 LaunchTimer t(c, 0);
                 r = wide ? launch_prefill_tc_wide(a, c->tmK64, c->tmV64, c->cfg.device, c->stream, &msg)
-                         : launch_prefill_tc(a, c->tmK, c->tmV, c->cfg.device, c->stream, &msg);
+                         : launch_prefill_tc(a, c->tmK, c->tmV, c->cfg.device, c->sm_count, c->stream, &msg);
             }
             if (r) return fail(c, r, msg);
             c->launches++;
@@ -848,8 +1000,21 @@ int prefill_common(ggr_attn_ctx* c, int layer, int seq, int base_pos, int m, con
             int t_max = std::max(1, ve - vs);
             visible_host(c, layer, base_pos + j0, &vs, &ve);
             t_max = std::max(t_max, ve - vs);
+            GateSpec gs{nullptr, gate_head_stride, 0};
+            if (gate) {
+                if (widen_gate) {
+                    const size_t off = (size_t)j0 * gate_row, cnt_e = ((size_t)cnt * c->kv.Hq - 1) * gate_head_stride + c->D;
+                    gate_to_f32_kernel<<<(unsigned)std::min<size_t>(1024, (cnt_e + 255) / 256), 256, 0, c->stream>>>(
+                        reinterpret_cast<const __nv_bfloat16*>(dgate) + off, c->d_gate_f32 + off, cnt_e);
+                    CUDA_TRY(c, cudaGetLastError());
+                    c->launches++;
+                    gs.p = c->d_gate_f32 + off;
+                } else {
+                    gs.p = reinterpret_cast<const float*>(dgate) + (size_t)j0 * gate_row;
+                }
+            }
             int r = launch_attention(c, layer, it, t_max, c->d_qrot + (size_t)j0 * c->q_dim, dout + (size_t)j0 * c->q_dim,
-                                     nullptr, false);
+                                     nullptr, false, nullptr, nullptr, &gs);
             if (r) return r;
         }
         return GGR_OK;
@@ -875,10 +1040,21 @@ int prefill_common(ggr_attn_ctx* c, int layer, int seq, int base_pos, int m, con
                                     cudaMemcpyHostToDevice, c->copy_in));
         CUDA_TRY(c, cudaMemcpyAsync(c->d_stage[2] + ko, static_cast<const unsigned char*>(v) + ko, (size_t)n * c->kv_dim * es,
                                     cudaMemcpyHostToDevice, c->copy_in));
+        if (gate) {
+            const size_t go = (size_t)i0 * gate_row * es;
+            const size_t gn = (((size_t)n * c->kv.Hq - 1) * gate_head_stride + c->D) * es;
+            CUDA_TRY(c, cudaMemcpyAsync(c->d_stage[4] + go, static_cast<const unsigned char*>(gate) + go, gn,
+                                        cudaMemcpyHostToDevice, c->copy_in));
+        }
         CUDA_TRY(c, cudaEventRecord(c->ev_in[p], c->copy_in));
         CUDA_TRY(c, cudaStreamWaitEvent(c->stream, c->ev_in[p], 0));
-        if ((rc = append_rows(i0, n))) return rc;
-        if ((rc = attend_rows(i0, n))) return rc;
+        if ((rc = append_rows(i0, n)) || (rc = attend_rows(i0, n))) {
+            // copies of this and earlier pieces may still be in flight on buffers the next call may free
+            cudaStreamSynchronize(c->copy_in);
+            cudaStreamSynchronize(c->copy_out);
+            cudaStreamSynchronize(c->stream);
+            return rc;
+        }
         CUDA_TRY(c, cudaEventRecord(c->ev_done[p], c->stream));
         CUDA_TRY(c, cudaStreamWaitEvent(c->copy_out, c->ev_done[p], 0));
         CUDA_TRY(c, cudaMemcpyAsync(out + (size_t)i0 * c->q_dim, dout + (size_t)i0 * c->q_dim,
@@ -1083,6 +1259,10 @@ int ggr_attn_create(const ggr_attn_config* cfg, ggr_attn_ctx** out) {
         c->have_tmaps16 = make_tmap_bf16(&c->tmK16, kv.k, (uint64_t)c->kv_dim, (uint64_t)rows, kTmaTK) &&
                           make_tmap_bf16(&c->tmV16, kv.v, (uint64_t)c->kv_dim, (uint64_t)rows, kTmaTK);
     }
+    if (cfg->exchange_wait_us < 0) return cleanup(GGR_ERR_INVALID, "exchange_wait_us must not be negative");
+    c->x_wait_ns = cfg->exchange_wait_us > 0 ? (unsigned long long)cfg->exchange_wait_us * 1000ull : 1000000000ull;
+    // decode scratch for max_batch sequences, so that the token loop never allocates (see ggr_attn_reserve)
+    if (int rr = reserve_decode(c, std::min(cfg->max_batch, kMaxArgItems))) return cleanup(rr, c->err);
     if (cudaStreamSynchronize(c->stream) != cudaSuccess) return cleanup(GGR_ERR_CUDA, "device initialisation failed");
     g_create_err.clear();
     *out = c;
@@ -1112,6 +1292,9 @@ void ggr_attn_destroy(ggr_attn_ctx* c) {
     cudaFree(c->d_part);
     cudaFree(c->d_counters);
     for (auto* p : c->d_stage) cudaFree(p);
+    cudaFree(c->d_gate_f32);
+    cudaFree(c->d_pin_in);
+    if (c->h_pin) cudaFreeHost(c->h_pin);
     for (int r = 0; r < kMaxPeers; ++r)
         if (c->x_opened[r]) cudaIpcCloseMemHandle(c->x_peer[r]);
     cudaFree(c->x_local);
@@ -1150,11 +1333,7 @@ int ggr_attn_synchronize(ggr_attn_ctx* c) {
     if (!c) return GGR_ERR_INVALID;
     DeviceGuard guard(c->cfg.device);
     CUDA_TRY(c, cudaStreamSynchronize(c->stream));
-    if (c->h_err && *c->h_err) {
-        *c->h_err = 0;
-        return fail(c, GGR_ERR_TIMEOUT, "a bounded wait inside a kernel ran out");
-    }
-    return GGR_OK;
+    return take_device_error(c, "a bounded wait inside a kernel ran out");
 }
 
 int ggr_attn_set_kernel_timing(ggr_attn_ctx* c, int32_t enable) {
@@ -1246,6 +1425,19 @@ int ggr_attn_decode(ggr_attn_ctx* c, int32_t layer, const int32_t* pos, int32_t 
     return decode_common(c, layer, pos, B, q, k, v, out, nullptr, ptr_kind);
 }
 
+int ggr_attn_decode_gated(ggr_attn_ctx* c, int32_t layer, const int32_t* pos, int32_t B, const float* q, const float* k,
+                          const float* v, const float* gate, int32_t gate_head_stride, float* out, int32_t ptr_kind) {
+    if (!out || !gate) return fail(c, GGR_ERR_INVALID, "null buffer");
+    return decode_common(c, layer, pos, B, q, k, v, out, nullptr, ptr_kind, gate, gate_head_stride);
+}
+
+int ggr_attn_reserve(ggr_attn_ctx* c, int32_t B) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    if (B <= 0 || B > c->cfg.max_batch) return fail(c, GGR_ERR_RANGE, "batch larger than max_batch");
+    return reserve_decode(c, B);
+}
+
 int ggr_attn_decode_partial(ggr_attn_ctx* c, int32_t layer, const int32_t* pos, int32_t B, const float* q,
                             const float* k, const float* v, float* partial, int32_t ptr_kind) {
     if (!partial) return fail(c, GGR_ERR_INVALID, "null buffer");
@@ -1270,7 +1462,7 @@ int ggr_attn_combine_partials(ggr_attn_ctx* c, const float* parts, int32_t n_par
     {
         LaunchTimer t(c, 2);
         combine_partials_kernel<<<dim3(c->kv.Hq, B), 128, 0, c->stream>>>(reinterpret_cast<const float*>(dp), n_parts,
-                                                                          B, c->kv.Hq, c->D, dout);
+                                                                          B, c->kv.Hq, c->D, dout, nullptr, 0);
     }
     CUDA_TRY(c, cudaGetLastError());
     c->launches++;
@@ -1284,6 +1476,13 @@ int ggr_attn_combine_partials(ggr_attn_ctx* c, const float* parts, int32_t n_par
 int ggr_attn_prefill(ggr_attn_ctx* c, int32_t layer, int32_t seq, int32_t base_pos, int32_t m, const void* q,
                      const void* k, const void* v, int32_t in_dtype, float* out, int32_t ptr_kind) {
     return prefill_common(c, layer, seq, base_pos, m, q, k, v, in_dtype, out, ptr_kind, false);
+}
+
+int ggr_attn_prefill_gated(ggr_attn_ctx* c, int32_t layer, int32_t seq, int32_t base_pos, int32_t m, const void* q,
+                           const void* k, const void* v, const void* gate, int32_t gate_head_stride, int32_t in_dtype,
+                           float* out, int32_t ptr_kind) {
+    if (!gate) return fail(c, GGR_ERR_INVALID, "null buffer");
+    return prefill_common(c, layer, seq, base_pos, m, q, k, v, in_dtype, out, ptr_kind, false, gate, gate_head_stride);
 }
 
 int ggr_attn_prefill_block(ggr_attn_ctx* c, int32_t layer, int32_t seq, int32_t base_pos, int32_t m, const void* q,
@@ -1387,40 +1586,95 @@ static int kv_rows_check(ggr_attn_ctx* c, int layer, int seq, int row0, int nrow
     return GGR_OK;
 }
 
+// One row range of one layer as contiguous spans: {device base, bytes per row} pairs of every array the format keeps.
+struct RowSpans {
+    int n;
+    unsigned char* dev[8];
+    size_t row_bytes[8];
+};
+
+static RowSpans row_spans(const ggr_attn_ctx* c) {
+    RowSpans r{};
+    const KvView& kv = c->kv;
+    const size_t n = (size_t)c->kv_dim;
+    if (kv.fmt == KV_TURBO) {
+        const size_t h = (size_t)kv.Hkv * sizeof(float);
+        unsigned char* dev[8] = {(unsigned char*)kv.k, (unsigned char*)kv.v, kv.k_sign, kv.v_sign, (unsigned char*)kv.ks,
+                                 (unsigned char*)kv.vs, (unsigned char*)kv.k_rn, (unsigned char*)kv.v_rn};
+        const size_t rb[8] = {n / 4, n / 4, n / 8, n / 8, h, h, h, h};
+        r.n = 8;
+        for (int i = 0; i < 8; ++i) r.dev[i] = dev[i], r.row_bytes[i] = rb[i];
+    } else {
+        const size_t sb = (size_t)kv.n_scales * sizeof(float);
+        unsigned char* dev[4] = {(unsigned char*)kv.k, (unsigned char*)kv.v, (unsigned char*)kv.ks, (unsigned char*)kv.vs};
+        const size_t rb[4] = {n, n, sb, sb};
+        r.n = 4;
+        for (int i = 0; i < 4; ++i) r.dev[i] = dev[i], r.row_bytes[i] = rb[i];
+    }
+    return r;
+}
+
+static int move_rows(ggr_attn_ctx* c, int layer, int seq, int row0, int nrows, void* const* host, bool to_host) {
+    int rc = kv_rows_check(c, layer, seq, row0, nrows);
+    if (rc) return rc;
+    const RowSpans sp = row_spans(c);
+    for (int i = 0; i < sp.n; ++i)
+        if (!host[i]) return fail(c, GGR_ERR_INVALID, "null buffer");
+    if (nrows == 0) return GGR_OK;
+    CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    const int64_t r = c->kv.row(seq, layer, row0);
+    for (int i = 0; i < sp.n; ++i) {
+        unsigned char* d = sp.dev[i] + (size_t)r * sp.row_bytes[i];
+        const size_t nb = (size_t)nrows * sp.row_bytes[i];
+        if (to_host)
+            CUDA_TRY(c, cudaMemcpy(host[i], d, nb, cudaMemcpyDeviceToHost));
+        else
+            CUDA_TRY(c, cudaMemcpy(d, host[i], nb, cudaMemcpyHostToDevice));
+    }
+    return GGR_OK;
+}
+
 int ggr_attn_kv_export(ggr_attn_ctx* c, int32_t layer, int32_t seq, int32_t row0, int32_t nrows, int8_t* k_q8,
                        int8_t* v_q8, float* k_scale, float* v_scale) {
     if (!c) return GGR_ERR_INVALID;
     DeviceGuard guard(c->cfg.device);
-    if (c->kv.fmt != KV_Q8_ROW) return fail(c, GGR_ERR_UNSUPPORTED, "export needs the q8 row-scale cache format");
-    int rc = kv_rows_check(c, layer, seq, row0, nrows);
-    if (rc) return rc;
-    if (nrows == 0) return GGR_OK;
-    CUDA_TRY(c, cudaStreamSynchronize(c->stream));
-    const int64_t r = c->kv.row(seq, layer, row0);
-    const size_t nb = (size_t)nrows * c->kv_dim;
-    CUDA_TRY(c, cudaMemcpy(k_q8, (int8_t*)c->kv.k + r * c->kv_dim, nb, cudaMemcpyDeviceToHost));
-    CUDA_TRY(c, cudaMemcpy(v_q8, (int8_t*)c->kv.v + r * c->kv_dim, nb, cudaMemcpyDeviceToHost));
-    CUDA_TRY(c, cudaMemcpy(k_scale, c->kv.ks + r, (size_t)nrows * sizeof(float), cudaMemcpyDeviceToHost));
-    CUDA_TRY(c, cudaMemcpy(v_scale, c->kv.vs + r, (size_t)nrows * sizeof(float), cudaMemcpyDeviceToHost));
-    return GGR_OK;
+    if (c->kv.fmt != KV_Q8_ROW && c->kv.fmt != KV_Q8_BLOCK32)
+        return fail(c, GGR_ERR_UNSUPPORTED, "export needs a q8 cache format (row or block-32 scales)");
+    void* host[4] = {k_q8, v_q8, k_scale, v_scale};
+    return move_rows(c, layer, seq, row0, nrows, host, true);
 }
 
 int ggr_attn_kv_import(ggr_attn_ctx* c, int32_t layer, int32_t seq, int32_t row0, int32_t nrows, const int8_t* k_q8,
                        const int8_t* v_q8, const float* k_scale, const float* v_scale) {
     if (!c) return GGR_ERR_INVALID;
     DeviceGuard guard(c->cfg.device);
-    if (c->kv.fmt != KV_Q8_ROW) return fail(c, GGR_ERR_UNSUPPORTED, "import needs the q8 row-scale cache format");
-    int rc = kv_rows_check(c, layer, seq, row0, nrows);
-    if (rc) return rc;
-    if (nrows == 0) return GGR_OK;
-    CUDA_TRY(c, cudaStreamSynchronize(c->stream));
-    const int64_t r = c->kv.row(seq, layer, row0);
-    const size_t nb = (size_t)nrows * c->kv_dim;
-    CUDA_TRY(c, cudaMemcpy((int8_t*)c->kv.k + r * c->kv_dim, k_q8, nb, cudaMemcpyHostToDevice));
-    CUDA_TRY(c, cudaMemcpy((int8_t*)c->kv.v + r * c->kv_dim, v_q8, nb, cudaMemcpyHostToDevice));
-    CUDA_TRY(c, cudaMemcpy(c->kv.ks + r, k_scale, (size_t)nrows * sizeof(float), cudaMemcpyHostToDevice));
-    CUDA_TRY(c, cudaMemcpy(c->kv.vs + r, v_scale, (size_t)nrows * sizeof(float), cudaMemcpyHostToDevice));
-    return GGR_OK;
+    if (c->kv.fmt != KV_Q8_ROW && c->kv.fmt != KV_Q8_BLOCK32)
+        return fail(c, GGR_ERR_UNSUPPORTED, "import needs a q8 cache format (row or block-32 scales)");
+    void* host[4] = {const_cast<int8_t*>(k_q8), const_cast<int8_t*>(v_q8), const_cast<float*>(k_scale),
+                     const_cast<float*>(v_scale)};
+    return move_rows(c, layer, seq, row0, nrows, host, false);
+}
+
+int ggr_attn_kv_export_turbo(ggr_attn_ctx* c, int32_t layer, int32_t seq, int32_t row0, int32_t nrows, uint8_t* k_base,
+                             uint8_t* v_base, uint8_t* k_sign, uint8_t* v_sign, float* k_scale, float* v_scale,
+                             float* k_rnorm, float* v_rnorm) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    if (c->kv.fmt != KV_TURBO) return fail(c, GGR_ERR_UNSUPPORTED, "the cache is not in the TurboQuant format");
+    void* host[8] = {k_base, v_base, k_sign, v_sign, k_scale, v_scale, k_rnorm, v_rnorm};
+    return move_rows(c, layer, seq, row0, nrows, host, true);
+}
+
+int ggr_attn_kv_import_turbo(ggr_attn_ctx* c, int32_t layer, int32_t seq, int32_t row0, int32_t nrows,
+                             const uint8_t* k_base, const uint8_t* v_base, const uint8_t* k_sign, const uint8_t* v_sign,
+                             const float* k_scale, const float* v_scale, const float* k_rnorm, const float* v_rnorm) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    if (c->kv.fmt != KV_TURBO) return fail(c, GGR_ERR_UNSUPPORTED, "the cache is not in the TurboQuant format");
+    void* host[8] = {const_cast<uint8_t*>(k_base), const_cast<uint8_t*>(v_base), const_cast<uint8_t*>(k_sign),
+                     const_cast<uint8_t*>(v_sign), const_cast<float*>(k_scale), const_cast<float*>(v_scale),
+                     const_cast<float*>(k_rnorm), const_cast<float*>(v_rnorm)};
+    return move_rows(c, layer, seq, row0, nrows, host, false);
 }
 
 int ggr_attn_kv_read_row(ggr_attn_ctx* c, int32_t seq, int32_t layer, int32_t pos, float* k_out, float* v_out) {
@@ -1549,15 +1803,6 @@ extern "C" int ggr_attn_attention_tokens_static(ggr_attn_ctx* c, int32_t layer, 
     const size_t part_cap = (GGR_STATIC_SCRATCH_BYTES - GGR_STATIC_TICKET_BYTES) / sizeof(float);
     const size_t per_split = (size_t)B * c->kv.Hq * (c->D + 2);
     const size_t tickets = (size_t)B * c->kv.Hkv;
-    if (2 * per_split > part_cap || tickets * sizeof(unsigned) > GGR_STATIC_TICKET_BYTES) {
-        char buf[200];
-        snprintf(buf, sizeof buf,
-                 "static scratch too small: B*n_heads*(head_dim+2) = %zu floats per split, the 8 MiB array holds two "
-                 "splits only up to %zu", per_split, part_cap / 2);
-        return fail(c, GGR_ERR_RANGE, buf);
-    }
-    unsigned char* scratch = nullptr;
-    if ((rc = static_scratch(c, &scratch))) return rc;
 
     Items it{};
     it.mode = 0;
@@ -1574,24 +1819,29 @@ extern "C" int ggr_attn_attention_tokens_static(ggr_attn_ctx* c, int32_t layer, 
     a.out = out_dev;
     a.partial_out = nullptr;
     a.shard_count = c->shard_count;
-    const bool mma = use_mma_decode(c);
-    const bool tma = mma && c->have_tmaps16 && c->cfg.decode_impl != GGR_IMPL_MMA;
     a.err = c->d_err;
-    SimtPlan p = simt_plan(c);
-    size_t smem = p.smem;
-    int ctas_per_sm = p.ctas_per_sm, min_keys = p.nw * kSimtTK * 2;
-    if (mma) {
-        MmaPlan mp = tma ? mma_tma_plan(c->D, c->smem_optin) : mma_plan(c->D, c->smem_optin);
-        smem = mp.smem;
-        ctas_per_sm = mp.ctas_per_sm;
-        min_keys = mp.min_keys;
-    }
+    const DecodePlan dp = decode_plan(c, true);
+    const bool mma = dp.mma, tma = dp.tma;
+    SimtPlan p = dp.p;
+    size_t smem = dp.smem;
     a.stage_bytes = p.stage_bytes;
     const int t_max = t_max_of(c, layer, pos, B);
-    int fit = (int)std::min<size_t>(512, part_cap / per_split);  // splits the array can hold
-    if (c->cfg.max_splits > 0) fit = std::min(fit, c->cfg.max_splits);
-    a.n_split = choose_splits((int64_t)c->kv.Hkv * B, (int64_t)c->sm_count * ctas_per_sm, t_max, min_keys, fit,
-                              2.0 * c->D * c->kv.elem_bytes, tma ? 65e9 : 40e9);
+    // The split count comes first: a call that runs unsplit (a short context, or so many (sequence, kv head)
+    // groups that they fill the GPU by themselves) needs no scratch and is never rejected for its size.
+    a.n_split = plan_splits(c, dp, B, t_max, c->cfg.max_splits);
+    if (a.n_split > 1) {
+        const size_t fit = part_cap / per_split;  // splits the array can hold
+        if (fit < 2 || tickets * sizeof(unsigned) > GGR_STATIC_TICKET_BYTES) {
+            char buf[200];
+            snprintf(buf, sizeof buf,
+                     "static scratch too small: B*n_heads*(head_dim+2) = %zu floats per split, the 8 MiB array holds two "
+                     "splits only up to %zu", per_split, part_cap / 2);
+            return fail(c, GGR_ERR_RANGE, buf);
+        }
+        a.n_split = (int)std::min<size_t>((size_t)a.n_split, fit);
+    }
+    unsigned char* scratch = nullptr;
+    if ((rc = static_scratch(c, &scratch))) return rc;
     c->last_splits = a.n_split;
     const size_t merge_smem = a.n_split > 1 ? ((size_t)2 * c->G * a.n_split + 2 * c->G) * sizeof(float) : 0;
     smem = std::max(smem, merge_smem);
@@ -1704,7 +1954,9 @@ int exchange_send(ggr_attn_ctx* c, int layer, const int32_t* pos, int B, const f
     int in_bf16 = 0;
     if ((rc = apply_fixups(c, layer, B, &dq, &dk, &dv, &in_bf16))) return rc;
     const int n = c->cfg.n_ranks, me = c->cfg.rank;
-    const int epoch = ++c->x_epoch;
+    // the step counter moves only once the kernel is in the stream: a send that fails on the host leaves the
+    // ranks' counters in agreement
+    const int epoch = c->x_epoch + 1;
     const size_t slot = x_slot_floats(c), parity_off = (size_t)(epoch & 1) * n * slot;
     PeerExchange px{};
     px.enabled = 1;
@@ -1723,8 +1975,11 @@ int exchange_send(ggr_attn_ctx* c, int layer, const int32_t* pos, int B, const f
     it.n = B;
     for (int i = 0; i < B; ++i) it.pos[i] = pos[i];
     const RawDecodeInputs raw{static_cast<const float*>(dq), static_cast<const float*>(dk), static_cast<const float*>(dv)};
-    return launch_attention(c, layer, it, t_max_of(c, layer, pos, B), c->d_qrot, nullptr, nullptr, true, &raw, &px);
+    rc = launch_attention(c, layer, it, t_max_of(c, layer, pos, B), c->d_qrot, nullptr, nullptr, true, &raw, &px);
+    if (rc == GGR_OK) c->x_epoch = epoch;
+    return rc;
 }
+
 
 // receive half: bounded wait for every rank's flag of the current step, then the merge
 int exchange_receive(ggr_attn_ctx* c, int B, float* out, int ptr_kind) {
@@ -1743,17 +1998,14 @@ int exchange_receive(ggr_attn_ctx* c, int B, float* out, int ptr_kind) {
         LaunchTimer t(c, 2);
         combine_exchange_kernel<<<dim3(c->kv.Hq, B), 128, 0, c->stream>>>(
             reinterpret_cast<const float*>(c->x_local + x_flag_bytes()) + parity_off, reinterpret_cast<const int*>(c->x_local),
-            epoch, n, (int64_t)slot, c->kv.Hq, c->D, dout, c->d_err);
+            epoch, n, (int64_t)slot, c->kv.Hq, c->D, dout, c->d_err, c->x_wait_ns, nullptr, 0);
     }
     CUDA_TRY(c, cudaGetLastError());
     c->launches++;
     if (ptr_kind == GGR_PTR_HOST) {
         CUDA_TRY(c, cudaMemcpyAsync(out, dout, qb, cudaMemcpyDeviceToHost, c->stream));
         CUDA_TRY(c, cudaStreamSynchronize(c->stream));
-        if (c->h_err && *c->h_err) {
-            *c->h_err = 0;
-            return fail(c, GGR_ERR_TIMEOUT, "a peer's partial states did not arrive in time");
-        }
+        return take_device_error(c, "a peer's partial states did not arrive in time");
     }
     return GGR_OK;
 }
@@ -1767,6 +2019,22 @@ extern "C" int ggr_attn_exchange_send(ggr_attn_ctx* c, int32_t layer, const int3
     int rc = exchange_send(c, layer, pos, B, q, k, v, ptr_kind);
     if (rc == GGR_OK && ptr_kind == GGR_PTR_HOST) CUDA_TRY(c, cudaStreamSynchronize(c->stream));
     return rc;
+}
+
+extern "C" int32_t ggr_attn_exchange_epoch(const ggr_attn_ctx* c) { return c ? c->x_epoch : 0; }
+
+extern "C" int ggr_attn_exchange_resync(ggr_attn_ctx* c, int32_t epoch) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    if (!c->x_connected) return fail(c, GGR_ERR_INVALID, "connect the exchange buffers first");
+    if (epoch < c->x_epoch) return fail(c, GGR_ERR_INVALID, "the step counter only moves forward: pass the maximum over all ranks");
+    // nothing of an abandoned step may still be in flight when the counters are realigned
+    CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+    if (c->h_err) *c->h_err = 0;
+    // a send that never completed its groups leaves a partial count behind
+    CUDA_TRY(c, cudaMemset(c->d_done, 0, sizeof(unsigned)));
+    c->x_epoch = epoch;
+    return GGR_OK;
 }
 
 extern "C" int ggr_attn_exchange_receive(ggr_attn_ctx* c, int32_t B, float* out, int32_t ptr_kind) {

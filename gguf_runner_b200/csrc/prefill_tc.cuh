@@ -48,6 +48,10 @@ struct PrefillTcArgs {
     int* err;                // device-visible error word (mapped host memory)
     int* sched;              // [0] work items handed out beyond the first wave, [1] CTAs that have left (persistent kernel)
     int n_items;             // query-tile pairs x query heads
+    // optional output gate (src/engine/runtime/inference.rs:3509-3519), f32 or bf16: head h of row i at
+    // gate + (i * Hq + h) * gate_head_stride elements
+    const void* gate;
+    int gate_bf16, gate_head_stride;
 #ifdef GGR_TC_TRACE
     long long* trace;        // cycle counters of CTA 0 (diagnostic builds only)
 #endif
@@ -65,6 +69,22 @@ struct PrefillTcArgs {
 #define TRACE_ADD(var)
 #define TRACE_MARK()
 #endif
+
+// out = finite_or_zero(o * sigmoid(gate)) on four consecutive head elements (src/engine/kernels/math.rs:399-402)
+__device__ __forceinline__ float4 prefill_gate4(float4 o, const void* gate_row, int gate_bf16, int d) {
+    float g[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        g[i] = gate_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(gate_row)[d + i])
+                         : static_cast<const float*>(gate_row)[d + i];
+    float r[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float v = r[i] * (1.0f / (1.0f + expf(-g[i])));
+        r[i] = isfinite(v) ? v : 0.0f;
+    }
+    return make_float4(r[0], r[1], r[2], r[3]);
+}
 
 constexpr int kTcBM = 128;       // query rows per tile
 constexpr int kTcBN = 128;       // keys per tile
@@ -528,12 +548,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 if (valid) {
                     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
                     float* orow_g = a.out + ((int64_t)qi * Hq + w.h) * D;
+                    const void* grow = nullptr;
+                    if (a.gate)
+                        grow = static_cast<const unsigned char*>(a.gate) +
+                               ((int64_t)qi * Hq + w.h) * a.gate_head_stride * (a.gate_bf16 ? 2 : 4);
 #pragma unroll
                     for (int cidx = 0; cidx < D / 32; ++cidx)
 #pragma unroll
                         for (int i = 0; i < 32; i += 4) {
                             float4 o4 = make_float4(__uint_as_float(orow[cidx][i]) * inv, __uint_as_float(orow[cidx][i + 1]) * inv,
                                                     __uint_as_float(orow[cidx][i + 2]) * inv, __uint_as_float(orow[cidx][i + 3]) * inv);
+                            if (grow) o4 = prefill_gate4(o4, grow, a.gate_bf16, cidx * 32 + i);
                             *reinterpret_cast<float4*>(orow_g + cidx * 32 + i) = o4;
                         }
                 }
@@ -583,19 +608,17 @@ inline size_t prefill_tc_smem(int D) { return (size_t)6 * (D / 64) * 128 * 128 +
 
 template <int D>
 inline int launch_prefill_tc_inst(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                                  const PrefillTcArgs& a, int device, cudaStream_t stream, std::string* msg) {
-    static int configured_for = -1;
+                                  const PrefillTcArgs& a, int device, int sm_count, cudaStream_t stream,
+                                  std::string* msg) {
+    static KernelSmemSetup setup;
     const size_t smem = prefill_tc_smem(D);
-    if (configured_for != device) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    {
+        const cudaError_t e = setup.ensure(prefill_tc_kernel<D>, device, 0, (int)smem);
         if (e != cudaSuccess) {
             *msg = std::string("prefill kernel attribute: ") + cudaGetErrorString(e);
             return 2;
         }
-        configured_for = device;
     }
-    static int sm_count = 0;
-    if (sm_count == 0 && cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) sm_count = 0;
     if (sm_count <= 0 || !a.sched) {
         *msg = "prefill kernel: no SM count or no scheduler counters";
         return 2;
@@ -615,15 +638,15 @@ inline int launch_prefill_tc_inst(const CUtensorMap& tq, const CUtensorMap& tk, 
 
 // tk / tv describe the whole K and V cache arrays as [rows][kv_dim].
 inline int launch_prefill_tc(const PrefillTcArgs& a, const CUtensorMap& tk, const CUtensorMap& tv, int device,
-                             cudaStream_t stream, std::string* msg) {
+                             int sm_count, cudaStream_t stream, std::string* msg) {
     CUtensorMap tq;
     if (!make_tmap_bf16(&tq, a.q, (uint64_t)a.kv.Hq * a.kv.D, (uint64_t)a.m)) {
         *msg = "cuTensorMapEncodeTiled failed for the query tensor";
         return 2;
     }
     switch (a.kv.D) {
-        case 64: return launch_prefill_tc_inst<64>(tq, tk, tv, a, device, stream, msg);
-        case 128: return launch_prefill_tc_inst<128>(tq, tk, tv, a, device, stream, msg);
+        case 64: return launch_prefill_tc_inst<64>(tq, tk, tv, a, device, sm_count, stream, msg);
+        case 128: return launch_prefill_tc_inst<128>(tq, tk, tv, a, device, sm_count, stream, msg);
         default: *msg = "no tensor-core prefill kernel for this head_dim"; return 5;
     }
 }

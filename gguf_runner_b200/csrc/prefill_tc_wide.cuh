@@ -37,7 +37,7 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     constexpr uint32_t O_COL0 = 128;
 
     extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t bars[16];  // 15 used
+    __shared__ __align__(8) uint64_t bars[20];  // 18 used
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
 
@@ -55,8 +55,14 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     auto v_full = [&](int s) { return bar0 + 8u * (5 + s); };
     auto v_empty = [&](int s) { return bar0 + 8u * (7 + s); };
     auto s_full = [&](int b) { return bar0 + 8u * (9 + b); };
-    auto p_half = [&](int half) { return bar0 + 8u * (11 + half); };  // P keys 0-31 / 32-63 stored
-    const uint32_t pv_done = bar0 + 8u * 13, o_final = bar0 + 8u * 14;
+    // P and "P V landed" barriers exist once per score buffer. Q K^T of step n + 1 is issued before P V of step n,
+    // so the softmax warps can be a whole step ahead of the MMA warp: with one barrier for both buffers they could
+    // complete its phase n + 1 before the MMA warp had looked at phase n, and a parity wait cannot tell phase n
+    // from phase n + 2 (the kernel then sat in a wait until its bound ran out). A buffer's own barrier cannot run
+    // ahead: its next phase needs the next-but-one score tile, which the MMA warp issues after it has seen this one.
+    auto p_half = [&](int buf, int half) { return bar0 + 8u * (11 + 2 * buf + half); };  // P keys 0-31 / 32-63 stored
+    auto pv_done = [&](int buf) { return bar0 + 8u * (15 + buf); };
+    const uint32_t o_final = bar0 + 8u * 17;
 
     const int Hq = a.kv.Hq, G = a.kv.G;
     const int n_tiles = (a.m + kTcBM - 1) / kTcBM;
@@ -84,10 +90,10 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             mbar_init(v_full(s), 1);
             mbar_init(v_empty(s), 1);
             mbar_init(s_full(s), 1);
+            mbar_init(p_half(s, 0), kTcBM);
+            mbar_init(p_half(s, 1), kTcBM);
+            mbar_init(pv_done(s), 1);
         }
-        mbar_init(p_half(0), kTcBM);
-        mbar_init(p_half(1), kTcBM);
-        mbar_init(pv_done, 1);
         mbar_init(o_final, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -171,14 +177,14 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 }
                 if (!(ok = mbar_wait_warp(v_full(s), (n >> 1) & 1, abortp))) break;
                 TRACE_ADD(tr_v);
-                if (!(ok = mbar_wait_warp(p_half(0), n & 1, abortp))) break;
+                if (!(ok = mbar_wait_warp(p_half(n & 1, 0), (n >> 1) & 1, abortp))) break;
                 TRACE_ADD(tr_p0);
                 fence_after_sync();
                 issue_pv_half(n & 1, s, 0, n > 0);
-                if (!(ok = mbar_wait_warp(p_half(1), n & 1, abortp))) break;
+                if (!(ok = mbar_wait_warp(p_half(n & 1, 1), (n >> 1) & 1, abortp))) break;
                 fence_after_sync();
                 issue_pv_half(n & 1, s, 1, true);
-                mma_commit_e(pv_done);
+                mma_commit_e(pv_done(n & 1));
                 mma_commit_e(v_empty(s));
                 if (j == hi - 1) mma_commit_e(o_final);
                 TRACE_ADD(tr_issue);
@@ -251,7 +257,7 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             // the wait is normally over already.
             const bool rescale_now = n > 0 && __any_sync(0xffffffffu, need);
             if (rescale_now) {
-                if (!(ok = mbar_wait(pv_done, (n - 1) & 1, abortp))) break;
+                if (!(ok = mbar_wait(pv_done((n - 1) & 1), ((n - 1) >> 1) & 1, abortp))) break;
                 fence_after_sync();
 #pragma unroll
                 for (int cidx = 0; cidx < D / 32; ++cidx) {
@@ -300,7 +306,7 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                     // keys 0-31 of P are in TMEM: their half of P V starts while the other half is computed
                     tmem_wait_st();
                     fence_before_sync();
-                    mbar_arrive(p_half(0));
+                    mbar_arrive(p_half(buf, 0));
                 }
             }
             {
@@ -310,8 +316,8 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             }
             tmem_wait_st();
             fence_before_sync();
-            mbar_arrive(p_half(1));
-            if (n > 0 && !rescale_now && !(ok = mbar_wait(pv_done, (n - 1) & 1, abortp))) break;
+            mbar_arrive(p_half(buf, 1));
+            if (n > 0 && !rescale_now && !(ok = mbar_wait(pv_done((n - 1) & 1), ((n - 1) >> 1) & 1, abortp))) break;
             TRACE_ADD(ts_exp);
         }
 #ifdef GGR_TC_TRACE
@@ -325,6 +331,10 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             fence_after_sync();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             float* orow_g = a.out + ((int64_t)qi * Hq + h) * D;
+            const void* grow = nullptr;
+            if (a.gate && valid)
+                grow = static_cast<const unsigned char*>(a.gate) +
+                       ((int64_t)qi * Hq + h) * a.gate_head_stride * (a.gate_bf16 ? 2 : 4);
 #pragma unroll
             for (int cidx = 0; cidx < D / 32; ++cidx) {
                 uint32_t orow[32];
@@ -335,6 +345,7 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                     for (int i = 0; i < 32; i += 4) {
                         float4 o4 = make_float4(__uint_as_float(orow[i]) * inv, __uint_as_float(orow[i + 1]) * inv,
                                                 __uint_as_float(orow[i + 2]) * inv, __uint_as_float(orow[i + 3]) * inv);
+                        if (grow) o4 = prefill_gate4(o4, grow, a.gate_bf16, cidx * 32 + i);
                         *reinterpret_cast<float4*>(orow_g + cidx * 32 + i) = o4;
                     }
                 }
@@ -366,16 +377,14 @@ inline int launch_prefill_tc_wide(const PrefillTcArgs& a, const CUtensorMap& tk,
         *msg = "the wide tensor-core prefill kernel is built for head_dim 256";
         return 5;
     }
-    static int configured_for = -1;
+    static KernelSmemSetup setup;
     const size_t smem = prefill_tc_wide_smem(256);
-    if (configured_for != device) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_tc_wide_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)smem);
+    {
+        const cudaError_t e = setup.ensure(prefill_tc_wide_kernel<256>, device, 0, (int)smem);
         if (e != cudaSuccess) {
             *msg = std::string("prefill kernel attribute: ") + cudaGetErrorString(e);
             return 2;
         }
-        configured_for = device;
     }
     const int n_tiles = (a.m + kTcBM - 1) / kTcBM;
     prefill_tc_wide_kernel<256><<<n_tiles * a.kv.Hq, kTwThreads, smem, stream>>>(tq, tk, tv, a);

@@ -28,7 +28,7 @@
 extern "C" {
 #endif
 
-#define GGR_ATTN_ABI_VERSION 1
+#define GGR_ATTN_ABI_VERSION 2
 
 typedef enum ggr_status {
     GGR_OK = 0,
@@ -94,6 +94,9 @@ typedef struct ggr_attn_config {
     int32_t max_splits;   /* 0 = automatic split-KV factor */
     int32_t decode_fusion; /* 0 = decode rotates q and appends k/v inside the attention kernel (one launch per
                               layer) where the shape allows; 1 = separate rope/append launch */
+    int32_t exchange_wait_us; /* bound, in microseconds, of the device-side wait for the peers' partial states in
+                                 the fused shard exchange; 0 selects 1 000 000. On expiry the call reports
+                                 GGR_ERR_TIMEOUT and the context stays usable. */
 } ggr_attn_config;
 
 /* Fills *cfg with the reference's defaults (theta 5e5, swa theta 1e4,
@@ -157,6 +160,28 @@ int ggr_attn_decode(ggr_attn_ctx* ctx, int32_t layer, const int32_t* pos, int32_
                     const float* k, const float* v, float* out, int32_t ptr_kind);
 
 /*
+ * ggr_attn_decode followed by the Qwen3Next / Qwen3.5 output gate of the same call site
+ * (src/engine/runtime/inference.rs:3509-3519: sigmoid_mul_inplace on every head, then
+ * sanitize_finite_inplace): out[h][i] = finite_or_zero(attn[h][i] * sigmoid(gate[h][i])), applied in the
+ * epilogue of the attention kernel. gate is f32; head h of batch entry b starts at
+ * gate + (b * n_heads + h) * gate_head_stride, so the second halves of the reference's packed q / gate
+ * projection (RunState::hb, head stride 2 * head_dim) can be passed as they lie; a dense [B][q_dim]
+ * gate has gate_head_stride = head_dim.
+ */
+int ggr_attn_decode_gated(ggr_attn_ctx* ctx, int32_t layer, const int32_t* pos, int32_t B, const float* q,
+                          const float* k, const float* v, const float* gate, int32_t gate_head_stride, float* out,
+                          int32_t ptr_kind);
+
+/*
+ * Scratch reservation for decode (no counterpart in the reference, whose RunState is sized once by
+ * malloc_run_state): allocates the rotated-query rows, split-KV partial states, tickets and, for host-pointer
+ * calls, the pinned and device staging buffers for batches of up to B sequences, so that the decode loop that
+ * follows never allocates, frees or synchronises for memory. Split-KV factors are then limited to what the
+ * reservation holds. ggr_attn_create reserves for max_batch (at most 128) itself; call this only to change it.
+ */
+int ggr_attn_reserve(ggr_attn_ctx* ctx, int32_t B);
+
+/*
  * Prefill of m consecutive tokens of sequence `seq` starting at base_pos;
  * token i sees exactly what attention_token would at position base_pos + i.
  * Replaces the per-token loop of transformer_prefill_batch
@@ -167,6 +192,12 @@ int ggr_attn_decode(ggr_attn_ctx* ctx, int32_t layer, const int32_t* pos, int32_
  */
 int ggr_attn_prefill(ggr_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t base_pos, int32_t m, const void* q,
                      const void* k, const void* v, int32_t in_dtype, float* out, int32_t ptr_kind);
+
+/* ggr_attn_prefill with the output gate of ggr_attn_decode_gated; gate is in in_dtype, head h of token i at
+ * gate + (i * n_heads + h) * gate_head_stride. */
+int ggr_attn_prefill_gated(ggr_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t base_pos, int32_t m, const void* q,
+                           const void* k, const void* v, const void* gate, int32_t gate_head_stride, int32_t in_dtype,
+                           float* out, int32_t ptr_kind);
 
 /* Staged prefill of one complete image block: every row is roped and appended
  * first, then every row attends with block-wide visibility. Replaces the two
@@ -232,15 +263,33 @@ int ggr_attn_decode_exchange(ggr_attn_ctx* ctx, int32_t layer, const int32_t* po
 int ggr_attn_exchange_send(ggr_attn_ctx* ctx, int32_t layer, const int32_t* pos, int32_t B, const float* q,
                            const float* k, const float* v, int32_t ptr_kind);
 int ggr_attn_exchange_receive(ggr_attn_ctx* ctx, int32_t B, float* out, int32_t ptr_kind);
+/* Step counter of the exchange: the number of sends this rank has issued. A send that fails on the host
+ * (before its kernel is launched) does not count. After a failed step (GGR_ERR_TIMEOUT, or a peer that
+ * reported an error) the ranks agree on a value on the host (the maximum of their counters is always safe)
+ * and each calls ggr_attn_exchange_resync with it; the next send then uses value + 1 on every rank. A
+ * receive that finds a flag ahead of its own step reports GGR_ERR_COMM instead of merging stale states. */
+int32_t ggr_attn_exchange_epoch(const ggr_attn_ctx* ctx);
+int ggr_attn_exchange_resync(ggr_attn_ctx* ctx, int32_t epoch);
 
 /* Rows [row0, row0 + nrows) of one layer of one sequence in the reference's
- * Q8 row layout (int8 codes [nrows][kv_dim] and one f32 scale per row), the
- * layout its prefill cache serialises (src/app/prefill_cache.rs:214-249) and
- * re-injects (:380-510). Only for kv_format GGR_KV_Q8_ROW. Host buffers. */
+ * Q8 layouts, as its prefill cache serialises them (src/app/prefill_cache.rs:11-19, :214-249) and
+ * re-injects them (:380-510): int8 codes [nrows][kv_dim] and, per row, one f32 scale
+ * (GGR_KV_Q8_ROW, the blob's q8_block = 0) or kv_dim / 32 scales (GGR_KV_Q8_BLOCK32, q8_block = 1).
+ * Host buffers. */
 int ggr_attn_kv_export(ggr_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t row0, int32_t nrows, int8_t* k_q8,
                        int8_t* v_q8, float* k_scale, float* v_scale);
 int ggr_attn_kv_import(ggr_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t row0, int32_t nrows,
                        const int8_t* k_q8, const int8_t* v_q8, const float* k_scale, const float* v_scale);
+/* The same for the TurboQuant cache (the blob's kv_format = 1): the eight sections of
+ * src/app/prefill_cache.rs:16-18 for rows [row0, row0 + nrows) of one layer: 2-bit codes
+ * [nrows][kv_dim / 4], residual sign bits [nrows][kv_dim / 8], sigma and residual norm [nrows][n_kv_heads],
+ * for K and for V. Host buffers; only for kv_format GGR_KV_TURBO. */
+int ggr_attn_kv_export_turbo(ggr_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t row0, int32_t nrows, uint8_t* k_base,
+                             uint8_t* v_base, uint8_t* k_sign, uint8_t* v_sign, float* k_scale, float* v_scale,
+                             float* k_rnorm, float* v_rnorm);
+int ggr_attn_kv_import_turbo(ggr_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t row0, int32_t nrows,
+                             const uint8_t* k_base, const uint8_t* v_base, const uint8_t* k_sign, const uint8_t* v_sign,
+                             const float* k_scale, const float* v_scale, const float* k_rnorm, const float* v_rnorm);
 /* Dequantised f32 view of one cache row (any format), for tests. Host buffers. */
 int ggr_attn_kv_read_row(ggr_attn_ctx* ctx, int32_t seq, int32_t layer, int32_t pos, float* k_out, float* v_out);
 /* Raw TurboQuant row in the reference's layout (src/engine/runtime/inference.rs:1919-1963): 2-bit codes

@@ -913,6 +913,24 @@ void ora_qkv_bias_and_norm(ora_ctx* ctx, int32_t layer, float* q, float* k, floa
     qkv_bias_and_norm(ctx, layer, q, k, v);
 }
 
+// Output gate of the decode call site (src/engine/runtime/inference.rs:3509-3519): per head
+// sigmoid_mul_inplace (scalar branch, src/engine/kernels/math.rs:399-402: s = 1 / (1 + exp(-g)),
+// d = finite_or_zero(d * s)), then sanitize_finite_inplace over the row (:458-462).
+void ora_sigmoid_gate(ora_ctx* ctx, float* xb, const float* gate, int32_t gate_head_stride) {
+    const int D = ctx->D;
+    for (int h = 0; h < ctx->c.n_heads; ++h) {
+        float* dst = xb + (size_t)h * D;
+        const float* g = gate + (size_t)h * gate_head_stride;
+        for (int i = 0; i < D; ++i) {
+            const float s = 1.0f / (1.0f + std::exp(-g[i]));
+            const float v = dst[i] * s;
+            dst[i] = std::isfinite(v) ? v : 0.0f;
+        }
+    }
+    for (int i = 0; i < ctx->q_dim; ++i)
+        if (!std::isfinite(xb[i])) xb[i] = 0.0f;
+}
+
 void ora_rope_angles(ora_ctx* ctx, int32_t layer, int32_t pos, float* c, float* s) {
     rope_angles(ctx, layer, pos, c, s);
 }

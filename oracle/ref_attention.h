@@ -57,6 +57,10 @@ int ora_set_layer_fixups(ora_ctx* ctx, int32_t layer, const float* q_bias, const
                          const float* q_norm, const float* k_norm, float eps);
 void ora_qkv_bias_and_norm(ora_ctx* ctx, int32_t layer, float* q, float* k, float* v);
 
+/* Qwen3Next / Qwen3.5 output gate on one token's attention output xb [n_heads*head_dim]: head h reads its gate at
+ * gate + h * gate_head_stride (src/engine/runtime/inference.rs:3509-3519) */
+void ora_sigmoid_gate(ora_ctx* ctx, float* xb, const float* gate, int32_t gate_head_stride);
+
 /* the three reference functions, with explicit buffers instead of RunState */
 void ora_rope_angles(ora_ctx* ctx, int32_t layer, int32_t pos, float* cos_out, float* sin_out);
 void ora_apply_rope_qk(ora_ctx* ctx, int32_t layer, int32_t pos, float* q, float* k);

@@ -36,11 +36,37 @@ def build(force: bool = False) -> str:
     return path
 
 
-def lib() -> C.CDLL:
-    global _LIB
+def build_native() -> str:
+    """The same source compiled for the host it runs on (-O3 -march=native), for the CPU-baseline timing legs
+    only: it is built where it is used (a library built for one CPU may not run on another) and never checked
+    against golden vectors; parity always uses the strict build above."""
+    out_dir = os.path.join(ORACLE_DIR, "_native")
+    os.makedirs(out_dir, exist_ok=True)
+    path = os.path.join(out_dir, "libggr_oracle_native.so")
+    src = os.path.join(ORACLE_DIR, "ref_attention.cpp")
+    if not os.path.exists(path) or os.path.getmtime(src) > os.path.getmtime(path):
+        subprocess.run([os.environ.get("CXX", "g++"), "-O3", "-march=native", "-ffp-contract=off", "-fno-fast-math",
+                        "-funroll-loops", "-fPIC", "-std=c++17", "-pthread", "-shared", "-o", path, src],
+                       check=True, capture_output=True)
+    return path
+
+
+_NATIVE = None
+
+
+def lib(native: bool = False) -> C.CDLL:
+    global _LIB, _NATIVE
+    if native:
+        if _NATIVE is None:
+            _NATIVE = _bind(C.CDLL(build_native()))
+        return _NATIVE
     if _LIB is not None:
         return _LIB
-    L = C.CDLL(build())
+    _LIB = _bind(C.CDLL(build()))
+    return _LIB
+
+
+def _bind(L: C.CDLL) -> C.CDLL:
     vp, i32, i64 = C.c_void_p, C.c_int32, C.c_int64
     L.ora_create.argtypes = [C.POINTER(OraConfig), C.POINTER(vp), C.POINTER(C.c_char_p)]
     L.ora_destroy.argtypes = [vp]
@@ -52,6 +78,8 @@ def lib() -> C.CDLL:
     L.ora_set_layer_fixups.argtypes = [vp, i32, vp, vp, vp, vp, vp, C.c_float]
     L.ora_qkv_bias_and_norm.argtypes = [vp, i32, vp, vp, vp]
     L.ora_qkv_bias_and_norm.restype = None
+    L.ora_sigmoid_gate.argtypes = [vp, vp, vp, i32]
+    L.ora_sigmoid_gate.restype = None
     L.ora_rope_angles.argtypes = [vp, i32, i32, vp, vp]
     L.ora_rope_angles.restype = None
     L.ora_apply_rope_qk.argtypes = [vp, i32, i32, vp, vp]
@@ -95,7 +123,6 @@ def lib() -> C.CDLL:
     L.ora_f32_to_bf16.restype = C.c_uint16
     L.ora_bf16_to_f32.argtypes = [C.c_uint16]
     L.ora_bf16_to_f32.restype = C.c_float
-    _LIB = L
     return L
 
 
@@ -144,8 +171,8 @@ class Oracle:
     """CPU restatement of the reference attention path, configured from the same
     fields as gguf_runner_b200.AttnConfig (any object with those attributes)."""
 
-    def __init__(self, cfg, threads: int = 1):
-        self.L = lib()
+    def __init__(self, cfg, threads: int = 1, native: bool = False):
+        self.L = lib(native)
         self.cfg = cfg
         c = OraConfig()
         for name in ("n_layers", "n_heads", "n_kv_heads", "head_dim", "rope_dim", "seq_len", "max_batch",
@@ -226,6 +253,17 @@ class Oracle:
         q, k, v = _f32(q), _f32(k), _f32(v)
         out = np.empty((pos.shape[0], self.q_dim), np.float32)
         self.L.ora_decode(self.h, layer, _p(pos), pos.shape[0], _p(q), _p(k), _p(v), _p(out))
+        return out
+
+    def sigmoid_gate(self, out, gate, gate_head_stride=None):
+        """Applies the output gate in place to rows of attention output [n][q_dim]; gate rows hold
+        n_heads heads at a stride of gate_head_stride elements (default head_dim)."""
+        stride = gate_head_stride or self.cfg.head_dim
+        gate = _f32(gate)
+        row = self.cfg.n_heads * stride
+        for i in range(out.shape[0]):
+            g = gate.reshape(-1)[i * row:]
+            self.L.ora_sigmoid_gate(self.h, C.c_void_p(out[i].ctypes.data), C.c_void_p(g.ctypes.data), stride)
         return out
 
     def prefill(self, layer, base_pos, q, k, v, seq=0, block=False):
