@@ -807,6 +807,61 @@ def bench_decode_head_shard(torch, dist, args, rank, world, local_rank, peaks, B
     return res
 
 
+def run_decode_stamps():
+    """Phase time stamps of the decode kernels (diagnostic build of the library, -DGGR_TC_TRACE): every CTA writes
+    %globaltimer at the start, after the fused prologue, after streaming its keys, after the CTA merge and at the
+    end; the last CTA of a (sequence, kv head) also stamps its ticket and the (m, l) loads of the split merge.
+    Run as `GGR_ATTN_LIBRARY=gguf_runner_b200/libggr_attn_trace.so python bench.py --case decode_stamps`
+    after `python -m gguf_runner_b200.build --trace`."""
+    import ctypes as C
+    import torch
+    import gguf_runner_b200 as g
+    from gguf_runner_b200 import presets
+    from gguf_runner_b200.binding import KV_F32
+    L_ = g.lib()
+    if not hasattr(L_, "ggr_attn_debug_set_trace"):
+        raise SystemExit("this library has no trace hooks: build with `python -m gguf_runner_b200.build --trace` and set "
+                         "GGR_ATTN_LIBRARY to gguf_runner_b200/libggr_attn_trace.so")
+    L_.ggr_attn_debug_set_trace.argtypes = [C.c_void_p]
+    L_.ggr_attn_debug_set_trace.restype = None
+    torch.cuda.set_device(0)
+    cases = [("configs[0] f32 T=2048 B=1", presets.qwen3_0p6b_decode(n_layers=2, seq_len=2048, kv_format=KV_F32), 1, 2048),
+             ("configs[2] bf16 T=32768 B=1", presets.qwen3_30b_a3b_decode(n_layers=2, seq_len=32768, max_batch=1), 1, 32768),
+             ("configs[2] bf16 T=32768 B=8", presets.qwen3_30b_a3b_decode(n_layers=2, seq_len=32768, max_batch=8), 8, 32768)]
+    for name, cfg, B, T in cases:
+        tr = torch.zeros(8 * 8192, dtype=torch.int64, device="cuda")
+        L_.ggr_attn_debug_set_trace(C.c_void_p(tr.data_ptr()))
+        ctx = g.AttnContext(cfg)
+        fill_cache_random(torch, ctx, 3)
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(1)
+        q = torch.randn(B, cfg.q_dim, generator=gen, device="cuda")
+        k = torch.randn(B, cfg.kv_dim, generator=gen, device="cuda")
+        v = torch.randn(B, cfg.kv_dim, generator=gen, device="cuda")
+        out = torch.empty(B, cfg.q_dim, device="cuda")
+        for _ in range(5):
+            for l in range(2):
+                ctx.decode(l, [T - 1] * B, q, k, v, out=out)
+        torch.cuda.synchronize()
+        tr.zero_()
+        ctx.decode(0, [T - 1] * B, q, k, v, out=out)
+        torch.cuda.synchronize()
+        n = ctx.last_split_count * cfg.n_kv_heads * B
+        t = tr.cpu().numpy()[:n * 8].reshape(n, 8).astype(np.float64)
+        t0 = t[:, 0].min()
+        print(f"{name}: splits={ctx.last_split_count} CTAs={n}: first start to last end {(t[:, 4].max() - t0) / 1e3:.1f} us")
+        print("  CTA start offsets (us): min %.1f median %.1f max %.1f" % tuple(np.percentile(t[:, 0] - t0, [0, 50, 100]) / 1e3))
+        for a_, b_, nm in ((0, 1, "prologue (rope, append)"), (1, 2, "stream"), (2, 3, "cta merge"), (3, 4, "ticket / split merge")):
+            d = (t[:, b_] - t[:, a_]) / 1e3
+            print("  %-26s median %.1f us  max %.1f us" % (nm, np.median(d), d.max()))
+        last = t[t[:, 5] > 0]
+        if len(last):
+            print("  last CTAs: ticket %.1f us, (m, l) loads and weights %.1f us, output loads and stores %.1f us" % (
+                np.median(last[:, 5] - last[:, 3]) / 1e3, np.median(last[:, 6] - last[:, 5]) / 1e3,
+                np.median(last[:, 4] - last[:, 6]) / 1e3))
+        ctx.close()
+
+
 def run_small_case(args):
     """Small single-GPU cases for profiler captures (`ncu ... python bench.py --case NAME`): a few launches of
     one kernel on inputs above the L2 size but at most ~1 GB on the device. Prints no benchmark line."""
@@ -941,10 +996,14 @@ def main():
     ap.add_argument("--decode-batch", type=int, default=8)
     ap.add_argument("--cpu-stride", type=int, default=16)
     ap.add_argument("--case", default=None, help="run a small profiling case (prefill_small, prefill_gemma_small, decode_small, "
-                                                 "decode_b1_small, decode_cfg1_small, decode_turbo_small) and exit")
+                                                 "decode_b1_small, decode_cfg1_small, decode_turbo_small) or print the "
+                                                 "decode kernels' phase stamps (decode_stamps, diagnostic library build) and exit")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
+    if args.case == "decode_stamps":
+        run_decode_stamps()
+        return
     if args.case:
         run_small_case(args)
         return

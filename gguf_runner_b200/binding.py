@@ -82,7 +82,9 @@ EXPORTED_SYMBOLS = [
 
 
 def library_path() -> str:
-    return os.path.join(_PKG, "libggr_attn.so")
+    """libggr_attn.so beside this file; GGR_ATTN_LIBRARY names another build of the same library (e.g. the
+    diagnostic build libggr_attn_trace.so, whose kernels also write phase time stamps)."""
+    return os.environ.get("GGR_ATTN_LIBRARY") or os.path.join(_PKG, "libggr_attn.so")
 
 
 def lib() -> C.CDLL:

@@ -342,6 +342,7 @@ __global__ void __launch_bounds__(kTmaWarps * 32) attn_mma_tma_decode_kernel(con
     // ring addresses, TMA coordinates) is warp-uniform
     const int tid = threadIdx.x, lane = tid & 31, warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
     const int gq = lane >> 2, tq = lane & 3;
+    peer_allow_dependents(a);
 
     int seq, pos;
     a.items.get(item, seq, pos);

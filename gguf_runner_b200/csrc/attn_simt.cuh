@@ -62,6 +62,7 @@ struct AttnArgs {
     float* partial_out;   // [items][Hq][D + 2] (o / l, m, l) for cross-rank merging, or null
     int shard_count;      // positions held locally
     int stage_bytes;      // bytes of one ring stage of one warp
+    int tile_stages;      // ring stages of the CTA-tile kernel (1 or 2)
     int* err;             // raised when a bounded wait runs out (kernels that wait on mbarriers)
     FusedRope fused;
     PeerExchange px;
@@ -323,6 +324,13 @@ __device__ __forceinline__ void cta_merge_store(const AttnArgs& a, const float* 
     }
 }
 
+// Start of a kernel that feeds the fused shard exchange: lets the merge kernel enqueued behind it (launched with
+// programmatic stream serialisation) become resident once every CTA of this grid has started, so that its launch
+// and its wait for the peers' flags overlap this grid's work. A no-op for every other launch.
+__device__ __forceinline__ void peer_allow_dependents(const AttnArgs& a) {
+    if (a.px.enabled) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // Called by the CTA that stored the final states of a (token, kv head) group. When every group of the
 // launch has finished, this rank's flag is raised on all peers (system-scope release after the stores).
 __device__ __forceinline__ void peer_group_done(const AttnArgs& a) {
@@ -340,6 +348,9 @@ __device__ __forceinline__ void peer_group_done(const AttnArgs& a) {
         }
     }
 }
+
+// floats the split merge needs behind its weights for the sub-results of warps that share a head
+inline size_t split_merge_sub_floats(int G, int D) { return G <= 4 ? (size_t)G * 4 * (D + 2) : 0; }
 
 // The last CTA of a (token, kv head) to arrive (atomic ticket) merges the
 // per-split states from the scratch buffer and resets the ticket. `wsm` is
@@ -366,22 +377,108 @@ __device__ __forceinline__ void split_merge_store(const AttnArgs& a, int item, i
     // splits in one lane-strided batch of 8-byte loads, the split outputs in batches of 16 or 32 independent
     // 8-byte loads per lane (rows of D + 2 floats are 8-byte aligned).
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    if (D == 128) {
+        // head_dim 128 (two 64-float spans per lane). Several warps share a head when there are more warps than
+        // heads: warp (g, sub) merges the splits sub, sub + wph, ... with its own maximum, so that up to 16 * wph
+        // splits travel in one round trip; the outputs of a warp's first 16 splits are requested before their
+        // (m, l) pairs, so both arrive together. The sub-results are then folded in shared memory.
+        int wph = 1;
+        while (wph < 4 && G * wph * 2 <= nwarp && 16 * wph < NS) wph <<= 1;
+        float* sub_o = wsm + (size_t)G * 2 * NS;  // [G][wph][D + 2]
+        for (int gw = warp; gw < G * wph; gw += nwarp) {
+            const int g = gw / wph, sub = gw - g * wph;
+            const float* hb = base + (int64_t)g * NS * (D + 2);
+            float* w = wsm + (size_t)g * 2 * NS;  // [NS] weights, [NS] l
+            const float* pp = hb + 2 * lane;
+            float2 xa[16], xb[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int sidx = sub + i * wph;
+                const bool in = sidx < NS;
+                xa[i] = in ? __ldcg(reinterpret_cast<const float2*>(pp + (int64_t)sidx * (D + 2))) : make_float2(0.0f, 0.0f);
+                xb[i] = in ? __ldcg(reinterpret_cast<const float2*>(pp + (int64_t)sidx * (D + 2) + 64)) : make_float2(0.0f, 0.0f);
+            }
+            float ms = -INFINITY;
+            for (int sidx = sub + lane * wph; sidx < NS; sidx += 32 * wph) {
+                const float2 ml = __ldcg(reinterpret_cast<const float2*>(hb + (int64_t)sidx * (D + 2) + D));
+                w[sidx] = ml.x;
+                w[NS + sidx] = ml.y;
+                ms = fmaxf(ms, ml.x);
+            }
+            ms = warp_max(ms);
+            float ls = 0.0f;
+            for (int sidx = sub + lane * wph; sidx < NS; sidx += 32 * wph) {
+                const float mw = w[sidx];
+                const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - ms);
+                w[sidx] = f;
+                ls += f * w[NS + sidx];
+            }
+            ls = warp_sum(ls);
+            __syncwarp();
+            DECODE_STAMP(6);
+            float ax = 0.0f, ay = 0.0f, bx = 0.0f, by = 0.0f;
+            for (int i0 = 0; sub + i0 * wph < NS; i0 += 16) {
+                if (i0 > 0) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int sidx = sub + (i0 + i) * wph;
+                        const bool in = sidx < NS;
+                        xa[i] = in ? __ldcg(reinterpret_cast<const float2*>(pp + (int64_t)sidx * (D + 2))) : make_float2(0.0f, 0.0f);
+                        xb[i] = in ? __ldcg(reinterpret_cast<const float2*>(pp + (int64_t)sidx * (D + 2) + 64))
+                                   : make_float2(0.0f, 0.0f);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int sidx = sub + (i0 + i) * wph;
+                    const float f = sidx < NS ? w[sidx] : 0.0f;
+                    ax = fmaf(f, xa[i].x, ax);
+                    ay = fmaf(f, xa[i].y, ay);
+                    bx = fmaf(f, xb[i].x, bx);
+                    by = fmaf(f, xb[i].y, by);
+                }
+            }
+            if (wph == 1) {
+                const int h = kvh * G + g;
+                store_final(a, item, h, 2 * lane, ax, ms, ls);
+                store_final(a, item, h, 2 * lane + 1, ay, ms, ls);
+                store_final(a, item, h, 2 * lane + 64, bx, ms, ls);
+                store_final(a, item, h, 2 * lane + 65, by, ms, ls);
+            } else {
+                float* so = sub_o + ((size_t)g * wph + sub) * (D + 2);
+                *reinterpret_cast<float2*>(so + 2 * lane) = make_float2(ax, ay);
+                *reinterpret_cast<float2*>(so + 2 * lane + 64) = make_float2(bx, by);
+                if (lane == 0) {
+                    so[D] = ms;
+                    so[D + 1] = ls;
+                }
+            }
+        }
+        if (wph > 1) {
+            __syncthreads();
+            for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+                const int g = idx / D, d = idx - g * D;
+                const float* so = sub_o + (size_t)g * wph * (D + 2);
+                float ms = -INFINITY;
+                for (int q = 0; q < wph; ++q) ms = fmaxf(ms, so[q * (D + 2) + D]);
+                float o = 0.0f, ls = 0.0f;
+                for (int q = 0; q < wph; ++q) {
+                    const float mq = so[q * (D + 2) + D];
+                    const float f = (mq == -INFINITY) ? 0.0f : exp2f(mq - ms);
+                    o = fmaf(f, so[q * (D + 2) + d], o);
+                    ls = fmaf(f, so[q * (D + 2) + D + 1], ls);
+                }
+                store_final(a, item, kvh * G + g, d, o, ms, ls);
+            }
+        }
+        if (threadIdx.x == 0) a.counters[item * a.kv.Hkv + kvh] = 0u;  // ready for the next launch
+        peer_group_done(a);
+        return;
+    }
     for (int g = warp; g < G; g += nwarp) {
         const float* hb = base + (int64_t)g * NS * (D + 2);
         float* w = wsm + (size_t)g * 2 * NS;  // [NS] weights, [NS] l
-        // head_dim 128 (two 64-float spans per lane): the outputs of the first 16 splits are requested before
-        // the (m, l) pairs, so both travel in the same round trip; 16 splits or fewer need no second one
-        float2 xa[16], xb[16];
-        const bool fast = D == 128;
-        if (fast) {
-            const float* pp = hb + 2 * lane;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const bool in = i < NS;
-                xa[i] = in ? __ldcg(reinterpret_cast<const float2*>(pp + (int64_t)i * (D + 2))) : make_float2(0.0f, 0.0f);
-                xb[i] = in ? __ldcg(reinterpret_cast<const float2*>(pp + (int64_t)i * (D + 2) + 64)) : make_float2(0.0f, 0.0f);
-            }
-        }
+        float2 xa[16];
         float ms = -INFINITY;
         for (int sidx = lane; sidx < NS; sidx += 32) {
             const float2 ml = __ldcg(reinterpret_cast<const float2*>(hb + (int64_t)sidx * (D + 2) + D));
@@ -400,36 +497,6 @@ __device__ __forceinline__ void split_merge_store(const AttnArgs& a, int item, i
         ls = warp_sum(ls);
         __syncwarp();
         DECODE_STAMP(6);
-        if (fast) {
-            const float* pp = hb + 2 * lane;
-            float ax = 0.0f, ay = 0.0f, bx = 0.0f, by = 0.0f;
-            for (int s0 = 0; s0 < NS; s0 += 16) {
-                if (s0 > 0) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const bool in = s0 + i < NS;
-                        xa[i] = in ? __ldcg(reinterpret_cast<const float2*>(pp + (int64_t)(s0 + i) * (D + 2)))
-                                   : make_float2(0.0f, 0.0f);
-                        xb[i] = in ? __ldcg(reinterpret_cast<const float2*>(pp + (int64_t)(s0 + i) * (D + 2) + 64))
-                                   : make_float2(0.0f, 0.0f);
-                    }
-                }
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float f = s0 + i < NS ? w[s0 + i] : 0.0f;
-                    ax = fmaf(f, xa[i].x, ax);
-                    ay = fmaf(f, xa[i].y, ay);
-                    bx = fmaf(f, xb[i].x, bx);
-                    by = fmaf(f, xb[i].y, by);
-                }
-            }
-            const int h = kvh * G + g;
-            store_final(a, item, h, 2 * lane, ax, ms, ls);
-            store_final(a, item, h, 2 * lane + 1, ay, ms, ls);
-            store_final(a, item, h, 2 * lane + 64, bx, ms, ls);
-            store_final(a, item, h, 2 * lane + 65, by, ms, ls);
-            continue;
-        }
         for (int d0 = 2 * lane; d0 < D; d0 += 64) {
             const float* pp = hb + d0;
             float ox = 0.0f, oy = 0.0f;
@@ -549,6 +616,7 @@ __global__ void __launch_bounds__(kSimtWarps * 32) attn_simt_kernel(AttnArgs a) 
     const int nw = blockDim.x >> 5;  // 1, 2 or 4 warps, each with its own ring
     const int rowbytes = D * a.kv.elem_bytes;
     DECODE_STAMP(0);
+    peer_allow_dependents(a);
 
     int seq, pos;
     a.items.get(item, seq, pos);

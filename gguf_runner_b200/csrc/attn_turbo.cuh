@@ -143,7 +143,7 @@ inline size_t turbo_attn_smem_floats(int D, int G, int GH, int n_split) {
     const size_t prep = (size_t)2 * G * D;                                 // rotated and projected queries
     const size_t part = (size_t)kTurboGroups * GH * (2 * D + 2);           // per-group accumulators, m, l
     const size_t fin = (size_t)GH * 2 * D + 3 * GH + 8;                    // merged head states
-    const size_t merge = n_split > 1 ? (size_t)2 * G * n_split + 2 * G : 0;  // split merge weights
+    const size_t merge = n_split > 1 ? (size_t)2 * G * n_split + 2 * G + split_merge_sub_floats(G, D) : 0;  // split merge weights, sub-results
     return prep + (part + fin > merge ? part + fin : merge);
 }
 

@@ -36,7 +36,7 @@ inline bool turbo_mma_supported(int D, int G) { return D == kTmD && G <= 16; }
 inline size_t turbo_mma_prep_offset(int G, int n_split) {
     const size_t work = (size_t)kTmWarps * kTmWarpBytes;
     const size_t merge = ((size_t)kTmWarps * 16 * kTmLD + 2 * kTmWarps * 16 + 96 + (size_t)16 * 2 * kTmD) * 4;
-    const size_t split = n_split > 1 ? ((size_t)2 * G * n_split + 2 * G) * 4 : 0;
+    const size_t split = n_split > 1 ? ((size_t)2 * G * n_split + 2 * G + split_merge_sub_floats(G, kTmD)) * 4 : 0;
     size_t m = work > merge ? work : merge;
     if (split > m) m = split;
     return (m + 127) & ~(size_t)127;

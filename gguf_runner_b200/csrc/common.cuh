@@ -35,6 +35,10 @@ struct KernelSmemSetup {
         }
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, want);
         if (e != cudaSuccess) return e;
+        // these kernels stage everything in shared memory: ask for the largest carve-out, so that as many CTAs
+        // as the kernel's own footprint allows are resident (the default left one where two fit)
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return e;
         if (tracked) done.fetch_or(1ull << device, std::memory_order_release);
         return cudaSuccess;
     }

@@ -15,6 +15,7 @@
 #include "../../include/ggr_attn.h"
 #include "attn_mma.cuh"
 #include "attn_simt.cuh"
+#include "attn_tile.cuh"
 #include "attn_turbo.cuh"
 #include "attn_turbo_mma.cuh"
 #include "common.cuh"
@@ -469,11 +470,11 @@ int launch_simt(ggr_attn_ctx* c, const AttnArgs& a, dim3 grid, const SimtPlan& p
 // costs a little per split. The constants are measured on B200 (TMA-fed decode kernel: ~65 GB/s per
 // CTA alone, ~6.6 TB/s for the whole GPU, ~8 us per wave). Picks the n with the smallest modelled time.
 int choose_splits(int64_t base_ctas, int64_t slots, int t_max, int min_keys, int max_splits, double bytes_per_key,
-                  double cta_rate) {
+                  double cta_rate, double t_wave = 8e-6) {
     int limit = std::max(1, t_max / std::max(1, min_keys));
     limit = std::min(limit, 512);
     if (max_splits > 0) limit = std::min(limit, max_splits);
-    const double hbm_rate = 6.6e12, t_wave = 8e-6;
+    const double hbm_rate = 6.6e12;
     int best = 1;
     double best_cost = -1.0;
     for (int n = 1; n <= limit; ++n) {
@@ -483,7 +484,8 @@ int choose_splits(int64_t base_ctas, int64_t slots, int t_max, int min_keys, int
         double cost = 0.0;
         if (full > 0) cost += (double)full * (t_wave + bytes / std::min(cta_rate, hbm_rate / (double)slots));
         if (rem > 0) cost += t_wave + bytes / std::min(cta_rate, hbm_rate / (double)rem);
-        if (n > 1) cost += 2e-6 + 0.25e-6 * n;
+        // the split merge fetches the states of 16 splits per round trip (~1.4 us each)
+        if (n > 1) cost += 2e-6 + 1.4e-6 * ((n + 15) / 16);
         if (best_cost < 0.0 || cost < best_cost) {
             best_cost = cost;
             best = n;
@@ -499,14 +501,30 @@ bool use_mma_decode(const ggr_attn_ctx* c) {
     return can && c->G >= 3;
 }
 
+// shared memory of the split merge: one weight and one l per (head, split), and the sub-results of the warps
+// that share a head (only when a CTA has at least twice as many warps as heads, i.e. up to four heads)
+size_t split_merge_smem_bytes(const ggr_attn_ctx* c, int n_split) {
+    if (n_split <= 1) return 0;
+    return ((size_t)2 * c->G * n_split + 2 * c->G + split_merge_sub_floats(c->G, c->D)) * sizeof(float);
+}
+
 // Kernel family and launch geometry of a decode / generic attention launch.
 struct DecodePlan {
-    bool mma, tma;
+    bool mma, tma, tile;
     SimtPlan p;
+    TilePlan tp;
     size_t smem;
     int ctas_per_sm, min_keys;
     double cta_rate;
 };
+
+void use_tile_plan(const ggr_attn_ctx* c, DecodePlan& d, int nst) {
+    d.tp = tile_plan(c->kv.fmt, c->D, nst, c->smem_optin);
+    d.smem = d.tp.smem;
+    d.ctas_per_sm = d.tp.ctas_per_sm;
+    d.min_keys = d.tp.tk;
+    d.cta_rate = 20e9;
+}
 
 DecodePlan decode_plan(const ggr_attn_ctx* c, bool allow_mma) {
     DecodePlan d{};
@@ -516,19 +534,33 @@ DecodePlan decode_plan(const ggr_attn_ctx* c, bool allow_mma) {
     d.smem = d.p.smem;
     d.ctas_per_sm = d.p.ctas_per_sm;
     d.min_keys = d.p.nw * kSimtTK * 2;
+    d.cta_rate = d.tma ? 65e9 : 40e9;
     if (d.mma) {
         MmaPlan mp = d.tma ? mma_tma_plan(c->D, c->smem_optin) : mma_plan(c->D, c->smem_optin);
         d.smem = mp.smem;
         d.ctas_per_sm = mp.ctas_per_sm;
         d.min_keys = mp.min_keys;
+    } else if (allow_mma && c->cfg.decode_impl != GGR_IMPL_SIMT && tile_decode_supported(c->kv.fmt, c->D)) {
+        // decode of the formats / groupings the tensor-core kernels do not take: the CTA-tile kernel
+        d.tile = true;
+        use_tile_plan(c, d, 1);
     }
-    d.cta_rate = d.tma ? 65e9 : 40e9;
     return d;
 }
 
-int plan_splits(const ggr_attn_ctx* c, const DecodePlan& d, int n_items, int t_max, int max_splits) {
-    return choose_splits((int64_t)c->kv.Hkv * n_items, (int64_t)c->sm_count * d.ctas_per_sm, t_max, d.min_keys, max_splits,
-                         2.0 * c->D * c->kv.elem_bytes, d.cta_rate);
+// Split-KV factor of a launch. The CTA-tile kernel streams with one ring stage when every CTA gets a single tile
+// and with two otherwise, which changes its occupancy and so the split count: settle both here.
+int plan_splits(const ggr_attn_ctx* c, DecodePlan& d, int n_items, int t_max, int max_splits) {
+    auto pick = [&]() {
+        return choose_splits((int64_t)c->kv.Hkv * n_items, (int64_t)c->sm_count * d.ctas_per_sm, t_max, d.min_keys,
+                             max_splits, 2.0 * c->D * c->kv.elem_bytes, d.cta_rate, d.tile ? 3e-6 : 8e-6);
+    };
+    int n = pick();
+    if (d.tile && ((t_max + n - 1) / n + d.tp.tk - 1) / d.tp.tk > 1) {
+        use_tile_plan(c, d, 2);
+        n = pick();
+    }
+    return n;
 }
 
 // Output gate of a call (src/engine/runtime/inference.rs:3509-3519); p == nullptr = none.
@@ -634,16 +666,30 @@ int launch_attention(ggr_attn_ctx* c, int layer, const Items& items, int t_max, 
         return GGR_OK;
     }
 
-    const DecodePlan dp = decode_plan(c, allow_mma);
-    const bool mma = dp.mma, tma = dp.tma;
+    DecodePlan dp = decode_plan(c, allow_mma);
+    int n_split = plan_splits(c, dp, items.n, t_max, c->cfg.max_splits);
+    {
+        // with a reservation in place the split count never outgrows the reserved scratch (as long as that
+        // holds two splits): the decode loop then neither allocates nor synchronises for memory
+        const size_t per_split = (size_t)items.n * c->kv.Hq * (c->D + 2);
+        if (c->reserved_batch > 0 && per_split * n_split > c->part_cap) {
+            const int fit = (int)std::min<size_t>(512, c->part_cap / per_split);
+            if (fit >= 2) n_split = std::min(n_split, fit);
+        }
+    }
+    const bool mma = dp.mma, tma = dp.tma, tile = dp.tile;
     SimtPlan p = dp.p;
+    if (tile) p.smem = dp.smem;  // one size governs below: the tile kernel replaces the per-warp-ring kernel
     size_t smem = dp.smem;
     a.stage_bytes = p.stage_bytes;
+    a.tile_stages = dp.tp.nst;
     a.err = c->d_err;
     if (raw) {
         const size_t fb = fused_rope_smem_bytes(c->kv, c->rope_half);
         const size_t base = (std::max(smem, p.smem) + 15) & ~(size_t)15;
-        const bool kernel_ok = !mma || tma;  // the cp.async-fed tensor-core kernel has no fused prologue
+        // the cp.async-fed tensor-core kernel has no fused prologue; the tile kernel reads the rotated query as
+        // 16-byte pieces, which the scratch layout guarantees for an even number of rotated pairs
+        const bool kernel_ok = (!mma || tma) && !(tile && (c->rope_half & 1));
         if (c->cfg.decode_fusion == 0 && kernel_ok && base + fb + 4096 <= (size_t)c->smem_optin) {
             a.fused.enabled = 1;
             a.fused.rope = rope_params(c, layer);
@@ -660,20 +706,10 @@ int launch_attention(ggr_attn_ctx* c, int layer, const Items& items, int t_max, 
         }
     }
 
-    int n_split = plan_splits(c, dp, items.n, t_max, c->cfg.max_splits);
-    {
-        // with a reservation in place the split count never outgrows the reserved scratch (as long as that
-        // holds two splits): the decode loop then neither allocates nor synchronises for memory
-        const size_t per_split = (size_t)items.n * c->kv.Hq * (c->D + 2);
-        if (c->reserved_batch > 0 && per_split * n_split > c->part_cap) {
-            const int fit = (int)std::min<size_t>(512, c->part_cap / per_split);
-            if (fit >= 2) n_split = std::min(n_split, fit);
-        }
-    }
     a.n_split = n_split;
     c->last_splits = n_split;
     // the split merge stages one weight per (head, split) in shared memory
-    const size_t merge_smem = n_split > 1 ? ((size_t)2 * c->G * n_split + 2 * c->G) * sizeof(float) : 0;
+    const size_t merge_smem = split_merge_smem_bytes(c, n_split);
     smem = std::max(smem, merge_smem);
     p.smem = std::max(p.smem, merge_smem);
     if (a.fused.enabled && merge_smem > (size_t)a.fused.smem_off) {
@@ -705,6 +741,16 @@ int launch_attention(ggr_attn_ctx* c, int layer, const Items& items, int t_max, 
                      : launch_mma_decode(a, grid, smem, c->smem_optin, c->cfg.device, c->stream);
         }
         if (rc != 0) return fail(c, GGR_ERR_CUDA, std::string("mma decode launch: ") + cudaGetErrorString((cudaError_t)rc));
+        c->launches++;
+        return GGR_OK;
+    }
+    if (tile) {
+        int rc;
+        {
+            LaunchTimer t(c, 0);
+            rc = launch_tile_decode(a, grid, smem, c->smem_optin, c->cfg.device, c->stream);
+        }
+        if (rc != 0) return fail(c, GGR_ERR_CUDA, std::string("tile decode launch: ") + cudaGetErrorString((cudaError_t)rc));
         c->launches++;
         return GGR_OK;
     }
@@ -766,9 +812,9 @@ int reserve_decode(ggr_attn_ctx* c, int B) {
         if ((rc = ensure(c, &c->d_krot, &c->krot_cap, (size_t)B * c->kv_dim))) return rc;
     } else {
         // the split count is not monotone in the context length: take the largest over a sweep of lengths
-        const DecodePlan dp = decode_plan(c, true);
         const int chunk = std::min(B, kMaxArgItems);
         for (int t = c->shard_count; t >= 1; t = t * 3 / 4) {
+            DecodePlan dp = decode_plan(c, true);
             splits = std::max(splits, plan_splits(c, dp, chunk, t, c->cfg.max_splits));
             if (t == 1) break;
         }
@@ -1820,15 +1866,17 @@ extern "C" int ggr_attn_attention_tokens_static(ggr_attn_ctx* c, int32_t layer, 
     a.partial_out = nullptr;
     a.shard_count = c->shard_count;
     a.err = c->d_err;
-    const DecodePlan dp = decode_plan(c, true);
-    const bool mma = dp.mma, tma = dp.tma;
-    SimtPlan p = dp.p;
-    size_t smem = dp.smem;
-    a.stage_bytes = p.stage_bytes;
+    DecodePlan dp = decode_plan(c, true);
     const int t_max = t_max_of(c, layer, pos, B);
     // The split count comes first: a call that runs unsplit (a short context, or so many (sequence, kv head)
     // groups that they fill the GPU by themselves) needs no scratch and is never rejected for its size.
     a.n_split = plan_splits(c, dp, B, t_max, c->cfg.max_splits);
+    const bool mma = dp.mma, tma = dp.tma, tile = dp.tile;
+    SimtPlan p = dp.p;
+    if (tile) p.smem = dp.smem;
+    size_t smem = dp.smem;
+    a.stage_bytes = p.stage_bytes;
+    a.tile_stages = dp.tp.nst;
     if (a.n_split > 1) {
         const size_t fit = part_cap / per_split;  // splits the array can hold
         if (fit < 2 || tickets * sizeof(unsigned) > GGR_STATIC_TICKET_BYTES) {
@@ -1843,7 +1891,7 @@ extern "C" int ggr_attn_attention_tokens_static(ggr_attn_ctx* c, int32_t layer, 
     unsigned char* scratch = nullptr;
     if ((rc = static_scratch(c, &scratch))) return rc;
     c->last_splits = a.n_split;
-    const size_t merge_smem = a.n_split > 1 ? ((size_t)2 * c->G * a.n_split + 2 * c->G) * sizeof(float) : 0;
+    const size_t merge_smem = split_merge_smem_bytes(c, a.n_split);
     smem = std::max(smem, merge_smem);
     p.smem = std::max(p.smem, merge_smem);
     if (a.n_split > 1) {
@@ -1861,6 +1909,16 @@ extern "C" int ggr_attn_attention_tokens_static(ggr_attn_ctx* c, int32_t layer, 
                     : launch_mma_decode(a, grid, smem, c->smem_optin, c->cfg.device, c->stream);
         }
         if (e != 0) return fail(c, GGR_ERR_CUDA, std::string("mma decode launch: ") + cudaGetErrorString((cudaError_t)e));
+        c->launches++;
+        return GGR_OK;
+    }
+    if (tile) {
+        int e;
+        {
+            LaunchTimer t(c, 0);
+            e = launch_tile_decode(a, grid, smem, c->smem_optin, c->cfg.device, c->stream);
+        }
+        if (e != 0) return fail(c, GGR_ERR_CUDA, std::string("tile decode launch: ") + cudaGetErrorString((cudaError_t)e));
         c->launches++;
         return GGR_OK;
     }
@@ -1982,7 +2040,11 @@ int exchange_send(ggr_attn_ctx* c, int layer, const int32_t* pos, int B, const f
 
 
 // receive half: bounded wait for every rank's flag of the current step, then the merge
-int exchange_receive(ggr_attn_ctx* c, int B, float* out, int ptr_kind) {
+// `after_own_send`: the merge kernel is enqueued right behind this rank's own send kernel. It may then start while
+// that kernel is still running (programmatic dependent launch: the send kernels signal launch_dependents as soon as
+// all their CTAs are resident), so its launch latency and its wait for the peers overlap the local decode instead of
+// following it. The merge never reads anything but what the flags guard, so it needs no grid dependency wait.
+int exchange_receive(ggr_attn_ctx* c, int B, float* out, int ptr_kind, bool after_own_send = false) {
     if (!c->x_connected || c->x_epoch == 0) return fail(c, GGR_ERR_INVALID, "nothing was sent on this exchange yet");
     if (B <= 0 || B > c->x_max_b || !out) return fail(c, GGR_ERR_INVALID, "invalid receive arguments");
     const size_t qb = (size_t)B * c->q_dim * sizeof(float);
@@ -1996,9 +2058,25 @@ int exchange_receive(ggr_attn_ctx* c, int B, float* out, int ptr_kind) {
     const size_t slot = x_slot_floats(c), parity_off = (size_t)(epoch & 1) * n * slot;
     {
         LaunchTimer t(c, 2);
-        combine_exchange_kernel<<<dim3(c->kv.Hq, B), 128, 0, c->stream>>>(
-            reinterpret_cast<const float*>(c->x_local + x_flag_bytes()) + parity_off, reinterpret_cast<const int*>(c->x_local),
-            epoch, n, (int64_t)slot, c->kv.Hq, c->D, dout, c->d_err, c->x_wait_ns, nullptr, 0);
+        const float* parts = reinterpret_cast<const float*>(c->x_local + x_flag_bytes()) + parity_off;
+        const int* flags = reinterpret_cast<const int*>(c->x_local);
+        if (after_own_send && !c->timing) {
+            cudaLaunchConfig_t lc{};
+            lc.gridDim = dim3(c->kv.Hq, B);
+            lc.blockDim = dim3(128);
+            lc.dynamicSmemBytes = 0;
+            lc.stream = c->stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            lc.attrs = attr;
+            lc.numAttrs = 1;
+            CUDA_TRY(c, cudaLaunchKernelEx(&lc, combine_exchange_kernel, parts, flags, epoch, n, (int64_t)slot, (int)c->kv.Hq,
+                                           (int)c->D, dout, c->d_err, c->x_wait_ns, (const float*)nullptr, 0));
+        } else {
+            combine_exchange_kernel<<<dim3(c->kv.Hq, B), 128, 0, c->stream>>>(parts, flags, epoch, n, (int64_t)slot, c->kv.Hq,
+                                                                              c->D, dout, c->d_err, c->x_wait_ns, nullptr, 0);
+        }
     }
     CUDA_TRY(c, cudaGetLastError());
     c->launches++;
@@ -2049,7 +2127,7 @@ extern "C" int ggr_attn_decode_exchange(ggr_attn_ctx* c, int32_t layer, const in
     DeviceGuard guard(c->cfg.device);
     int rc = exchange_send(c, layer, pos, B, q, k, v, ptr_kind);
     if (rc) return rc;
-    return exchange_receive(c, B, out, ptr_kind);
+    return exchange_receive(c, B, out, ptr_kind, true);
 }
 
 // ---- per-layer pre-attention fixups ----------------------------------------------------------------------
