@@ -12,6 +12,7 @@ from .binding import (  # noqa: F401
     GgrError,
     MediaAttentionPlan,
     RopePositionPlan,
+    Weights,
     gemma_layer_windows,
     lib,
     library_path,

@@ -30,6 +30,8 @@ IMAGE_CAUSAL, IMAGE_BIDIRECTIONAL = 0, 1
 SHARD_NONE, SHARD_KV_SEQUENCE = 0, 2
 IMPL_AUTO, IMPL_SIMT, IMPL_MMA, IMPL_TCGEN05 = 0, 1, 2, 3
 
+W_F32, W_BF16, W_Q8_0 = 0, 1, 2
+
 KV_FORMATS = {"f32": KV_F32, "bf16": KV_BF16, "q8_row": KV_Q8_ROW, "q8_block32": KV_Q8_BLOCK32, "turbo": KV_TURBO}
 
 
@@ -75,6 +77,7 @@ EXPORTED_SYMBOLS = [
     "ggr_attn_exchange_send", "ggr_attn_exchange_receive", "ggr_attn_set_layer_fixups",
     "ggr_attn_exchange_epoch", "ggr_attn_exchange_resync", "ggr_attn_decode_gated", "ggr_attn_prefill_gated",
     "ggr_attn_reserve", "ggr_attn_kv_export_turbo", "ggr_attn_kv_import_turbo",
+    "ggr_weights_upload", "ggr_weights_free", "ggr_proj_matmul", "ggr_attn_layer_decode", "ggr_attn_layer_prefill",
     "ggr_rope_plan_new", "ggr_rope_plan_free", "ggr_rope_plan_append_text", "ggr_rope_plan_append_grid",
     "ggr_rope_plan_len", "ggr_rope_plan_next_text", "ggr_rope_plan_at", "ggr_rope_plan_export",
     "ggr_rope_axis", "ggr_media_plan_validate", "ggr_media_chunk_end", "ggr_gemma_layer_windows",
@@ -141,6 +144,12 @@ def lib() -> C.CDLL:
     L.ggr_attn_decode_gated.argtypes = [vp, i32, vp, i32, vp, vp, vp, vp, i32, vp, i32]
     L.ggr_attn_prefill_gated.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp, i32, i32, vp, i32]
     L.ggr_attn_reserve.argtypes = [vp, i32]
+    L.ggr_weights_upload.argtypes = [i32, i32, i32, i32, vp, C.POINTER(vp)]
+    L.ggr_weights_free.argtypes = [vp]
+    L.ggr_weights_free.restype = None
+    L.ggr_proj_matmul.argtypes = [vp, vp, vp, i32, vp, i32]
+    L.ggr_attn_layer_decode.argtypes = [vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, i32]
+    L.ggr_attn_layer_prefill.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, i32]
     L.ggr_attn_kv_export_turbo.argtypes = [vp, i32, i32, i32, i32] + [vp] * 8
     L.ggr_attn_kv_import_turbo.argtypes = [vp, i32, i32, i32, i32] + [vp] * 8
     L.ggr_attn_set_kernel_timing.argtypes = [vp, i32]
@@ -229,6 +238,34 @@ class AttnConfig:
         c.n_layer_windows = len(self.layer_windows)
         c.layer_windows = C.cast(windows, C.POINTER(C.c_int32))
         return c, windows
+
+
+class Weights:
+    """One projection matrix [rows][cols] resident on a device, uploaded from the GGML row layout the reference maps
+    from the GGUF file (F32, BF16, or Q8_0 blocks of one f16 scale and 32 int8 codes)."""
+
+    def __init__(self, wtype: int, rows: int, cols: int, data: np.ndarray, device: int = 0):
+        self._L = lib()
+        data = np.ascontiguousarray(data)
+        want = rows * cols * 4 if wtype == W_F32 else (rows * cols * 2 if wtype == W_BF16 else rows * (cols // 32) * 34)
+        if data.nbytes != want:
+            raise ValueError(f"weight data has {data.nbytes} bytes, the layout needs {want}")
+        h = C.c_void_p()
+        st = self._L.ggr_weights_upload(device, wtype, rows, cols, C.c_void_p(data.ctypes.data), C.byref(h))
+        if st != 0:
+            raise GgrError(st, self._L.ggr_attn_create_error().decode())
+        self._h, self.wtype, self.rows, self.cols = h, wtype, rows, cols
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._L.ggr_weights_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 class RawCuda:
@@ -396,6 +433,37 @@ class AttnContext:
         (qp, kind), (kp, _), (vp, _), (gp, _), (op, _) = _ptr(q), _ptr(k), _ptr(v), _ptr(gate), _ptr(out)
         self._check(self._L.ggr_attn_decode_gated(self._h, layer, C.c_void_p(pos.ctypes.data), B, qp, kp, vp, gp,
                                                    gate_head_stride or self.config.head_dim, op, kind))
+        return out
+
+    def proj_matmul(self, w: "Weights", x, out=None):
+        """out [n][w.rows] = x [n][w.cols] W^T (matmul_quantized_with_scratch, src/engine/kernels/quant.rs:7225)."""
+        n = x.shape[0]
+        if out is None:
+            out = self._out_like(x, (n, w.rows))
+        self._follow_torch_stream(x)
+        (xp, kind), (op, _) = _ptr(x), _ptr(out)
+        self._check(self._L.ggr_proj_matmul(self._h, w._h, xp, n, op, kind))
+        return out
+
+    def layer_decode(self, layer: int, pos, xb, wq, wk, wv, wo, out=None):
+        """q/k/v projections, rope + append + attention, output projection for one token per sequence."""
+        pos = np.ascontiguousarray(np.asarray(pos, dtype=np.int32).reshape(-1))
+        if out is None:
+            out = self._out_like(xb, (pos.shape[0], wo.rows))
+        self._follow_torch_stream(xb)
+        (xp, kind), (op, _) = _ptr(xb), _ptr(out)
+        self._check(self._L.ggr_attn_layer_decode(self._h, layer, C.c_void_p(pos.ctypes.data), pos.shape[0], xp, wq._h,
+                                                   wk._h, wv._h, wo._h, op, kind))
+        return out
+
+    def layer_prefill(self, layer: int, base_pos: int, xb, wq, wk, wv, wo, seq: int = 0, out=None):
+        m = xb.shape[0]
+        if out is None:
+            out = self._out_like(xb, (m, wo.rows))
+        self._follow_torch_stream(xb)
+        (xp, kind), (op, _) = _ptr(xb), _ptr(out)
+        self._check(self._L.ggr_attn_layer_prefill(self._h, layer, seq, base_pos, m, xp, wq._h, wk._h, wv._h, wo._h, op,
+                                                    kind))
         return out
 
     def reserve(self, B: int):

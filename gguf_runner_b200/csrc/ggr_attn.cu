@@ -21,6 +21,7 @@
 #include "common.cuh"
 #include "prefill_tc.cuh"
 #include "prefill_tc_wide.cuh"
+#include "proj.cuh"
 #include "rope_append.cuh"
 
 using namespace ggr;
@@ -56,6 +57,14 @@ struct ggr_attn_ctx {
     size_t stage_cap[5] = {0, 0, 0, 0, 0};
     float* d_gate_f32 = nullptr;  // f32 image of a bf16 gate for the kernels that take f32 gates
     size_t gate_f32_cap = 0;
+    // projections: staged hidden rows (in / out), q | k | v rows, attention output rows, bf16 activation rows
+    float* d_px = nullptr;
+    float* d_pqkv = nullptr;
+    float* d_patt = nullptr;
+    float* d_pout = nullptr;
+    __nv_bfloat16* d_pact = nullptr;
+    __nv_bfloat16* d_pqkv_h = nullptr;
+    size_t px_cap = 0, pqkv_cap = 0, patt_cap = 0, pout_cap = 0, pact_cap = 0, pqkv_h_cap = 0;
     // pinned host staging of host-pointer decode calls: q | k | v | gate travel as one copy, the output as one
     unsigned char* h_pin = nullptr;
     size_t pin_cap = 0;
@@ -1339,6 +1348,12 @@ void ggr_attn_destroy(ggr_attn_ctx* c) {
     cudaFree(c->d_counters);
     for (auto* p : c->d_stage) cudaFree(p);
     cudaFree(c->d_gate_f32);
+    cudaFree(c->d_px);
+    cudaFree(c->d_pqkv);
+    cudaFree(c->d_patt);
+    cudaFree(c->d_pout);
+    cudaFree(c->d_pact);
+    cudaFree(c->d_pqkv_h);
     cudaFree(c->d_pin_in);
     if (c->h_pin) cudaFreeHost(c->h_pin);
     for (int r = 0; r < kMaxPeers; ++r)
@@ -2160,5 +2175,309 @@ extern "C" int ggr_attn_set_layer_fixups(ggr_attn_ctx* c, int32_t layer, const f
     if ((rc = upload(&f.q_norm, q_norm, c->D))) return rc;
     if ((rc = upload(&f.k_norm, k_norm, c->D))) return rc;
     f.eps = eps;
+    return GGR_OK;
+}
+
+
+// ---- projections either side of the path -----------------------------------------------------------------------------
+
+struct ggr_weights {
+    int device = 0, wtype = 0, rows = 0, cols = 0;
+    void* d_main = nullptr;            // F32 / BF16 values, or the Q8_0 code plane
+    __half* d_scales = nullptr;        // Q8_0 block scales [rows][cols / 32]
+    __nv_bfloat16* d_bf16 = nullptr;   // bf16 image for the tensor-core kernel (d_main itself for BF16)
+    CUtensorMap tmB;                   // [rows][cols] bf16, box 64 x 256
+    bool have_tmap = false;
+};
+
+namespace {
+
+float half_bits_to_float(uint16_t h) {  // IEEE half -> single (src/engine/io/gguf.rs:27-52)
+    const uint32_t sign = ((uint32_t)(h & 0x8000u)) << 16;
+    int exp = (h >> 10) & 0x1f;
+    uint32_t mant = h & 0x03ffu, bits;
+    if (exp == 0) {
+        if (mant == 0) {
+            bits = sign;
+        } else {
+            while ((mant & 0x0400u) == 0) {
+                mant <<= 1;
+                exp -= 1;
+            }
+            exp += 1;
+            mant &= ~0x0400u;
+            bits = sign | ((uint32_t)(exp + 112) << 23) | (mant << 13);
+        }
+    } else if (exp == 31) {
+        bits = sign | 0x7f800000u | (mant << 13);
+    } else {
+        bits = sign | ((uint32_t)(exp + 112) << 23) | (mant << 13);
+    }
+    float f;
+    std::memcpy(&f, &bits, 4);
+    return f;
+}
+
+uint16_t float_to_bf16_bits(float f) {  // round to nearest even (src/engine/io/gguf.rs:107-116)
+    uint32_t u;
+    std::memcpy(&u, &f, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x0040u);
+    u += 0x7fffu + ((u >> 16) & 1u);
+    return (uint16_t)(u >> 16);
+}
+
+// xout [n][w->rows] = x [n][w->cols] W^T, device pointers
+int matmul_device(ggr_attn_ctx* c, const ggr_weights* w, const float* x, int n, float* out, __nv_bfloat16* out_h, int ld_out,
+                  int sanitize) {
+    if (w->device != c->cfg.device) return fail(c, GGR_ERR_INVALID, "the weights live on another device than the context");
+    if (n <= 16 && !out_h) {
+        GemvArgs a{};
+        a.w = w->d_main;
+        a.scales = w->d_scales;
+        a.rows = w->rows;
+        a.cols = w->cols;
+        a.x = x;
+        a.n = n;
+        a.out = out;
+        a.ld_out = ld_out;
+        a.sanitize = sanitize;
+        CUDA_TRY(c, launch_gemv(w->wtype, a, c->stream));
+        c->launches++;
+        return GGR_OK;
+    }
+    if (!w->have_tmap) return fail(c, GGR_ERR_UNSUPPORTED, "no tensor map for these weights (driver entry point missing)");
+    int rc = ensure(c, &c->d_pact, &c->pact_cap, (size_t)n * w->cols);
+    if (rc) return rc;
+    const size_t elems = (size_t)n * w->cols;
+    proj_to_bf16_kernel<<<(unsigned)std::min<size_t>(2048, (elems / 4 + 255) / 256 + 1), 256, 0, c->stream>>>(x, c->d_pact, elems);
+    CUDA_TRY(c, cudaGetLastError());
+    c->launches++;
+    CUtensorMap tmA;
+    if (!make_tmap_bf16(&tmA, c->d_pact, (uint64_t)w->cols, (uint64_t)n, kGemmBM))
+        return fail(c, GGR_ERR_CUDA, "cuTensorMapEncodeTiled failed for the activation rows");
+    GemmArgs g{};
+    g.m = n;
+    g.N = w->rows;
+    g.K = w->cols;
+    g.out = out;
+    g.out_h = out_h;
+    g.ld_out = ld_out;
+    g.sanitize = sanitize;
+    g.err = c->d_err;
+    CUDA_TRY(c, launch_gemm(tmA, w->tmB, g, c->cfg.device, c->stream));
+    c->launches++;
+    return GGR_OK;
+}
+
+int check_layer_weights(ggr_attn_ctx* c, const ggr_weights* wq, const ggr_weights* wk, const ggr_weights* wv,
+                        const ggr_weights* wo) {
+    if (!wq || !wk || !wv || !wo) return fail(c, GGR_ERR_INVALID, "null weights");
+    if (wq->rows != c->q_dim || wk->rows != c->kv_dim || wv->rows != c->kv_dim || wo->cols != c->q_dim ||
+        wk->cols != wq->cols || wv->cols != wq->cols)
+        return fail(c, GGR_ERR_INVALID, "projection shapes do not match the attention shape (wq [q_dim][dim], wk / wv "
+                                        "[kv_dim][dim], wo [dim][q_dim])");
+    return GGR_OK;
+}
+
+}  // namespace
+
+extern "C" int ggr_weights_upload(int32_t device, int32_t wtype, int32_t rows, int32_t cols, const void* host_data,
+                                  ggr_weights** out) {
+    auto bad = [&](int st, const char* msg) {
+        g_create_err = msg;
+        return st;
+    };
+    if (!out || !host_data) return bad(GGR_ERR_INVALID, "null argument");
+    *out = nullptr;
+    if (wtype < GGR_W_F32 || wtype > GGR_W_Q8_0) return bad(GGR_ERR_INVALID, "unknown weight type");
+    if (rows <= 0 || cols <= 0 || rows % 8 != 0 || cols % (wtype == GGR_W_Q8_0 ? 32 : 8) != 0)
+        return bad(GGR_ERR_UNSUPPORTED, "rows must be a multiple of 8, cols of 8 (32 for Q8_0)");
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || device < 0 || device >= ndev) return bad(GGR_ERR_CUDA, "no such CUDA device");
+    DeviceGuard guard(device);
+    ggr_weights* w = new ggr_weights();
+    w->device = device;
+    w->wtype = wtype;
+    w->rows = rows;
+    w->cols = cols;
+    const size_t n = (size_t)rows * cols;
+    auto fail_up = [&](const char* msg) {
+        cudaGetLastError();
+        ggr_weights_free(w);
+        return bad(GGR_ERR_ALLOC, msg);
+    };
+    std::vector<uint16_t> image;  // bf16 image of F32 / Q8_0 weights
+    if (wtype == GGR_W_BF16) {
+        if (cudaMalloc(&w->d_main, n * 2) != cudaSuccess) return fail_up("unable to allocate the weights");
+        if (cudaMemcpy(w->d_main, host_data, n * 2, cudaMemcpyHostToDevice) != cudaSuccess) return fail_up("weight upload failed");
+        w->d_bf16 = static_cast<__nv_bfloat16*>(w->d_main);
+    } else if (wtype == GGR_W_F32) {
+        if (cudaMalloc(&w->d_main, n * 4) != cudaSuccess) return fail_up("unable to allocate the weights");
+        if (cudaMemcpy(w->d_main, host_data, n * 4, cudaMemcpyHostToDevice) != cudaSuccess) return fail_up("weight upload failed");
+        image.resize(n);
+        const float* src = static_cast<const float*>(host_data);
+        for (size_t i = 0; i < n; ++i) image[i] = float_to_bf16_bits(src[i]);
+    } else {
+        // 34-byte blocks -> a code plane [rows][cols] and a scale plane [rows][cols / 32]
+        const size_t nb = n / 32;
+        std::vector<int8_t> codes(n);
+        std::vector<uint16_t> scales(nb);
+        image.resize(n);
+        const uint8_t* src = static_cast<const uint8_t*>(host_data);
+        for (size_t b = 0; b < nb; ++b) {
+            const uint8_t* blk = src + b * 34;
+            scales[b] = (uint16_t)(blk[0] | (blk[1] << 8));
+            const float d = half_bits_to_float(scales[b]);
+            for (int j = 0; j < 32; ++j) {
+                const int8_t q = (int8_t)blk[2 + j];
+                codes[b * 32 + j] = q;
+                image[b * 32 + j] = float_to_bf16_bits((float)q * d);
+            }
+        }
+        if (cudaMalloc(&w->d_main, n) != cudaSuccess || cudaMalloc((void**)&w->d_scales, nb * 2) != cudaSuccess)
+            return fail_up("unable to allocate the weights");
+        if (cudaMemcpy(w->d_main, codes.data(), n, cudaMemcpyHostToDevice) != cudaSuccess ||
+            cudaMemcpy(w->d_scales, scales.data(), nb * 2, cudaMemcpyHostToDevice) != cudaSuccess)
+            return fail_up("weight upload failed");
+    }
+    if (!image.empty()) {
+        if (cudaMalloc((void**)&w->d_bf16, n * 2) != cudaSuccess) return fail_up("unable to allocate the bf16 weight image");
+        if (cudaMemcpy(w->d_bf16, image.data(), n * 2, cudaMemcpyHostToDevice) != cudaSuccess) return fail_up("weight upload failed");
+    }
+    w->have_tmap = make_tmap_bf16(&w->tmB, w->d_bf16, (uint64_t)cols, (uint64_t)rows, kGemmBN);
+    g_create_err.clear();
+    *out = w;
+    return GGR_OK;
+}
+
+extern "C" void ggr_weights_free(ggr_weights* w) {
+    if (!w) return;
+    DeviceGuard guard(w->device);
+    if (w->d_bf16 && w->d_bf16 != w->d_main) cudaFree(w->d_bf16);
+    cudaFree(w->d_main);
+    cudaFree(w->d_scales);
+    delete w;
+}
+
+extern "C" int ggr_proj_matmul(ggr_attn_ctx* c, const ggr_weights* w, const float* x, int32_t n, float* xout, int32_t ptr_kind) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    if (!w || !x || !xout || n <= 0) return fail(c, GGR_ERR_INVALID, "invalid matmul arguments");
+    const size_t in_elems = (size_t)n * w->cols, out_elems = (size_t)n * w->rows;
+    const float* dx = x;
+    float* dout = xout;
+    int rc;
+    if (ptr_kind == GGR_PTR_HOST) {
+        if ((rc = ensure(c, &c->d_px, &c->px_cap, in_elems))) return rc;
+        if ((rc = ensure(c, &c->d_pout, &c->pout_cap, out_elems))) return rc;
+        CUDA_TRY(c, cudaMemcpyAsync(c->d_px, x, in_elems * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+        dx = c->d_px;
+        dout = c->d_pout;
+    }
+    if ((rc = matmul_device(c, w, dx, n, dout, nullptr, w->rows, 0))) return rc;
+    if (ptr_kind == GGR_PTR_HOST) {
+        CUDA_TRY(c, cudaMemcpyAsync(xout, dout, out_elems * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+        CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+        return take_device_error(c, "a bounded wait inside the matmul kernel ran out");
+    }
+    return GGR_OK;
+}
+
+extern "C" int ggr_attn_layer_decode(ggr_attn_ctx* c, int32_t layer, const int32_t* pos, int32_t B, const float* xb,
+                                     const ggr_weights* wq, const ggr_weights* wk, const ggr_weights* wv,
+                                     const ggr_weights* wo, float* xb2, int32_t ptr_kind) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    int rc = check_layer(c, layer);
+    if (rc) return rc;
+    if (!pos || !xb || !xb2) return fail(c, GGR_ERR_INVALID, "null buffer");
+    if (B <= 0 || B > c->cfg.max_batch) return fail(c, GGR_ERR_RANGE, "batch larger than max_batch");
+    if (c->cfg.shard_mode != GGR_SHARD_NONE) return fail(c, GGR_ERR_UNSUPPORTED, "not available on a KV-sequence shard");
+    if ((rc = check_layer_weights(c, wq, wk, wv, wo))) return rc;
+    const int dim = wq->cols, dim_out = wo->rows;
+    const size_t qkv = (size_t)c->q_dim + 2 * c->kv_dim;
+    const float* dx = xb;
+    float* dout = xb2;
+    if ((rc = ensure(c, &c->d_pqkv, &c->pqkv_cap, (size_t)B * qkv))) return rc;
+    if ((rc = ensure(c, &c->d_patt, &c->patt_cap, (size_t)B * c->q_dim))) return rc;
+    if (ptr_kind == GGR_PTR_HOST) {
+        const size_t in_bytes = (size_t)B * dim * sizeof(float), out_bytes = (size_t)B * dim_out * sizeof(float);
+        if ((rc = ensure_pinned(c, in_bytes, out_bytes))) return rc;
+        if ((rc = ensure(c, &c->d_pout, &c->pout_cap, (size_t)B * dim_out))) return rc;
+        std::memcpy(c->h_pin, xb, in_bytes);
+        CUDA_TRY(c, cudaMemcpyAsync(c->d_pin_in, c->h_pin, in_bytes, cudaMemcpyHostToDevice, c->stream));
+        dx = reinterpret_cast<const float*>(c->d_pin_in);
+        dout = c->d_pout;
+    }
+    float* dq = c->d_pqkv;
+    float* dk = dq + (size_t)B * c->q_dim;
+    float* dv = dk + (size_t)B * c->kv_dim;
+    if ((rc = matmul_device(c, wq, dx, B, dq, nullptr, c->q_dim, 0))) return rc;
+    if ((rc = matmul_device(c, wk, dx, B, dk, nullptr, c->kv_dim, 0))) return rc;
+    if ((rc = matmul_device(c, wv, dx, B, dv, nullptr, c->kv_dim, 0))) return rc;
+    if ((rc = decode_common(c, layer, pos, B, dq, dk, dv, c->d_patt, nullptr, GGR_PTR_DEVICE))) return rc;
+    if ((rc = matmul_device(c, wo, c->d_patt, B, dout, nullptr, dim_out, 1))) return rc;
+    if (ptr_kind == GGR_PTR_HOST) {
+        const size_t out_bytes = (size_t)B * dim_out * sizeof(float);
+        unsigned char* h_out = c->h_pin + (c->pin_cap - out_bytes);
+        CUDA_TRY(c, cudaMemcpyAsync(h_out, dout, out_bytes, cudaMemcpyDeviceToHost, c->stream));
+        CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+        std::memcpy(xb2, h_out, out_bytes);
+        return take_device_error(c, "a bounded wait inside a kernel ran out");
+    }
+    return GGR_OK;
+}
+
+extern "C" int ggr_attn_layer_prefill(ggr_attn_ctx* c, int32_t layer, int32_t seq, int32_t base_pos, int32_t m,
+                                      const float* xb, const ggr_weights* wq, const ggr_weights* wk, const ggr_weights* wv,
+                                      const ggr_weights* wo, float* xb2, int32_t ptr_kind) {
+    if (!c) return GGR_ERR_INVALID;
+    DeviceGuard guard(c->cfg.device);
+    int rc = check_layer(c, layer);
+    if (rc) return rc;
+    if (!xb || !xb2 || m <= 0) return fail(c, GGR_ERR_INVALID, "invalid prefill arguments");
+    if ((rc = check_layer_weights(c, wq, wk, wv, wo))) return rc;
+    const int dim = wq->cols, dim_out = wo->rows;
+    const size_t qkv = (size_t)c->q_dim + 2 * c->kv_dim;
+    const float* dx = xb;
+    float* dout = xb2;
+    if ((rc = ensure(c, &c->d_patt, &c->patt_cap, (size_t)m * c->q_dim))) return rc;
+    if (ptr_kind == GGR_PTR_HOST) {
+        if ((rc = ensure(c, &c->d_px, &c->px_cap, (size_t)m * dim))) return rc;
+        if ((rc = ensure(c, &c->d_pout, &c->pout_cap, (size_t)m * dim_out))) return rc;
+        CUDA_TRY(c, cudaMemcpyAsync(c->d_px, xb, (size_t)m * dim * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+        dx = c->d_px;
+        dout = c->d_pout;
+    }
+    // Chunks on the tensor-core kernel hand q / k / v on in bf16 when the cache is bf16 (what the tcgen05 attention
+    // kernel reads anyway); the weight-streaming kernel and the other cache formats stay in f32.
+    const bool fixups = (size_t)layer < c->fixups.size() && c->fixups[layer].any();
+    const bool half_out = m > 16 && c->kv.fmt == KV_BF16 && !fixups;
+    if (half_out) {
+        if ((rc = ensure(c, &c->d_pqkv_h, &c->pqkv_h_cap, (size_t)m * qkv))) return rc;
+        __nv_bfloat16* hq = c->d_pqkv_h;
+        __nv_bfloat16* hk = hq + (size_t)m * c->q_dim;
+        __nv_bfloat16* hv = hk + (size_t)m * c->kv_dim;
+        if ((rc = matmul_device(c, wq, dx, m, nullptr, hq, c->q_dim, 0))) return rc;
+        if ((rc = matmul_device(c, wk, dx, m, nullptr, hk, c->kv_dim, 0))) return rc;
+        if ((rc = matmul_device(c, wv, dx, m, nullptr, hv, c->kv_dim, 0))) return rc;
+        rc = prefill_common(c, layer, seq, base_pos, m, hq, hk, hv, GGR_DTYPE_BF16, c->d_patt, GGR_PTR_DEVICE, false);
+    } else {
+        if ((rc = ensure(c, &c->d_pqkv, &c->pqkv_cap, (size_t)m * qkv))) return rc;
+        float* dq = c->d_pqkv;
+        float* dk = dq + (size_t)m * c->q_dim;
+        float* dv = dk + (size_t)m * c->kv_dim;
+        if ((rc = matmul_device(c, wq, dx, m, dq, nullptr, c->q_dim, 0))) return rc;
+        if ((rc = matmul_device(c, wk, dx, m, dk, nullptr, c->kv_dim, 0))) return rc;
+        if ((rc = matmul_device(c, wv, dx, m, dv, nullptr, c->kv_dim, 0))) return rc;
+        rc = prefill_common(c, layer, seq, base_pos, m, dq, dk, dv, GGR_DTYPE_F32, c->d_patt, GGR_PTR_DEVICE, false);
+    }
+    if (rc) return rc;
+    if ((rc = matmul_device(c, wo, c->d_patt, m, dout, nullptr, dim_out, 1))) return rc;
+    if (ptr_kind == GGR_PTR_HOST) {
+        CUDA_TRY(c, cudaMemcpyAsync(xb2, dout, (size_t)m * dim_out * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+        CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+        return take_device_error(c, "a bounded wait inside a kernel ran out");
+    }
     return GGR_OK;
 }

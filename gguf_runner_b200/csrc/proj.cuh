@@ -1,0 +1,288 @@
+// The matmuls either side of the attention path: q / k / v projections in front of it and the output
+// projection behind it (src/engine/runtime/inference.rs:3144-3476 and :3520-3527; one activation row against
+// every weight row, matmul_quantized_with_scratch, src/engine/kernels/quant.rs:7225; batched rows in
+// transformer_prefill_batch). With the weights resident on the device only the hidden-state rows cross PCIe.
+//
+// Two kernels:
+//   proj_gemv_kernel  decode, a few activation rows: bound by reading the weights once. One warp per two weight
+//                     rows, 16-byte loads along the row, the activation rows come from L1, shuffle reduction.
+//                     Weight formats F32, BF16 and Q8_0 (codes and f16 block scales repacked into two planes at
+//                     upload, so that the codes are 16-byte aligned).
+//   proj_gemm_kernel  prefill chunks: tcgen05 GEMM, bf16 x bf16 -> f32 in TMEM. A = activations [m][K] (bf16), B =
+//                     weights [N][K] (bf16; Q8_0 / F32 weights use a bf16 image made at upload), 128 x 256 output
+//                     tile per CTA, 64-column k-steps through a four-stage TMA ring, one MMA issuer, four epilogue
+//                     warps reading the accumulator out of TMEM. Every wait is bounded.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "sm100_utils.cuh"
+
+namespace ggr {
+
+enum ProjWeightType : int { PW_F32 = 0, PW_BF16 = 1, PW_Q8_0 = 2 };
+
+struct GemvArgs {
+    const void* w;         // F32 / BF16 values [rows][cols], or Q8_0 codes int8 [rows][cols]
+    const __half* scales;  // Q8_0: [rows][cols / 32]
+    int rows, cols;
+    const float* x;        // [n][cols]
+    int n;
+    float* out;            // [n][ld_out]
+    int ld_out;
+    int sanitize;          // non-finite results become 0 (sanitize_finite_inplace after the output projection)
+};
+
+constexpr int kGemvWarps = 8;
+constexpr int kGemvRPW = 2;  // weight rows per warp
+
+template <int WT, int TT>
+__global__ void __launch_bounds__(kGemvWarps * 32) proj_gemv_kernel(GemvArgs a) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int r0 = (blockIdx.x * kGemvWarps + warp) * kGemvRPW;
+    if (r0 >= a.rows) return;
+    const int cols = a.cols;
+    for (int t0 = 0; t0 < a.n; t0 += TT) {
+        float acc[kGemvRPW][TT];
+#pragma unroll
+        for (int r = 0; r < kGemvRPW; ++r)
+#pragma unroll
+            for (int t = 0; t < TT; ++t) acc[r][t] = 0.0f;
+        constexpr int CPL = WT == PW_Q8_0 ? 16 : 8;  // columns per lane and step
+        for (int c0 = lane * CPL; c0 < cols; c0 += 32 * CPL) {
+            float wv[kGemvRPW][CPL];
+#pragma unroll
+            for (int r = 0; r < kGemvRPW; ++r) {
+                const int row = min(r0 + r, a.rows - 1);
+                if (WT == PW_F32) {
+                    const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(a.w) + (size_t)row * cols + c0);
+                    const float4 u0 = __ldg(p), u1 = __ldg(p + 1);
+                    wv[r][0] = u0.x; wv[r][1] = u0.y; wv[r][2] = u0.z; wv[r][3] = u0.w;
+                    wv[r][4] = u1.x; wv[r][5] = u1.y; wv[r][6] = u1.z; wv[r][7] = u1.w;
+                } else if (WT == PW_BF16) {
+                    const uint4 u = __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.w) + (size_t)row * cols + c0));
+                    const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        wv[r][2 * i] = __uint_as_float(w4[i] << 16);
+                        wv[r][2 * i + 1] = __uint_as_float(w4[i] & 0xffff0000u);
+                    }
+                } else {
+                    const uint4 u = __ldg(reinterpret_cast<const uint4*>(static_cast<const int8_t*>(a.w) + (size_t)row * cols + c0));
+                    const float d = __half2float(a.scales[(size_t)row * (cols >> 5) + (c0 >> 5)]);
+                    const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        wv[r][i] = (float)(signed char)((w4[i >> 2] >> (8 * (i & 3))) & 0xff) * d;
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < TT; ++t) {
+                if (t0 + t < a.n) {
+                    const float4* xp = reinterpret_cast<const float4*>(a.x + (size_t)(t0 + t) * cols + c0);
+#pragma unroll
+                    for (int i = 0; i < CPL; i += 4) {
+                        const float4 xx = __ldg(xp + (i >> 2));
+#pragma unroll
+                        for (int r = 0; r < kGemvRPW; ++r) {
+                            acc[r][t] = fmaf(xx.x, wv[r][i], acc[r][t]);
+                            acc[r][t] = fmaf(xx.y, wv[r][i + 1], acc[r][t]);
+                            acc[r][t] = fmaf(xx.z, wv[r][i + 2], acc[r][t]);
+                            acc[r][t] = fmaf(xx.w, wv[r][i + 3], acc[r][t]);
+                        }
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < kGemvRPW; ++r)
+#pragma unroll
+            for (int t = 0; t < TT; ++t) {
+                float v = warp_sum(acc[r][t]);
+                if (lane == 0 && r0 + r < a.rows && t0 + t < a.n) {
+                    if (a.sanitize && !isfinite(v)) v = 0.0f;
+                    a.out[(size_t)(t0 + t) * a.ld_out + r0 + r] = v;
+                }
+            }
+    }
+}
+
+template <int WT>
+inline cudaError_t launch_gemv_wt(const GemvArgs& a, cudaStream_t stream) {
+    const int grid = (a.rows + kGemvWarps * kGemvRPW - 1) / (kGemvWarps * kGemvRPW);
+    if (a.n == 1)
+        proj_gemv_kernel<WT, 1><<<grid, kGemvWarps * 32, 0, stream>>>(a);
+    else if (a.n == 2)
+        proj_gemv_kernel<WT, 2><<<grid, kGemvWarps * 32, 0, stream>>>(a);
+    else
+        proj_gemv_kernel<WT, 4><<<grid, kGemvWarps * 32, 0, stream>>>(a);
+    return cudaGetLastError();
+}
+
+inline cudaError_t launch_gemv(int wtype, const GemvArgs& a, cudaStream_t stream) {
+    switch (wtype) {
+        case PW_F32: return launch_gemv_wt<PW_F32>(a, stream);
+        case PW_BF16: return launch_gemv_wt<PW_BF16>(a, stream);
+        default: return launch_gemv_wt<PW_Q8_0>(a, stream);
+    }
+}
+
+// f32 rows -> bf16 rows (activations on their way into the tensor-core GEMM)
+__global__ void proj_to_bf16_kernel(const float* src, __nv_bfloat16* dst, size_t n) {
+    for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (size_t)gridDim.x * blockDim.x * 4) {
+        if (i + 4 <= n) {
+            const float4 v = *reinterpret_cast<const float4*>(src + i);
+            __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+            uint2 u;
+            u.x = *reinterpret_cast<uint32_t*>(&a);
+            u.y = *reinterpret_cast<uint32_t*>(&b);
+            *reinterpret_cast<uint2*>(dst + i) = u;
+        } else {
+            for (size_t j = i; j < n; ++j) dst[j] = __float2bfloat16_rn(src[j]);
+        }
+    }
+}
+
+// ---- tcgen05 GEMM ------------------------------------------------------------------------------------------
+
+struct GemmArgs {
+    int m, N, K;
+    float* out;             // [m][ld_out] f32, or null
+    __nv_bfloat16* out_h;   // [m][ld_out] bf16, or null
+    int ld_out;
+    int sanitize;
+    int* err;               // raised when a bounded wait runs out
+};
+
+constexpr int kGemmBM = 128, kGemmBN = 256, kGemmBK = 64, kGemmStages = 4;
+constexpr int kGemmThreads = 192;  // four epilogue warps, a TMA producer, an MMA issuer
+constexpr uint32_t kGemmABytes = kGemmBM * kGemmBK * 2, kGemmBBytes = kGemmBN * kGemmBK * 2;
+inline size_t proj_gemm_smem() { return (size_t)kGemmStages * (kGemmABytes + kGemmBBytes) + 1024; }
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+proj_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmArgs a) {
+    using namespace tc;
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t bars[2 * kGemmStages + 1];
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort;
+
+    const int tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sA = smem_base, sB = smem_base + kGemmStages * kGemmABytes;
+    const uint32_t bar0 = smem_u32(bars);
+    auto full = [&](int s) { return bar0 + 8u * s; };
+    auto empty = [&](int s) { return bar0 + 8u * (kGemmStages + s); };
+    const uint32_t acc_full = bar0 + 8u * (2 * kGemmStages);
+
+    if (tid == 0) {
+        s_abort = 0;
+        for (int s = 0; s < kGemmStages; ++s) {
+            mbar_init(full(s), 1);
+            mbar_init(empty(s), 1);
+        }
+        mbar_init(acc_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) {
+        tmem_alloc(smem_u32(&s_tmem_base), kGemmBN);
+        tmem_relinquish();
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem = s_tmem_base;
+    volatile int* abortp = &s_abort;
+    const int n0 = blockIdx.x * kGemmBN, m0 = blockIdx.y * kGemmBM;
+    const int nk = (a.K + kGemmBK - 1) / kGemmBK;
+
+    if (warp == 4) {
+        if (lane == 0) {
+            for (int k = 0; k < nk; ++k) {
+                const int s = k % kGemmStages;
+                if (!mbar_wait(empty(s), ((k / kGemmStages) & 1) ^ 1, abortp)) break;
+                mbar_expect_tx(full(s), kGemmABytes + kGemmBBytes);
+                tma_load_2d(sA + s * kGemmABytes, &tmA, k * kGemmBK, m0, full(s));
+                tma_load_2d(sB + s * kGemmBBytes, &tmB, k * kGemmBK, n0, full(s));
+            }
+        }
+    } else if (warp == 5) {
+        constexpr uint32_t IDESC = idesc_bf16(kGemmBN, 0);
+        const uint64_t dA = smem_desc(sA, 16, 1024), dB = smem_desc(sB, 16, 1024);
+        const uint32_t tm = __shfl_sync(0xffffffffu, s_tmem_base, 0);
+        bool ok = true;
+        for (int k = 0; k < nk && ok; ++k) {
+            const int s = k % kGemmStages;
+            if (!(ok = mbar_wait_warp(full(s), (k / kGemmStages) & 1, abortp))) break;
+            fence_after_sync();
+            const uint64_t a0 = dA + (uint64_t)((s * kGemmABytes) >> 4), b0 = dB + (uint64_t)((s * kGemmBBytes) >> 4);
+#pragma unroll
+            for (int ks = 0; ks < kGemmBK / 16; ++ks)
+                mma_ss_e(tm, a0 + (uint64_t)((ks * 32) >> 4), b0 + (uint64_t)((ks * 32) >> 4), IDESC, (k > 0 || ks > 0) ? 1u : 0u);
+            mma_commit_e(empty(s));
+        }
+        if (ok) mma_commit_e(acc_full);
+    } else {
+        // epilogue: thread = output row of the tile (TMEM lane), 32 columns per tcgen05.ld
+        const int row = m0 + warp * 32 + lane;
+        if (mbar_wait(acc_full, 0, abortp)) {
+            fence_after_sync();
+            const uint32_t t0 = tmem + ((uint32_t)(warp * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < kGemmBN / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(t0 + c * 32, v);
+                tmem_wait_ld();
+                const int col0 = n0 + c * 32;
+                if (row < a.m && col0 < a.N) {
+                    const int ncol = min(32, a.N - col0);
+                    if (a.out) {
+                        float* o = a.out + (size_t)row * a.ld_out + col0;
+                        for (int i = 0; i < ncol; i += 4) {
+                            float4 f = make_float4(__uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]),
+                                                   __uint_as_float(v[i + 3]));
+                            if (a.sanitize) {
+                                f.x = isfinite(f.x) ? f.x : 0.0f;
+                                f.y = isfinite(f.y) ? f.y : 0.0f;
+                                f.z = isfinite(f.z) ? f.z : 0.0f;
+                                f.w = isfinite(f.w) ? f.w : 0.0f;
+                            }
+                            *reinterpret_cast<float4*>(o + i) = f;
+                        }
+                    }
+                    if (a.out_h) {
+                        __nv_bfloat16* o = a.out_h + (size_t)row * a.ld_out + col0;
+                        for (int i = 0; i < ncol; i += 2) {
+                            __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+                            *reinterpret_cast<__nv_bfloat162*>(o + i) = p;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (s_abort) {
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);  // let copies in flight land
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    if (warp == 5) tmem_dealloc(tmem, kGemmBN);
+    if (tid == 0 && s_abort && a.err) atomicExch(a.err, 1);
+}
+
+// tmA: activations [m][K] with a 64 x 128 box; tmB: weights [N][K] with a 64 x 256 box
+inline cudaError_t launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& a, int device,
+                               cudaStream_t stream) {
+    static KernelSmemSetup setup;
+    const size_t smem = proj_gemm_smem();
+    cudaError_t e = setup.ensure(proj_gemm_kernel, device, 0, (int)smem);
+    if (e != cudaSuccess) return e;
+    dim3 grid((a.N + kGemmBN - 1) / kGemmBN, (a.m + kGemmBM - 1) / kGemmBM);
+    proj_gemm_kernel<<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, a);
+    return cudaGetLastError();
+}
+
+}  // namespace ggr

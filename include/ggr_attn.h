@@ -328,6 +328,44 @@ int ggr_attn_kv_read_turbo(ggr_attn_ctx* ctx, int32_t seq, int32_t layer, int32_
 int ggr_attn_attention_tokens_static(ggr_attn_ctx* ctx, int32_t layer, const int32_t* pos, int32_t B,
                                      const float* q_dev, float* out_dev);
 
+/*
+ * The matmuls either side of the path, so that q / k / v never visit the host: with the projection weights
+ * resident on the device a decode step moves one hidden-state row in and one out per layer instead of q, k, v
+ * and the attention output.
+ *
+ * ggr_weights is one weight matrix [rows][cols] on a device. host_data is the tensor as the reference maps it from
+ * the GGUF file (QuantizedTensor, row-major GGML rows): GGR_W_F32, GGR_W_BF16, or GGR_W_Q8_0 (blocks of one f16
+ * scale and 32 int8 codes, 34 bytes; src/engine/kernels/quant.rs:89, :105). cols must be a multiple of 32 for
+ * Q8_0 and of 8 otherwise, rows a multiple of 8. Q8_0 codes and scales are kept in two planes, and Q8_0 / F32
+ * matrices also keep a bf16 image (each weight rounded once) for the tensor-core kernel that multiplies chunks of
+ * rows.
+ */
+typedef struct ggr_weights ggr_weights;
+enum { GGR_W_F32 = 0, GGR_W_BF16 = 1, GGR_W_Q8_0 = 2 };
+int ggr_weights_upload(int32_t device, int32_t wtype, int32_t rows, int32_t cols, const void* host_data, ggr_weights** out);
+void ggr_weights_free(ggr_weights* w);
+/* xout[i][rows] = W x[i] for n rows of x [n][cols], f32 in and out. Replaces matmul_quantized_with_scratch
+ * (src/engine/kernels/quant.rs:7225) for one row and the batched prefill matmuls of transformer_prefill_batch
+ * (src/engine/runtime/inference.rs:2921-2979) for many: up to 16 rows run on a weight-streaming kernel with f32
+ * arithmetic (the reference's dot of f32 activations with the decoded weights); more rows run on the tensor cores
+ * with activations and weights in bf16 (tolerance of bf16 operands). */
+int ggr_proj_matmul(ggr_attn_ctx* ctx, const ggr_weights* w, const float* x, int32_t n, float* xout, int32_t ptr_kind);
+/*
+ * The attention half of a layer for one token of each of B sequences, from the normalised hidden state to the
+ * output projection: q, k, v = Wq xb, Wk xb, Wv xb (src/engine/runtime/inference.rs:3144-3476, the dense case with
+ * separate projections), bias / QK-norm fixups of the layer, rope + append + attention (:3499-3507), xb2 = Wo att
+ * with non-finite values zeroed (:3520-3527). xb is [B][wq.cols], xb2 is [B][wo.rows]; only these cross PCIe with
+ * GGR_PTR_HOST.
+ */
+int ggr_attn_layer_decode(ggr_attn_ctx* ctx, int32_t layer, const int32_t* pos, int32_t B, const float* xb,
+                          const ggr_weights* wq, const ggr_weights* wk, const ggr_weights* wv, const ggr_weights* wo,
+                          float* xb2, int32_t ptr_kind);
+/* The same for m consecutive tokens of one sequence (the attention half of transformer_prefill_batch,
+ * src/engine/runtime/inference.rs:2910-3030): xb is [m][wq.cols], xb2 is [m][wo.rows]. */
+int ggr_attn_layer_prefill(ggr_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t base_pos, int32_t m, const float* xb,
+                           const ggr_weights* wq, const ggr_weights* wk, const ggr_weights* wv, const ggr_weights* wo,
+                           float* xb2, int32_t ptr_kind);
+
 /* Number of kernels this context has launched since it was created. */
 int64_t ggr_attn_launch_count(const ggr_attn_ctx* ctx);
 /* Split-KV factor the most recent decode / attention launch of this context used. */

@@ -931,6 +931,71 @@ void ora_sigmoid_gate(ora_ctx* ctx, float* xb, const float* gate, int32_t gate_h
         if (!std::isfinite(xb[i])) xb[i] = 0.0f;
 }
 
+// ---- projections either side of the path (scalar branches of the reference's matmul) ----------------
+// IEEE half to single, as src/engine/io/gguf.rs:27-52 (subnormals normalised, infinities and NaNs kept).
+static float fp16_to_fp32(uint16_t h) {
+    const uint32_t sign = ((uint32_t)(h & 0x8000u)) << 16;
+    int32_t exp = (h >> 10) & 0x1f;
+    uint32_t mant = h & 0x03ffu;
+    uint32_t bits;
+    if (exp == 0) {
+        if (mant == 0) {
+            bits = sign;
+        } else {
+            while ((mant & 0x0400u) == 0) {
+                mant <<= 1;
+                exp -= 1;
+            }
+            exp += 1;
+            mant &= ~0x0400u;
+            bits = sign | ((uint32_t)(exp + (127 - 15)) << 23) | (mant << 13);
+        }
+    } else if (exp == 31) {
+        bits = sign | 0x7f800000u | (mant << 13);
+    } else {
+        bits = sign | ((uint32_t)(exp + (127 - 15)) << 23) | (mant << 13);
+    }
+    float f;
+    std::memcpy(&f, &bits, 4);
+    return f;
+}
+
+// xout[r] = dot(row r of W, x) for one activation row, W in the GGML row layouts the reference multiplies with
+// (matmul_quantized_with_scratch, src/engine/kernels/quant.rs:7225): wtype 0 = F32 (vec_dot_f32 :1167),
+// 1 = BF16 (vec_dot_bf16 scalar tail :1313-1316), 2 = Q8_0 (vec_dot_q8_0 scalar branch :2043-2059: per block of 32,
+// the f32 dot of x with the int8 codes, times the block's f16 scale). Sequential f32 sums.
+void ora_matmul(int32_t wtype, int32_t rows, int32_t cols, const void* w, const float* x, float* xout) {
+    const uint8_t* wb = static_cast<const uint8_t*>(w);
+    for (int r = 0; r < rows; ++r) {
+        float sum = 0.0f;
+        if (wtype == 0) {
+            const float* row = reinterpret_cast<const float*>(wb) + (size_t)r * cols;
+            for (int i = 0; i < cols; ++i) sum += x[i] * row[i];
+        } else if (wtype == 1) {
+            const uint16_t* row = reinterpret_cast<const uint16_t*>(wb) + (size_t)r * cols;
+            for (int i = 0; i < cols; ++i) {
+                const uint32_t bits = (uint32_t)row[i] << 16;
+                float wv;
+                std::memcpy(&wv, &bits, 4);
+                sum += x[i] * wv;
+            }
+        } else {
+            const int nb = cols / 32;
+            const uint8_t* row = wb + (size_t)r * nb * 34;
+            for (int b = 0; b < nb; ++b) {
+                const uint8_t* blk = row + (size_t)b * 34;
+                const float d = fp16_to_fp32((uint16_t)(blk[0] | (blk[1] << 8)));
+                float block_sum = 0.0f;
+                for (int j = 0; j < 32; ++j) block_sum += x[b * 32 + j] * (float)(int8_t)blk[2 + j];
+                sum += block_sum * d;
+            }
+        }
+        xout[r] = sum;
+    }
+}
+
+float ora_fp16_to_fp32(uint16_t h) { return fp16_to_fp32(h); }
+
 void ora_rope_angles(ora_ctx* ctx, int32_t layer, int32_t pos, float* c, float* s) {
     rope_angles(ctx, layer, pos, c, s);
 }

@@ -94,6 +94,15 @@ pub struct GgrRopePlan {
     _private: [u8; 0],
 }
 
+#[repr(C)]
+pub struct GgrWeights {
+    _private: [u8; 0],
+}
+
+pub const GGR_W_F32: i32 = 0;
+pub const GGR_W_BF16: i32 = 1;
+pub const GGR_W_Q8_0: i32 = 2;
+
 #[link(name = "ggr_attn")]
 extern "C" {
     pub fn ggr_attn_config_init(cfg: *mut GgrAttnConfig);
@@ -160,6 +169,17 @@ extern "C" {
         k_rnorm: *mut f32, v_rnorm: *mut f32) -> i32;
     pub fn ggr_attn_attention_tokens_static(ctx: *mut GgrAttnCtx, layer: i32, pos: *const i32, b: i32,
         q_dev: *const f32, out_dev: *mut f32) -> i32;
+    pub fn ggr_weights_upload(device: i32, wtype: i32, rows: i32, cols: i32, host_data: *const c_void,
+        out: *mut *mut GgrWeights) -> i32;
+    pub fn ggr_weights_free(w: *mut GgrWeights);
+    pub fn ggr_proj_matmul(ctx: *mut GgrAttnCtx, w: *const GgrWeights, x: *const f32, n: i32, xout: *mut f32,
+        ptr_kind: i32) -> i32;
+    pub fn ggr_attn_layer_decode(ctx: *mut GgrAttnCtx, layer: i32, pos: *const i32, b: i32, xb: *const f32,
+        wq: *const GgrWeights, wk: *const GgrWeights, wv: *const GgrWeights, wo: *const GgrWeights,
+        xb2: *mut f32, ptr_kind: i32) -> i32;
+    pub fn ggr_attn_layer_prefill(ctx: *mut GgrAttnCtx, layer: i32, seq: i32, base_pos: i32, m: i32,
+        xb: *const f32, wq: *const GgrWeights, wk: *const GgrWeights, wv: *const GgrWeights,
+        wo: *const GgrWeights, xb2: *mut f32, ptr_kind: i32) -> i32;
     pub fn ggr_attn_launch_count(ctx: *const GgrAttnCtx) -> i64;
     pub fn ggr_attn_last_split_count(ctx: *const GgrAttnCtx) -> i32;
     pub fn ggr_attn_set_kernel_timing(ctx: *mut GgrAttnCtx, enable: i32) -> i32;

@@ -78,6 +78,10 @@ def _bind(L: C.CDLL) -> C.CDLL:
     L.ora_set_layer_fixups.argtypes = [vp, i32, vp, vp, vp, vp, vp, C.c_float]
     L.ora_qkv_bias_and_norm.argtypes = [vp, i32, vp, vp, vp]
     L.ora_qkv_bias_and_norm.restype = None
+    L.ora_matmul.argtypes = [i32, i32, i32, vp, vp, vp]
+    L.ora_matmul.restype = None
+    L.ora_fp16_to_fp32.argtypes = [C.c_uint16]
+    L.ora_fp16_to_fp32.restype = C.c_float
     L.ora_sigmoid_gate.argtypes = [vp, vp, vp, i32]
     L.ora_sigmoid_gate.restype = None
     L.ora_rope_angles.argtypes = [vp, i32, i32, vp, vp]
@@ -307,6 +311,31 @@ class Oracle:
         if self.L.ora_turbo_transform(self.h, layer, kv_head, first_slot, second_slot, _p(v)) != 0:
             raise ValueError("not a TurboQuant cache")
         return v
+
+
+def matmul(wtype: int, rows: int, cols: int, w_raw: np.ndarray, x: np.ndarray) -> np.ndarray:
+    """Reference matmul of every row of x [n][cols] with W (raw GGML bytes): returns [n][rows]."""
+    x = _f32(x).reshape(-1, cols)
+    w_raw = np.ascontiguousarray(w_raw)
+    out = np.empty((x.shape[0], rows), np.float32)
+    for i in range(x.shape[0]):
+        lib().ora_matmul(wtype, rows, cols, _p(w_raw), _p(x[i]), C.c_void_p(out[i].ctypes.data))
+    return out
+
+
+def quantize_q8_0(w: np.ndarray) -> np.ndarray:
+    """GGML Q8_0 bytes of a float matrix [rows][cols] (cols % 32 == 0): per block of 32 one f16 scale
+    d = max|w| / 127 and the codes round(w / d). Test helper: the reference only reads this layout."""
+    rows, cols = w.shape
+    blocks = w.reshape(rows, cols // 32, 32).astype(np.float32)
+    d = (np.abs(blocks).max(axis=2) / 127.0).astype(np.float16)
+    df = d.astype(np.float32)
+    inv = np.where(df > 0, 1.0 / np.where(df > 0, df, 1.0), 0.0)
+    q = np.clip(np.rint(blocks * inv[..., None]), -127, 127).astype(np.int8)
+    out = np.empty((rows, cols // 32, 34), np.uint8)
+    out[..., :2] = d.view(np.uint8).reshape(rows, cols // 32, 2)
+    out[..., 2:] = q.view(np.uint8)
+    return out.reshape(rows, -1)
 
 
 def bf16_round(a: np.ndarray) -> np.ndarray:
