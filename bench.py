@@ -15,6 +15,8 @@ The same line carries one object per remaining BASELINE.json config, each with i
                                      ranks (also at N = 1), with `decode_scaling`
   decode_head_shard      configs[2]  at B = 32 / 64 with the KV heads split over the ranks (N > 1)
   decode_turboquant      configs[2]  shape over the reference's default 3-bit cache
+  projections            the matmuls either side of the path (weight-streaming and tensor-core kernels) and the
+                         configs[0] attention half-layer from host hidden states
 
 `--impl reference` times the CPU restatement of the reference's attention (oracle/) on the host
 cores for the headline workload, on a bounded sample.
@@ -292,7 +294,7 @@ def instrumented(torch, ctx, fn, steps):
         fn()
     torch.cuda.synchronize()
     out = {}
-    for kind in (0, 1, 2):
+    for kind in (0, 1, 2, 3):
         ms, n = ctx.kernel_time(kind)
         out[kind] = (ms / n if n else 0.0, n / steps)
     ctx.set_kernel_timing(False)
@@ -630,6 +632,102 @@ def bench_decode_turbo(torch, args, local_rank, peaks, B=8):
     return res
 
 
+def bench_projections(torch, args, local_rank, peaks):
+    """The matmuls either side of the path with device-resident weights: the weight-streaming kernel on a
+    Llama-3-8B-shaped 14336 x 4096 matrix (Q8_0 and BF16), the tcgen05 GEMM on the same matrix for a 4096-token chunk, and the Qwen3-0.6B-shaped attention half-layer of configs[0] end to end from host hidden states."""
+    import gguf_runner_b200 as g
+    from gguf_runner_b200 import presets
+    from gguf_runner_b200.binding import KV_Q8_ROW, W_BF16, W_Q8_0, Weights
+    from tests.oracle_binding import bf16_bits, quantize_q8_0
+    rng = np.random.default_rng(77)
+    res = {}
+    ctx = g.AttnContext(presets.qwen3_0p6b_decode(n_layers=1, seq_len=64, device=local_rank))
+    rows, cols = 14336, 4096  # an FFN-sized matrix: at 4096 x 4096 a launch is bound by its fixed ~10 us, not by HBM
+    wf = (rng.standard_normal((rows, cols)) / 64.0).astype(np.float32)
+    # several matrices are cycled so that the weights come from HBM, not from the 126 MB L2
+    n_mats = 6
+    for name, wtype, raw, nbytes in (("q8_0", W_Q8_0, quantize_q8_0(wf), rows * cols * 34 // 32),
+                                     ("bf16", W_BF16, bf16_bits(wf), rows * cols * 2)):
+        mats = [Weights(wtype, rows, cols, raw, device=local_rank) for _ in range(n_mats)]
+        for n in (1, 4):
+            x = torch.randn(n, cols, device="cuda")
+            out = torch.empty(n, rows, device="cuda")
+            state = {"i": 0}
+
+            def step():
+                ctx.proj_matmul(mats[state["i"] % n_mats], x, out=out)
+                state["i"] += 1
+
+            for _ in range(6):
+                step()
+            kern_ms = instrumented(torch, ctx, step, 24)[3][0]
+            res[f"gemv_{name}_n{n}"] = hbm_roofline(peaks, nbytes, kern_ms, kernel="proj_gemv_kernel", shape=f"{rows}x{cols}, {n} row(s)",
+                                                    bytes_per_launch=nbytes, avg_launch_ms=kern_ms, traffic=None,
+                                                    note="event pair around every launch (which adds ~5 us), 6 matrices cycled so the weights come from HBM")
+        if name == "bf16":
+            m = 4096
+            x = torch.randn(m, cols, device="cuda")
+            out = torch.empty(m, rows, device="cuda")  # [4096 x 4096] x [14336 x 4096]^T
+            gemm_step = lambda: ctx.proj_matmul(mats[0], x, out=out)
+            for _ in range(3):
+                gemm_step()
+            ms = instrumented(torch, ctx, gemm_step, 10)[3][0]
+            flops = 2.0 * m * rows * cols
+            res["gemm_bf16_m4096"] = tensor_roofline(peaks, flops, ms, kernel="proj_gemm_kernel",
+                                                     shape=f"[{m} x {cols}] x [{rows} x {cols}]^T", avg_call_ms=ms, traffic=None)
+        for w in mats:
+            w.close()
+    ctx.close()
+    # configs[0] from hidden states: 28 layers, hidden 1024, Q8_0 weights, q8_row cache (the reference's formats)
+    T, L, dim = 2048, 28, 1024
+    cfg = presets.qwen3_0p6b_decode(n_layers=L, seq_len=T, kv_format=KV_Q8_ROW, device=local_rank)
+    ctx = g.AttnContext(cfg)
+    shapes = [(cfg.q_dim, dim), (cfg.kv_dim, dim), (cfg.kv_dim, dim), (dim, cfg.q_dim)]
+    layers = []
+    for l in range(L):
+        layers.append([Weights(W_Q8_0, r, c, quantize_q8_0((rng.standard_normal((r, c)) / np.sqrt(c)).astype(np.float32)),
+                               device=local_rank) for r, c in shapes])
+    xb = rng.standard_normal((1, dim)).astype(np.float32)
+    out = np.empty((1, dim), np.float32)
+    # fill the cache through the path itself (a prompt of T - 1 tokens per layer)
+    prompt = torch.randn(T - 1, dim, device="cuda")
+    for l in range(L):
+        ctx.layer_prefill(l, 0, prompt, *layers[l])
+    torch.cuda.synchronize()
+
+    def host_step():
+        for l in range(L):
+            ctx.layer_decode(l, [T - 1], xb, *layers[l], out=out)
+
+    for _ in range(3):
+        host_step()
+    t0 = time.perf_counter()
+    for _ in range(20):
+        host_step()
+    host_s = (time.perf_counter() - t0) / 20
+    dxb = torch.from_numpy(xb).cuda()
+    dout = torch.empty(1, dim, device="cuda")
+
+    def dev_step():
+        for l in range(L):
+            ctx.layer_decode(l, [T - 1], dxb, *layers[l], out=dout)
+
+    dev_ms = timed_steps(torch, dev_step, 20)
+    res["layer_decode_configs0"] = {
+        "workload": "configs[0] attention half-layer from the hidden state: 28 layers, hidden 1024, Q8_0 projection weights, "
+                    "q8_row cache, T=2048, batch 1 (q / k / v projections, rope + append + attention, output projection)",
+        "ms_per_step_device_resident": dev_ms, "tokens_per_s_device_resident": 1.0 / (dev_ms * 1e-3),
+        "e2e": {"value": 1.0 / host_s, "unit": "tokens/s", "ms_per_step": host_s * 1e3,
+                "h2d_bytes_per_step": L * dim * 4, "d2h_bytes_per_step": L * dim * 4,
+                "call": "ggr_attn_layer_decode(GGR_PTR_HOST): one hidden row in and one out per layer"}}
+    ctx.close()
+    for ws in layers:
+        for w in ws:
+            w.close()
+    torch.cuda.empty_cache()
+    return res
+
+
 def seq_split_run(torch, dist, args, world, rank, local_rank, peaks, use_nccl):
     """One measurement of configs[4] with the KV sequence split over `world` ranks (world = 1: the whole
     sequence on this GPU, same kernels and exchange)."""
@@ -961,6 +1059,7 @@ def run_ours(args):
             extras["prefill_chunked_gemma"] = bench_prefill_gemma(torch, args, local_rank, peaks)
             extras["decode_small_f32"] = bench_decode_cfg1(torch, args, local_rank, peaks, with_cpu)
             extras["decode_turboquant"] = bench_decode_turbo(torch, args, local_rank, peaks, B=args.decode_batch)
+            extras["projections"] = bench_projections(torch, args, local_rank, peaks)
         seq, scaling = bench_decode_seq_split(torch, dist, args, rank, world, local_rank, peaks)
         extras["decode_seq_split"] = seq
         extras["decode_scaling"] = scaling

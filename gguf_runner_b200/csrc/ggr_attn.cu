@@ -110,10 +110,10 @@ struct ggr_attn_ctx {
     // copy streams and events of the pipelined host-buffer prefill
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
     std::vector<cudaEvent_t> ev_in, ev_done;
-    // optional per-kernel timing: event pairs per kind (0 attention, 1 rope/append, 2 merge)
+    // optional per-kernel timing: event pairs per kind (0 attention, 1 rope/append, 2 merge, 3 projection)
     bool timing = false;
-    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> ev[3];
-    size_t ev_used[3] = {0, 0, 0};
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> ev[4];
+    size_t ev_used[4] = {0, 0, 0, 0};
 };
 
 // defined in host_plan.cpp
@@ -1022,6 +1022,9 @@ int prefill_common(ggr_attn_ctx* c, int layer, int seq, int base_pos, int m, con
             a.score_scale = (c->cfg.scale_mode == GGR_SCALE_SCORE ? c->attn_scale : 1.0f) * kLog2e;
             a.err = c->d_err;
             a.sched = c->d_sched;
+            // the rope / append kernel of these rows is the launch right in front of this one (event records of the
+            // per-kernel timing would come between them)
+            a.dependent = c->timing ? 0 : 1;
             if (gate) {
                 a.gate = dgate + (size_t)i0 * gate_row * es;
                 a.gate_bf16 = in_dtype == GGR_DTYPE_BF16;
@@ -1407,7 +1410,7 @@ int ggr_attn_set_kernel_timing(ggr_attn_ctx* c, int32_t enable) {
 }
 
 int ggr_attn_kernel_time(ggr_attn_ctx* c, int32_t kind, double* total_ms, int64_t* launches, int32_t reset) {
-    if (!c || kind < 0 || kind > 2 || !total_ms || !launches) return fail(c, GGR_ERR_INVALID, "invalid timing query");
+    if (!c || kind < 0 || kind > 3 || !total_ms || !launches) return fail(c, GGR_ERR_INVALID, "invalid timing query");
     DeviceGuard guard(c->cfg.device);
     CUDA_TRY(c, cudaStreamSynchronize(c->stream));
     double sum = 0.0;
@@ -2230,7 +2233,7 @@ uint16_t float_to_bf16_bits(float f) {  // round to nearest even (src/engine/io/
 int matmul_device(ggr_attn_ctx* c, const ggr_weights* w, const float* x, int n, float* out, __nv_bfloat16* out_h, int ld_out,
                   int sanitize) {
     if (w->device != c->cfg.device) return fail(c, GGR_ERR_INVALID, "the weights live on another device than the context");
-    if (n <= 16 && !out_h) {
+    if (n <= 16 && !out_h && w->cols <= kGemvMaxCols) {
         GemvArgs a{};
         a.w = w->d_main;
         a.scales = w->d_scales;
@@ -2241,7 +2244,10 @@ int matmul_device(ggr_attn_ctx* c, const ggr_weights* w, const float* x, int n, 
         a.out = out;
         a.ld_out = ld_out;
         a.sanitize = sanitize;
-        CUDA_TRY(c, launch_gemv(w->wtype, a, c->stream));
+        {
+            LaunchTimer t(c, 3);
+            CUDA_TRY(c, launch_gemv(w->wtype, a, c->cfg.device, c->sm_count, c->stream));
+        }
         c->launches++;
         return GGR_OK;
     }
@@ -2264,7 +2270,10 @@ int matmul_device(ggr_attn_ctx* c, const ggr_weights* w, const float* x, int n, 
     g.ld_out = ld_out;
     g.sanitize = sanitize;
     g.err = c->d_err;
-    CUDA_TRY(c, launch_gemm(tmA, w->tmB, g, c->cfg.device, c->stream));
+    {
+        LaunchTimer t(c, 3);
+        CUDA_TRY(c, launch_gemm(tmA, w->tmB, g, c->cfg.device, c->stream));
+    }
     c->launches++;
     return GGR_OK;
 }

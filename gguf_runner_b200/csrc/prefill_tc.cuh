@@ -52,6 +52,9 @@ struct PrefillTcArgs {
     // gate + (i * Hq + h) * gate_head_stride elements
     const void* gate;
     int gate_bf16, gate_head_stride;
+    // launched with programmatic stream serialisation behind the rope / append kernel of the same call: the CTA sets
+    // itself up (barriers, tensor memory) while that kernel drains and waits for it before it touches memory
+    int dependent;
 #ifdef GGR_TC_TRACE
     long long* trace;        // cycle counters of CTA 0 (diagnostic builds only)
 #endif
@@ -216,6 +219,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     volatile int* itemp = s_item;
     const int64_t row_base = a.kv.row(a.seq, a.layer, 0);
     const int Hq = a.kv.Hq;
+    if (a.dependent) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp >= 8) {
       // control warpgroup: gives registers up; warps 10 and 11 have no role
@@ -627,8 +631,23 @@ inline int launch_prefill_tc_inst(const CUtensorMap& tq, const CUtensorMap& tk, 
     const int n_pairs = (a.m + 2 * kTcBM - 1) / (2 * kTcBM);
     args.n_items = n_pairs * a.kv.Hq;
     const int grid = args.n_items < sm_count ? args.n_items : sm_count;  // one persistent CTA per SM
-    prefill_tc_kernel<D><<<grid, kTcThreads, smem, stream>>>(tq, tk, tv, args);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e;
+    if (args.dependent) {
+        cudaLaunchConfig_t lc{};
+        lc.gridDim = dim3(grid);
+        lc.blockDim = dim3(kTcThreads);
+        lc.dynamicSmemBytes = smem;
+        lc.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        lc.attrs = attr;
+        lc.numAttrs = 1;
+        e = cudaLaunchKernelEx(&lc, prefill_tc_kernel<D>, tq, tk, tv, args);
+    } else {
+        prefill_tc_kernel<D><<<grid, kTcThreads, smem, stream>>>(tq, tk, tv, args);
+        e = cudaGetLastError();
+    }
     if (e != cudaSuccess) {
         *msg = std::string("prefill kernel launch: ") + cudaGetErrorString(e);
         return 2;

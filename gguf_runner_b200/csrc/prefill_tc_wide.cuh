@@ -107,6 +107,7 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     const uint32_t tmem = s_tmem_base;
     volatile int* abortp = &s_abort;
     const int64_t row_base = a.kv.row(a.seq, a.layer, 0);
+    if (a.dependent) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp == 4) {
         // ---------------- TMA producer ----------------
@@ -387,8 +388,23 @@ inline int launch_prefill_tc_wide(const PrefillTcArgs& a, const CUtensorMap& tk,
         }
     }
     const int n_tiles = (a.m + kTcBM - 1) / kTcBM;
-    prefill_tc_wide_kernel<256><<<n_tiles * a.kv.Hq, kTwThreads, smem, stream>>>(tq, tk, tv, a);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e;
+    if (a.dependent) {
+        cudaLaunchConfig_t lc{};
+        lc.gridDim = dim3(n_tiles * a.kv.Hq);
+        lc.blockDim = dim3(kTwThreads);
+        lc.dynamicSmemBytes = smem;
+        lc.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        lc.attrs = attr;
+        lc.numAttrs = 1;
+        e = cudaLaunchKernelEx(&lc, prefill_tc_wide_kernel<256>, tq, tk, tv, a);
+    } else {
+        prefill_tc_wide_kernel<256><<<n_tiles * a.kv.Hq, kTwThreads, smem, stream>>>(tq, tk, tv, a);
+        e = cudaGetLastError();
+    }
     if (e != cudaSuccess) {
         *msg = std::string("prefill kernel launch: ") + cudaGetErrorString(e);
         return 2;

@@ -38,94 +38,206 @@ struct GemvArgs {
 constexpr int kGemvWarps = 8;
 constexpr int kGemvRPW = 2;  // weight rows per warp
 
+// 16 bytes of weights, read once: kept out of L1 so that the activation rows (re-read by every warp) stay there
+__device__ __forceinline__ uint4 ld_weights16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+// int8 code -> float without the conversion unit: the byte, biased by 128, becomes the low mantissa bits of 2^23
+// (one byte permute), and subtracting 2^23 + 128 leaves the signed value exactly.
+__device__ __forceinline__ float q8_byte_to_float(uint32_t biased_word, int byte) {
+    const uint32_t sel = 0x7650u | (uint32_t)byte;  // result bytes: [b, 0x00, 0x00, 0x4B]
+    return __uint_as_float(__byte_perm(biased_word, 0x4B000000u, sel)) - 8388736.0f;
+}
+
+template <int CPL>
+__host__ __device__ inline size_t gemv_row_floats_dev(int cols) {
+    const int per_step = 32 * CPL;
+    return (size_t)((cols + per_step - 1) / per_step) * per_step;
+}
+
+template <int WT>
+struct GemvGeom {
+    static constexpr int CPL = WT == PW_Q8_0 ? 16 : 8;  // columns per lane and step (one 16-byte load; two for F32)
+    static constexpr int UN = WT == PW_F32 ? 4 : 8;      // steps whose weight loads are in flight together
+    static constexpr int SPAN = 32 * CPL * UN;           // columns one batch of loads covers
+    static constexpr int NL = WT == PW_F32 ? 2 : 1;      // 16-byte loads per lane, step and row
+};
+
+// floats of shared memory one staged activation row takes: whole steps of 32 lanes x CPL columns
+template <int WT>
+inline size_t gemv_row_floats(int cols) {
+    const int per_step = 32 * GemvGeom<WT>::CPL;
+    return (size_t)((cols + per_step - 1) / per_step) * per_step;
+}
+
 template <int WT, int TT>
 __global__ void __launch_bounds__(kGemvWarps * 32) proj_gemv_kernel(GemvArgs a) {
+    using Ge = GemvGeom<WT>;
+    constexpr int CPL = Ge::CPL, UN = Ge::UN, NL = Ge::NL, Q = CPL / 4;
+    extern __shared__ __align__(16) float xs[];  // [TT][row_floats]: the activation rows of the pass, read by every warp
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int r0 = (blockIdx.x * kGemvWarps + warp) * kGemvRPW;
-    if (r0 >= a.rows) return;
     const int cols = a.cols;
-    for (int t0 = 0; t0 < a.n; t0 += TT) {
-        float acc[kGemvRPW][TT];
+    const int n_groups = (a.rows + kGemvWarps * kGemvRPW - 1) / (kGemvWarps * kGemvRPW);
+    const int ncb = (cols + Ge::SPAN - 1) / Ge::SPAN;                       // load batches per row
+    const int my_groups = n_groups > (int)blockIdx.x ? (n_groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int n_units = my_groups * ncb;                                    // (row group, batch) units of this CTA
+    const int row4 = (int)(gemv_row_floats_dev<CPL>(cols) >> 2);            // float4 pieces per staged row
+
+    uint4 raw[UN][kGemvRPW][NL];
+    float dsc[UN][kGemvRPW];
+    // requests the weights of unit u: UN steps of both rows, 16 (32 for F32) independent 16-byte loads per lane
+    auto load_unit = [&](int u) {
+        const int grp = blockIdx.x + (u / ncb) * gridDim.x, cb = (u % ncb) * Ge::SPAN;
+        const int r0 = (grp * kGemvWarps + warp) * kGemvRPW;
 #pragma unroll
-        for (int r = 0; r < kGemvRPW; ++r)
-#pragma unroll
-            for (int t = 0; t < TT; ++t) acc[r][t] = 0.0f;
-        constexpr int CPL = WT == PW_Q8_0 ? 16 : 8;  // columns per lane and step
-        for (int c0 = lane * CPL; c0 < cols; c0 += 32 * CPL) {
-            float wv[kGemvRPW][CPL];
+        for (int s = 0; s < UN; ++s) {
+            const int c0 = cb + s * 32 * CPL + lane * CPL;
 #pragma unroll
             for (int r = 0; r < kGemvRPW; ++r) {
                 const int row = min(r0 + r, a.rows - 1);
-                if (WT == PW_F32) {
-                    const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(a.w) + (size_t)row * cols + c0);
-                    const float4 u0 = __ldg(p), u1 = __ldg(p + 1);
-                    wv[r][0] = u0.x; wv[r][1] = u0.y; wv[r][2] = u0.z; wv[r][3] = u0.w;
-                    wv[r][4] = u1.x; wv[r][5] = u1.y; wv[r][6] = u1.z; wv[r][7] = u1.w;
-                } else if (WT == PW_BF16) {
-                    const uint4 u = __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.w) + (size_t)row * cols + c0));
-                    const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        wv[r][2 * i] = __uint_as_float(w4[i] << 16);
-                        wv[r][2 * i + 1] = __uint_as_float(w4[i] & 0xffff0000u);
-                    }
-                } else {
-                    const uint4 u = __ldg(reinterpret_cast<const uint4*>(static_cast<const int8_t*>(a.w) + (size_t)row * cols + c0));
-                    const float d = __half2float(a.scales[(size_t)row * (cols >> 5) + (c0 >> 5)]);
-                    const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        wv[r][i] = (float)(signed char)((w4[i >> 2] >> (8 * (i & 3))) & 0xff) * d;
-                }
-            }
-#pragma unroll
-            for (int t = 0; t < TT; ++t) {
-                if (t0 + t < a.n) {
-                    const float4* xp = reinterpret_cast<const float4*>(a.x + (size_t)(t0 + t) * cols + c0);
-#pragma unroll
-                    for (int i = 0; i < CPL; i += 4) {
-                        const float4 xx = __ldg(xp + (i >> 2));
-#pragma unroll
-                        for (int r = 0; r < kGemvRPW; ++r) {
-                            acc[r][t] = fmaf(xx.x, wv[r][i], acc[r][t]);
-                            acc[r][t] = fmaf(xx.y, wv[r][i + 1], acc[r][t]);
-                            acc[r][t] = fmaf(xx.z, wv[r][i + 2], acc[r][t]);
-                            acc[r][t] = fmaf(xx.w, wv[r][i + 3], acc[r][t]);
-                        }
+                dsc[s][r] = 1.0f;
+                if (c0 < cols) {
+                    if (WT == PW_F32) {
+                        const uint4* p = reinterpret_cast<const uint4*>(static_cast<const float*>(a.w) + (size_t)row * cols + c0);
+                        raw[s][r][0] = ld_weights16(p);
+                        raw[s][r][NL - 1] = ld_weights16(p + 1);
+                    } else if (WT == PW_BF16) {
+                        raw[s][r][0] = ld_weights16(static_cast<const __nv_bfloat16*>(a.w) + (size_t)row * cols + c0);
+                    } else {
+                        raw[s][r][0] = ld_weights16(static_cast<const int8_t*>(a.w) + (size_t)row * cols + c0);
+                        dsc[s][r] = __half2float(a.scales[(size_t)row * (cols >> 5) + (c0 >> 5)]);
                     }
                 }
             }
         }
+    };
+
+    for (int t0 = 0; t0 < a.n; t0 += TT) {
+        // the first unit's weights are requested before the activation rows are staged: both latencies overlap
+        if (n_units > 0) load_unit(0);
+        __syncthreads();  // every warp is done with the rows of the previous pass
+        // A lane multiplies CPL consecutive columns per step, i.e. CPL / 4 float4 pieces that lie 4 * CPL bytes apart
+        // from its neighbour's: read straight, that is a 4-way (Q8_0) or 2-way bank conflict on every load. The rows
+        // are therefore stored piece-major: piece q of step s of all 32 lanes is contiguous.
+        const int c4n = cols >> 2;
+        for (int i4 = threadIdx.x; i4 < TT * c4n; i4 += kGemvWarps * 32) {
+            const int t = i4 / c4n, col4 = i4 - t * c4n;
+            float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (t0 + t < a.n) v = __ldg(reinterpret_cast<const float4*>(a.x + (size_t)(t0 + t) * cols) + col4);
+            const int step = col4 / (32 * Q), ln = (col4 % (32 * Q)) / Q, q = col4 % Q;
+            reinterpret_cast<float4*>(xs)[(size_t)t * row4 + (step * Q + q) * 32 + ln] = v;
+        }
+        __syncthreads();
+        float acc[kGemvRPW][TT];
+        for (int u = 0; u < n_units; ++u) {
+            const int grp = blockIdx.x + (u / ncb) * gridDim.x, cbi = u % ncb, cb = cbi * Ge::SPAN;
+            const int r0 = (grp * kGemvWarps + warp) * kGemvRPW;
+            if (cbi == 0) {
 #pragma unroll
-        for (int r = 0; r < kGemvRPW; ++r)
+                for (int r = 0; r < kGemvRPW; ++r)
 #pragma unroll
-            for (int t = 0; t < TT; ++t) {
-                float v = warp_sum(acc[r][t]);
-                if (lane == 0 && r0 + r < a.rows && t0 + t < a.n) {
-                    if (a.sanitize && !isfinite(v)) v = 0.0f;
-                    a.out[(size_t)(t0 + t) * a.ld_out + r0 + r] = v;
+                    for (int t = 0; t < TT; ++t) acc[r][t] = 0.0f;
+            }
+            if (u > 0) load_unit(u);
+#pragma unroll
+            for (int s = 0; s < UN; ++s) {
+                const int c0 = cb + s * 32 * CPL + lane * CPL;
+                if (c0 >= cols) continue;
+                float wv[kGemvRPW][CPL];
+#pragma unroll
+                for (int r = 0; r < kGemvRPW; ++r) {
+                    if (WT == PW_F32) {
+                        const uint4 u0 = raw[s][r][0], u1 = raw[s][r][NL - 1];
+                        wv[r][0] = __uint_as_float(u0.x); wv[r][1] = __uint_as_float(u0.y);
+                        wv[r][2] = __uint_as_float(u0.z); wv[r][3] = __uint_as_float(u0.w);
+                        wv[r][4 % CPL] = __uint_as_float(u1.x); wv[r][5 % CPL] = __uint_as_float(u1.y);
+                        wv[r][6 % CPL] = __uint_as_float(u1.z); wv[r][7 % CPL] = __uint_as_float(u1.w);
+                    } else if (WT == PW_BF16) {
+                        const uint4 q = raw[s][r][0];
+                        const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            wv[r][2 * i] = __uint_as_float(w4[i] << 16);
+                            wv[r][2 * i + 1] = __uint_as_float(w4[i] & 0xffff0000u);
+                        }
+                    } else {
+                        const uint4 q = raw[s][r][0];
+                        const uint32_t w4[4] = {q.x ^ 0x80808080u, q.y ^ 0x80808080u, q.z ^ 0x80808080u, q.w ^ 0x80808080u};
+#pragma unroll
+                        for (int i = 0; i < CPL; ++i) wv[r][i] = q8_byte_to_float(w4[(i >> 2) & 3], i & 3);
+                    }
+                }
+                const int step = (cb + s * 32 * CPL) / (32 * CPL);
+#pragma unroll
+                for (int t = 0; t < TT; ++t) {
+                    const float4* xp = reinterpret_cast<const float4*>(xs) + (size_t)t * row4 + (size_t)step * Q * 32 + lane;
+                    float part[kGemvRPW];
+#pragma unroll
+                    for (int r = 0; r < kGemvRPW; ++r) part[r] = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < CPL; i += 4) {
+                        const float4 xx = xp[(i >> 2) * 32];
+#pragma unroll
+                        for (int r = 0; r < kGemvRPW; ++r) {
+                            part[r] = fmaf(xx.x, wv[r][i], part[r]);
+                            part[r] = fmaf(xx.y, wv[r][i + 1], part[r]);
+                            part[r] = fmaf(xx.z, wv[r][i + 2], part[r]);
+                            part[r] = fmaf(xx.w, wv[r][i + 3], part[r]);
+                        }
+                    }
+                    // Q8_0: the block scale multiplies the partial sum of the block's codes, as in the reference
+#pragma unroll
+                    for (int r = 0; r < kGemvRPW; ++r) acc[r][t] = fmaf(part[r], dsc[s][r], acc[r][t]);
                 }
             }
+            if (cbi == ncb - 1) {
+#pragma unroll
+                for (int r = 0; r < kGemvRPW; ++r)
+#pragma unroll
+                    for (int t = 0; t < TT; ++t) {
+                        float v = warp_sum(acc[r][t]);
+                        if (lane == 0 && r0 + r < a.rows && t0 + t < a.n) {
+                            if (a.sanitize && !isfinite(v)) v = 0.0f;
+                            a.out[(size_t)(t0 + t) * a.ld_out + r0 + r] = v;
+                        }
+                    }
+            }
+        }
     }
 }
 
-template <int WT>
-inline cudaError_t launch_gemv_wt(const GemvArgs& a, cudaStream_t stream) {
-    const int grid = (a.rows + kGemvWarps * kGemvRPW - 1) / (kGemvWarps * kGemvRPW);
-    if (a.n == 1)
-        proj_gemv_kernel<WT, 1><<<grid, kGemvWarps * 32, 0, stream>>>(a);
-    else if (a.n == 2)
-        proj_gemv_kernel<WT, 2><<<grid, kGemvWarps * 32, 0, stream>>>(a);
-    else
-        proj_gemv_kernel<WT, 4><<<grid, kGemvWarps * 32, 0, stream>>>(a);
+constexpr int kGemvMaxCols = 12288;  // activation rows are staged in shared memory: up to 48 KB per row
+
+template <int WT, int TT>
+inline cudaError_t launch_gemv_inst(const GemvArgs& a, int device, int sm_count, cudaStream_t stream) {
+    static KernelSmemSetup setup;
+    const size_t smem = (size_t)TT * gemv_row_floats<WT>(a.cols) * sizeof(float);
+    cudaError_t e = setup.ensure(proj_gemv_kernel<WT, TT>, device, 0, (int)((size_t)TT * gemv_row_floats<WT>(kGemvMaxCols) * sizeof(float)));
+    if (e != cudaSuccess) return e;
+    const int groups = (a.rows + kGemvWarps * kGemvRPW - 1) / (kGemvWarps * kGemvRPW);
+    // row groups are dealt round robin to a grid that fills the SMs about twice (the staged rows are loaded once per CTA)
+    const int grid = groups < 2 * sm_count ? groups : 2 * sm_count;
+    proj_gemv_kernel<WT, TT><<<grid, kGemvWarps * 32, smem, stream>>>(a);
     return cudaGetLastError();
 }
 
-inline cudaError_t launch_gemv(int wtype, const GemvArgs& a, cudaStream_t stream) {
+template <int WT>
+inline cudaError_t launch_gemv_wt(const GemvArgs& a, int device, int sm_count, cudaStream_t stream) {
+    if (a.n == 1) return launch_gemv_inst<WT, 1>(a, device, sm_count, stream);
+    if (a.n == 2) return launch_gemv_inst<WT, 2>(a, device, sm_count, stream);
+    return launch_gemv_inst<WT, 4>(a, device, sm_count, stream);
+}
+
+inline cudaError_t launch_gemv(int wtype, const GemvArgs& a, int device, int sm_count, cudaStream_t stream) {
     switch (wtype) {
-        case PW_F32: return launch_gemv_wt<PW_F32>(a, stream);
-        case PW_BF16: return launch_gemv_wt<PW_BF16>(a, stream);
-        default: return launch_gemv_wt<PW_Q8_0>(a, stream);
+        case PW_F32: return launch_gemv_wt<PW_F32>(a, device, sm_count, stream);
+        case PW_BF16: return launch_gemv_wt<PW_BF16>(a, device, sm_count, stream);
+        default: return launch_gemv_wt<PW_Q8_0>(a, device, sm_count, stream);
     }
 }
 

@@ -70,8 +70,14 @@ __device__ __forceinline__ int8_t q8_code(float x, float inv) {
     return (int8_t)r;
 }
 
+// The attention kernel of a prefill call is launched with programmatic stream serialisation behind these kernels:
+// signalling at the start lets its CTAs set themselves up while this grid drains (they wait for this grid's
+// completion before reading anything). Without such a dependent the instruction does nothing.
+__device__ __forceinline__ void rope_allow_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __global__ void __launch_bounds__(256) rope_append_kernel(RopeAppendArgs a) {
     extern __shared__ float sm[];
+    rope_allow_dependents();
     const int D = a.kv.D, kv_dim = a.kv.kv_dim, q_dim = a.kv.Hq * D;
     const int half = a.rope.rope_half;
     float* cs = sm;
@@ -287,6 +293,7 @@ inline bool rope_append_fast_ok(const RopeAppendArgs& a) {
 
 __global__ void __launch_bounds__(256) rope_append_bf16_kernel(RopeAppendArgs a) {
     __shared__ float cs[128], sn[128];
+    rope_allow_dependents();
     const int D = a.kv.D, kv_dim = a.kv.kv_dim, Hq = a.kv.Hq, Hkv = a.kv.Hkv, q_dim = Hq * D;
     const int half = a.rope.rope_half;
     const int item = blockIdx.x, tid = threadIdx.x;
@@ -396,6 +403,7 @@ inline bool rope_append_vec_ok(const RopeAppendArgs& a) {
 
 template <typename TIn>
 __global__ void __launch_bounds__(256) rope_append_vec_kernel(RopeAppendArgs a) {
+    rope_allow_dependents();
     extern __shared__ float sm[];
     const int D = a.kv.D, kv_dim = a.kv.kv_dim, Hq = a.kv.Hq, Hkv = a.kv.Hkv, q_dim = Hq * D;
     const int half = a.rope.rope_half;

@@ -374,7 +374,7 @@ int32_t ggr_attn_last_split_count(const ggr_attn_ctx* ctx);
 /* Per-kernel device timing (the counterpart of the reference's PROF_ATTN_NS
  * counter, src/engine/profiling.rs:8-41): when enabled, every launch is
  * bracketed by CUDA events on the context's stream. kind 0 = attention
- * kernels, 1 = rope/append kernels, 2 = partial-state merges.
+ * kernels, 1 = rope/append kernels, 2 = partial-state merges, 3 = projection matmuls.
  * ggr_attn_kernel_time synchronises the stream, returns the summed device
  * time in milliseconds and the number of launches since the last reset, and
  * resets the counters when `reset` is nonzero. */
