@@ -383,7 +383,7 @@ def bench_prefill(torch, dist, args, rank, world, local_rank, peaks):
         # DRAM bytes of one launch of this shape, read + write, taken from an ncu capture of the same kernel and shape
         # (not measured by this run): the kernel is bound by the tensor cores and the MUFU unit, its traffic is the
         # q / K / V minimum plus the part of the output that left L2
-        traffic=65.7e6, traffic_unit="bytes per launch",
+        traffic=64.6e6, traffic_unit="bytes per launch",
         traffic_source="constant: dram__bytes_read.sum + dram__bytes_write.sum of an ncu capture of this kernel at this shape",
         flops_per_launch=flops_per_launch, avg_launch_ms=attn_ms, launches_per_step=attn_per_step,
         rope_append_avg_ms=rope_ms, rope_append_launches_per_step=rope_per_step,
@@ -528,7 +528,9 @@ def bench_decode_cfg1(torch, args, local_rank, peaks, with_cpu):
            "tokens_per_s": 1.0 / (best * 1e-3), "split_count": ctx.last_split_count,
            "roofline": hbm_roofline(peaks, bytes_per_layer, per_kind[0][0], kernel="split-KV decode attention (one launch per layer)",
                                     bytes_per_launch=bytes_per_layer, avg_launch_ms=per_kind[0][0],
-                                    step_frac=L * bytes_per_layer / (best * 1e-3) / 1e9 / peaks["hbm_gbs"], traffic=None,
+                                    step_frac=L * bytes_per_layer / (best * 1e-3) / 1e9 / peaks["hbm_gbs"], traffic=16.9e6,
+                                    traffic_unit="bytes per launch",
+                                    traffic_source="constant: ncu capture of this kernel at this shape (16.8 MB of cache)",
                                     note="`frac` is the kernel alone; `step_frac` the whole 28-layer step, which is "
                                          "bound by launch latency (2.6 us of HBM time per layer)"),
            "e2e": {"value": 1.0 / host_s, "unit": "tokens/s", "ms_per_step": host_s * 1e3,
@@ -580,9 +582,9 @@ def bench_decode_cfg3(torch, args, local_rank, peaks, B=8, n_res=None):
                                     step_frac=L * bytes_per_launch / (ms_per_step * 1e-3) / 1e9 / peaks["hbm_gbs"],
                                     # every cache byte is read exactly once, so the traffic of another batch size is
                                     # the B = 8 capture scaled by B
-                                    traffic=541.4e6 * B / 8, traffic_unit="bytes per launch",
-                                    traffic_source="constant: ncu capture of this kernel at B=8 (537.1 MB read + 4.3 MB "
-                                                   "written for 536.9 MB of cache), scaled by B")}
+                                    traffic=540.6e6 * B / 8, traffic_unit="bytes per launch",
+                                    traffic_source="constant: ncu capture of this kernel at B=8 (540.6 MB of DRAM traffic for "
+                                                   "536.9 MB of cache), scaled by B")}
     ctx.close()
     torch.cuda.empty_cache()
     return res
@@ -1013,6 +1015,22 @@ def run_small_case(args):
         for _ in range(2):
             for l in range(28):
                 out = ctx.decode(l, [2047], q, k, v)
+    elif args.case == "proj_small":
+        # the projection kernels on a 4096 x 4096 matrix: tensor-core GEMM for 2048 rows, weight-streaming kernel for
+        # one row over six Q8_0 matrices (0.2 GB on the device)
+        from gguf_runner_b200.binding import W_BF16, W_Q8_0, Weights
+        from tests.oracle_binding import bf16_bits, quantize_q8_0
+        rng = np.random.default_rng(5)
+        wf = (rng.standard_normal((4096, 4096)) / 64.0).astype(np.float32)
+        wb = Weights(W_BF16, 4096, 4096, bf16_bits(wf))
+        wq = [Weights(W_Q8_0, 4096, 4096, quantize_q8_0(wf)) for _ in range(6)]
+        ctx = g.AttnContext(presets.qwen3_0p6b_decode(n_layers=1, seq_len=64))
+        xm = torch.randn(2048, 4096, generator=gen, device="cuda")
+        x1 = torch.randn(1, 4096, generator=gen, device="cuda")
+        for _ in range(3):
+            out = ctx.proj_matmul(wb, xm)
+        for i in range(12):
+            out1 = ctx.proj_matmul(wq[i % 6], x1)
     elif args.case == "decode_turbo_small":
         # two layers of the config-3 decode shape over a TurboQuant cache: T=32768, B=8 (0.25 GB on the device);
         # the cache keeps its zero rows (timing of the tensor-core kernel does not depend on the code values)
@@ -1095,7 +1113,7 @@ def main():
     ap.add_argument("--decode-batch", type=int, default=8)
     ap.add_argument("--cpu-stride", type=int, default=16)
     ap.add_argument("--case", default=None, help="run a small profiling case (prefill_small, prefill_gemma_small, decode_small, "
-                                                 "decode_b1_small, decode_cfg1_small, decode_turbo_small) or print the "
+                                                 "decode_b1_small, decode_cfg1_small, decode_turbo_small, proj_small) or print the "
                                                  "decode kernels' phase stamps (decode_stamps, diagnostic library build) and exit")
     args = ap.parse_args()
     if args.warmup < 3:
