@@ -2,15 +2,18 @@
 // different tiling because the output accumulator alone takes 256 TMEM columns.
 //
 // One CTA owns ONE 128-row query tile of one query head and walks the visible 64-key tiles:
-//   warp 4       TMA producer (Q once; K and V tiles of 64 keys into 2-stage rings)
+//   warp 4       TMA producer (K and V tiles of 64 keys into 3-stage rings)
 //   warp 5       MMA issuer: S[b] = Q K^T (N = 64) into one of two S buffers, O += P V (N = 256)
-//   warps 0-3    softmax, one thread per query row
-// TMEM columns: S0 0-63, S1 64-127, O 128-383. The score tile of step j+1 is computed while the
+//   warps 0-3    softmax, one thread per query row; they also place Q in tensor memory at the start
+// TMEM columns: S0 0-63, S1 64-127, O 128-383, Q 384-511 (bf16 pairs, the A operand of Q K^T). With Q in
+// shared memory an N = 64 instruction fetched 4 KB of Q and 2 KB of K for 32 cycles of arithmetic and
+// ran at the shared-memory rate (48 cycles); from tensor memory only the K fetch remains, and the 64 KB
+// of shared memory Q occupied hold a third K / V stage. The score tile of step j+1 is computed while the
 // softmax of step j runs. Because QK(j+1) is issued before PV(j), O is still being written when the
 // softmax of step j+1 starts: a step that has to rescale O waits for PV(j) (pv_done) first, every other
 // step only observes that barrier after its exponentials, where the wait is normally over. P is
 // published in two 32-key halves so that P V starts under the second half of the softmax.
-// Shared memory: Q 64 KB + 2 x 32 KB K + 2 x 32 KB V = 192 KB. Every wait is bounded.
+// Shared memory: 3 x 32 KB K + 3 x 32 KB V = 192 KB. Every wait is bounded.
 #pragma once
 
 #include <string>
@@ -23,46 +26,46 @@ namespace ggr {
 
 constexpr int kTwBN = 64;        // keys per tile
 constexpr int kTwThreads = 256;  // softmax warpgroup + control warpgroup
+constexpr int kTwStages = 3;     // K / V ring depth
 
 template <int D>
 __global__ void __launch_bounds__(kTwThreads, 1)
-prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                       const __grid_constant__ CUtensorMap tmV, PrefillTcArgs a) {
+prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, PrefillTcArgs a) {
     using namespace tc;
     constexpr int NBLK = D / 64;
-    constexpr uint32_t QBLK = 128 * 128;         // [128 rows][128 bytes]
     constexpr uint32_t KBLK = kTwBN * 128;       // [64 rows][128 bytes]
-    constexpr uint32_t Q_BYTES = NBLK * QBLK;
     constexpr uint32_t KV_BYTES = NBLK * KBLK;
     constexpr uint32_t O_COL0 = 128;
+    constexpr uint32_t Q_COL0 = O_COL0 + D;      // D / 2 columns of bf16 pairs
+    constexpr int NST = kTwStages;
+    static_assert(Q_COL0 + D / 2 <= 512, "tensor memory columns");
 
     extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t bars[20];  // 18 used
+    __shared__ __align__(8) uint64_t bars[24];  // 22 used
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
 
     // the warp index goes through a broadcast so that the compiler knows the role branches are warp-uniform
     const int tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t sQ = smem_base;
-    const uint32_t sK = sQ + Q_BYTES;        // [2 stages][KV_BYTES]
-    const uint32_t sV = sK + 2 * KV_BYTES;   // [2 stages][KV_BYTES]
+    const uint32_t sK = smem_base;             // [NST stages][KV_BYTES]
+    const uint32_t sV = sK + NST * KV_BYTES;   // [NST stages][KV_BYTES]
 
     const uint32_t bar0 = smem_u32(bars);
     const uint32_t q_full = bar0;
     auto k_full = [&](int s) { return bar0 + 8u * (1 + s); };
-    auto k_empty = [&](int s) { return bar0 + 8u * (3 + s); };
-    auto v_full = [&](int s) { return bar0 + 8u * (5 + s); };
-    auto v_empty = [&](int s) { return bar0 + 8u * (7 + s); };
-    auto s_full = [&](int b) { return bar0 + 8u * (9 + b); };
+    auto k_empty = [&](int s) { return bar0 + 8u * (4 + s); };
+    auto v_full = [&](int s) { return bar0 + 8u * (7 + s); };
+    auto v_empty = [&](int s) { return bar0 + 8u * (10 + s); };
+    auto s_full = [&](int b) { return bar0 + 8u * (13 + b); };
     // P and "P V landed" barriers exist once per score buffer. Q K^T of step n + 1 is issued before P V of step n,
     // so the softmax warps can be a whole step ahead of the MMA warp: with one barrier for both buffers they could
     // complete its phase n + 1 before the MMA warp had looked at phase n, and a parity wait cannot tell phase n
     // from phase n + 2 (the kernel then sat in a wait until its bound ran out). A buffer's own barrier cannot run
     // ahead: its next phase needs the next-but-one score tile, which the MMA warp issues after it has seen this one.
-    auto p_half = [&](int buf, int half) { return bar0 + 8u * (11 + 2 * buf + half); };  // P keys 0-31 / 32-63 stored
-    auto pv_done = [&](int buf) { return bar0 + 8u * (15 + buf); };
-    const uint32_t o_final = bar0 + 8u * 17;
+    auto p_half = [&](int buf, int half) { return bar0 + 8u * (15 + 2 * buf + half); };  // P keys 0-31 / 32-63 stored
+    auto pv_done = [&](int buf) { return bar0 + 8u * (19 + buf); };
+    const uint32_t o_final = bar0 + 8u * 21;
 
     const int Hq = a.kv.Hq, G = a.kv.G;
     const int n_tiles = (a.m + kTcBM - 1) / kTcBM;
@@ -83,12 +86,14 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 
     if (tid == 0) {
         s_abort = 0;
-        mbar_init(q_full, 1);
-        for (int s = 0; s < 2; ++s) {
+        mbar_init(q_full, kTcBM);
+        for (int s = 0; s < NST; ++s) {
             mbar_init(k_full(s), 1);
             mbar_init(k_empty(s), 1);
             mbar_init(v_full(s), 1);
             mbar_init(v_empty(s), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
             mbar_init(s_full(s), 1);
             mbar_init(p_half(s, 0), kTcBM);
             mbar_init(p_half(s, 1), kTcBM);
@@ -112,11 +117,9 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     if (warp == 4) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            mbar_expect_tx(q_full, Q_BYTES);
-            for (int b = 0; b < NBLK; ++b) tma_load_2d(sQ + b * QBLK, &tmQ, h * D + b * 64, q_row0, q_full);
+            int s = 0;
+            uint32_t ph = 1;  // stage and phase of the ring position: the first pass finds every stage free
             for (int j = lo; j < hi; ++j) {
-                const int n = j - lo, s = n & 1;
-                const uint32_t ph = ((n >> 1) & 1) ^ 1;
                 const int y = (int)(row_base + (int64_t)j * kTwBN);
                 if (!mbar_wait(k_empty(s), ph, abortp)) break;
                 mbar_expect_tx(k_full(s), KV_BYTES);
@@ -126,6 +129,7 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 mbar_expect_tx(v_full(s), KV_BYTES);
                 for (int b = 0; b < NBLK; ++b)
                     tma_load_2d(sV + s * KV_BYTES + b * KBLK, &tmV, kvh * D + b * 64, y, v_full(s));
+                if (++s == NST) s = 0, ph ^= 1u;
             }
         }
     } else if (warp == 5) {
@@ -133,15 +137,15 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         if (hi > lo) {  // the whole warp runs the loop, one elected lane issues
             constexpr uint32_t IDESC_QK = idesc_bf16(kTwBN, 0);
             constexpr uint32_t IDESC_PV = idesc_bf16(D, 1);
-            const uint64_t dQ = smem_desc(sQ, 16, 1024), dK = smem_desc(sK, 16, 1024), dV = smem_desc(sV, KBLK, 1024);
+            const uint64_t dK = smem_desc(sK, 16, 1024), dV = smem_desc(sV, KBLK, 1024);
             const uint32_t tmem = __shfl_sync(0xffffffffu, s_tmem_base, 0);  // shadows the CTA-wide copy: provably uniform
             auto issue_qk = [&](int buf, int s) {
                 const uint64_t b0 = dK + (uint64_t)((s * KV_BYTES) >> 4);
                 const uint32_t d = tmem + buf * kTwBN;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
-                    mma_ss_e(d, dQ + (uint64_t)(((ks >> 2) * QBLK + (ks & 3) * 32) >> 4),
-                           b0 + (uint64_t)(((ks >> 2) * KBLK + (ks & 3) * 32) >> 4), IDESC_QK, ks > 0 ? 1u : 0u);
+                    mma_ts_e(d, tmem + Q_COL0 + ks * 8, b0 + (uint64_t)(((ks >> 2) * KBLK + (ks & 3) * 32) >> 4), IDESC_QK,
+                             ks > 0 ? 1u : 0u);
                 }
             };
             auto issue_pv_half = [&](int buf, int s, int half, bool accumulate) {
@@ -164,19 +168,23 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 mma_commit_e(s_full(0));
                 mma_commit_e(k_empty(0));
             }
+            int s = 0;
+            uint32_t ring_ph = 0;  // ring stage of step n and the phase its "full" barriers complete in this pass
             for (int j = lo; ok && j < hi; ++j) {
-                const int n = j - lo, s = n & 1;
+                const int n = j - lo;
+                const int s1 = s + 1 == NST ? 0 : s + 1;
+                const uint32_t ring_ph1 = s + 1 == NST ? ring_ph ^ 1u : ring_ph;
                 TRACE_MARK();
                 if (j + 1 < hi) {
-                    if (!(ok = mbar_wait_warp(k_full(s ^ 1), ((n + 1) >> 1) & 1, abortp))) break;
+                    if (!(ok = mbar_wait_warp(k_full(s1), ring_ph1, abortp))) break;
                     TRACE_ADD(tr_k);
                     fence_after_sync();
-                    issue_qk((n + 1) & 1, s ^ 1);
+                    issue_qk((n + 1) & 1, s1);
                     mma_commit_e(s_full((n + 1) & 1));
-                    mma_commit_e(k_empty(s ^ 1));
+                    mma_commit_e(k_empty(s1));
                     TRACE_ADD(tr_issue_qk);
                 }
-                if (!(ok = mbar_wait_warp(v_full(s), (n >> 1) & 1, abortp))) break;
+                if (!(ok = mbar_wait_warp(v_full(s), ring_ph, abortp))) break;
                 TRACE_ADD(tr_v);
                 if (!(ok = mbar_wait_warp(p_half(n & 1, 0), (n >> 1) & 1, abortp))) break;
                 TRACE_ADD(tr_p0);
@@ -189,6 +197,8 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 mma_commit_e(v_empty(s));
                 if (j == hi - 1) mma_commit_e(o_final);
                 TRACE_ADD(tr_issue);
+                s = s1;
+                ring_ph = ring_ph1;
             }
 #ifdef GGR_TC_TRACE
             if (blockIdx.x == 0 && a.trace) {
@@ -213,6 +223,24 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 #ifdef GGR_TC_TRACE
         long long ts_wait = 0, ts_ld = 0, ts_max = 0, ts_resc = 0, ts_exp = 0, ts_t0 = clock64(), tr_x;
 #endif
+        if (hi > lo) {
+            // this thread's query row goes to tensor memory as the A operand of Q K^T: lane = row, one column per
+            // two consecutive head elements; rows past the end of the chunk are zero
+            const uint4* qrow = reinterpret_cast<const uint4*>(a.q + ((int64_t)qi * Hq + h) * D);
+#pragma unroll
+            for (int cidx = 0; cidx < D / 64; ++cidx) {
+                uint32_t qr[32];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint4 v4 = valid ? __ldg(qrow + cidx * 8 + i) : make_uint4(0u, 0u, 0u, 0u);
+                    qr[4 * i] = v4.x, qr[4 * i + 1] = v4.y, qr[4 * i + 2] = v4.z, qr[4 * i + 3] = v4.w;
+                }
+                tmem_st32(tmem + lane_addr + Q_COL0 + cidx * 32, qr);
+            }
+            tmem_wait_st();
+            fence_before_sync();
+            mbar_arrive(q_full);
+        }
         for (int j = lo; j < hi; ++j) {
             const int n = j - lo, buf = n & 1;
             const uint32_t tS = tmem + lane_addr + buf * kTwBN;
@@ -364,16 +392,11 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     if (tid == 0 && s_abort && a.err) atomicExch(a.err, 1);
 }
 
-inline size_t prefill_tc_wide_smem(int D) { return (size_t)(D / 64) * (128 * 128 + 4 * kTwBN * 128) + 1024; }
+inline size_t prefill_tc_wide_smem(int D) { return (size_t)(D / 64) * (2 * kTwStages * kTwBN * 128) + 1024; }
 
-// tq: [m][q_dim] with a 64 x 128 box; tk / tv: whole cache arrays with a 64 x 64 box
+// tk / tv: whole cache arrays with a 64 x 64 box; the queries are read with plain loads
 inline int launch_prefill_tc_wide(const PrefillTcArgs& a, const CUtensorMap& tk, const CUtensorMap& tv, int device,
                                   cudaStream_t stream, std::string* msg) {
-    CUtensorMap tq;
-    if (!make_tmap_bf16(&tq, a.q, (uint64_t)a.kv.Hq * a.kv.D, (uint64_t)a.m)) {
-        *msg = "cuTensorMapEncodeTiled failed for the query tensor";
-        return 2;
-    }
     if (a.kv.D != 256) {
         *msg = "the wide tensor-core prefill kernel is built for head_dim 256";
         return 5;
@@ -400,9 +423,9 @@ inline int launch_prefill_tc_wide(const PrefillTcArgs& a, const CUtensorMap& tk,
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         lc.attrs = attr;
         lc.numAttrs = 1;
-        e = cudaLaunchKernelEx(&lc, prefill_tc_wide_kernel<256>, tq, tk, tv, a);
+        e = cudaLaunchKernelEx(&lc, prefill_tc_wide_kernel<256>, tk, tv, a);
     } else {
-        prefill_tc_wide_kernel<256><<<n_tiles * a.kv.Hq, kTwThreads, smem, stream>>>(tq, tk, tv, a);
+        prefill_tc_wide_kernel<256><<<n_tiles * a.kv.Hq, kTwThreads, smem, stream>>>(tk, tv, a);
         e = cudaGetLastError();
     }
     if (e != cudaSuccess) {
