@@ -4,7 +4,10 @@
 // One CTA owns ONE 128-row query tile of one query head and walks the visible 64-key tiles:
 //   warp 4       TMA producer (K and V tiles of 64 keys into 3-stage rings)
 //   warp 5       MMA issuer: S[b] = Q K^T (N = 64) into one of two S buffers, O += P V (N = 256)
-//   warps 0-3    softmax, one thread per query row; they also place Q in tensor memory at the start
+//   warps 0-3    softmax, one thread per query row; they also place Q in tensor memory at the start and send the
+//                output rows out at the end, both as one bulk copy per row through shared memory (a warp that
+//                reads or writes one 16-byte piece per row touches 32 cache lines per instruction: that took
+//                3.3 us for Q and 8.2 us for the output of a 28 us CTA)
 // TMEM columns: S0 0-63, S1 64-127, O 128-383, Q 384-511 (bf16 pairs, the A operand of Q K^T). With Q in
 // shared memory an N = 64 instruction fetched 4 KB of Q and 2 KB of K for 32 cycles of arithmetic and
 // ran at the shared-memory rate (48 cycles); from tensor memory only the K fetch remains, and the 64 KB
@@ -13,7 +16,8 @@
 // softmax of step j+1 starts: a step that has to rescale O waits for PV(j) (pv_done) first, every other
 // step only observes that barrier after its exponentials, where the wait is normally over. P is
 // published in two 32-key halves so that P V starts under the second half of the softmax.
-// Shared memory: 3 x 32 KB K + 3 x 32 KB V = 192 KB. Every wait is bounded.
+// Shared memory: 3 stages of (32 KB K, 32 KB V) = 192 KB; the third stage first holds the staged Q rows, and the
+// whole ring holds the output rows once the last MMA has completed. Every wait is bounded.
 #pragma once
 
 #include <string>
@@ -27,6 +31,7 @@ namespace ggr {
 constexpr int kTwBN = 64;        // keys per tile
 constexpr int kTwThreads = 256;  // softmax warpgroup + control warpgroup
 constexpr int kTwStages = 3;     // K / V ring depth
+constexpr uint32_t kTwTailBytes = 2048;  // room past the last stage for the row pitch of the staged Q tile
 
 template <int D>
 __global__ void __launch_bounds__(kTwThreads, 1)
@@ -40,16 +45,31 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     constexpr int NST = kTwStages;
     static_assert(Q_COL0 + D / 2 <= 512, "tensor memory columns");
 
+#ifdef GGR_TC_TRACE
+    // wall-clock stamps (ns) of the first and the last CTA of diagnostic builds: trace slots 32.. / 40..
+#define TW_STAMP(slot) do { if (a.trace && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) { unsigned long long t_; \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); a.trace[(blockIdx.x == 0 ? 32 : 40) + (slot)] = (long long)t_; } } while (0)
+    if (threadIdx.x == 0) TW_STAMP(0);
+#else
+#define TW_STAMP(slot)
+#endif
     extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t bars[24];  // 22 used
+    __shared__ __align__(8) uint64_t bars[24];  // 23 used
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
 
     // the warp index goes through a broadcast so that the compiler knows the role branches are warp-uniform
     const int tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t sK = smem_base;             // [NST stages][KV_BYTES]
-    const uint32_t sV = sK + NST * KV_BYTES;   // [NST stages][KV_BYTES]
+    constexpr uint32_t STAGE_BYTES = 2 * KV_BYTES;   // K tile, then V tile
+    const uint32_t sK = smem_base;                   // stage s at + s * STAGE_BYTES
+    const uint32_t sV = smem_base + KV_BYTES;
+    // Rows staged for one-thread-per-row access are pitched 16 bytes past a multiple of 128, which spreads the
+    // eight rows of a quarter warp over all banks.
+    constexpr uint32_t Q_PITCH = D * 2 + 16, O_PITCH = D * 4 + 16;
+    const uint32_t sQst = smem_base + (NST - 1) * STAGE_BYTES;   // last stage (+ the tail of the buffer)
+    static_assert(kTcBM * Q_PITCH <= STAGE_BYTES + kTwTailBytes, "staged Q rows");
+    static_assert(kTcBM * O_PITCH <= NST * STAGE_BYTES, "staged output rows");
 
     const uint32_t bar0 = smem_u32(bars);
     const uint32_t q_full = bar0;
@@ -66,6 +86,7 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     auto p_half = [&](int buf, int half) { return bar0 + 8u * (15 + 2 * buf + half); };  // P keys 0-31 / 32-63 stored
     auto pv_done = [&](int buf) { return bar0 + 8u * (19 + buf); };
     const uint32_t o_final = bar0 + 8u * 21;
+    const uint32_t q_staged = bar0 + 8u * 22;   // the bulk copies of the Q rows have landed
 
     const int Hq = a.kv.Hq, G = a.kv.G;
     const int n_tiles = (a.m + kTcBM - 1) / kTcBM;
@@ -100,6 +121,7 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             mbar_init(pv_done(s), 1);
         }
         mbar_init(o_final, 1);
+        mbar_init(q_staged, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 5) {
@@ -112,7 +134,9 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     const uint32_t tmem = s_tmem_base;
     volatile int* abortp = &s_abort;
     const int64_t row_base = a.kv.row(a.seq, a.layer, 0);
+    if (threadIdx.x == 0) TW_STAMP(1);
     if (a.dependent) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (threadIdx.x == 0) TW_STAMP(2);
 
     if (warp == 4) {
         // ---------------- TMA producer ----------------
@@ -121,14 +145,16 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             uint32_t ph = 1;  // stage and phase of the ring position: the first pass finds every stage free
             for (int j = lo; j < hi; ++j) {
                 const int y = (int)(row_base + (int64_t)j * kTwBN);
+                // the last stage holds the staged Q rows until they are in tensor memory
+                if (j - lo == NST - 1 && !mbar_wait(q_full, 0, abortp)) break;
                 if (!mbar_wait(k_empty(s), ph, abortp)) break;
                 mbar_expect_tx(k_full(s), KV_BYTES);
                 for (int b = 0; b < NBLK; ++b)
-                    tma_load_2d(sK + s * KV_BYTES + b * KBLK, &tmK, kvh * D + b * 64, y, k_full(s));
+                    tma_load_2d(sK + s * STAGE_BYTES + b * KBLK, &tmK, kvh * D + b * 64, y, k_full(s));
                 if (!mbar_wait(v_empty(s), ph, abortp)) break;
                 mbar_expect_tx(v_full(s), KV_BYTES);
                 for (int b = 0; b < NBLK; ++b)
-                    tma_load_2d(sV + s * KV_BYTES + b * KBLK, &tmV, kvh * D + b * 64, y, v_full(s));
+                    tma_load_2d(sV + s * STAGE_BYTES + b * KBLK, &tmV, kvh * D + b * 64, y, v_full(s));
                 if (++s == NST) s = 0, ph ^= 1u;
             }
         }
@@ -140,7 +166,7 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             const uint64_t dK = smem_desc(sK, 16, 1024), dV = smem_desc(sV, KBLK, 1024);
             const uint32_t tmem = __shfl_sync(0xffffffffu, s_tmem_base, 0);  // shadows the CTA-wide copy: provably uniform
             auto issue_qk = [&](int buf, int s) {
-                const uint64_t b0 = dK + (uint64_t)((s * KV_BYTES) >> 4);
+                const uint64_t b0 = dK + (uint64_t)((s * STAGE_BYTES) >> 4);
                 const uint32_t d = tmem + buf * kTwBN;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
@@ -149,7 +175,7 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
                 }
             };
             auto issue_pv_half = [&](int buf, int s, int half, bool accumulate) {
-                const uint64_t b0 = dV + (uint64_t)((s * KV_BYTES) >> 4);
+                const uint64_t b0 = dV + (uint64_t)((s * STAGE_BYTES) >> 4);
                 const uint32_t p0 = tmem + buf * kTwBN;
 #pragma unroll
                 for (int kk = 0; kk < kTwBN / 32; ++kk) {
@@ -226,22 +252,33 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
         if (hi > lo) {
             // this thread's query row goes to tensor memory as the A operand of Q K^T: lane = row, one column per
             // two consecutive head elements; rows past the end of the chunk are zero
-            const uint4* qrow = reinterpret_cast<const uint4*>(a.q + ((int64_t)qi * Hq + h) * D);
-#pragma unroll
-            for (int cidx = 0; cidx < D / 64; ++cidx) {
+            // (the row comes in as one bulk copy; the thread then reads it back 16 bytes at a time)
+            const int n_valid = min(kTcBM, a.m - q_row0);
+            if (tid == 0) mbar_expect_tx(q_staged, (uint32_t)n_valid * (uint32_t)(D * 2));
+            if (valid) bulk_load(sQst + row * Q_PITCH, a.q + ((int64_t)qi * Hq + h) * D, D * 2, q_staged);
+            ok = mbar_wait(q_staged, 0, abortp);
+            // (rolled loops here and in the epilogue: unrolled, this once-per-CTA code missed the instruction cache
+            // line after line, and the epilogue took 12 us instead of 5)
+#pragma unroll 1
+            for (int cidx = 0; ok && cidx < D / 64; ++cidx) {
                 uint32_t qr[32];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    const uint4 v4 = valid ? __ldg(qrow + cidx * 8 + i) : make_uint4(0u, 0u, 0u, 0u);
+                    uint4 v4 = make_uint4(0u, 0u, 0u, 0u);
+                    if (valid)
+                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(v4.x), "=r"(v4.y), "=r"(v4.z), "=r"(v4.w)
+                                     : "r"(sQst + row * Q_PITCH + (uint32_t)(cidx * 8 + i) * 16u));
                     qr[4 * i] = v4.x, qr[4 * i + 1] = v4.y, qr[4 * i + 2] = v4.z, qr[4 * i + 3] = v4.w;
                 }
                 tmem_st32(tmem + lane_addr + Q_COL0 + cidx * 32, qr);
             }
             tmem_wait_st();
             fence_before_sync();
-            mbar_arrive(q_full);
+            if (ok) mbar_arrive(q_full);
+            if (threadIdx.x == 0) TW_STAMP(3);
         }
-        for (int j = lo; j < hi; ++j) {
+        for (int j = lo; ok && j < hi; ++j) {
             const int n = j - lo, buf = n & 1;
             const uint32_t tS = tmem + lane_addr + buf * kTwBN;
             TRACE_MARK();
@@ -288,7 +325,8 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             if (rescale_now) {
                 if (!(ok = mbar_wait(pv_done((n - 1) & 1), ((n - 1) >> 1) & 1, abortp))) break;
                 fence_after_sync();
-#pragma unroll
+// (a rolled loop: the path is rare, and straight-line code that runs once costs an instruction-cache miss per line)
+#pragma unroll 1
                 for (int cidx = 0; cidx < D / 32; ++cidx) {
                     uint32_t orow[32];
                     tmem_ld32(tO + cidx * 32, orow);
@@ -355,7 +393,9 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             o[0] = clock64() - ts_t0; o[1] = ts_wait; o[2] = ts_ld; o[3] = ts_max; o[4] = ts_resc; o[5] = ts_exp; o[6] = hi - lo;
         }
 #endif
+        if (threadIdx.x == 0) TW_STAMP(4);
         if (ok && hi > lo) ok = mbar_wait(o_final, 0, abortp);
+        if (threadIdx.x == 0) TW_STAMP(5);
         if (ok && hi > lo) {
             fence_after_sync();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
@@ -364,7 +404,12 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             if (a.gate && valid)
                 grow = static_cast<const unsigned char*>(a.gate) +
                        ((int64_t)qi * Hq + h) * a.gate_head_stride * (a.gate_bf16 ? 2 : 4);
-#pragma unroll
+            // Every load into the K / V stages has landed and every MMA that read them has completed (o_final): the
+            // thread lays its output row down there and sends it out as one bulk copy. A row base that is not
+            // 16-byte aligned takes plain stores.
+            const bool bulk_out = ((reinterpret_cast<uintptr_t>(orow_g) & 15u) == 0);
+            const uint32_t sOrow = smem_base + row * O_PITCH;
+#pragma unroll 1
             for (int cidx = 0; cidx < D / 32; ++cidx) {
                 uint32_t orow[32];
                 tmem_ld32(tO + cidx * 32, orow);
@@ -375,13 +420,24 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
                         float4 o4 = make_float4(__uint_as_float(orow[i]) * inv, __uint_as_float(orow[i + 1]) * inv,
                                                 __uint_as_float(orow[i + 2]) * inv, __uint_as_float(orow[i + 3]) * inv);
                         if (grow) o4 = prefill_gate4(o4, grow, a.gate_bf16, cidx * 32 + i);
-                        *reinterpret_cast<float4*>(orow_g + cidx * 32 + i) = o4;
+                        if (bulk_out)
+                            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};"
+                                         ::"r"(sOrow + (uint32_t)(cidx * 32 + i) * 4u), "f"(o4.x), "f"(o4.y), "f"(o4.z), "f"(o4.w)
+                                         : "memory");
+                        else
+                            *reinterpret_cast<float4*>(orow_g + cidx * 32 + i) = o4;
                     }
                 }
+            }
+            if (valid && bulk_out) {
+                fence_smem_to_async_proxy();
+                bulk_store(orow_g, sOrow, D * 4);
+                bulk_store_commit_and_wait();
             }
         }
     }
 
+    if (threadIdx.x == 0) TW_STAMP(6);
     if (s_abort) {
         for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     }
@@ -389,10 +445,11 @@ prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     __syncthreads();
     fence_after_sync();
     if (warp == 5) tmem_dealloc(tmem, 512);
+    if (threadIdx.x == 0) TW_STAMP(7);
     if (tid == 0 && s_abort && a.err) atomicExch(a.err, 1);
 }
 
-inline size_t prefill_tc_wide_smem(int D) { return (size_t)(D / 64) * (2 * kTwStages * kTwBN * 128) + 1024; }
+inline size_t prefill_tc_wide_smem(int D) { return (size_t)(D / 64) * (2 * kTwStages * kTwBN * 128) + kTwTailBytes + 1024; }
 
 // tk / tv: whole cache arrays with a 64 x 64 box; the queries are read with plain loads
 inline int launch_prefill_tc_wide(const PrefillTcArgs& a, const CUtensorMap& tk, const CUtensorMap& tv, int device,
