@@ -174,6 +174,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const uint32_t sQ = smem_base;                       // [2][TILE_BYTES]
     const uint32_t sK = sQ + 2 * TILE_BYTES;             // [2 stages][TILE_BYTES]
     const uint32_t sV = sK + 2 * TILE_BYTES;             // [2 stages][TILE_BYTES]
+    const uint32_t sOut = sV + 2 * TILE_BYTES;           // [8 softmax warps][32 rows][128 bytes]: output staging
 
     const uint32_t bar0 = smem_u32(bars);
     const uint32_t q_full = bar0, q_empty = bar0 + 8u;
@@ -414,10 +415,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         int cs = 0;  // key tiles this query tile has been through (phase of s_full)
 #ifdef GGR_TC_TRACE
         long long ts_wait = 0, ts_ld = 0, ts_max = 0, ts_resc = 0, ts_exp = 0, ts_t0 = clock64(), tr_x;
+        long long ts_item = 0, ts_ofin = 0, ts_epi = 0, ts_items = 0;
 #endif
         for (int it = 0; ok; ++it) {
             const int slot = it & 1;
+            TRACE_MARK();
             if (!(ok = mbar_wait(item_full(slot), (it >> 1) & 1, abortp))) break;
+            TRACE_ADD(ts_item);
             const int r = itemp[slot];
             __syncwarp();
             if (lane == 0) mbar_arrive(item_empty(slot));
@@ -473,8 +477,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                     m_used = mx;
                 }
                 if (k > 0 && __any_sync(0xffffffffu, need)) {
-#pragma unroll
-                    for (int cidx = 0; cidx < D / 32; ++cidx) {
+#pragma unroll 1
+                    for (int cidx = 0; cidx < D / 32; ++cidx) {  // rare path, kept small
                         uint32_t orow[32];
                         tmem_ld32(tO + cidx * 32, orow);
                         tmem_wait_ld();
@@ -540,40 +544,68 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             if (!ok) break;
             cs += n_t;
             // epilogue: O_t leaves TMEM as soon as its last P V has landed, then the next item may overwrite it
+            TRACE_MARK();
             if (!(ok = mbar_wait(o_final(t), it & 1, abortp))) break;
+            TRACE_ADD(ts_ofin);
             fence_after_sync();
             if (n_t > 0) {
-                uint32_t orow[D / 32][32];
+                // The rows leave through a per-warp staging area: a thread (one query row) lays 32 output columns
+                // down as 128 bytes, 16-byte pieces XOR-swizzled by the row so that the eight rows of a quarter
+                // warp hit different banks; the warp then reads the area back four rows at a time and stores
+                // whole 128-byte lines. One thread per row storing 16-byte pieces 16 KB apart cost a cache-line
+                // wavefront per lane and instruction, 3-4 us per item during which the tile's pipeline stood still.
+                const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+                const void* grow = nullptr;
+                if (a.gate && valid)
+                    grow = static_cast<const unsigned char*>(a.gate) +
+                           ((int64_t)qi * Hq + w.h) * a.gate_head_stride * (a.gate_bf16 ? 2 : 4);
+                const uint32_t stage = sOut + (uint32_t)warp * 4096u;
+                const int row_w = w.q_row0 + t * kTcBM + (warp & 3) * 32;   // first row of this warp
+                const int sub_row = lane >> 3, piece = lane & 7;
+                // (a rolled loop: this code runs once per item, and unrolled it missed the instruction cache line after
+                // line; the next item's first P V into O_t is a whole softmax tile away, so O_t may stay until the end)
+#pragma unroll 1
+                for (int cidx = 0; cidx < D / 32; ++cidx) {
+                    uint32_t orow[32];
+                    tmem_ld32(tO + cidx * 32, orow);
+                    tmem_wait_ld();
 #pragma unroll
-                for (int cidx = 0; cidx < D / 32; ++cidx) tmem_ld32(tO + cidx * 32, orow[cidx]);
-                tmem_wait_ld();
+                    for (int i = 0; i < 32; i += 4) {
+                        float4 o4 = make_float4(__uint_as_float(orow[i]) * inv, __uint_as_float(orow[i + 1]) * inv,
+                                                __uint_as_float(orow[i + 2]) * inv, __uint_as_float(orow[i + 3]) * inv);
+                        if (grow) o4 = prefill_gate4(o4, grow, a.gate_bf16, cidx * 32 + i);
+                        const uint32_t dst = stage + lane * 128u + (uint32_t)(((i >> 2) ^ (lane & 7)) << 4);
+                        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(o4.x), "f"(o4.y), "f"(o4.z), "f"(o4.w) : "memory");
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int k4 = 0; k4 < 8; ++k4) {
+                        const int rr = k4 * 4 + sub_row;
+                        float4 o4;
+                        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                     : "=f"(o4.x), "=f"(o4.y), "=f"(o4.z), "=f"(o4.w)
+                                     : "r"(stage + rr * 128u + (uint32_t)((piece ^ (rr & 7)) << 4)));
+                        if (row_w + rr < a.m)
+                            *reinterpret_cast<float4*>(a.out + ((int64_t)(row_w + rr) * Hq + w.h) * D + cidx * 32 + piece * 4) = o4;
+                    }
+                    __syncwarp();
+                }
                 fence_before_sync();
                 mbar_arrive(o_free(t));
-                if (valid) {
-                    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-                    float* orow_g = a.out + ((int64_t)qi * Hq + w.h) * D;
-                    const void* grow = nullptr;
-                    if (a.gate)
-                        grow = static_cast<const unsigned char*>(a.gate) +
-                               ((int64_t)qi * Hq + w.h) * a.gate_head_stride * (a.gate_bf16 ? 2 : 4);
-#pragma unroll
-                    for (int cidx = 0; cidx < D / 32; ++cidx)
-#pragma unroll
-                        for (int i = 0; i < 32; i += 4) {
-                            float4 o4 = make_float4(__uint_as_float(orow[cidx][i]) * inv, __uint_as_float(orow[cidx][i + 1]) * inv,
-                                                    __uint_as_float(orow[cidx][i + 2]) * inv, __uint_as_float(orow[cidx][i + 3]) * inv);
-                            if (grow) o4 = prefill_gate4(o4, grow, a.gate_bf16, cidx * 32 + i);
-                            *reinterpret_cast<float4*>(orow_g + cidx * 32 + i) = o4;
-                        }
-                }
             } else {
                 mbar_arrive(o_free(t));
             }
+            TRACE_ADD(ts_epi);
+#ifdef GGR_TC_TRACE
+            ++ts_items;
+#endif
         }
 #ifdef GGR_TC_TRACE
         if (blockIdx.x == 0 && a.trace && (tid & 127) == 0) {
             long long* o = a.trace + 8 + t * 8;
             o[0] = clock64() - ts_t0; o[1] = ts_wait; o[2] = ts_ld; o[3] = ts_max; o[4] = ts_resc; o[5] = ts_exp; o[6] = cs;
+            long long* o2 = a.trace + 128 + t * 4;
+            o2[0] = ts_item; o2[1] = ts_ofin; o2[2] = ts_epi; o2[3] = ts_items;
         }
 #endif
     }
@@ -608,7 +640,7 @@ inline bool prefill_tc_usable(int impl, int fmt, int D, int /*G*/) {
     return prefill_tc_shape_ok(fmt, D);
 }
 
-inline size_t prefill_tc_smem(int D) { return (size_t)6 * (D / 64) * 128 * 128 + 1024; }
+inline size_t prefill_tc_smem(int D) { return (size_t)6 * (D / 64) * 128 * 128 + 8 * 4096 + 1024; }
 
 template <int D>
 inline int launch_prefill_tc_inst(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
