@@ -335,14 +335,19 @@ __device__ __forceinline__ void peer_allow_dependents(const AttnArgs& a) {
 // launch has finished, this rank's flag is raised on all peers (system-scope release after the stores).
 __device__ __forceinline__ void peer_group_done(const AttnArgs& a) {
     if (!a.px.enabled) return;
-    __threadfence_system();
+    // One system-scope fence per CTA, issued after the CTA barrier by the thread that takes the ticket: the barrier
+    // orders every thread's stores before it and the fence is cumulative. (A fence in each of the 256 threads cost
+    // 16 us per launch: system-scope fences are served one after the other.)
     __syncthreads();
     if (threadIdx.x == 0) {
+        __threadfence_system();
         const unsigned prev = atomicAdd(a.px.done_counter, 1u);
         if (prev == (unsigned)a.px.groups_total - 1u) {
+            // one fence, then relaxed flag stores: a release store per peer is a system-scope fence each, and eight
+            // of them in a row cost 8 us at the end of every launch
             __threadfence_system();
             for (int r = 0; r < a.px.n_ranks; ++r) {
-                asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(a.px.flag[r]), "r"(a.px.epoch) : "memory");
+                asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(a.px.flag[r]), "r"(a.px.epoch) : "memory");
             }
             *a.px.done_counter = 0u;  // ready for the next launch
         }
@@ -839,25 +844,34 @@ __global__ void combine_exchange_kernel(const float* parts, const int* flags, in
                                         const float* gate, int gate_head_stride) {
     __shared__ int s_ok;
     const int h = blockIdx.x, item = blockIdx.y;
-    if (threadIdx.x == 0) {
+    if (threadIdx.x < 32) {
+        // lane r watches rank r's flag with relaxed loads; one system-scope fence after the last flag has arrived
+        // makes the peers' states visible (an acquire load per poll is a fence each: eight flags checked one after
+        // the other cost 8 us even when all of them were already set). More than 32 ranks: lanes take several.
         int ok = 1;
         unsigned long long t0;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-        for (int r = 0; r < n_parts && ok == 1; ++r) {
+        for (int r = threadIdx.x; r < n_parts; r += 32) {
             int seen = 0;
             for (uint32_t it = 0; it < (1u << 24); ++it) {
-                asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(flags + r) : "memory");
+                asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(flags + r) : "memory");
                 if (seen >= epoch) break;
                 unsigned long long now;
                 asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
                 if (now - t0 > wait_ns) break;
                 __nanosleep(100);
             }
-            if (seen < epoch) ok = 0;
+            if (seen < epoch) ok = min(ok, 0);
             else if (seen > epoch + 1) ok = -1;
         }
-        s_ok = ok;
-        if (ok != 1 && err) atomicExch(err, ok == 0 ? 1 : 2);
+        // worst status over the lanes: -1 (a flag ahead of this step) before 0 (a wait ran out) before 1
+        const bool any_ahead = __any_sync(0xffffffffu, ok == -1), any_late = __any_sync(0xffffffffu, ok == 0);
+        ok = any_ahead ? -1 : (any_late ? 0 : 1);
+        if (threadIdx.x == 0) {
+            __threadfence_system();
+            s_ok = ok;
+            if (ok != 1 && err) atomicExch(err, ok == 0 ? 1 : 2);
+        }
     }
     __syncthreads();
     const bool ok = s_ok == 1;
