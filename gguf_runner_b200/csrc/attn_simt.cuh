@@ -839,11 +839,13 @@ __global__ void combine_partials_kernel(const float* parts, int n_parts, int ite
 // iteration count; when it runs out the kernel stores 1 into the error word, writes zeros and returns.
 // A peer may legitimately be one step ahead (it has finished this step and sent the next one into the
 // other parity); a flag further ahead means the ranks' step counters disagree: error word 2, zeros.
+constexpr int kCombineHeads = 8;  // query heads (warps) per CTA of the exchange merge
+
 __global__ void combine_exchange_kernel(const float* parts, const int* flags, int epoch, int n_parts, int64_t part_stride,
                                         int Hq, int D, float* out, int* err, unsigned long long wait_ns,
                                         const float* gate, int gate_head_stride) {
     __shared__ int s_ok;
-    const int h = blockIdx.x, item = blockIdx.y;
+    const int item = blockIdx.y;
     if (threadIdx.x < 32) {
         // lane r watches rank r's flag with relaxed loads; one system-scope fence after the last flag has arrived
         // makes the peers' states visible (an acquire load per poll is a fence each: eight flags checked one after
@@ -875,20 +877,49 @@ __global__ void combine_exchange_kernel(const float* parts, const int* flags, in
     }
     __syncthreads();
     const bool ok = s_ok == 1;
+    // one warp per query head (kCombineHeads heads per CTA, so that few CTAs pay the wait and the fence); a lane owns
+    // pairs of output elements and fetches them from every rank with independent 8-byte loads
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.x * kCombineHeads + warp;
+    if (h >= Hq) return;
     const float* base = parts + ((int64_t)item * Hq + h) * (D + 2);
-    float ms = -INFINITY;
-    for (int r = 0; r < n_parts; ++r) ms = fmaxf(ms, __ldcg(base + r * part_stride + D));
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float o = 0.0f, ls = 0.0f;
-        for (int r = 0; r < n_parts; ++r) {
-            const float mw = __ldcg(base + r * part_stride + D), lw = __ldcg(base + r * part_stride + D + 1);
-            const float f = (mw == -INFINITY) ? 0.0f : lw * exp2f(mw - ms);
-            o += f * __ldcg(base + r * part_stride + d);
-            ls += f;
+    // everything a lane needs is requested before anything is used, so the merge costs one round trip: lane r
+    // fetches rank r's (m, l) (at most kMaxPeers ranks), every lane its output pairs of all ranks
+    float2 ml = make_float2(-INFINITY, 0.0f);
+    if (lane < n_parts) ml = __ldcg(reinterpret_cast<const float2*>(base + lane * part_stride + D));
+    for (int d0 = 0; d0 < D / 2; d0 += 64) {
+        const int da = d0 + lane, db = d0 + 32 + lane;
+        float2 oa[kMaxPeers], ob[kMaxPeers];
+#pragma unroll
+        for (int r = 0; r < kMaxPeers; ++r) {
+            const bool in = r < n_parts;
+            oa[r] = (in && da < D / 2) ? __ldcg(reinterpret_cast<const float2*>(base + r * part_stride) + da) : make_float2(0.0f, 0.0f);
+            ob[r] = (in && db < D / 2) ? __ldcg(reinterpret_cast<const float2*>(base + r * part_stride) + db) : make_float2(0.0f, 0.0f);
         }
-        float res = (ok && ls > 0.0f) ? o / ls : 0.0f;
-        if (ok && gate) res = gated_output(res, gate[((int64_t)item * Hq + h) * gate_head_stride + d]);
-        out[((int64_t)item * Hq + h) * D + d] = res;
+        const float ms = warp_max(ml.x);
+        const float fw = (ml.x == -INFINITY) ? 0.0f : ml.y * exp2f(ml.x - ms);  // weight of rank `lane`
+        const float ls = warp_sum(fw);
+        float ax = 0.0f, ay = 0.0f, bx = 0.0f, by = 0.0f;
+#pragma unroll
+        for (int r = 0; r < kMaxPeers; ++r) {
+            const float f = __shfl_sync(0xffffffffu, fw, r);
+            ax += f * oa[r].x;
+            ay += f * oa[r].y;
+            bx += f * ob[r].x;
+            by += f * ob[r].y;
+        }
+        const float inv = (ok && ls > 0.0f) ? 1.0f / ls : 0.0f;
+        const float* gr = (ok && gate) ? gate + ((int64_t)item * Hq + h) * gate_head_stride : nullptr;
+        if (da < D / 2) {
+            float rx = ax * inv, ry = ay * inv;
+            if (gr) rx = gated_output(rx, gr[2 * da]), ry = gated_output(ry, gr[2 * da + 1]);
+            *reinterpret_cast<float2*>(out + ((int64_t)item * Hq + h) * D + 2 * da) = make_float2(rx, ry);
+        }
+        if (db < D / 2) {
+            float rx = bx * inv, ry = by * inv;
+            if (gr) rx = gated_output(rx, gr[2 * db]), ry = gated_output(ry, gr[2 * db + 1]);
+            *reinterpret_cast<float2*>(out + ((int64_t)item * Hq + h) * D + 2 * db) = make_float2(rx, ry);
+        }
     }
 }
 

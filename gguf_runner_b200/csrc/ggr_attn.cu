@@ -2080,8 +2080,8 @@ int exchange_receive(ggr_attn_ctx* c, int B, float* out, int ptr_kind, bool afte
         const int* flags = reinterpret_cast<const int*>(c->x_local);
         if (after_own_send && !c->timing) {
             cudaLaunchConfig_t lc{};
-            lc.gridDim = dim3(c->kv.Hq, B);
-            lc.blockDim = dim3(128);
+            lc.gridDim = dim3((c->kv.Hq + kCombineHeads - 1) / kCombineHeads, B);
+            lc.blockDim = dim3(kCombineHeads * 32);
             lc.dynamicSmemBytes = 0;
             lc.stream = c->stream;
             cudaLaunchAttribute attr[1];
@@ -2092,7 +2092,7 @@ int exchange_receive(ggr_attn_ctx* c, int B, float* out, int ptr_kind, bool afte
             CUDA_TRY(c, cudaLaunchKernelEx(&lc, combine_exchange_kernel, parts, flags, epoch, n, (int64_t)slot, (int)c->kv.Hq,
                                            (int)c->D, dout, c->d_err, c->x_wait_ns, (const float*)nullptr, 0));
         } else {
-            combine_exchange_kernel<<<dim3(c->kv.Hq, B), 128, 0, c->stream>>>(parts, flags, epoch, n, (int64_t)slot, c->kv.Hq,
+            combine_exchange_kernel<<<dim3((c->kv.Hq + kCombineHeads - 1) / kCombineHeads, B), kCombineHeads * 32, 0, c->stream>>>(parts, flags, epoch, n, (int64_t)slot, c->kv.Hq,
                                                                               c->D, dout, c->d_err, c->x_wait_ns, nullptr, 0);
         }
     }
