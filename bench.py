@@ -383,7 +383,7 @@ def bench_prefill(torch, dist, args, rank, world, local_rank, peaks):
         # DRAM bytes of one launch of this shape, read + write, taken from an ncu capture of the same kernel and shape
         # (not measured by this run): the kernel is bound by the tensor cores and the MUFU unit, its traffic is the
         # q / K / V minimum plus the part of the output that left L2
-        traffic=64.6e6, traffic_unit="bytes per launch",
+        traffic=67.6e6, traffic_unit="bytes per launch",
         traffic_source="constant: dram__bytes_read.sum + dram__bytes_write.sum of an ncu capture of this kernel at this shape",
         flops_per_launch=flops_per_launch, avg_launch_ms=attn_ms, launches_per_step=attn_per_step,
         rope_append_avg_ms=rope_ms, rope_append_launches_per_step=rope_per_step,

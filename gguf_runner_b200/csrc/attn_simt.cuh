@@ -366,16 +366,19 @@ __device__ __forceinline__ void split_merge_store(const AttnArgs& a, int item, i
         return;
     }
     const int D = a.kv.D, G = a.kv.G, Hq = a.kv.Hq, NS = a.n_split;
-    __threadfence();
+    // one fence on each side of the ticket, issued by the thread that takes it: the CTA barrier before it orders
+    // every thread's stores of this CTA's state ahead of the fence, the barrier after it orders every thread's
+    // loads of the other CTAs' states behind it (fences are cumulative)
     __syncthreads();
     if (threadIdx.x == 0) {
+        __threadfence();
         unsigned prev = atomicAdd(&a.counters[item * a.kv.Hkv + kvh], 1u);
         *s_last = (prev == (unsigned)NS - 1u);
+        if (*s_last) __threadfence();
     }
     __syncthreads();
     if (!*s_last) return;
     DECODE_STAMP(5);
-    __threadfence();
     const float* base = a.part + ((int64_t)item * Hq + (int64_t)kvh * G) * NS * (D + 2);
     // One warp per head; this CTA runs alone at the end of the launch and a round trip to the states that other
     // SMs just wrote costs about 1.4 us, so everything is arranged for few dependent round trips: (m, l) of all

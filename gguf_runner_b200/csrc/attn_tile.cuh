@@ -113,7 +113,8 @@ __global__ void __launch_bounds__(kTileThreads) attn_tile_kernel(AttnArgs a) {
             float* vsc = ksc + TK * NSH;
             const int nsr = a.kv.n_scales;
             for (int id = tid; id < TK * NSH; id += kTileThreads) {
-                const int key = id / NSH, b = id - key * NSH;
+                constexpr int NS1 = NSH > 0 ? NSH : 1;  // (the branch is dead when NSH is 0)
+                const int key = id / NS1, b = id - key * NS1;
                 const int tk = key0 + key;
                 const int valid = tk < k1;
                 const int64_t si = (row0 + (valid ? tk : k1 - 1)) * nsr + (FMT == KV_Q8_ROW ? 0 : (int64_t)kvh * NSH + b);

@@ -427,7 +427,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             if (lane == 0) mbar_arrive(item_empty(slot));
             if (r < 0) break;
             const TcItem w = tc_item(a, r);
-            const int lo_t = w.lo_of(t), hi_t = w.hi_of(t), n_t = hi_t - lo_t, lo = w.lo;
+            const int lo_t = w.lo_of(t), hi_t = w.hi_of(t), n_t = hi_t - lo_t;
+#ifdef GGR_TC_TRACE
+            const int lo = w.lo;
+#endif
             const int qi = w.q_row0 + t * kTcBM + row;
             const bool valid = qi < a.m;
             int vs = 0, ve = 0;

@@ -288,7 +288,8 @@ inline bool rope_append_fast_ok(const RopeAppendArgs& a) {
     const int D = a.kv.D;
     return a.in_bf16 && a.kv.fmt == KV_BF16 && a.q_out_h && !a.q_out && !a.k_out &&
            a.flags == (RF_ROTATE | RF_WRITE_Q | RF_APPEND) && D % 8 == 0 && a.rope.rope_half <= 128 &&
-           (a.rope.style == 1 || (a.rope.rope_half % 8 == 0 && a.rope.rope_dim % 8 == 0)) && a.kv.pos_begin == 0;
+           ((a.rope.style == 1 && a.rope.rope_dim == D) || (a.rope.style == 0 && a.rope.rope_half % 8 == 0 && a.rope.rope_dim % 8 == 0)) &&
+           a.kv.pos_begin == 0;
 }
 
 __global__ void __launch_bounds__(256) rope_append_bf16_kernel(RopeAppendArgs a) {
@@ -397,7 +398,9 @@ __device__ __forceinline__ int rope_task8(const TIn* head, int vi, const RopePar
 }
 
 inline bool rope_append_vec_ok(const RopeAppendArgs& a) {
-    const bool span_ok = a.rope.style == 1 || (a.rope.rope_half % 8 == 0 && a.rope.rope_dim % 8 == 0);
+    // adjacent pairs: the vector kernels rotate every pair of the head, so the rotated span must be the whole head
+    const bool span_ok = (a.rope.style == 1 && a.rope.rope_dim == a.kv.D) ||
+                         (a.rope.style == 0 && a.rope.rope_half % 8 == 0 && a.rope.rope_dim % 8 == 0);
     return span_ok && a.kv.D % 8 == 0 && a.kv.fmt != KV_Q8_BLOCK32;
 }
 
