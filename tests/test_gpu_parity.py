@@ -209,6 +209,17 @@ def test_partial_rope_and_adjacent_style():
     check_prefill_then_decode(cfg, m=40, steps=2, seed=3)
 
 
+def test_adjacent_pairs_over_part_of_a_head_are_rejected():
+    """The adjacent-pair rotation of the reference walks the whole head (apply_rope_qk,
+    src/engine/runtime/inference.rs:1838-1866); a rope_dim below head_dim with that style is refused at create time,
+    so no kernel ever sees it."""
+    cfg = AttnConfig(n_layers=1, n_heads=8, n_kv_heads=2, head_dim=64, rope_dim=32, seq_len=64,
+                     rope_style=ROPE_ADJACENT, kv_format=KV_F32)
+    with pytest.raises(GgrError) as e:
+        g.AttnContext(cfg)
+    assert "rope_dim" in str(e.value)
+
+
 def test_position_plan_and_image_block_prefill():
     cfg = AttnConfig(n_layers=1, n_heads=4, n_kv_heads=2, head_dim=64, seq_len=64, rope_theta=1e6,
                      rope_sections=[8, 12, 12, 0], rope_layout=ROPE_INTERLEAVED, image_mode=1,
