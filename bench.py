@@ -636,11 +636,11 @@ def bench_decode_turbo(torch, args, local_rank, peaks, B=8):
 
 def bench_projections(torch, args, local_rank, peaks):
     """The matmuls either side of the path with device-resident weights: the weight-streaming kernel on a
-    Llama-3-8B-shaped 14336 x 4096 matrix (Q8_0 and BF16), the tcgen05 GEMM on the same matrix for a 4096-token chunk, and the Qwen3-0.6B-shaped attention half-layer of configs[0] end to end from host hidden states."""
+    Llama-3-8B-shaped 14336 x 4096 matrix (Q4_K, Q8_0 and BF16), the tcgen05 GEMM on the same matrix for a 4096-token chunk, and the Qwen3-0.6B-shaped attention half-layer of configs[0] end to end from host hidden states."""
     import gguf_runner_b200 as g
     from gguf_runner_b200 import presets
-    from gguf_runner_b200.binding import KV_Q8_ROW, W_BF16, W_Q8_0, Weights
-    from tests.oracle_binding import bf16_bits, quantize_q8_0
+    from gguf_runner_b200.binding import KV_Q8_ROW, W_BF16, W_Q4_K, W_Q8_0, Weights
+    from tests.oracle_binding import bf16_bits, quantize_q4_k, quantize_q8_0
     rng = np.random.default_rng(77)
     res = {}
     ctx = g.AttnContext(presets.qwen3_0p6b_decode(n_layers=1, seq_len=64, device=local_rank))
@@ -648,7 +648,8 @@ def bench_projections(torch, args, local_rank, peaks):
     wf = (rng.standard_normal((rows, cols)) / 64.0).astype(np.float32)
     # several matrices are cycled so that the weights come from HBM, not from the 126 MB L2
     n_mats = 6
-    for name, wtype, raw, nbytes in (("q8_0", W_Q8_0, quantize_q8_0(wf), rows * cols * 34 // 32),
+    for name, wtype, raw, nbytes in (("q4_k", W_Q4_K, quantize_q4_k(wf), rows * cols * 144 // 256),
+                                     ("q8_0", W_Q8_0, quantize_q8_0(wf), rows * cols * 34 // 32),
                                      ("bf16", W_BF16, bf16_bits(wf), rows * cols * 2)):
         mats = [Weights(wtype, rows, cols, raw, device=local_rank) for _ in range(n_mats)]
         for n in (1, 4):

@@ -30,7 +30,7 @@ IMAGE_CAUSAL, IMAGE_BIDIRECTIONAL = 0, 1
 SHARD_NONE, SHARD_KV_SEQUENCE = 0, 2
 IMPL_AUTO, IMPL_SIMT, IMPL_MMA, IMPL_TCGEN05 = 0, 1, 2, 3
 
-W_F32, W_BF16, W_Q8_0 = 0, 1, 2
+W_F32, W_BF16, W_Q8_0, W_Q4_K = 0, 1, 2, 3
 
 KV_FORMATS = {"f32": KV_F32, "bf16": KV_BF16, "q8_row": KV_Q8_ROW, "q8_block32": KV_Q8_BLOCK32, "turbo": KV_TURBO}
 
@@ -247,7 +247,8 @@ class Weights:
     def __init__(self, wtype: int, rows: int, cols: int, data: np.ndarray, device: int = 0):
         self._L = lib()
         data = np.ascontiguousarray(data)
-        want = rows * cols * 4 if wtype == W_F32 else (rows * cols * 2 if wtype == W_BF16 else rows * (cols // 32) * 34)
+        want = {W_F32: rows * cols * 4, W_BF16: rows * cols * 2, W_Q8_0: rows * (cols // 32) * 34,
+                W_Q4_K: rows * (cols // 256) * 144}.get(wtype, -1)
         if data.nbytes != want:
             raise ValueError(f"weight data has {data.nbytes} bytes, the layout needs {want}")
         h = C.c_void_p()

@@ -2187,7 +2187,8 @@ extern "C" int ggr_attn_set_layer_fixups(ggr_attn_ctx* c, int32_t layer, const f
 struct ggr_weights {
     int device = 0, wtype = 0, rows = 0, cols = 0;
     void* d_main = nullptr;            // F32 / BF16 values, or the Q8_0 code plane
-    __half* d_scales = nullptr;        // Q8_0 block scales [rows][cols / 32]
+    __half* d_scales = nullptr;        // Q8_0 block scales [rows][cols / 32]; Q4_K: (scale, min) byte pairs per 32 weights
+    __half2* d_dm = nullptr;           // Q4_K: (d, dmin) per super-block [rows][cols / 256]
     __nv_bfloat16* d_bf16 = nullptr;   // bf16 image for the tensor-core kernel (d_main itself for BF16)
     CUtensorMap tmB;                   // [rows][cols] bf16, box 64 x 256
     bool have_tmap = false;
@@ -2237,6 +2238,7 @@ int matmul_device(ggr_attn_ctx* c, const ggr_weights* w, const float* x, int n, 
         GemvArgs a{};
         a.w = w->d_main;
         a.scales = w->d_scales;
+        a.dm = w->d_dm;
         a.rows = w->rows;
         a.cols = w->cols;
         a.x = x;
@@ -2298,9 +2300,9 @@ extern "C" int ggr_weights_upload(int32_t device, int32_t wtype, int32_t rows, i
     };
     if (!out || !host_data) return bad(GGR_ERR_INVALID, "null argument");
     *out = nullptr;
-    if (wtype < GGR_W_F32 || wtype > GGR_W_Q8_0) return bad(GGR_ERR_INVALID, "unknown weight type");
-    if (rows <= 0 || cols <= 0 || rows % 8 != 0 || cols % (wtype == GGR_W_Q8_0 ? 32 : 8) != 0)
-        return bad(GGR_ERR_UNSUPPORTED, "rows must be a multiple of 8, cols of 8 (32 for Q8_0)");
+    if (wtype < GGR_W_F32 || wtype > GGR_W_Q4_K) return bad(GGR_ERR_INVALID, "unknown weight type");
+    if (rows <= 0 || cols <= 0 || rows % 8 != 0 || cols % (wtype == GGR_W_Q4_K ? 256 : (wtype == GGR_W_Q8_0 ? 32 : 8)) != 0)
+        return bad(GGR_ERR_UNSUPPORTED, "rows must be a multiple of 8, cols of 8 (32 for Q8_0, 256 for Q4_K)");
     int ndev = 0;
     if (cudaGetDeviceCount(&ndev) != cudaSuccess || device < 0 || device >= ndev) return bad(GGR_ERR_CUDA, "no such CUDA device");
     DeviceGuard guard(device);
@@ -2326,6 +2328,47 @@ extern "C" int ggr_weights_upload(int32_t device, int32_t wtype, int32_t rows, i
         image.resize(n);
         const float* src = static_cast<const float*>(host_data);
         for (size_t i = 0; i < n; ++i) image[i] = float_to_bf16_bits(src[i]);
+    } else if (wtype == GGR_W_Q4_K) {
+        // 144-byte super-blocks -> a nibble plane [rows][cols / 2] in which every 32 weights of one (scale, min) pair
+        // are 16 contiguous bytes (byte i = weight i | weight i + 16 << 4), a plane of (scale, min) byte pairs per 32
+        // weights and a plane of (d, dmin) per 256 (get_scale_min_k4, src/engine/kernels/quant.rs:118-126)
+        const size_t nsb = n / 256, nb32 = n / 32;
+        std::vector<uint8_t> codes(n / 2);
+        std::vector<uint16_t> sm(nb32);
+        std::vector<uint32_t> dm(nsb);
+        image.resize(n);
+        const uint8_t* src = static_cast<const uint8_t*>(host_data);
+        for (size_t b = 0; b < nsb; ++b) {
+            const uint8_t* blk = src + b * 144;
+            const uint16_t dh = (uint16_t)(blk[0] | (blk[1] << 8)), mh = (uint16_t)(blk[2] | (blk[3] << 8));
+            dm[b] = (uint32_t)dh | ((uint32_t)mh << 16);
+            const float d = half_bits_to_float(dh), dmin = half_bits_to_float(mh);
+            const uint8_t* sc = blk + 4;
+            const uint8_t* qs = blk + 16;
+            for (int j = 0; j < 8; ++j) {
+                int s6, m6;
+                if (j < 4) {
+                    s6 = sc[j] & 63;
+                    m6 = sc[j + 4] & 63;
+                } else {
+                    s6 = (sc[j + 4] & 0x0f) | ((sc[j - 4] >> 6) << 4);
+                    m6 = (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4);
+                }
+                sm[b * 8 + j] = (uint16_t)(s6 | (m6 << 8));
+                const float d1 = d * (float)s6, m1f = dmin * (float)m6;
+                uint8_t q[32];
+                for (int l = 0; l < 32; ++l) q[l] = (j & 1) ? (uint8_t)(qs[(j >> 1) * 32 + l] >> 4) : (uint8_t)(qs[(j >> 1) * 32 + l] & 0x0f);
+                for (int l = 0; l < 16; ++l) codes[(b * 8 + j) * 16 + l] = (uint8_t)(q[l] | (q[l + 16] << 4));
+                for (int l = 0; l < 32; ++l) image[b * 256 + j * 32 + l] = float_to_bf16_bits(d1 * (float)q[l] - m1f);
+            }
+        }
+        if (cudaMalloc(&w->d_main, n / 2) != cudaSuccess || cudaMalloc((void**)&w->d_scales, nb32 * 2) != cudaSuccess ||
+            cudaMalloc((void**)&w->d_dm, nsb * 4) != cudaSuccess)
+            return fail_up("unable to allocate the weights");
+        if (cudaMemcpy(w->d_main, codes.data(), n / 2, cudaMemcpyHostToDevice) != cudaSuccess ||
+            cudaMemcpy(w->d_scales, sm.data(), nb32 * 2, cudaMemcpyHostToDevice) != cudaSuccess ||
+            cudaMemcpy(w->d_dm, dm.data(), nsb * 4, cudaMemcpyHostToDevice) != cudaSuccess)
+            return fail_up("weight upload failed");
     } else {
         // 34-byte blocks -> a code plane [rows][cols] and a scale plane [rows][cols / 32]
         const size_t nb = n / 32;
@@ -2365,6 +2408,7 @@ extern "C" void ggr_weights_free(ggr_weights* w) {
     if (w->d_bf16 && w->d_bf16 != w->d_main) cudaFree(w->d_bf16);
     cudaFree(w->d_main);
     cudaFree(w->d_scales);
+    cudaFree(w->d_dm);
     delete w;
 }
 

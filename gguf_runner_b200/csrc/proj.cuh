@@ -6,8 +6,10 @@
 // Two kernels:
 //   proj_gemv_kernel  decode, a few activation rows: bound by reading the weights once. One warp per two weight
 //                     rows, 16-byte loads along the row, the activation rows come from L1, shuffle reduction.
-//                     Weight formats F32, BF16 and Q8_0 (codes and f16 block scales repacked into two planes at
-//                     upload, so that the codes are 16-byte aligned).
+//                     Weight formats F32, BF16, Q8_0 (codes and f16 block scales repacked into two planes at
+//                     upload, so that the codes are 16-byte aligned) and Q4_K (nibble plane in which the 32 weights
+//                     of a (scale, min) pair are one 16-byte load; w = d * scale * q - dmin * min is applied as
+//                     d * scale * sum(x q) - dmin * min * sum(x), one FMA per weight).
 //   proj_gemm_kernel  prefill chunks: tcgen05 GEMM, bf16 x bf16 -> f32 in TMEM. A = activations [m][K] (bf16), B =
 //                     weights [N][K] (bf16; Q8_0 / F32 weights use a bf16 image made at upload), 128 x 256 output
 //                     tile per CTA, 64-column k-steps through a four-stage TMA ring, one MMA issuer, four epilogue
@@ -22,11 +24,12 @@
 
 namespace ggr {
 
-enum ProjWeightType : int { PW_F32 = 0, PW_BF16 = 1, PW_Q8_0 = 2 };
+enum ProjWeightType : int { PW_F32 = 0, PW_BF16 = 1, PW_Q8_0 = 2, PW_Q4_K = 3 };
 
 struct GemvArgs {
-    const void* w;         // F32 / BF16 values [rows][cols], or Q8_0 codes int8 [rows][cols]
-    const __half* scales;  // Q8_0: [rows][cols / 32]
+    const void* w;         // F32 / BF16 values [rows][cols], Q8_0 codes int8 [rows][cols], or Q4_K nibbles [rows][cols / 2]
+    const __half* scales;  // Q8_0: f16 scale [rows][cols / 32]; Q4_K: (6-bit scale, 6-bit min) byte pair [rows][cols / 32]
+    const __half2* dm;     // Q4_K: (d, dmin) [rows][cols / 256]
     int rows, cols;
     const float* x;        // [n][cols]
     int n;
@@ -54,6 +57,12 @@ __device__ __forceinline__ float q8_byte_to_float(uint32_t biased_word, int byte
     return __uint_as_float(__byte_perm(biased_word, 0x4B000000u, sel)) - 8388736.0f;
 }
 
+// unsigned byte (0..255) of a word -> float the same way, without a bias
+__device__ __forceinline__ float nibble_byte_to_float(uint32_t word, int byte) {
+    const uint32_t sel = 0x7650u | (uint32_t)byte;
+    return __uint_as_float(__byte_perm(word, 0x4B000000u, sel)) - 8388608.0f;
+}
+
 template <int CPL>
 __host__ __device__ inline size_t gemv_row_floats_dev(int cols) {
     const int per_step = 32 * CPL;
@@ -62,8 +71,8 @@ __host__ __device__ inline size_t gemv_row_floats_dev(int cols) {
 
 template <int WT>
 struct GemvGeom {
-    static constexpr int CPL = WT == PW_Q8_0 ? 16 : 8;  // columns per lane and step (one 16-byte load; two for F32)
-    static constexpr int UN = WT == PW_F32 ? 4 : 8;      // steps whose weight loads are in flight together
+    static constexpr int CPL = WT == PW_Q4_K ? 32 : (WT == PW_Q8_0 ? 16 : 8);  // columns per lane and step (one 16-byte load; two for F32)
+    static constexpr int UN = (WT == PW_F32 || WT == PW_Q4_K) ? 4 : 8;          // steps whose weight loads are in flight together
     static constexpr int SPAN = 32 * CPL * UN;           // columns one batch of loads covers
     static constexpr int NL = WT == PW_F32 ? 2 : 1;      // 16-byte loads per lane, step and row
 };
@@ -90,6 +99,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32) proj_gemv_kernel(GemvArgs a) 
 
     uint4 raw[UN][kGemvRPW][NL];
     float dsc[UN][kGemvRPW];
+    float dmn[UN][kGemvRPW];  // Q4_K: dmin * min of the lane's 32 weights
     // requests the weights of unit u: UN steps of both rows, 16 (32 for F32) independent 16-byte loads per lane
     auto load_unit = [&](int u) {
         const int grp = blockIdx.x + (u / ncb) * gridDim.x, cb = (u % ncb) * Ge::SPAN;
@@ -108,9 +118,15 @@ __global__ void __launch_bounds__(kGemvWarps * 32) proj_gemv_kernel(GemvArgs a) 
                         raw[s][r][NL - 1] = ld_weights16(p + 1);
                     } else if (WT == PW_BF16) {
                         raw[s][r][0] = ld_weights16(static_cast<const __nv_bfloat16*>(a.w) + (size_t)row * cols + c0);
-                    } else {
+                    } else if (WT == PW_Q8_0) {
                         raw[s][r][0] = ld_weights16(static_cast<const int8_t*>(a.w) + (size_t)row * cols + c0);
                         dsc[s][r] = __half2float(a.scales[(size_t)row * (cols >> 5) + (c0 >> 5)]);
+                    } else {
+                        raw[s][r][0] = ld_weights16(static_cast<const uint8_t*>(a.w) + (((size_t)row * cols + c0) >> 1));
+                        const uint32_t sm = __ldg(reinterpret_cast<const unsigned short*>(a.scales) + (size_t)row * (cols >> 5) + (c0 >> 5));
+                        const float2 dd = __half22float2(__ldg(a.dm + (size_t)row * (cols >> 8) + (c0 >> 8)));
+                        dsc[s][r] = dd.x * (float)(sm & 0xffu);   // d * scale, as dequantize_row_q4_k forms it
+                        dmn[s][r] = dd.y * (float)(sm >> 8);      // dmin * min
                     }
                 }
             }
@@ -165,11 +181,24 @@ __global__ void __launch_bounds__(kGemvWarps * 32) proj_gemv_kernel(GemvArgs a) 
                             wv[r][2 * i] = __uint_as_float(w4[i] << 16);
                             wv[r][2 * i + 1] = __uint_as_float(w4[i] & 0xffff0000u);
                         }
-                    } else {
+                    } else if (WT == PW_Q8_0) {
                         const uint4 q = raw[s][r][0];
                         const uint32_t w4[4] = {q.x ^ 0x80808080u, q.y ^ 0x80808080u, q.z ^ 0x80808080u, q.w ^ 0x80808080u};
 #pragma unroll
                         for (int i = 0; i < CPL; ++i) wv[r][i] = q8_byte_to_float(w4[(i >> 2) & 3], i & 3);
+                    } else {
+                        // byte i of the 16 holds weights i (low nibble) and i + 16 (high nibble) of the lane's 32
+                        const uint4 q = raw[s][r][0];
+                        const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const uint32_t lo = w4[k] & 0x0f0f0f0fu, hi = (w4[k] >> 4) & 0x0f0f0f0fu;
+#pragma unroll
+                            for (int b = 0; b < 4; ++b) {
+                                wv[r][(4 * k + b) % CPL] = nibble_byte_to_float(lo, b);
+                                wv[r][(16 + 4 * k + b) % CPL] = nibble_byte_to_float(hi, b);
+                            }
+                        }
                     }
                 }
                 const int step = (cb + s * 32 * CPL) / (32 * CPL);
@@ -193,6 +222,17 @@ __global__ void __launch_bounds__(kGemvWarps * 32) proj_gemv_kernel(GemvArgs a) 
                     // Q8_0: the block scale multiplies the partial sum of the block's codes, as in the reference
 #pragma unroll
                     for (int r = 0; r < kGemvRPW; ++r) acc[r][t] = fmaf(part[r], dsc[s][r], acc[r][t]);
+                    if (WT == PW_Q4_K) {
+                        // sum over the lane's 32 weights of x (d s q - dmin m) = d s sum(x q) - dmin m sum(x)
+                        float xsum = 0.0f;
+#pragma unroll
+                        for (int i = 0; i < CPL; i += 4) {
+                            const float4 xx = xp[(i >> 2) * 32];
+                            xsum += (xx.x + xx.y) + (xx.z + xx.w);
+                        }
+#pragma unroll
+                        for (int r = 0; r < kGemvRPW; ++r) acc[r][t] = fmaf(-dmn[s][r], xsum, acc[r][t]);
+                    }
                 }
             }
             if (cbi == ncb - 1) {
@@ -237,6 +277,7 @@ inline cudaError_t launch_gemv(int wtype, const GemvArgs& a, int device, int sm_
     switch (wtype) {
         case PW_F32: return launch_gemv_wt<PW_F32>(a, device, sm_count, stream);
         case PW_BF16: return launch_gemv_wt<PW_BF16>(a, device, sm_count, stream);
+        case PW_Q4_K: return launch_gemv_wt<PW_Q4_K>(a, device, sm_count, stream);
         default: return launch_gemv_wt<PW_Q8_0>(a, device, sm_count, stream);
     }
 }

@@ -963,7 +963,7 @@ static float fp16_to_fp32(uint16_t h) {
 // xout[r] = dot(row r of W, x) for one activation row, W in the GGML row layouts the reference multiplies with
 // (matmul_quantized_with_scratch, src/engine/kernels/quant.rs:7225): wtype 0 = F32 (vec_dot_f32 :1167),
 // 1 = BF16 (vec_dot_bf16 scalar tail :1313-1316), 2 = Q8_0 (vec_dot_q8_0 scalar branch :2043-2059: per block of 32,
-// the f32 dot of x with the int8 codes, times the block's f16 scale). Sequential f32 sums.
+// the f32 dot of x with the int8 codes, times the block's f16 scale), 3 = Q4_K. Sequential f32 sums.
 void ora_matmul(int32_t wtype, int32_t rows, int32_t cols, const void* w, const float* x, float* xout) {
     const uint8_t* wb = static_cast<const uint8_t*>(w);
     for (int r = 0; r < rows; ++r) {
@@ -978,6 +978,47 @@ void ora_matmul(int32_t wtype, int32_t rows, int32_t cols, const void* w, const 
                 float wv;
                 std::memcpy(&wv, &bits, 4);
                 sum += x[i] * wv;
+            }
+        } else if (wtype == 3) {
+            // Q4_K (vec_dot_q4_k, scalar branch of the x86 build, src/engine/kernels/quant.rs:3490-3521): super-blocks
+            // of 256 = f16 d, f16 dmin, 12 bytes of packed 6-bit (scale, min) pairs (get_scale_min_k4 :118-126),
+            // 128 bytes of nibbles; four groups of 64 elements, low nibbles then high nibbles
+            const int nb = cols / 256;
+            const uint8_t* row = wb + (size_t)r * nb * 144;
+            for (int b = 0; b < nb; ++b) {
+                const uint8_t* blk = row + (size_t)b * 144;
+                const float d = fp16_to_fp32((uint16_t)(blk[0] | (blk[1] << 8)));
+                const float dmin = fp16_to_fp32((uint16_t)(blk[2] | (blk[3] << 8)));
+                const uint8_t* sc = blk + 4;
+                const uint8_t* q = blk + 16;
+                const float* xb = x + (size_t)b * 256;
+                auto scale_min = [&](int j, int* s_out, int* m_out) {
+                    if (j < 4) {
+                        *s_out = sc[j] & 63;
+                        *m_out = sc[j + 4] & 63;
+                    } else {
+                        *s_out = (sc[j + 4] & 0x0f) | ((sc[j - 4] >> 6) << 4);
+                        *m_out = (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4);
+                    }
+                };
+                float block_sum = 0.0f;
+                int is = 0;
+                for (int j = 0; j < 256; j += 64) {
+                    int sc1, m1, sc2, m2;
+                    scale_min(is, &sc1, &m1);
+                    scale_min(is + 1, &sc2, &m2);
+                    const float d1 = d * (float)sc1, m1f = dmin * (float)m1;
+                    const float d2 = d * (float)sc2, m2f = dmin * (float)m2;
+                    for (int l = 0; l < 32; ++l) {
+                        const uint8_t qv = q[l];
+                        const float w0 = d1 * (float)(qv & 0x0f) - m1f;
+                        const float w1 = d2 * (float)(qv >> 4) - m2f;
+                        block_sum += xb[j + l] * w0 + xb[j + 32 + l] * w1;
+                    }
+                    q += 32;
+                    is += 2;
+                }
+                sum += block_sum;
             }
         } else {
             const int nb = cols / 32;

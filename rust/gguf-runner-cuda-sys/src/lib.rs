@@ -102,6 +102,7 @@ pub struct GgrWeights {
 pub const GGR_W_F32: i32 = 0;
 pub const GGR_W_BF16: i32 = 1;
 pub const GGR_W_Q8_0: i32 = 2;
+pub const GGR_W_Q4_K: i32 = 3;
 
 #[link(name = "ggr_attn")]
 extern "C" {

@@ -338,6 +338,39 @@ def quantize_q8_0(w: np.ndarray) -> np.ndarray:
     return out.reshape(rows, -1)
 
 
+def quantize_q4_k(w: np.ndarray) -> np.ndarray:
+    """GGML Q4_K bytes of a float matrix [rows][cols] (cols % 256 == 0): super-blocks of 256 weights = f16 d,
+    f16 dmin, eight 6-bit (scale, min) pairs packed into 12 bytes the way get_scale_min_k4 reads them
+    (src/engine/kernels/quant.rs:118-126) and 128 bytes of nibbles (groups of 64: low nibbles, then high nibbles;
+    dequantize_row_q4_k :294-325). w ~ d * scale * q - dmin * min. Test helper: a simple min / max quantiser, the
+    reference only reads this layout."""
+    rows, cols = w.shape
+    nsb = cols // 256
+    x = w.reshape(rows, nsb, 8, 32).astype(np.float32)
+    lo = np.minimum(x.min(axis=3), 0.0)
+    hi = np.maximum(x.max(axis=3), lo + 1e-12)
+    step = (hi - lo) / 15.0                      # per 32 weights
+    off = -lo                                    # >= 0
+    d = (step.max(axis=2) / 63.0).astype(np.float16)
+    dmin = (off.max(axis=2) / 63.0).astype(np.float16)
+    df, mf = d.astype(np.float32)[..., None], dmin.astype(np.float32)[..., None]
+    s6 = np.clip(np.rint(np.where(df > 0, step / np.where(df > 0, df, 1.0), 0.0)), 0, 63).astype(np.uint8)
+    m6 = np.clip(np.rint(np.where(mf > 0, off / np.where(mf > 0, mf, 1.0), 0.0)), 0, 63).astype(np.uint8)
+    eff = df * s6.astype(np.float32)
+    q = np.where(eff[..., None] > 0, (x + (mf * m6.astype(np.float32))[..., None]) / np.where(eff > 0, eff, 1.0)[..., None], 0.0)
+    q = np.clip(np.rint(q), 0, 15).astype(np.uint8)          # [rows][nsb][8][32]
+    out = np.zeros((rows, nsb, 144), np.uint8)
+    out[..., 0:2] = d.view(np.uint8).reshape(rows, nsb, 2)
+    out[..., 2:4] = dmin.view(np.uint8).reshape(rows, nsb, 2)
+    for j in range(4):
+        out[..., 4 + j] = s6[..., j] | ((s6[..., j + 4] >> 4) << 6)
+        out[..., 8 + j] = m6[..., j] | ((m6[..., j + 4] >> 4) << 6)
+        out[..., 12 + j] = (s6[..., j + 4] & 0x0F) | ((m6[..., j + 4] & 0x0F) << 4)
+    for grp in range(4):
+        out[..., 16 + 32 * grp:16 + 32 * (grp + 1)] = q[:, :, 2 * grp, :] | (q[:, :, 2 * grp + 1, :] << 4)
+    return out.reshape(rows, -1)
+
+
 def bf16_round(a: np.ndarray) -> np.ndarray:
     """Round-to-nearest-even to bf16, returned as f32 (src/engine/io/gguf.rs:107-116)."""
     a = np.ascontiguousarray(a, dtype=np.float32)
