@@ -72,7 +72,9 @@ __host__ __device__ inline size_t gemv_row_floats_dev(int cols) {
 template <int WT>
 struct GemvGeom {
     static constexpr int CPL = WT == PW_Q4_K ? 32 : (WT == PW_Q8_0 ? 16 : 8);  // columns per lane and step (one 16-byte load; two for F32)
-    static constexpr int UN = (WT == PW_F32 || WT == PW_Q4_K) ? 4 : 8;          // steps whose weight loads are in flight together
+    // steps per batch of weight loads; two batches are in flight: the next one is requested before the current one is
+    // multiplied, so the memory pipe never waits for the arithmetic
+    static constexpr int UN = (WT == PW_F32 || WT == PW_Q4_K) ? 2 : 4;
     static constexpr int SPAN = 32 * CPL * UN;           // columns one batch of loads covers
     static constexpr int NL = WT == PW_F32 ? 2 : 1;      // 16-byte loads per lane, step and row
 };
@@ -97,11 +99,17 @@ __global__ void __launch_bounds__(kGemvWarps * 32) proj_gemv_kernel(GemvArgs a) 
     const int n_units = my_groups * ncb;                                    // (row group, batch) units of this CTA
     const int row4 = (int)(gemv_row_floats_dev<CPL>(cols) >> 2);            // float4 pieces per staged row
 
-    uint4 raw[UN][kGemvRPW][NL];
-    float dsc[UN][kGemvRPW];
-    float dmn[UN][kGemvRPW];  // Q4_K: dmin * min of the lane's 32 weights
-    // requests the weights of unit u: UN steps of both rows, 16 (32 for F32) independent 16-byte loads per lane
-    auto load_unit = [&](int u) {
+    struct Batch {
+        uint4 raw[UN][kGemvRPW][NL];
+        float dsc[UN][kGemvRPW];
+        float dmn[UN][kGemvRPW];  // Q4_K: dmin * min of the lane's 32 weights
+    };
+    Batch ba, bb;
+    // requests the weights of unit u: UN steps of both rows, independent 16-byte loads
+    auto load_unit = [&](int u, Batch& b) {
+        auto& raw = b.raw;
+        auto& dsc = b.dsc;
+        auto& dmn = b.dmn;
         const int grp = blockIdx.x + (u / ncb) * gridDim.x, cb = (u % ncb) * Ge::SPAN;
         const int r0 = (grp * kGemvWarps + warp) * kGemvRPW;
 #pragma unroll
@@ -135,7 +143,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32) proj_gemv_kernel(GemvArgs a) 
 
     for (int t0 = 0; t0 < a.n; t0 += TT) {
         // the first unit's weights are requested before the activation rows are staged: both latencies overlap
-        if (n_units > 0) load_unit(0);
+        if (n_units > 0) load_unit(0, ba);
         __syncthreads();  // every warp is done with the rows of the previous pass
         // A lane multiplies CPL consecutive columns per step, i.e. CPL / 4 float4 pieces that lie 4 * CPL bytes apart
         // from its neighbour's: read straight, that is a 4-way (Q8_0) or 2-way bank conflict on every load. The rows
@@ -150,7 +158,12 @@ __global__ void __launch_bounds__(kGemvWarps * 32) proj_gemv_kernel(GemvArgs a) 
         }
         __syncthreads();
         float acc[kGemvRPW][TT];
-        for (int u = 0; u < n_units; ++u) {
+        // multiplies unit u (its weights are in `b`) into the accumulators; the last unit of a row group stores
+        auto compute_unit = [&](int u, const Batch& b) {
+            const auto& raw = b.raw;
+            const auto& dsc = b.dsc;
+            const auto& dmn = b.dmn;
+            (void)dmn;
             const int grp = blockIdx.x + (u / ncb) * gridDim.x, cbi = u % ncb, cb = cbi * Ge::SPAN;
             const int r0 = (grp * kGemvWarps + warp) * kGemvRPW;
             if (cbi == 0) {
@@ -159,7 +172,6 @@ __global__ void __launch_bounds__(kGemvWarps * 32) proj_gemv_kernel(GemvArgs a) 
 #pragma unroll
                     for (int t = 0; t < TT; ++t) acc[r][t] = 0.0f;
             }
-            if (u > 0) load_unit(u);
 #pragma unroll
             for (int s = 0; s < UN; ++s) {
                 const int c0 = cb + s * 32 * CPL + lane * CPL;
@@ -246,6 +258,14 @@ __global__ void __launch_bounds__(kGemvWarps * 32) proj_gemv_kernel(GemvArgs a) 
                             a.out[(size_t)(t0 + t) * a.ld_out + r0 + r] = v;
                         }
                     }
+            }
+        };
+        for (int u = 0; u < n_units; u += 2) {
+            if (u + 1 < n_units) load_unit(u + 1, bb);
+            compute_unit(u, ba);
+            if (u + 1 < n_units) {
+                if (u + 2 < n_units) load_unit(u + 2, ba);
+                compute_unit(u + 1, bb);
             }
         }
     }
