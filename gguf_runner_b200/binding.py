@@ -30,7 +30,7 @@ IMAGE_CAUSAL, IMAGE_BIDIRECTIONAL = 0, 1
 SHARD_NONE, SHARD_KV_SEQUENCE = 0, 2
 IMPL_AUTO, IMPL_SIMT, IMPL_MMA, IMPL_TCGEN05 = 0, 1, 2, 3
 
-W_F32, W_BF16, W_Q8_0, W_Q4_K = 0, 1, 2, 3
+W_F32, W_BF16, W_Q8_0, W_Q4_K, W_Q6_K = 0, 1, 2, 3, 4
 
 KV_FORMATS = {"f32": KV_F32, "bf16": KV_BF16, "q8_row": KV_Q8_ROW, "q8_block32": KV_Q8_BLOCK32, "turbo": KV_TURBO}
 
@@ -248,7 +248,7 @@ class Weights:
         self._L = lib()
         data = np.ascontiguousarray(data)
         want = {W_F32: rows * cols * 4, W_BF16: rows * cols * 2, W_Q8_0: rows * (cols // 32) * 34,
-                W_Q4_K: rows * (cols // 256) * 144}.get(wtype, -1)
+                W_Q4_K: rows * (cols // 256) * 144, W_Q6_K: rows * (cols // 256) * 210}.get(wtype, -1)
         if data.nbytes != want:
             raise ValueError(f"weight data has {data.nbytes} bytes, the layout needs {want}")
         h = C.c_void_p()

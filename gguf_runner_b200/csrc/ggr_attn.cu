@@ -2189,6 +2189,7 @@ struct ggr_weights {
     void* d_main = nullptr;            // F32 / BF16 values, or the Q8_0 code plane
     __half* d_scales = nullptr;        // Q8_0 block scales [rows][cols / 32]; Q4_K: (scale, min) byte pairs per 32 weights
     __half2* d_dm = nullptr;           // Q4_K: (d, dmin) per super-block [rows][cols / 256]
+    float* d_scales_f32 = nullptr;     // Q6_K: d * scale per 16 weights [rows][cols / 16]
     __nv_bfloat16* d_bf16 = nullptr;   // bf16 image for the tensor-core kernel (d_main itself for BF16)
     CUtensorMap tmB;                   // [rows][cols] bf16, box 64 x 256
     bool have_tmap = false;
@@ -2239,6 +2240,7 @@ int matmul_device(ggr_attn_ctx* c, const ggr_weights* w, const float* x, int n, 
         a.w = w->d_main;
         a.scales = w->d_scales;
         a.dm = w->d_dm;
+        a.scales_f32 = w->d_scales_f32;
         a.rows = w->rows;
         a.cols = w->cols;
         a.x = x;
@@ -2300,9 +2302,10 @@ extern "C" int ggr_weights_upload(int32_t device, int32_t wtype, int32_t rows, i
     };
     if (!out || !host_data) return bad(GGR_ERR_INVALID, "null argument");
     *out = nullptr;
-    if (wtype < GGR_W_F32 || wtype > GGR_W_Q4_K) return bad(GGR_ERR_INVALID, "unknown weight type");
-    if (rows <= 0 || cols <= 0 || rows % 8 != 0 || cols % (wtype == GGR_W_Q4_K ? 256 : (wtype == GGR_W_Q8_0 ? 32 : 8)) != 0)
-        return bad(GGR_ERR_UNSUPPORTED, "rows must be a multiple of 8, cols of 8 (32 for Q8_0, 256 for Q4_K)");
+    if (wtype < GGR_W_F32 || wtype > GGR_W_Q6_K) return bad(GGR_ERR_INVALID, "unknown weight type");
+    const int col_unit = (wtype == GGR_W_Q4_K || wtype == GGR_W_Q6_K) ? 256 : (wtype == GGR_W_Q8_0 ? 32 : 8);
+    if (rows <= 0 || cols <= 0 || rows % 8 != 0 || cols % col_unit != 0)
+        return bad(GGR_ERR_UNSUPPORTED, "rows must be a multiple of 8, cols of 8 (32 for Q8_0, 256 for Q4_K and Q6_K)");
     int ndev = 0;
     if (cudaGetDeviceCount(&ndev) != cudaSuccess || device < 0 || device >= ndev) return bad(GGR_ERR_CUDA, "no such CUDA device");
     DeviceGuard guard(device);
@@ -2369,6 +2372,41 @@ extern "C" int ggr_weights_upload(int32_t device, int32_t wtype, int32_t rows, i
             cudaMemcpy(w->d_scales, sm.data(), nb32 * 2, cudaMemcpyHostToDevice) != cudaSuccess ||
             cudaMemcpy(w->d_dm, dm.data(), nsb * 4, cudaMemcpyHostToDevice) != cudaSuccess)
             return fail_up("weight upload failed");
+    } else if (wtype == GGR_W_Q6_K) {
+        // 210-byte super-blocks -> the weights as int8 codes (q - 32) [rows][cols] and one f32 scale d * sc per 16
+        // weights [rows][cols / 16] (weight e of a super-block uses scale e / 16: dequantize_row_q6_k,
+        // src/engine/kernels/quant.rs:484-517)
+        const size_t nsb = n / 256;
+        std::vector<int8_t> codes(n);
+        std::vector<float> sc16(n / 16);
+        image.resize(n);
+        const uint8_t* src = static_cast<const uint8_t*>(host_data);
+        for (size_t b = 0; b < nsb; ++b) {
+            const uint8_t* blk = src + b * 210;
+            const float d = half_bits_to_float((uint16_t)(blk[208] | (blk[209] << 8)));
+            const int8_t* sc = reinterpret_cast<const int8_t*>(blk + 192);
+            for (int g16 = 0; g16 < 16; ++g16) sc16[b * 16 + g16] = d * (float)sc[g16];
+            for (int half = 0; half < 2; ++half) {
+                const uint8_t* ql = blk + 64 * half;
+                const uint8_t* qh = blk + 128 + 32 * half;
+                for (int l = 0; l < 32; ++l) {
+                    const int q[4] = {(int)((ql[l] & 0x0f) | ((qh[l] & 0x03) << 4)) - 32,
+                                      (int)((ql[l + 32] & 0x0f) | (((qh[l] >> 2) & 0x03) << 4)) - 32,
+                                      (int)((ql[l] >> 4) | (((qh[l] >> 4) & 0x03) << 4)) - 32,
+                                      (int)((ql[l + 32] >> 4) | (((qh[l] >> 6) & 0x03) << 4)) - 32};
+                    for (int k = 0; k < 4; ++k) {
+                        const size_t e = b * 256 + 128 * half + 32 * k + l;
+                        codes[e] = (int8_t)q[k];
+                        image[e] = float_to_bf16_bits(sc16[e / 16] * (float)q[k]);
+                    }
+                }
+            }
+        }
+        if (cudaMalloc(&w->d_main, n) != cudaSuccess || cudaMalloc((void**)&w->d_scales_f32, (n / 16) * 4) != cudaSuccess)
+            return fail_up("unable to allocate the weights");
+        if (cudaMemcpy(w->d_main, codes.data(), n, cudaMemcpyHostToDevice) != cudaSuccess ||
+            cudaMemcpy(w->d_scales_f32, sc16.data(), (n / 16) * 4, cudaMemcpyHostToDevice) != cudaSuccess)
+            return fail_up("weight upload failed");
     } else {
         // 34-byte blocks -> a code plane [rows][cols] and a scale plane [rows][cols / 32]
         const size_t nb = n / 32;
@@ -2409,6 +2447,7 @@ extern "C" void ggr_weights_free(ggr_weights* w) {
     cudaFree(w->d_main);
     cudaFree(w->d_scales);
     cudaFree(w->d_dm);
+    cudaFree(w->d_scales_f32);
     delete w;
 }
 

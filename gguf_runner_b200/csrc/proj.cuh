@@ -9,7 +9,8 @@
 //                     Weight formats F32, BF16, Q8_0 (codes and f16 block scales repacked into two planes at
 //                     upload, so that the codes are 16-byte aligned) and Q4_K (nibble plane in which the 32 weights
 //                     of a (scale, min) pair are one 16-byte load; w = d * scale * q - dmin * min is applied as
-//                     d * scale * sum(x q) - dmin * min * sum(x), one FMA per weight).
+//                     d * scale * sum(x q) - dmin * min * sum(x), one FMA per weight) and Q6_K (kept as int8 codes
+//                     q - 32 with one f32 scale per 16 weights, which is one lane's load).
 //   proj_gemm_kernel  prefill chunks: tcgen05 GEMM, bf16 x bf16 -> f32 in TMEM. A = activations [m][K] (bf16), B =
 //                     weights [N][K] (bf16; Q8_0 / F32 weights use a bf16 image made at upload), 128 x 256 output
 //                     tile per CTA, 64-column k-steps through a four-stage TMA ring, one MMA issuer, four epilogue
@@ -24,12 +25,13 @@
 
 namespace ggr {
 
-enum ProjWeightType : int { PW_F32 = 0, PW_BF16 = 1, PW_Q8_0 = 2, PW_Q4_K = 3 };
+enum ProjWeightType : int { PW_F32 = 0, PW_BF16 = 1, PW_Q8_0 = 2, PW_Q4_K = 3, PW_Q6_K = 4 };
 
 struct GemvArgs {
     const void* w;         // F32 / BF16 values [rows][cols], Q8_0 codes int8 [rows][cols], or Q4_K nibbles [rows][cols / 2]
     const __half* scales;  // Q8_0: f16 scale [rows][cols / 32]; Q4_K: (6-bit scale, 6-bit min) byte pair [rows][cols / 32]
     const __half2* dm;     // Q4_K: (d, dmin) [rows][cols / 256]
+    const float* scales_f32;  // Q6_K (codes q - 32 as int8 in w): d * scale per 16 weights [rows][cols / 16]
     int rows, cols;
     const float* x;        // [n][cols]
     int n;
@@ -71,7 +73,7 @@ __host__ __device__ inline size_t gemv_row_floats_dev(int cols) {
 
 template <int WT>
 struct GemvGeom {
-    static constexpr int CPL = WT == PW_Q4_K ? 32 : (WT == PW_Q8_0 ? 16 : 8);  // columns per lane and step (one 16-byte load; two for F32)
+    static constexpr int CPL = WT == PW_Q4_K ? 32 : ((WT == PW_Q8_0 || WT == PW_Q6_K) ? 16 : 8);  // columns per lane and step (one 16-byte load; two for F32)
     // steps per batch of weight loads; two batches are in flight: the next one is requested before the current one is
     // multiplied, so the memory pipe never waits for the arithmetic
     static constexpr int UN = (WT == PW_F32 || WT == PW_Q4_K) ? 2 : 4;
@@ -129,6 +131,10 @@ __global__ void __launch_bounds__(kGemvWarps * 32) proj_gemv_kernel(GemvArgs a) 
                     } else if (WT == PW_Q8_0) {
                         raw[s][r][0] = ld_weights16(static_cast<const int8_t*>(a.w) + (size_t)row * cols + c0);
                         dsc[s][r] = __half2float(a.scales[(size_t)row * (cols >> 5) + (c0 >> 5)]);
+                    } else if (WT == PW_Q6_K) {
+                        // a lane's 16 codes are exactly the weights of one scale
+                        raw[s][r][0] = ld_weights16(static_cast<const int8_t*>(a.w) + (size_t)row * cols + c0);
+                        dsc[s][r] = __ldg(a.scales_f32 + (size_t)row * (cols >> 4) + (c0 >> 4));
                     } else {
                         raw[s][r][0] = ld_weights16(static_cast<const uint8_t*>(a.w) + (((size_t)row * cols + c0) >> 1));
                         const uint32_t sm = __ldg(reinterpret_cast<const unsigned short*>(a.scales) + (size_t)row * (cols >> 5) + (c0 >> 5));
@@ -193,7 +199,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32) proj_gemv_kernel(GemvArgs a) 
                             wv[r][2 * i] = __uint_as_float(w4[i] << 16);
                             wv[r][2 * i + 1] = __uint_as_float(w4[i] & 0xffff0000u);
                         }
-                    } else if (WT == PW_Q8_0) {
+                    } else if (WT == PW_Q8_0 || WT == PW_Q6_K) {
                         const uint4 q = raw[s][r][0];
                         const uint32_t w4[4] = {q.x ^ 0x80808080u, q.y ^ 0x80808080u, q.z ^ 0x80808080u, q.w ^ 0x80808080u};
 #pragma unroll
@@ -298,6 +304,7 @@ inline cudaError_t launch_gemv(int wtype, const GemvArgs& a, int device, int sm_
         case PW_F32: return launch_gemv_wt<PW_F32>(a, device, sm_count, stream);
         case PW_BF16: return launch_gemv_wt<PW_BF16>(a, device, sm_count, stream);
         case PW_Q4_K: return launch_gemv_wt<PW_Q4_K>(a, device, sm_count, stream);
+        case PW_Q6_K: return launch_gemv_wt<PW_Q6_K>(a, device, sm_count, stream);
         default: return launch_gemv_wt<PW_Q8_0>(a, device, sm_count, stream);
     }
 }

@@ -337,13 +337,15 @@ int ggr_attn_attention_tokens_static(ggr_attn_ctx* ctx, int32_t layer, const int
  * the GGUF file (QuantizedTensor, row-major GGML rows): GGR_W_F32, GGR_W_BF16, GGR_W_Q8_0 (blocks of one f16
  * scale and 32 int8 codes, 34 bytes; src/engine/kernels/quant.rs:89, :105) or GGR_W_Q4_K (super-blocks of 256
  * weights in 144 bytes: f16 d, f16 dmin, eight packed 6-bit (scale, min) pairs, 128 bytes of nibbles;
- * dequantize_row_q4_k, src/engine/kernels/quant.rs:294-325). cols must be a multiple of 256 for Q4_K, of 32 for
+ * dequantize_row_q4_k, src/engine/kernels/quant.rs:294-325) or GGR_W_Q6_K (super-blocks of 256 weights in 210
+ * bytes: low nibbles, high bit pairs, one int8 scale per 16 weights, f16 d; dequantize_row_q6_k :484-517). cols must
+ * be a multiple of 256 for the K types, of 32 for
  * Q8_0 and of 8 otherwise, rows a multiple of 8. Quantised codes and scales are kept in separate planes, and every
  * type but BF16 also keeps a bf16 image (each weight rounded once) for the tensor-core kernel that multiplies chunks
  * of rows.
  */
 typedef struct ggr_weights ggr_weights;
-enum { GGR_W_F32 = 0, GGR_W_BF16 = 1, GGR_W_Q8_0 = 2, GGR_W_Q4_K = 3 };
+enum { GGR_W_F32 = 0, GGR_W_BF16 = 1, GGR_W_Q8_0 = 2, GGR_W_Q4_K = 3, GGR_W_Q6_K = 4 };
 int ggr_weights_upload(int32_t device, int32_t wtype, int32_t rows, int32_t cols, const void* host_data, ggr_weights** out);
 void ggr_weights_free(ggr_weights* w);
 /* xout[i][rows] = W x[i] for n rows of x [n][cols], f32 in and out. Replaces matmul_quantized_with_scratch

@@ -963,7 +963,7 @@ static float fp16_to_fp32(uint16_t h) {
 // xout[r] = dot(row r of W, x) for one activation row, W in the GGML row layouts the reference multiplies with
 // (matmul_quantized_with_scratch, src/engine/kernels/quant.rs:7225): wtype 0 = F32 (vec_dot_f32 :1167),
 // 1 = BF16 (vec_dot_bf16 scalar tail :1313-1316), 2 = Q8_0 (vec_dot_q8_0 scalar branch :2043-2059: per block of 32,
-// the f32 dot of x with the int8 codes, times the block's f16 scale), 3 = Q4_K. Sequential f32 sums.
+// the f32 dot of x with the int8 codes, times the block's f16 scale), 3 = Q4_K, 4 = Q6_K. Sequential f32 sums.
 void ora_matmul(int32_t wtype, int32_t rows, int32_t cols, const void* w, const float* x, float* xout) {
     const uint8_t* wb = static_cast<const uint8_t*>(w);
     for (int r = 0; r < rows; ++r) {
@@ -1017,6 +1017,39 @@ void ora_matmul(int32_t wtype, int32_t rows, int32_t cols, const void* w, const 
                     }
                     q += 32;
                     is += 2;
+                }
+                sum += block_sum;
+            }
+        } else if (wtype == 4) {
+            // Q6_K (vec_dot_q6_k, scalar branch of the x86 build, src/engine/kernels/quant.rs:3654-3690): super-blocks of
+            // 256 = 128 bytes of low nibbles, 64 bytes of high bit pairs, 16 int8 scales (one per 16 weights), f16 d
+            const int nb = cols / 256;
+            const uint8_t* row = wb + (size_t)r * nb * 210;
+            for (int b = 0; b < nb; ++b) {
+                const uint8_t* blk = row + (size_t)b * 210;
+                const float d = fp16_to_fp32((uint16_t)(blk[208] | (blk[209] << 8)));
+                const uint8_t* ql = blk;
+                const uint8_t* qh = blk + 128;
+                const int8_t* sc = reinterpret_cast<const int8_t*>(blk + 192);
+                const float* xb = x + (size_t)b * 256;
+                float block_sum = 0.0f;
+                for (int n_outer = 0; n_outer < 256; n_outer += 128) {
+                    for (int l = 0; l < 32; ++l) {
+                        const int is = l / 16;
+                        const int q1 = (int)(int8_t)((ql[l] & 0x0f) | ((qh[l] & 0x03) << 4)) - 32;
+                        const int q2 = (int)(int8_t)((ql[l + 32] & 0x0f) | (((qh[l] >> 2) & 0x03) << 4)) - 32;
+                        const int q3 = (int)(int8_t)((ql[l] >> 4) | (((qh[l] >> 4) & 0x03) << 4)) - 32;
+                        const int q4 = (int)(int8_t)((ql[l + 32] >> 4) | (((qh[l] >> 6) & 0x03) << 4)) - 32;
+                        const float s0 = d * (float)sc[is], s1 = d * (float)sc[is + 2];
+                        const float s2 = d * (float)sc[is + 4], s3 = d * (float)sc[is + 6];
+                        block_sum += xb[n_outer + l] * (s0 * (float)q1);
+                        block_sum += xb[n_outer + 32 + l] * (s1 * (float)q2);
+                        block_sum += xb[n_outer + 64 + l] * (s2 * (float)q3);
+                        block_sum += xb[n_outer + 96 + l] * (s3 * (float)q4);
+                    }
+                    ql += 64;
+                    qh += 32;
+                    sc += 8;
                 }
                 sum += block_sum;
             }

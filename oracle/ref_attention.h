@@ -63,7 +63,7 @@ void ora_sigmoid_gate(ora_ctx* ctx, float* xb, const float* gate, int32_t gate_h
 
 /* The matmuls either side of the path, one activation row at a time (matmul_quantized_with_scratch,
  * src/engine/kernels/quant.rs:7225, scalar dots): wtype 0 = F32, 1 = BF16, 2 = Q8_0 blocks of (f16 scale, 32 int8),
- * 3 = Q4_K super-blocks of 256 (144 bytes). */
+ * 3 = Q4_K super-blocks of 256 (144 bytes), 4 = Q6_K super-blocks of 256 (210 bytes). */
 void ora_matmul(int32_t wtype, int32_t rows, int32_t cols, const void* w, const float* x, float* xout);
 float ora_fp16_to_fp32(uint16_t h);
 

@@ -103,6 +103,7 @@ pub const GGR_W_F32: i32 = 0;
 pub const GGR_W_BF16: i32 = 1;
 pub const GGR_W_Q8_0: i32 = 2;
 pub const GGR_W_Q4_K: i32 = 3;
+pub const GGR_W_Q6_K: i32 = 4;
 
 #[link(name = "ggr_attn")]
 extern "C" {

@@ -371,6 +371,32 @@ def quantize_q4_k(w: np.ndarray) -> np.ndarray:
     return out.reshape(rows, -1)
 
 
+def quantize_q6_k(w: np.ndarray) -> np.ndarray:
+    """GGML Q6_K bytes of a float matrix [rows][cols] (cols % 256 == 0): super-blocks of 256 weights = 128 bytes of
+    low nibbles, 64 bytes of high bit pairs, 16 int8 scales (one per 16 weights) and an f16 d, laid out the way
+    dequantize_row_q6_k reads them (src/engine/kernels/quant.rs:484-517): w ~ d * scale * (q - 32), q in 0..63.
+    Test helper: a simple max-abs quantiser, the reference only reads this layout."""
+    rows, cols = w.shape
+    nsb = cols // 256
+    x = w.reshape(rows, nsb, 16, 16).astype(np.float32)
+    amax = np.abs(x).max(axis=3)                                  # per 16 weights
+    d = (amax.max(axis=2) / 31.0 / 127.0).astype(np.float16)
+    df = d.astype(np.float32)[..., None]
+    sc = np.clip(np.rint(np.where(df > 0, amax / 31.0 / np.where(df > 0, df, 1.0), 0.0)), 1, 127).astype(np.int8)
+    eff = df * sc.astype(np.float32)
+    q = np.clip(np.rint(np.where(eff[..., None] > 0, x / np.where(eff > 0, eff, 1.0)[..., None], 0.0)), -32, 31).astype(np.int32) + 32
+    q = q.reshape(rows, nsb, 2, 4, 32).astype(np.uint8)           # [half of 128][k: 32-weight run][l]
+    out = np.zeros((rows, nsb, 210), np.uint8)
+    for half in range(2):
+        q1, q2, q3, q4 = (q[:, :, half, k, :] for k in range(4))
+        out[..., 64 * half:64 * half + 32] = (q1 & 0x0F) | ((q3 & 0x0F) << 4)
+        out[..., 64 * half + 32:64 * half + 64] = (q2 & 0x0F) | ((q4 & 0x0F) << 4)
+        out[..., 128 + 32 * half:128 + 32 * half + 32] = (q1 >> 4) | ((q2 >> 4) << 2) | ((q3 >> 4) << 4) | ((q4 >> 4) << 6)
+    out[..., 192:208] = sc.view(np.uint8)
+    out[..., 208:210] = d.view(np.uint8).reshape(rows, nsb, 2)
+    return out.reshape(rows, -1)
+
+
 def bf16_round(a: np.ndarray) -> np.ndarray:
     """Round-to-nearest-even to bf16, returned as f32 (src/engine/io/gguf.rs:107-116)."""
     a = np.ascontiguousarray(a, dtype=np.float32)

@@ -1,7 +1,7 @@
 """The matmuls either side of the attention path on the device, against the reference's scalar matmul.
 
-ggr_proj_matmul replaces matmul_quantized_with_scratch (src/engine/kernels/quant.rs:7225) for F32, BF16, Q8_0 and
-Q4_K weights; ggr_attn_layer_decode / ggr_attn_layer_prefill run q / k / v projections, the attention path and the output
+ggr_proj_matmul replaces matmul_quantized_with_scratch (src/engine/kernels/quant.rs:7225) for F32, BF16, Q8_0,
+Q4_K and Q6_K weights; ggr_attn_layer_decode / ggr_attn_layer_prefill run q / k / v projections, the attention path and the output
 projection (src/engine/runtime/inference.rs:3144-3527) with only hidden-state rows crossing the boundary. Up to 16
 rows use f32 arithmetic (relative tolerance 1e-3 of the output scale), more rows the tensor cores with bf16 operands
 (2e-2).
@@ -10,9 +10,9 @@ import numpy as np
 import pytest
 
 import gguf_runner_b200 as g
-from gguf_runner_b200.binding import (AttnConfig, GgrError, KV_BF16, KV_F32, KV_Q8_ROW, W_BF16, W_F32, W_Q4_K, W_Q8_0,
-                                      Weights)
-from tests.oracle_binding import Oracle, bf16_bits, matmul as ora_matmul, quantize_q4_k, quantize_q8_0
+from gguf_runner_b200.binding import (AttnConfig, GgrError, KV_BF16, KV_F32, KV_Q8_ROW, W_BF16, W_F32, W_Q4_K, W_Q6_K,
+                                      W_Q8_0, Weights)
+from tests.oracle_binding import Oracle, bf16_bits, matmul as ora_matmul, quantize_q4_k, quantize_q6_k, quantize_q8_0
 
 pytestmark = pytest.mark.gpu
 
@@ -20,15 +20,16 @@ pytestmark = pytest.mark.gpu
 def make_weights(rng, wtype, rows, cols):
     """(device weights, raw bytes for the oracle) of a random matrix scaled like a projection (1 / sqrt(cols))."""
     w = (rng.standard_normal((rows, cols)) / np.sqrt(cols)).astype(np.float32)
-    raw = {W_F32: lambda: w, W_BF16: lambda: bf16_bits(w), W_Q8_0: lambda: quantize_q8_0(w), W_Q4_K: lambda: quantize_q4_k(w)}[wtype]()
+    raw = {W_F32: lambda: w, W_BF16: lambda: bf16_bits(w), W_Q8_0: lambda: quantize_q8_0(w), W_Q4_K: lambda: quantize_q4_k(w),
+           W_Q6_K: lambda: quantize_q6_k(w)}[wtype]()
     return Weights(wtype, rows, cols, raw), np.ascontiguousarray(raw)
 
 
-@pytest.mark.parametrize("wtype", [W_F32, W_BF16, W_Q8_0, W_Q4_K])
+@pytest.mark.parametrize("wtype", [W_F32, W_BF16, W_Q8_0, W_Q4_K, W_Q6_K])
 @pytest.mark.parametrize("rows,cols,n", [(64, 256, 1), (1024, 1024, 3), (2048, 4096, 16), (1000, 1056, 7)])
 def test_weight_streaming_matmul_matches_reference(wtype, rows, cols, n):
-    if wtype == W_Q4_K and cols % 256:
-        cols = 1280   # Q4_K rows are whole super-blocks of 256
+    if wtype in (W_Q4_K, W_Q6_K) and cols % 256:
+        cols = 1280   # K-quant rows are whole super-blocks of 256
     rng = np.random.default_rng(rows + cols + n)
     cfg = AttnConfig(n_layers=1, n_heads=2, n_kv_heads=1, head_dim=64, seq_len=16, kv_format=KV_F32)
     w, raw = make_weights(rng, wtype, rows, cols)
@@ -40,11 +41,11 @@ def test_weight_streaming_matmul_matches_reference(wtype, rows, cols, n):
     w.close()
 
 
-@pytest.mark.parametrize("wtype", [W_BF16, W_Q8_0, W_F32, W_Q4_K])
+@pytest.mark.parametrize("wtype", [W_BF16, W_Q8_0, W_F32, W_Q4_K, W_Q6_K])
 @pytest.mark.parametrize("rows,cols,n", [(256, 256, 128), (4096, 1024, 300), (1000, 1056, 130), (512, 4096, 17)])
 def test_tensor_core_matmul_matches_reference(wtype, rows, cols, n):
     import torch
-    if wtype == W_Q4_K and cols % 256:
+    if wtype in (W_Q4_K, W_Q6_K) and cols % 256:
         cols = 1280
     rng = np.random.default_rng(rows + cols + n)
     cfg = AttnConfig(n_layers=1, n_heads=2, n_kv_heads=1, head_dim=64, seq_len=16, kv_format=KV_F32)
@@ -73,7 +74,7 @@ def reference_layer(ora, layer, pos_list, xb, raws, wtypes, dims, prefill_base=N
 
 
 @pytest.mark.parametrize("wtype,kv_format,tol", [(W_Q8_0, KV_Q8_ROW, 2e-3), (W_BF16, KV_F32, 2e-3), (W_Q8_0, KV_BF16, 2e-2),
-                                                  (W_Q4_K, KV_F32, 2e-3)])
+                                                  (W_Q4_K, KV_F32, 2e-3), (W_Q6_K, KV_Q8_ROW, 2e-3)])
 def test_layer_decode_and_prefill_match_reference(wtype, kv_format, tol):
     # Qwen3-0.6B-shaped attention half-layer: hidden 1024, 16 query / 8 kv heads of 128
     dim, B = 1024, 2
