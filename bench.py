@@ -716,10 +716,25 @@ def bench_projections(torch, args, local_rank, peaks):
             ctx.layer_decode(l, [T - 1], dxb, *layers[l], out=dout)
 
     dev_ms = timed_steps(torch, dev_step, 20)
+    # the same step replayed from a CUDA graph: without the host's launch cost (the ctypes loop above issues 84 launches)
+    graph_ms = None
+    try:
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            dev_step()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                dev_step()
+        torch.cuda.synchronize()
+        graph_ms = timed_steps(torch, graph.replay, 50)
+    except Exception:  # capture is an optimisation of the host loop, not part of the path
+        graph_ms = None
     res["layer_decode_configs0"] = {
         "workload": "configs[0] attention half-layer from the hidden state: 28 layers, hidden 1024, Q8_0 projection weights, "
                     "q8_row cache, T=2048, batch 1 (q / k / v projections, rope + append + attention, output projection)",
         "ms_per_step_device_resident": dev_ms, "tokens_per_s_device_resident": 1.0 / (dev_ms * 1e-3),
+        "ms_per_step_cuda_graph": graph_ms, "launches_per_step": 3 * L,
         "e2e": {"value": 1.0 / host_s, "unit": "tokens/s", "ms_per_step": host_s * 1e3,
                 "h2d_bytes_per_step": L * dim * 4, "d2h_bytes_per_step": L * dim * 4,
                 "call": "ggr_attn_layer_decode(GGR_PTR_HOST): one hidden row in and one out per layer"}}

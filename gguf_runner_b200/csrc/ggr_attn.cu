@@ -2232,22 +2232,26 @@ uint16_t float_to_bf16_bits(float f) {  // round to nearest even (src/engine/io/
 }
 
 // xout [n][w->rows] = x [n][w->cols] W^T, device pointers
+void fill_gemv(GemvArgs& a, const ggr_weights* w, const float* x, int n, float* out, int ld_out, int sanitize) {
+    a.w = w->d_main;
+    a.scales = w->d_scales;
+    a.dm = w->d_dm;
+    a.scales_f32 = w->d_scales_f32;
+    a.rows = w->rows;
+    a.cols = w->cols;
+    a.x = x;
+    a.n = n;
+    a.out = out;
+    a.ld_out = ld_out;
+    a.sanitize = sanitize;
+}
+
 int matmul_device(ggr_attn_ctx* c, const ggr_weights* w, const float* x, int n, float* out, __nv_bfloat16* out_h, int ld_out,
                   int sanitize) {
     if (w->device != c->cfg.device) return fail(c, GGR_ERR_INVALID, "the weights live on another device than the context");
     if (n <= 16 && !out_h && w->cols <= kGemvMaxCols) {
         GemvArgs a{};
-        a.w = w->d_main;
-        a.scales = w->d_scales;
-        a.dm = w->d_dm;
-        a.scales_f32 = w->d_scales_f32;
-        a.rows = w->rows;
-        a.cols = w->cols;
-        a.x = x;
-        a.n = n;
-        a.out = out;
-        a.ld_out = ld_out;
-        a.sanitize = sanitize;
+        fill_gemv(a, w, x, n, out, ld_out, sanitize);
         {
             LaunchTimer t(c, 3);
             CUDA_TRY(c, launch_gemv(w->wtype, a, c->cfg.device, c->sm_count, c->stream));
@@ -2504,9 +2508,33 @@ extern "C" int ggr_attn_layer_decode(ggr_attn_ctx* c, int32_t layer, const int32
     float* dq = c->d_pqkv;
     float* dk = dq + (size_t)B * c->q_dim;
     float* dv = dk + (size_t)B * c->kv_dim;
-    if ((rc = matmul_device(c, wq, dx, B, dq, nullptr, c->q_dim, 0))) return rc;
-    if ((rc = matmul_device(c, wk, dx, B, dk, nullptr, c->kv_dim, 0))) return rc;
-    if ((rc = matmul_device(c, wv, dx, B, dv, nullptr, c->kv_dim, 0))) return rc;
+    if (B <= 16 && wq->cols <= kGemvMaxCols && wk->wtype == wq->wtype && wv->wtype == wq->wtype) {
+        // the three projections read the same rows: one launch over the rows of wq, wk and wv
+        GemvArgs a{};
+        fill_gemv(a, wq, dx, B, dq, c->q_dim, 0);
+        const ggr_weights* extra[2] = {wk, wv};
+        float* outs[2] = {dk, dv};
+        a.n_extra = 2;
+        a.rows_all = wq->rows + wk->rows + wv->rows;
+        for (int i = 0; i < 2; ++i) {
+            a.w_x[i] = extra[i]->d_main;
+            a.scales_x[i] = extra[i]->d_scales;
+            a.dm_x[i] = extra[i]->d_dm;
+            a.scales_f32_x[i] = extra[i]->d_scales_f32;
+            a.rows_x[i] = extra[i]->rows;
+            a.out_x[i] = outs[i];
+            a.ld_out_x[i] = c->kv_dim;
+        }
+        {
+            LaunchTimer t(c, 3);
+            CUDA_TRY(c, launch_gemv(wq->wtype, a, c->cfg.device, c->sm_count, c->stream));
+        }
+        c->launches++;
+    } else {
+        if ((rc = matmul_device(c, wq, dx, B, dq, nullptr, c->q_dim, 0))) return rc;
+        if ((rc = matmul_device(c, wk, dx, B, dk, nullptr, c->kv_dim, 0))) return rc;
+        if ((rc = matmul_device(c, wv, dx, B, dv, nullptr, c->kv_dim, 0))) return rc;
+    }
     if ((rc = decode_common(c, layer, pos, B, dq, dk, dv, c->d_patt, nullptr, GGR_PTR_DEVICE))) return rc;
     if ((rc = matmul_device(c, wo, c->d_patt, B, dout, nullptr, dim_out, 1))) return rc;
     if (ptr_kind == GGR_PTR_HOST) {

@@ -38,7 +38,43 @@ struct GemvArgs {
     float* out;            // [n][ld_out]
     int ld_out;
     int sanitize;          // non-finite results become 0 (sanitize_finite_inplace after the output projection)
+    // Up to two more matrices of the same type and column count multiplied with the same rows in the same launch (the
+    // k and v projections behind the q projection): their rows continue the row numbering of the first matrix.
+    // `rows` stays the row count of the first matrix, rows_all is the total.
+    int n_extra, rows_all;
+    const void* w_x[2];
+    const __half* scales_x[2];
+    const __half2* dm_x[2];
+    const float* scales_f32_x[2];
+    int rows_x[2];
+    float* out_x[2];
+    int ld_out_x[2];
 };
+
+// the matrix a (global) row belongs to: its planes, its output and the row's index inside it
+struct GemvRowRef {
+    const void* w;
+    const __half* scales;
+    const __half2* dm;
+    const float* scales_f32;
+    float* out;
+    int ld_out, row;
+};
+__device__ __forceinline__ GemvRowRef gemv_row_ref(const GemvArgs& a, int row) {
+    GemvRowRef r{a.w, a.scales, a.dm, a.scales_f32, a.out, a.ld_out, row};
+    if (a.n_extra > 0 && row >= a.rows) {
+        const bool second = a.n_extra > 1 && row >= a.rows + a.rows_x[0];
+        const int i = second ? 1 : 0;  // (selects, not indexed parameter loads)
+        r.w = second ? a.w_x[1] : a.w_x[0];
+        r.scales = second ? a.scales_x[1] : a.scales_x[0];
+        r.dm = second ? a.dm_x[1] : a.dm_x[0];
+        r.scales_f32 = second ? a.scales_f32_x[1] : a.scales_f32_x[0];
+        r.out = second ? a.out_x[1] : a.out_x[0];
+        r.ld_out = second ? a.ld_out_x[1] : a.ld_out_x[0];
+        r.row = row - a.rows - (i ? a.rows_x[0] : 0);
+    }
+    return r;
+}
 
 constexpr int kGemvWarps = 8;
 constexpr int kGemvRPW = 2;  // weight rows per warp
@@ -95,7 +131,8 @@ __global__ void __launch_bounds__(kGemvWarps * 32) proj_gemv_kernel(GemvArgs a) 
     extern __shared__ __align__(16) float xs[];  // [TT][row_floats]: the activation rows of the pass, read by every warp
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int cols = a.cols;
-    const int n_groups = (a.rows + kGemvWarps * kGemvRPW - 1) / (kGemvWarps * kGemvRPW);
+    const int rows_all = a.n_extra > 0 ? a.rows_all : a.rows;
+    const int n_groups = (rows_all + kGemvWarps * kGemvRPW - 1) / (kGemvWarps * kGemvRPW);
     const int ncb = (cols + Ge::SPAN - 1) / Ge::SPAN;                       // load batches per row
     const int my_groups = n_groups > (int)blockIdx.x ? (n_groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     const int n_units = my_groups * ncb;                                    // (row group, batch) units of this CTA
@@ -119,26 +156,27 @@ __global__ void __launch_bounds__(kGemvWarps * 32) proj_gemv_kernel(GemvArgs a) 
             const int c0 = cb + s * 32 * CPL + lane * CPL;
 #pragma unroll
             for (int r = 0; r < kGemvRPW; ++r) {
-                const int row = min(r0 + r, a.rows - 1);
+                const GemvRowRef rr = gemv_row_ref(a, min(r0 + r, rows_all - 1));
+                const int row = rr.row;
                 dsc[s][r] = 1.0f;
                 if (c0 < cols) {
                     if (WT == PW_F32) {
-                        const uint4* p = reinterpret_cast<const uint4*>(static_cast<const float*>(a.w) + (size_t)row * cols + c0);
+                        const uint4* p = reinterpret_cast<const uint4*>(static_cast<const float*>(rr.w) + (size_t)row * cols + c0);
                         raw[s][r][0] = ld_weights16(p);
                         raw[s][r][NL - 1] = ld_weights16(p + 1);
                     } else if (WT == PW_BF16) {
-                        raw[s][r][0] = ld_weights16(static_cast<const __nv_bfloat16*>(a.w) + (size_t)row * cols + c0);
+                        raw[s][r][0] = ld_weights16(static_cast<const __nv_bfloat16*>(rr.w) + (size_t)row * cols + c0);
                     } else if (WT == PW_Q8_0) {
-                        raw[s][r][0] = ld_weights16(static_cast<const int8_t*>(a.w) + (size_t)row * cols + c0);
-                        dsc[s][r] = __half2float(a.scales[(size_t)row * (cols >> 5) + (c0 >> 5)]);
+                        raw[s][r][0] = ld_weights16(static_cast<const int8_t*>(rr.w) + (size_t)row * cols + c0);
+                        dsc[s][r] = __half2float(rr.scales[(size_t)row * (cols >> 5) + (c0 >> 5)]);
                     } else if (WT == PW_Q6_K) {
                         // a lane's 16 codes are exactly the weights of one scale
-                        raw[s][r][0] = ld_weights16(static_cast<const int8_t*>(a.w) + (size_t)row * cols + c0);
-                        dsc[s][r] = __ldg(a.scales_f32 + (size_t)row * (cols >> 4) + (c0 >> 4));
+                        raw[s][r][0] = ld_weights16(static_cast<const int8_t*>(rr.w) + (size_t)row * cols + c0);
+                        dsc[s][r] = __ldg(rr.scales_f32 + (size_t)row * (cols >> 4) + (c0 >> 4));
                     } else {
-                        raw[s][r][0] = ld_weights16(static_cast<const uint8_t*>(a.w) + (((size_t)row * cols + c0) >> 1));
-                        const uint32_t sm = __ldg(reinterpret_cast<const unsigned short*>(a.scales) + (size_t)row * (cols >> 5) + (c0 >> 5));
-                        const float2 dd = __half22float2(__ldg(a.dm + (size_t)row * (cols >> 8) + (c0 >> 8)));
+                        raw[s][r][0] = ld_weights16(static_cast<const uint8_t*>(rr.w) + (((size_t)row * cols + c0) >> 1));
+                        const uint32_t sm = __ldg(reinterpret_cast<const unsigned short*>(rr.scales) + (size_t)row * (cols >> 5) + (c0 >> 5));
+                        const float2 dd = __half22float2(__ldg(rr.dm + (size_t)row * (cols >> 8) + (c0 >> 8)));
                         dsc[s][r] = dd.x * (float)(sm & 0xffu);   // d * scale, as dequantize_row_q4_k forms it
                         dmn[s][r] = dd.y * (float)(sm >> 8);      // dmin * min
                     }
@@ -259,9 +297,10 @@ __global__ void __launch_bounds__(kGemvWarps * 32) proj_gemv_kernel(GemvArgs a) 
 #pragma unroll
                     for (int t = 0; t < TT; ++t) {
                         float v = warp_sum(acc[r][t]);
-                        if (lane == 0 && r0 + r < a.rows && t0 + t < a.n) {
+                        if (lane == 0 && r0 + r < rows_all && t0 + t < a.n) {
                             if (a.sanitize && !isfinite(v)) v = 0.0f;
-                            a.out[(size_t)(t0 + t) * a.ld_out + r0 + r] = v;
+                            const GemvRowRef rr = gemv_row_ref(a, r0 + r);
+                            rr.out[(size_t)(t0 + t) * rr.ld_out + rr.row] = v;
                         }
                     }
             }
@@ -285,7 +324,7 @@ inline cudaError_t launch_gemv_inst(const GemvArgs& a, int device, int sm_count,
     const size_t smem = (size_t)TT * gemv_row_floats<WT>(a.cols) * sizeof(float);
     cudaError_t e = setup.ensure(proj_gemv_kernel<WT, TT>, device, 0, (int)((size_t)TT * gemv_row_floats<WT>(kGemvMaxCols) * sizeof(float)));
     if (e != cudaSuccess) return e;
-    const int groups = (a.rows + kGemvWarps * kGemvRPW - 1) / (kGemvWarps * kGemvRPW);
+    const int groups = ((a.n_extra > 0 ? a.rows_all : a.rows) + kGemvWarps * kGemvRPW - 1) / (kGemvWarps * kGemvRPW);
     // row groups are dealt round robin to a grid that fills the SMs about twice (the staged rows are loaded once per CTA)
     const int grid = groups < 2 * sm_count ? groups : 2 * sm_count;
     proj_gemv_kernel<WT, TT><<<grid, kGemvWarps * 32, smem, stream>>>(a);
