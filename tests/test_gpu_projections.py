@@ -111,6 +111,29 @@ def test_layer_decode_and_prefill_match_reference(wtype, kv_format, tol):
         w.close()
 
 
+def test_layer_decode_with_mixed_weight_types():
+    """A Q4_K_M-style layer: wq / wk in Q4_K, wv in Q6_K, wo in Q8_0. The three input projections then run as
+    separate launches (one launch serves several matrices only when their types agree); the result is the
+    reference composition of the four matmuls around the path."""
+    dim, B = 1024, 3
+    cfg = AttnConfig(n_layers=1, n_heads=16, n_kv_heads=8, head_dim=128, seq_len=64, max_batch=B, rope_theta=1e6,
+                     kv_format=KV_F32)
+    rng = np.random.default_rng(91)
+    wtypes = [W_Q4_K, W_Q4_K, W_Q6_K, W_Q8_0]
+    shapes = [(cfg.q_dim, dim), (cfg.kv_dim, dim), (cfg.kv_dim, dim), (dim, cfg.q_dim)]
+    ws, raws = zip(*[make_weights(rng, t, r, c) for t, (r, c) in zip(wtypes, shapes)])
+    ctx, ora = g.AttnContext(cfg), Oracle(cfg, threads=8)
+    for step in range(3):
+        pos = [step] * B
+        xb = rng.standard_normal((B, dim)).astype(np.float32)
+        want = reference_layer(ora, 0, pos, xb, raws, wtypes, (cfg.q_dim, cfg.kv_dim, dim))
+        got = ctx.layer_decode(0, pos, xb, *ws)
+        assert np.max(np.abs(got - want)) <= 2e-3 * max(1.0, float(np.max(np.abs(want))))
+    ctx.close()
+    for w in ws:
+        w.close()
+
+
 def test_weight_upload_rejects_bad_shapes():
     with pytest.raises(GgrError):
         Weights(W_Q8_0, 64, 48, np.zeros(64 * 34, np.uint8))        # Q8_0 needs cols % 32 == 0
