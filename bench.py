@@ -663,10 +663,18 @@ def bench_projections(torch, args, local_rank, peaks):
 
             for _ in range(6):
                 step()
-            kern_ms = instrumented(torch, ctx, step, 24)[3][0]
+            pair_ms = instrumented(torch, ctx, step, 24)[3][0]
+
+            def burst():
+                for _ in range(24):
+                    step()
+
+            kern_ms = timed_steps(torch, burst, 5) / 24.0
             res[f"gemv_{name}_n{n}"] = hbm_roofline(peaks, nbytes, kern_ms, kernel="proj_gemv_kernel", shape=f"{rows}x{cols}, {n} row(s)",
-                                                    bytes_per_launch=nbytes, avg_launch_ms=kern_ms, traffic=None,
-                                                    note="event pair around every launch (which adds ~5 us), 6 matrices cycled so the weights come from HBM")
+                                                    bytes_per_launch=nbytes, avg_launch_ms=kern_ms, avg_launch_ms_event_pair=pair_ms,
+                                                    traffic=None,
+                                                    note="24 back-to-back launches between one pair of events, 6 matrices cycled so the "
+                                                         "weights come from HBM; an event pair around every launch adds ~5 us to each")
         if name == "bf16":
             m = 4096
             x = torch.randn(m, cols, device="cuda")
@@ -1047,6 +1055,17 @@ def run_small_case(args):
             out = ctx.proj_matmul(wb, xm)
         for i in range(12):
             out1 = ctx.proj_matmul(wq[i % 6], x1)
+    elif args.case == "proj_gemv_big":
+        # the weight-streaming kernel on an FFN-sized 14336 x 4096 Q8_0 matrix, one row, six matrices cycled (0.4 GB)
+        from gguf_runner_b200.binding import W_Q8_0, Weights
+        from tests.oracle_binding import quantize_q8_0
+        rng = np.random.default_rng(6)
+        raw = quantize_q8_0((rng.standard_normal((14336, 4096)) / 64.0).astype(np.float32))
+        wq = [Weights(W_Q8_0, 14336, 4096, raw) for _ in range(6)]
+        ctx = g.AttnContext(presets.qwen3_0p6b_decode(n_layers=1, seq_len=64))
+        x1 = torch.randn(1, 4096, generator=gen, device="cuda")
+        for i in range(12):
+            out = ctx.proj_matmul(wq[i % 6], x1)
     elif args.case == "decode_turbo_small":
         # two layers of the config-3 decode shape over a TurboQuant cache: T=32768, B=8 (0.25 GB on the device);
         # the cache keeps its zero rows (timing of the tensor-core kernel does not depend on the code values)
@@ -1129,7 +1148,7 @@ def main():
     ap.add_argument("--decode-batch", type=int, default=8)
     ap.add_argument("--cpu-stride", type=int, default=16)
     ap.add_argument("--case", default=None, help="run a small profiling case (prefill_small, prefill_gemma_small, decode_small, "
-                                                 "decode_b1_small, decode_cfg1_small, decode_turbo_small, proj_small) or print the "
+                                                 "decode_b1_small, decode_cfg1_small, decode_turbo_small, proj_small, proj_gemv_big) or print the "
                                                  "decode kernels' phase stamps (decode_stamps, diagnostic library build) and exit")
     args = ap.parse_args()
     if args.warmup < 3:

@@ -125,7 +125,9 @@ inline size_t gemv_row_floats(int cols) {
 }
 
 template <int WT, int TT>
-__global__ void __launch_bounds__(kGemvWarps * 32) proj_gemv_kernel(GemvArgs a) {
+// (two CTAs per SM, i.e. at most 128 registers, wherever that needs no spills: one activation row, or unquantised weights;
+// the quantised types with several rows need the registers for their decoded weights and accumulators)
+__global__ void __launch_bounds__(kGemvWarps * 32, (TT == 1 || WT == PW_F32 || WT == PW_BF16) ? 2 : 1) proj_gemv_kernel(GemvArgs a) {
     using Ge = GemvGeom<WT>;
     constexpr int CPL = Ge::CPL, UN = Ge::UN, NL = Ge::NL, Q = CPL / 4;
     extern __shared__ __align__(16) float xs[];  // [TT][row_floats]: the activation rows of the pass, read by every warp
