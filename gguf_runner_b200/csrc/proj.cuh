@@ -95,6 +95,12 @@ __device__ __forceinline__ float q8_byte_to_float(uint32_t biased_word, int byte
     return __uint_as_float(__byte_perm(biased_word, 0x4B000000u, sel)) - 8388736.0f;
 }
 
+// byte `byte` of a word as the low mantissa bits of 2^23: the float 8388608 + b (the caller subtracts)
+__device__ __forceinline__ float byte_in_mantissa(uint32_t word, int byte) {
+    const uint32_t sel = 0x7650u | (uint32_t)byte;  // result bytes: [b, 0x00, 0x00, 0x4B]
+    return __uint_as_float(__byte_perm(word, 0x4B000000u, sel));
+}
+
 // unsigned byte (0..255) of a word -> float the same way, without a bias
 __device__ __forceinline__ float nibble_byte_to_float(uint32_t word, int byte) {
     const uint32_t sel = 0x7650u | (uint32_t)byte;
@@ -222,39 +228,49 @@ __global__ void __launch_bounds__(kGemvWarps * 32, (TT == 1 || WT == PW_F32 || W
             for (int s = 0; s < UN; ++s) {
                 const int c0 = cb + s * 32 * CPL + lane * CPL;
                 if (c0 >= cols) continue;
-                float wv[kGemvRPW][CPL];
+                // decoded weights as packed pairs: the arithmetic below handles two weights per instruction
+                // (add.f32x2 / fma.rn.f32x2), which is what the kernel is bound by
+                using tc::add_f32x2;
+                using tc::fma_f32x2;
+                using tc::pack_f32x2;
+                uint64_t w2[kGemvRPW][CPL / 2];
 #pragma unroll
                 for (int r = 0; r < kGemvRPW; ++r) {
                     if (WT == PW_F32) {
                         const uint4 u0 = raw[s][r][0], u1 = raw[s][r][NL - 1];
-                        wv[r][0] = __uint_as_float(u0.x); wv[r][1] = __uint_as_float(u0.y);
-                        wv[r][2] = __uint_as_float(u0.z); wv[r][3] = __uint_as_float(u0.w);
-                        wv[r][4 % CPL] = __uint_as_float(u1.x); wv[r][5 % CPL] = __uint_as_float(u1.y);
-                        wv[r][6 % CPL] = __uint_as_float(u1.z); wv[r][7 % CPL] = __uint_as_float(u1.w);
+                        w2[r][0] = pack_f32x2(__uint_as_float(u0.x), __uint_as_float(u0.y));
+                        w2[r][1] = pack_f32x2(__uint_as_float(u0.z), __uint_as_float(u0.w));
+                        w2[r][2 % (CPL / 2)] = pack_f32x2(__uint_as_float(u1.x), __uint_as_float(u1.y));
+                        w2[r][3 % (CPL / 2)] = pack_f32x2(__uint_as_float(u1.z), __uint_as_float(u1.w));
                     } else if (WT == PW_BF16) {
                         const uint4 q = raw[s][r][0];
                         const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            wv[r][2 * i] = __uint_as_float(w4[i] << 16);
-                            wv[r][2 * i + 1] = __uint_as_float(w4[i] & 0xffff0000u);
-                        }
+                        for (int i = 0; i < 4; ++i)
+                            w2[r][i] = pack_f32x2(__uint_as_float(w4[i] << 16), __uint_as_float(w4[i] & 0xffff0000u));
                     } else if (WT == PW_Q8_0 || WT == PW_Q6_K) {
+                        // code byte, biased by 128, in the low mantissa bits of 2^23; the bias leaves in one packed add
                         const uint4 q = raw[s][r][0];
                         const uint32_t w4[4] = {q.x ^ 0x80808080u, q.y ^ 0x80808080u, q.z ^ 0x80808080u, q.w ^ 0x80808080u};
+                        const uint64_t neg = pack_f32x2(-8388736.0f, -8388736.0f);
 #pragma unroll
-                        for (int i = 0; i < CPL; ++i) wv[r][i] = q8_byte_to_float(w4[(i >> 2) & 3], i & 3);
+                        for (int i = 0; i < CPL; i += 2)
+                            w2[r][i >> 1] = add_f32x2(pack_f32x2(byte_in_mantissa(w4[(i >> 2) & 3], i & 3),
+                                                                 byte_in_mantissa(w4[(i >> 2) & 3], (i & 3) + 1)), neg);
                     } else {
                         // byte i of the 16 holds weights i (low nibble) and i + 16 (high nibble) of the lane's 32
                         const uint4 q = raw[s][r][0];
                         const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
+                        const uint64_t neg = pack_f32x2(-8388608.0f, -8388608.0f);
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
                             const uint32_t lo = w4[k] & 0x0f0f0f0fu, hi = (w4[k] >> 4) & 0x0f0f0f0fu;
 #pragma unroll
-                            for (int b = 0; b < 4; ++b) {
-                                wv[r][(4 * k + b) % CPL] = nibble_byte_to_float(lo, b);
-                                wv[r][(16 + 4 * k + b) % CPL] = nibble_byte_to_float(hi, b);
+                            for (int b = 0; b < 4; b += 2) {
+                                w2[r][((4 * k + b) >> 1) % (CPL / 2)] =
+                                    add_f32x2(pack_f32x2(byte_in_mantissa(lo, b), byte_in_mantissa(lo, b + 1)), neg);
+                                w2[r][((16 + 4 * k + b) >> 1) % (CPL / 2)] =
+                                    add_f32x2(pack_f32x2(byte_in_mantissa(hi, b), byte_in_mantissa(hi, b + 1)), neg);
                             }
                         }
                     }
@@ -264,18 +280,24 @@ __global__ void __launch_bounds__(kGemvWarps * 32, (TT == 1 || WT == PW_F32 || W
                 for (int t = 0; t < TT; ++t) {
                     const float4* xp = reinterpret_cast<const float4*>(xs) + (size_t)t * row4 + (size_t)step * Q * 32 + lane;
                     float part[kGemvRPW];
+                    uint64_t pacc[kGemvRPW];  // (even, odd) sums
 #pragma unroll
-                    for (int r = 0; r < kGemvRPW; ++r) part[r] = 0.0f;
+                    for (int r = 0; r < kGemvRPW; ++r) pacc[r] = 0ull;
 #pragma unroll
                     for (int i = 0; i < CPL; i += 4) {
                         const float4 xx = xp[(i >> 2) * 32];
+                        const uint64_t x01 = pack_f32x2(xx.x, xx.y), x23 = pack_f32x2(xx.z, xx.w);
 #pragma unroll
                         for (int r = 0; r < kGemvRPW; ++r) {
-                            part[r] = fmaf(xx.x, wv[r][i], part[r]);
-                            part[r] = fmaf(xx.y, wv[r][i + 1], part[r]);
-                            part[r] = fmaf(xx.z, wv[r][i + 2], part[r]);
-                            part[r] = fmaf(xx.w, wv[r][i + 3], part[r]);
+                            pacc[r] = fma_f32x2(x01, w2[r][i >> 1], pacc[r]);
+                            pacc[r] = fma_f32x2(x23, w2[r][(i >> 1) + 1], pacc[r]);
                         }
+                    }
+#pragma unroll
+                    for (int r = 0; r < kGemvRPW; ++r) {
+                        float lo, hi;
+                        tc::unpack_f32x2(pacc[r], lo, hi);
+                        part[r] = lo + hi;
                     }
                     // Q8_0: the block scale multiplies the partial sum of the block's codes, as in the reference
 #pragma unroll
