@@ -1086,11 +1086,24 @@ int prefill_common(ggr_attn_ctx* c, int layer, int seq, int base_pos, int m, con
     // Host buffers: rows move in pieces so that the copy-in of piece p+1, the kernels of piece p and the
     // copy-out of piece p-1 overlap (three streams). A staged image block needs all its rows appended
     // before any row attends, so it is one piece.
-    const int piece = block_mode ? m : 1024;
-    const int n_pieces = (m + piece - 1) / piece;
+    std::vector<std::pair<int, int>> pieces;  // (first row, rows)
+    if (block_mode) {
+        pieces.push_back({0, m});
+    } else {
+        // a smaller first piece: nothing overlaps its copy-in, so the output stream starts that much earlier
+        // (32-layer S=4096 pass: 57.9 ms with 1024 rows first, 56.2 ms with 512 or 256, 57.2 ms with 128)
+        const int first_rows = 512;
+        int i0 = 0;
+        while (i0 < m) {
+            const int n = std::min(i0 == 0 ? first_rows : 1024, m - i0);
+            pieces.push_back({i0, n});
+            i0 += n;
+        }
+    }
+    const int n_pieces = (int)pieces.size();
     if ((rc = ensure_copy_streams(c, n_pieces))) return rc;
     for (int p = 0; p < n_pieces; ++p) {
-        const int i0 = p * piece, n = std::min(piece, m - i0);
+        const int i0 = pieces[p].first, n = pieces[p].second;
         const size_t qo = (size_t)i0 * c->q_dim * es, ko = (size_t)i0 * c->kv_dim * es;
         CUDA_TRY(c, cudaMemcpyAsync(c->d_stage[0] + qo, static_cast<const unsigned char*>(q) + qo, (size_t)n * c->q_dim * es,
                                     cudaMemcpyHostToDevice, c->copy_in));
