@@ -67,6 +67,7 @@ struct ggr_attn_ctx {
     size_t px_cap = 0, pqkv_cap = 0, patt_cap = 0, pout_cap = 0, pact_cap = 0, pqkv_h_cap = 0;
     // pinned host staging of host-pointer decode calls: q | k | v | gate travel as one copy, the output as one
     unsigned char* h_pin = nullptr;
+    unsigned char* d_pin_alias = nullptr;  // device address of h_pin (mapped pinned memory), or null
     size_t pin_cap = 0;
     unsigned char* d_pin_in = nullptr;  // device image of the inbound half
     size_t pin_in_cap = 0;
@@ -802,14 +803,24 @@ int ensure_pinned(ggr_attn_ctx* c, size_t in_bytes, size_t out_bytes) {
         c->h_pin = nullptr;
         c->pin_cap = 0;
         const size_t want = std::max(need, (size_t)4096);
-        if (cudaHostAlloc((void**)&c->h_pin, want, cudaHostAllocDefault) != cudaSuccess) {
+        if (cudaHostAlloc((void**)&c->h_pin, want, cudaHostAllocMapped) != cudaSuccess) {
             cudaGetLastError();
             return fail(c, GGR_ERR_ALLOC, "unable to allocate pinned staging memory");
         }
         c->pin_cap = want;
+        // the device's view of the buffer: decode kernels write their few KB of output straight into it
+        void* alias = nullptr;
+        if (cudaHostGetDevicePointer(&alias, c->h_pin, 0) != cudaSuccess) {
+            cudaGetLastError();
+            alias = nullptr;
+        }
+        c->d_pin_alias = static_cast<unsigned char*>(alias);
     }
     return ensure(c, &c->d_pin_in, &c->pin_in_cap, in_bytes);
 }
+
+// outputs up to this size are written by the decode kernels straight into mapped pinned host memory
+constexpr size_t kZeroCopyOutBytes = 64 * 1024;
 
 // Sizes of the decode scratch for batches of up to B items (see ggr_attn_reserve).
 int reserve_decode(ggr_attn_ctx* c, int B) {
@@ -870,6 +881,7 @@ int decode_common(ggr_attn_ctx* c, int layer, const int32_t* pos, int B, const f
     const void *dq = q, *dk = k, *dv = v;
     const float* dgate = gate;
     float* dout = partial ? partial : out;
+    bool zero_copy_out = false;
     if (ptr_kind == GGR_PTR_HOST) {
         const size_t in_bytes = qb + 2 * kb + gb;
         if ((rc = ensure_pinned(c, in_bytes, out_elems * sizeof(float)))) return rc;
@@ -884,6 +896,12 @@ int decode_common(ggr_attn_ctx* c, int layer, const int32_t* pos, int B, const f
         dv = c->d_pin_in + qb + kb;
         if (gate) dgate = reinterpret_cast<const float*>(c->d_pin_in + qb + 2 * kb);
         dout = reinterpret_cast<float*>(c->d_stage[3]);
+        // small outputs (a few rows) go straight into the mapped pinned buffer: one copy and its launch less per call
+        if (c->d_pin_alias && out_elems * sizeof(float) <= kZeroCopyOutBytes) {
+            const size_t off = c->pin_cap - out_elems * sizeof(float);
+            dout = reinterpret_cast<float*>(c->d_pin_alias + off);
+            zero_copy_out = true;
+        }
     }
     if ((rc = ensure(c, &c->d_qrot, &c->qrot_cap, (size_t)B * c->q_dim))) return rc;
     int in_bf16 = 0;
@@ -910,7 +928,8 @@ int decode_common(ggr_attn_ctx* c, int layer, const int32_t* pos, int B, const f
     }
     if (ptr_kind == GGR_PTR_HOST) {
         unsigned char* h_out = c->h_pin + (c->pin_cap - out_elems * sizeof(float));
-        CUDA_TRY(c, cudaMemcpyAsync(h_out, dout, out_elems * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+        if (!zero_copy_out)
+            CUDA_TRY(c, cudaMemcpyAsync(h_out, dout, out_elems * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
         CUDA_TRY(c, cudaStreamSynchronize(c->stream));
         std::memcpy(partial ? partial : out, h_out, out_elems * sizeof(float));
         if (c->h_err && *c->h_err) {
