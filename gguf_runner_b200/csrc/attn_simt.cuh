@@ -36,7 +36,7 @@ struct FusedRope {
 // Fused exchange of KV-sequence shards: instead of handing its partial states to a collective, the
 // decode kernel stores them straight into the receive slot every rank keeps for this rank (peer memory
 // over NVLink, plain stores), and the last (token, kv head) group to finish raises this rank's flag on
-// every peer. No TMA and no multicast are involved; waits on the flags are bounded.
+// every peer with plain stores; waits on the flags are bounded.
 constexpr int kMaxPeers = 8;
 struct PeerExchange {
     int enabled;
