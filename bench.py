@@ -931,6 +931,88 @@ def bench_decode_head_shard(torch, dist, args, rank, world, local_rank, peaks, B
     return res
 
 
+def run_prefill_trace():
+    """Cycle counters and wall-clock stamps of the tensor-core prefill kernels (diagnostic build of the library,
+    -DGGR_TC_TRACE): CTA 0 accumulates, per role, the cycles it spends in each wait and each phase of a key tile and of
+    an item; the head_dim-256 kernel also stamps %globaltimer at its set-up, Q placement, loop end and epilogue in
+    its first and last CTA. Run as
+    `GGR_ATTN_LIBRARY=gguf_runner_b200/libggr_attn_trace.so python bench.py --case prefill_trace`
+    after `python -m gguf_runner_b200.build --trace`."""
+    import ctypes as C
+    import torch
+    import gguf_runner_b200 as g
+    from gguf_runner_b200 import presets
+    L_ = g.lib()
+    if not hasattr(L_, "ggr_attn_debug_set_trace"):
+        raise SystemExit("this library has no trace hooks: build with `python -m gguf_runner_b200.build --trace` and set "
+                         "GGR_ATTN_LIBRARY to gguf_runner_b200/libggr_attn_trace.so")
+    L_.ggr_attn_debug_set_trace.argtypes = [C.c_void_p]
+    L_.ggr_attn_debug_set_trace.restype = None
+    torch.cuda.set_device(0)
+    tr = torch.zeros(160, dtype=torch.int64, device="cuda")
+    L_.ggr_attn_debug_set_trace(C.c_void_p(tr.data_ptr()))
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1)
+
+    def rows(m, cfg):
+        return (torch.randn(m, cfg.q_dim, generator=gen, device="cuda").to(torch.bfloat16),
+                torch.randn(m, cfg.kv_dim, generator=gen, device="cuda").to(torch.bfloat16),
+                torch.randn(m, cfg.kv_dim, generator=gen, device="cuda").to(torch.bfloat16))
+
+    # head_dim 128: one Llama-3-8B-shaped layer, S = 4096
+    cfg = presets.llama3_8b_prefill(n_layers=1, seq_len=S_PREFILL)
+    ctx = g.AttnContext(cfg)
+    q, k, v = rows(S_PREFILL, cfg)
+    for _ in range(3):
+        ctx.prefill(0, 0, q, k, v)
+    torch.cuda.synchronize()
+    t = tr.cpu().tolist()
+    n = max(1, t[6])
+    print(f"prefill_tc_kernel<128>, S={S_PREFILL}, CTA 0: MMA issuer {t[0]} cycles over {n} key tiles; per tile: wait V {t[1] / n:.0f}, "
+          f"wait P (tile 0 / 1) {t[2] / n:.0f} / {t[3] / n:.0f}, wait K {t[4] / n:.0f}, issue P V {t[5] / n:.0f}, issue Q K^T {t[7] / n:.0f}")
+    for w in (0, 1):
+        o = t[8 + 8 * w:16 + 8 * w]
+        nt = max(1, o[6])
+        print(f"  softmax warpgroup {w}: {o[0]} cycles over {nt} tiles; per tile: wait S {o[1] / nt:.0f}, load {o[2] / nt:.0f}, "
+              f"max and mask {o[3] / nt:.0f}, rescale {o[4] / nt:.0f}, exponentials and store {o[5] / nt:.0f}")
+        o2 = t[128 + 4 * w:132 + 4 * w]
+        ni = max(1, o2[3])
+        print(f"    {o2[3]} items; per item: wait for the item {o2[0] / ni:.0f}, wait for the last P V {o2[1] / ni:.0f}, "
+              f"epilogue {o2[2] / ni:.0f} cycles")
+    ctx.close()
+
+    # head_dim 256: a window layer and a global layer of the Gemma-3-4B shape, one 2048-row chunk at context 4096
+    cfg = presets.gemma3_4b_prefill(n_layers=6, seq_len=8192)
+    ctx = g.AttnContext(cfg)
+    m = 2048
+    q, k, v = rows(m, cfg)
+    for layer, what in ((4, "window layer"), (5, "global layer")):
+        for _ in range(3):
+            ctx.prefill(layer, 4096, q, k, v)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(20):
+            ctx.prefill(layer, 4096, q, k, v)
+        e1.record()
+        torch.cuda.synchronize()
+        t = tr.cpu().tolist()
+        ns = max(1, t[6])
+        print(f"prefill_tc_wide_kernel<256>, {what}, rows 4096-6143: {e0.elapsed_time(e1) / 20 * 1e3:.1f} us per call (rope + attention)")
+        print(f"  CTA 0 MMA issuer: {t[0]} cycles over {ns} key tiles; per tile: wait K {t[4] / ns:.0f}, issue Q K^T {t[7] / ns:.0f}, "
+              f"wait V {t[1] / ns:.0f}, wait P {t[2] / ns:.0f}, issue P V {t[5] / ns:.0f}")
+        o = t[8:16]
+        nt = max(1, o[6])
+        print(f"  CTA 0 softmax: {o[0]} cycles; per tile: wait S {o[1] / nt:.0f}, load {o[2] / nt:.0f}, max and mask {o[3] / nt:.0f}, "
+              f"rescale {o[4] / nt:.0f}, exponentials and store {o[5] / nt:.0f}")
+        for name, base in (("first CTA", 32), ("last CTA", 40)):
+            b = t[base]
+            print(f"  {name} (ns after its start): set-up {t[base + 1] - b}, dependency wait over {t[base + 2] - b}, Q in tensor memory "
+                  f"{t[base + 3] - b}, key loop done {t[base + 4] - b}, last P V landed {t[base + 5] - b}, rows sent {t[base + 6] - b}, "
+                  f"exit {t[base + 7] - b}")
+    ctx.close()
+
+
 def run_decode_stamps():
     """Phase time stamps of the decode kernels (diagnostic build of the library, -DGGR_TC_TRACE): every CTA writes
     %globaltimer at the start, after the fused prologue, after streaming its keys, after the CTA merge and at the
@@ -1149,12 +1231,16 @@ def main():
     ap.add_argument("--cpu-stride", type=int, default=16)
     ap.add_argument("--case", default=None, help="run a small profiling case (prefill_small, prefill_gemma_small, decode_small, "
                                                  "decode_b1_small, decode_cfg1_small, decode_turbo_small, proj_small, proj_gemv_big) or print the "
-                                                 "decode kernels' phase stamps (decode_stamps, diagnostic library build) and exit")
+                                                 "decode kernels' phase stamps or the prefill kernels' cycle counters (decode_stamps, prefill_trace: diagnostic "
+                                                 "library build) and exit")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
     if args.case == "decode_stamps":
         run_decode_stamps()
+        return
+    if args.case == "prefill_trace":
+        run_prefill_trace()
         return
     if args.case:
         run_small_case(args)
