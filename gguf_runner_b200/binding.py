@@ -242,7 +242,8 @@ class AttnConfig:
 
 class Weights:
     """One projection matrix [rows][cols] resident on a device, uploaded from the GGML row layout the reference maps
-    from the GGUF file (F32, BF16, or Q8_0 blocks of one f16 scale and 32 int8 codes)."""
+    from the GGUF file (F32, BF16, Q8_0 blocks of one f16 scale and 32 int8 codes, Q4_K super-blocks of 144 bytes or
+    Q6_K super-blocks of 210 bytes per 256 weights)."""
 
     def __init__(self, wtype: int, rows: int, cols: int, data: np.ndarray, device: int = 0):
         self._L = lib()

@@ -137,5 +137,9 @@ def test_layer_decode_with_mixed_weight_types():
 def test_weight_upload_rejects_bad_shapes():
     with pytest.raises(GgrError):
         Weights(W_Q8_0, 64, 48, np.zeros(64 * 34, np.uint8))        # Q8_0 needs cols % 32 == 0
+    with pytest.raises(GgrError):
+        Weights(W_Q4_K, 64, 384, np.zeros(64 * 144, np.uint8))      # K-quant rows are whole super-blocks of 256
+    with pytest.raises(GgrError):
+        Weights(W_Q6_K, 60, 256, np.zeros(60 * 210, np.uint8))      # rows must be a multiple of 8
     with pytest.raises(ValueError):
         Weights(W_BF16, 64, 64, np.zeros(10, np.uint16))
